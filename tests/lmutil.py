@@ -1,0 +1,99 @@
+"""Shared helpers for the parity tests: model configs, seeded weights and synthetic batches.
+
+Weights follow the reference's initial distributions (values only matter for being realistic):
+token embedding N(0, 1/d) (LanguageModel.cs:44), projections N(0, 2/(rows+cols)) (LanguageModel.cs:53,93;
+MultiHeadAttention.cs:75), FFN He-normal N(0, 2/fan_in) (Neural Network/Data.cs:135-143), LayerNorm gamma=1,
+beta=0 (TransformerBlock.cs:88-92), biases 0.  Parity runs inject identical weights on both sides, so System.Random
+is not reproduced; small random biases/gammas are added so that every gradient path carries signal.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from oracle import ACT, LMConfig
+
+
+def lm_config(vocab=0, F=0, O=None, d=64, H=4, L=2, f=128, act="Relu", discrete=True, loss="ce", causal=True, align=64):
+    c = LMConfig()
+    c.vocab_size = vocab
+    c.input_feature_dim = F
+    c.output_dim = vocab if (discrete and O is None) else int(O)
+    c.embedding_dim, c.num_heads, c.num_layers, c.ffn_dim = d, H, L, f
+    c.ffn_activation = ACT[act]
+    c.discrete = 1 if discrete else 0
+    c.loss_kind = 0 if loss == "ce" else 1
+    c.causal = 1 if causal else 0
+    c.align_floats = align
+    return c
+
+
+def init_params(oracle, cfg, seed=0, dtype=np.float32):
+    """Flat arena with seeded weights; padding between tensors stays zero."""
+    rng = np.random.default_rng(seed)
+    total = oracle.lm_param_count(cfg)
+    P = np.zeros(total, dtype)
+    tensors = oracle.lm_tensors(cfg)
+    d, f = cfg.embedding_dim, cfg.ffn_dim
+    n0 = 1 if cfg.discrete else 2
+    for idx, (off, r, c) in enumerate(tensors):
+        n = r * c
+        if idx < n0:
+            if cfg.discrete:
+                v = rng.normal(0, np.sqrt(1.0 / d), n)
+            elif idx == 0:
+                v = rng.normal(0, np.sqrt(2.0 / (cfg.input_feature_dim + d)), n)
+            else:
+                v = rng.normal(0, 0.02, n)
+        elif idx < n0 + 16 * cfg.num_layers:
+            t = (idx - n0) % 16
+            if t < 4:
+                v = rng.normal(0, np.sqrt(2.0 / (2 * d)), n)
+            elif t < 8:
+                v = rng.normal(0, 0.02, n)
+            elif t in (8, 10):
+                v = 1.0 + rng.normal(0, 0.05, n)
+            elif t in (9, 11):
+                v = rng.normal(0, 0.05, n)
+            elif t == 12:
+                v = rng.normal(0, np.sqrt(2.0 / d), n)
+            elif t == 14:
+                v = rng.normal(0, np.sqrt(2.0 / f), n)
+            else:
+                v = rng.normal(0, 0.02, n)
+        elif idx == n0 + 16 * cfg.num_layers:
+            v = rng.normal(0, np.sqrt(2.0 / (d + cfg.output_dim)), n)
+        else:
+            v = rng.normal(0, 0.02, n)
+        P[off:off + n] = v.astype(dtype)
+    return P
+
+
+def token_batch(rng, n_seq, vocab, min_len=2, max_len=64, fixed_len=None, zipf=None):
+    """Sequences [START=1, ids in [4, vocab), END=2] as (tokens, offsets)."""
+    toks, off = [], [0]
+    for _ in range(n_seq):
+        n = fixed_len if fixed_len else int(rng.integers(min_len, max_len + 1))
+        body = max(n - 2, 0)
+        if zipf:
+            ranks = np.arange(1, vocab - 4 + 1, dtype=np.float64)
+            p = ranks ** (-zipf)
+            p /= p.sum()
+            ids = 4 + rng.choice(vocab - 4, size=body, p=p)
+        else:
+            ids = rng.integers(4, vocab, size=body)
+        seq = [1] + list(ids) + [2]
+        seq = seq[:max(n, 2)]
+        toks += seq
+        off.append(len(toks))
+    return np.asarray(toks, np.int32), np.asarray(off, np.int32)
+
+
+def random_walk_batch(rng, n_seq, seq_len, F, target_feature=3):
+    """Per-feature Gaussian random walks (step sigma 0.01) min-max normalised to [0,1]; regression target is the
+    given feature (the trainer itself applies the one-step shift)."""
+    x = np.cumsum(rng.normal(0, 0.01, (n_seq, seq_len, F)), axis=1)
+    mn, mx = x.min(axis=1, keepdims=True), x.max(axis=1, keepdims=True)
+    x = ((x - mn) / np.maximum(mx - mn, 1e-12)).astype(np.float32)
+    tgt = x[:, :, target_feature:target_feature + 1].copy()
+    off = np.arange(0, (n_seq + 1) * seq_len, seq_len, dtype=np.int32)
+    return x.reshape(-1, F), tgt.reshape(-1, 1), off
