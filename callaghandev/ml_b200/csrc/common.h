@@ -1,0 +1,173 @@
+// Shared host-side definitions of libcallaghan_b200: the context object, status helpers and the launcher
+// prototypes of every kernel family.  All launchers take DEVICE pointers and enqueue on ctx->stream.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../../include/callaghan_b200.h"
+
+struct RopeTable {
+    float* dev = nullptr;  // [rows][headDim/2][2] = (cos, sin), computed on the host with the oracle's libm calls
+    int rows = 0;
+};
+
+struct b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaStream_t own_stream = nullptr;
+    std::string err;
+    std::mutex mu;
+    int gemm_mode = B200_GEMM_AUTO;
+    int cc_major = 0, sm_count = 0;
+    int64_t launches = 0;
+    // grow-only scratch for the per-op (host pointer) API
+    char* pool = nullptr;
+    size_t pool_bytes = 0, pool_used = 0;
+    // small grow-only device workspace for reductions / split-K partials owned by kernels
+    float* ws = nullptr;
+    size_t ws_floats = 0;
+    float* pinned = nullptr;  // 4 KiB pinned staging for scalars
+    std::map<std::pair<int, uint32_t>, RopeTable> rope;  // key: (headDim, bits of baseTheta)
+    void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
+};
+
+namespace b200 {
+
+int fail(b200_ctx* ctx, int code, const char* fmt, ...);
+
+#define B200_CUDA(ctx, expr)                                                                               \
+    do {                                                                                                   \
+        cudaError_t e__ = (expr);                                                                          \
+        if (e__ != cudaSuccess)                                                                            \
+            return b200::fail(ctx, B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                              __FILE__, __LINE__);                                                         \
+    } while (0)
+#define B200_TRY(expr)              \
+    do {                            \
+        int rc__ = (expr);          \
+        if (rc__ != B200_OK) return rc__; \
+    } while (0)
+#define B200_LAUNCH_CHECK(ctx)                                                                                  \
+    do {                                                                                                        \
+        (ctx)->launches++;                                                                                      \
+        cudaError_t e__ = cudaGetLastError();                                                                   \
+        if (e__ != cudaSuccess)                                                                                 \
+            return b200::fail(ctx, B200_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e__), \
+                              __FILE__, __LINE__);                                                              \
+    } while (0)
+
+// Ensure ctx->ws holds at least n floats (contents are not preserved).
+int ensure_ws(b200_ctx* ctx, size_t n);
+// cos/sin table for rotary embeddings covering positions [0, rows).
+int rope_table(b200_ctx* ctx, int headDim, float baseTheta, int rows, const float** out);
+
+// ------------------------------------------------------------------------------------------------ GEMM
+// C[M,N] = epilogue(alpha * op(A) * op(B)).  op(A) is [M,K]: stored [M,K] row-major (transA=0, leading dim lda) or
+// [K,M] row-major (transA=1).  op(B) is [K,N]: stored [K,N] row-major (transB=0) or [N,K] row-major (transB=1).
+// Epilogue, in order, for element (m,n) with v = alpha * acc (times *alpha_dev when given):
+//   v += bias[n]; zout[m,n] = v; (act != NONE or dout) -> a = act(v), dout[m,n] = act'(v), v = a;
+//   v *= act'(mulz[m,n]) (FFN derivative conventions); v *= mulmat[m,n]; v += addmat[m,n];
+//   sgd_lr != 0 -> C = C - sgd_lr * (v + sgd_lambda * C); else accumulate ? C += v : C = v.
+struct Gemm {
+    int M = 0, N = 0, K = 0;
+    const float* A = nullptr; int lda = 0; int transA = 0;
+    const float* B = nullptr; int ldb = 0; int transB = 0;
+    float* C = nullptr; int ldc = 0;
+    float alpha = 1.f; const float* alpha_dev = nullptr;
+    int accumulate = 0;
+    const float* bias = nullptr;
+    float* zout = nullptr; int ldz = 0;
+    int act = B200_ACT_NONE; int act_conv = 0;  // 0: transformer-FFN conventions, 1: batch-MLP conventions
+    float* dout = nullptr; int lddo = 0;
+    const float* mulz = nullptr; int ldmulz = 0; int mulz_act = B200_ACT_NONE;
+    const float* mulmat = nullptr; int ldmul = 0;
+    const float* addmat = nullptr; int ldadd = 0;
+    float sgd_lr = 0.f, sgd_lambda = 0.f;
+};
+int gemm(b200_ctx* ctx, const Gemm& g);            // picks the engine from ctx->gemm_mode and the shape
+int gemm_simt(b200_ctx* ctx, const Gemm& g);       // FP32 SIMT, any shape
+int gemm_tcgen05(b200_ctx* ctx, const Gemm& g);    // TF32 tcgen05/TMEM/TMA; B200_ERR_UNSUPPORTED if the shape does not qualify
+bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g);
+// Y[rows,outDim] (leading dim ldy) = X[rows,inDim] * W[outDim,inDim]^T + bias
+int linear_fwd(b200_ctx* ctx, const float* X, int rows, int inDim, const float* W, const float* bias, int outDim, float* Y, int ldy);
+// Wg[outDim,inDim] += dY^T X ; bg[outDim] += column sums of dY
+int wgrad(b200_ctx* ctx, const float* dY, int lddy, const float* X, int ldx, int rows, int outDim, int inDim, float* Wg, float* bg);
+// dX[rows,inDim] (+)= dY[rows,outDim] * W[outDim,inDim]
+int dgrad(b200_ctx* ctx, const float* dY, int lddy, const float* W, int rows, int outDim, int inDim, float* dX, int accumulate);
+// Stable counting sort of rows by token id (host): seg_id = distinct ids ascending, seg_off = start of each id's run in
+// perm (plus the end), perm = row indices grouped by id with ascending row order inside a group.
+void sort_rows_by_id(const int32_t* ids, int n, int vocab, std::vector<int32_t>& seg_id, std::vector<int32_t>& seg_off, std::vector<int32_t>& perm);
+
+// ------------------------------------------------------------------------------------------------ elementwise / reductions
+int k_add_inplace(b200_ctx*, float* target, const float* addend, int64_t n);
+int k_scale_inplace(b200_ctx*, float* x, int64_t n, float scale);
+int k_sgd_update(b200_ctx*, float* w, const float* g, int64_t n, float lr);
+// x[i] *= act'(z[i]) with the transformer-FFN derivative conventions.
+int k_mul_act_deriv(b200_ctx*, float* x, const float* z, int act, int64_t n);
+int k_sqnorm(b200_ctx*, const float* x, int64_t n, float* out_dev);  // out_dev[0] = sum x^2 (deterministic two-stage)
+// out[j] (+)= sum_i x[i, j] over rows; x has leading dimension ld.
+int k_colsum(b200_ctx*, const float* x, int rows, int cols, int ld, float* out, int accumulate);
+int k_embed(b200_ctx*, const int32_t* ids_dev, int count, const float* emb, int embDim, float* out);
+// Deterministic scatter-add: rows of (dXa [+ dXb]) sorted by id on the host.  seg_id[s] = vocabulary row, rows of
+// segment s are perm[seg_off[s] .. seg_off[s+1]) in ascending original order.
+int k_embed_scatter(b200_ctx*, float* eg, const float* dXa, const float* dXb, const int32_t* seg_id, const int32_t* seg_off,
+                    const int32_t* perm, int nSeg, int embDim);
+// Rotary embedding in place on `count` row-major matrices sharing one launch: matrix m = base + m*matStride, rows x ld,
+// heads are numHeads slices of headDim columns starting at startCol.  pos_dev (per row) or row index when NULL.
+int k_rope(b200_ctx*, float* base, int64_t matStride, int count, int rows, int ld, int startCol, int numHeads, int headDim,
+           const float* table, const int32_t* pos_dev, int inverse);
+// Residual + LayerNorm forward.  sub, mean, var, normalized, residual may be null.
+int k_ln_forward(b200_ctx*, const float* x, const float* sub, const float* gamma, const float* beta, int rows, int d, float eps,
+                 float* out, float* mean, float* var, float* normalized, float* residual);
+// LayerNorm backward on dOut = dOutA (+ dOutB).  dGamma/dBeta: accumulate ? += : =.
+int k_ln_backward(b200_ctx*, const float* dOutA, const float* dOutB, const float* x, const float* gamma, const float* mean,
+                  const float* var, int rows, int d, float eps, float* dx, float* dGamma, float* dBeta, int accumulate);
+// Softmax cross-entropy, in place capable (dLogits may alias logits).  Per row i < effRows:
+//   row_loss[i] = -log(p_t + 1e-10), row_ok[i] = all gradient entries finite, dLogits = (p - onehot) * row_scale[i]
+// (row_scale_dev per row, or the constant row_scale when null).  Rows >= effRows are zeroed.
+int k_cross_entropy(b200_ctx*, const float* logits, int rows, int V, const int32_t* targets_dev, int effRows, const float* row_scale_dev,
+                    float row_scale, float* dLogits, float* row_loss, int32_t* row_ok);
+// MSE: dOut = 2*(pred - target)*row_scale; row_loss[i] = sum_j diff^2.
+int k_mse(b200_ctx*, const float* pred, int rows, int O, const float* targets_dev, int effRows, const float* row_scale_dev, float row_scale,
+          float* dOut, float* row_loss, int32_t* row_ok);
+// Batch-MLP output delta (GPUB:315-322 with the six cost derivatives of NN:314-390): delta = -costDeriv(a, y) * D.
+int k_mlp_output_delta(b200_ctx*, const float* A, const float* D, const float* Y, int64_t n, int cost, float huberDelta, float* delta);
+int k_mlp_scale_inputs(b200_ctx*, const float* X, int B, int F, const float* mn, const float* mx, float* out);
+int k_mlp_clip_scale(b200_ctx*, const float* sumsq_dev, int nParts, float thr, float* scale_norm_dev);  // [0]=scale, [1]=norm
+int k_bias_update(b200_ctx*, float* b, const float* delta, int rows, int cols, float slr, const float* scale_dev);
+
+// ------------------------------------------------------------------------------------------------ attention
+// Segment table: segment s covers query rows [qStart, qStart+qLen) and key rows [kStart, kStart+kLen).
+struct AttnSeg { int qStart, qLen, kStart, kLen; };
+struct Attn {
+    const float *Q = nullptr, *K = nullptr, *V = nullptr;  // heads are column slices h*headDim..; leading dims below
+    int ldq = 0, ldk = 0, ldv = 0;
+    int numHeads = 0, headDim = 0;
+    float scale = 1.f;
+    int causal = 0;
+    const uint8_t* mask = nullptr;  // only with a single segment: [qLen, kLen]
+    const AttnSeg* segs_dev = nullptr; int nSeg = 0; int maxQLen = 0, maxKLen = 0;
+    int totalQ = 0, totalK = 0;
+    float* O = nullptr; int ldo = 0;
+    float* rowMax = nullptr; float* rowSum = nullptr;  // [totalQ, numHeads]
+    // backward
+    const float* dO = nullptr; int lddo = 0;
+    float *dQ = nullptr, *dK = nullptr, *dV = nullptr; int lddq = 0, lddk = 0, lddv = 0;
+    float* rowDot = nullptr;  // [totalQ, numHeads] scratch: sum_k dO*O
+};
+int attn_forward(b200_ctx*, const Attn& a);
+int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from the forward
+
+// ------------------------------------------------------------------------------------------------ parameter step
+// One cooperative kernel: sumsq of (g*gscale) -> clip factor -> SGD or Adam update.  out_dev[0] = grad norm,
+// out_dev[1] = applied clip factor.  A non-finite norm zeroes g and leaves w untouched.
+int k_fused_step(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
+                 int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev);
+
+}  // namespace b200

@@ -1,0 +1,51 @@
+// The fused GEMM epilogue shared by the FP32 SIMT kernel and the TF32 tcgen05 kernel (see struct Gemm in common.h
+// for the order of operations).  Passed to kernels by value.
+#pragma once
+#include "device_math.cuh"
+
+namespace b200 {
+
+struct Epilogue {
+    float* C; int ldc;
+    float alpha; const float* alpha_dev;
+    int accumulate;
+    const float* bias;
+    float* zout; int ldz;
+    int act, act_conv;
+    float* dout; int lddo;
+    const float* mulz; int ldmulz; int mulz_act;
+    const float* mulmat; int ldmul;
+    const float* addmat; int ldadd;
+    float sgd_lr, sgd_lambda;
+};
+
+__device__ __forceinline__ void epilogue_store(const Epilogue& e, int m, int n, float acc, float alpha) {
+    float v = alpha * acc;
+    if (e.bias) v += e.bias[n];
+    if (e.zout) e.zout[(size_t)m * e.ldz + n] = v;
+    if (e.act != B200_ACT_NONE || e.dout) {
+        float a, d;
+        if (e.act_conv) mlp_act_der(v, e.act, a, d);
+        else ffn_act_der(v, e.act, a, d);
+        if (e.dout) e.dout[(size_t)m * e.lddo + n] = d;
+        v = a;
+    }
+    if (e.mulz) {
+        float a, d;
+        ffn_act_der(e.mulz[(size_t)m * e.ldmulz + n], e.mulz_act, a, d);
+        v *= d;
+    }
+    if (e.mulmat) v *= e.mulmat[(size_t)m * e.ldmul + n];
+    if (e.addmat) v += e.addmat[(size_t)m * e.ldadd + n];
+    float* c = e.C + (size_t)m * e.ldc + n;
+    if (e.sgd_lr != 0.f) {
+        float w = *c;
+        *c = w - e.sgd_lr * (v + e.sgd_lambda * w);
+    } else if (e.accumulate) {
+        *c += v;
+    } else {
+        *c = v;
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,732 @@
+// C ABI, part B: the resident language-model trainer.  Weights, gradients and activation caches stay in HBM; the
+// host side below restates the orchestration of TransformerTrainer.TrainBatchDiscrete / TrainBatchContinuous
+// (TransformerTrainer.cs:217-486), ForwardFromEmbeddingWithCache (:540-590) and BackpropFromOutput / BackpropBlock /
+// BackpropAttention (:874-987) over PACKED passes: the valid sequences of a batch are concatenated (any mix of
+// lengths) up to max_rows_per_pass rows, attention runs per sequence through a segment table, and the loss scale is
+// per row (1/len of the row's sequence), which is exactly the reference's "mean over a bucket, times the bucket's
+// sequence count".  Gradients accumulate across passes; one fused kernel then scales, clips and steps.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "common.h"
+
+using namespace b200;
+
+namespace {
+
+struct LayerOff { int64_t WQ, WK, WV, WO, bQ, bK, bV, bO, g1, b1n, g2, b2n, W1, fb1, W2, fb2; };
+struct Layout {
+    int64_t in0 = 0, in1 = -1;
+    std::vector<LayerOff> layer;
+    int64_t Wout = 0, bout = 0, total = 0;
+};
+int64_t al(int64_t x, int a) { return a <= 1 ? x : (x + a - 1) / a * a; }
+
+Layout make_layout(const b200_lm_config& c) {
+    Layout o;
+    int a = c.align_floats < 1 ? 1 : c.align_floats, d = c.embedding_dim, f = c.ffn_dim;
+    int64_t p = 0;
+    if (c.discrete) { o.in0 = p; p = al(p + (int64_t)c.vocab_size * d, a); }
+    else { o.in0 = p; p = al(p + (int64_t)d * c.input_feature_dim, a); o.in1 = p; p = al(p + d, a); }
+    o.layer.resize((size_t)c.num_layers);
+    for (auto& L : o.layer) {
+        L.WQ = p; p = al(p + (int64_t)d * d, a);
+        L.WK = p; p = al(p + (int64_t)d * d, a);
+        L.WV = p; p = al(p + (int64_t)d * d, a);
+        L.WO = p; p = al(p + (int64_t)d * d, a);
+        L.bQ = p; p = al(p + d, a);
+        L.bK = p; p = al(p + d, a);
+        L.bV = p; p = al(p + d, a);
+        L.bO = p; p = al(p + d, a);
+        L.g1 = p; p = al(p + d, a);
+        L.b1n = p; p = al(p + d, a);
+        L.g2 = p; p = al(p + d, a);
+        L.b2n = p; p = al(p + d, a);
+        L.W1 = p; p = al(p + (int64_t)f * d, a);
+        L.fb1 = p; p = al(p + f, a);
+        L.W2 = p; p = al(p + (int64_t)d * f, a);
+        L.fb2 = p; p = al(p + d, a);
+    }
+    o.Wout = p; p = al(p + (int64_t)c.output_dim * d, a);
+    o.bout = p; p = al(p + c.output_dim, a);
+    o.total = p;
+    return o;
+}
+
+bool config_ok(const b200_lm_config* c) {
+    if (!c) return false;
+    if (c->embedding_dim <= 0 || c->num_heads <= 0 || c->num_layers < 0 || c->ffn_dim <= 0 || c->output_dim <= 0) return false;
+    if (c->embedding_dim % c->num_heads) return false;
+    int hd = c->embedding_dim / c->num_heads;
+    if ((hd & 1) || hd > 128) return false;
+    if (c->discrete ? c->vocab_size <= 0 : c->input_feature_dim <= 0) return false;
+    if (c->ffn_activation < 0 || c->ffn_activation > 5) return false;
+    if (c->loss_kind == 0 && c->discrete && c->output_dim != c->vocab_size) return false;
+    return true;
+}
+
+struct LayerCache {
+    float *x, *qkv, *attnO, *rowMax, *rowSum, *ln1In, *mean1, *var1, *n1, *z1, *a1, *ln2In, *mean2, *var2;
+};
+
+struct Seq { int index, start, len; };  // len = input length (sequence length - 1)
+
+}  // namespace
+
+struct b200_lm {
+    b200_ctx* ctx = nullptr;
+    b200_lm_config cfg{};
+    Layout lay;
+    float *P = nullptr, *G = nullptr, *M = nullptr, *V = nullptr;
+    bool ownP = false, ownG = false;
+    int opt = B200_OPT_SGD;
+    float beta1 = 0.9f, beta2 = 0.999f, adam_eps = 1e-8f;
+    int step_index = 0;
+    int maxRows = 0, maxSeqs = 0;
+    char* block = nullptr;
+    std::vector<LayerCache> cache;
+    float *xFinal = nullptr, *logits = nullptr, *proj = nullptr, *gbuf[4] = {nullptr, nullptr, nullptr, nullptr}, *dqkv = nullptr, *d1 = nullptr,
+          *rowDot = nullptr, *contIn = nullptr, *regTgt = nullptr, *rowScale = nullptr, *rowLoss = nullptr, *stepOut = nullptr;
+    int32_t *rowOk = nullptr, *ids = nullptr, *targets = nullptr, *pos = nullptr, *segId = nullptr, *segOff = nullptr, *perm = nullptr;
+    AttnSeg* segs = nullptr;
+    // pinned host staging
+    int32_t* h_int = nullptr;
+    float* h_float = nullptr;
+    size_t nDistinct = 0;  // distinct token ids of the staged pass
+    std::vector<char> t_has_bwd;  // per group of four timing events: was the backward-end event recorded
+    b200_grad_ready_fn cb = nullptr;
+    void* cb_user = nullptr;
+    std::vector<cudaEvent_t> cb_events;
+    size_t cb_used = 0;
+    std::vector<cudaEvent_t> t_events;
+    size_t t_used = 0;
+    float timings[4] = {0, 0, 0, 0};
+    const float* rope = nullptr;
+};
+
+namespace {
+
+int lm_fail(b200_lm* lm, int code, const char* msg) { return fail(lm->ctx, code, "%s", msg); }
+
+cudaEvent_t next_event(std::vector<cudaEvent_t>& pool, size_t& used) {
+    if (used == pool.size()) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        pool.push_back(e);
+    }
+    return pool[used++];
+}
+
+void fire(b200_lm* lm, int64_t off, int64_t count) {
+    if (!lm->cb || count <= 0) return;
+    cudaEvent_t e = next_event(lm->cb_events, lm->cb_used);
+    cudaEventRecord(e, lm->ctx->stream);
+    lm->cb(lm->cb_user, off, count, (void*)e);
+}
+
+// ---- one packed pass ---------------------------------------------------------------------------------------------
+struct Pass {
+    std::vector<Seq> seqs;
+    int rows = 0, maxLen = 0;
+};
+
+struct Batch {  // host views of the caller's batch
+    const int32_t* tokens = nullptr;
+    const float* feats = nullptr;
+    const float* regT = nullptr;
+    const int32_t* clsT = nullptr;
+    const int32_t* off = nullptr;
+};
+
+int stage_pass(b200_lm* lm, const Batch& b, const Pass& p) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    const int N = p.rows, S = (int)p.seqs.size(), F = c.input_feature_dim, O = c.output_dim;
+    int32_t* hi = lm->h_int;
+    int32_t *h_ids = hi, *h_tgt = hi + lm->maxRows, *h_pos = hi + 2 * (size_t)lm->maxRows;
+    AttnSeg* h_segs = (AttnSeg*)(hi + 3 * (size_t)lm->maxRows);
+    float* hf = lm->h_float;
+    float* h_scale = hf;
+    float* h_cont = hf + lm->maxRows;
+    float* h_reg = h_cont + (size_t)lm->maxRows * (c.discrete ? 0 : F);
+    int r = 0;
+    for (int s = 0; s < S; s++) {
+        const Seq& q = p.seqs[s];
+        h_segs[s] = AttnSeg{r, q.len, r, q.len};
+        float sc = c.loss_kind == 0 ? 1.0f / (float)q.len : 1.0f / ((float)q.len * O);
+        for (int t = 0; t < q.len; t++, r++) {
+            h_pos[r] = t;
+            h_scale[r] = sc;
+            if (c.discrete) {
+                h_ids[r] = b.tokens[q.start + t];
+                h_tgt[r] = b.tokens[q.start + t + 1];
+            } else {
+                memcpy(h_cont + (size_t)r * F, b.feats + (size_t)(q.start + t) * F, sizeof(float) * F);
+                if (c.loss_kind == 1) memcpy(h_reg + (size_t)r * O, b.regT + (size_t)(q.start + t + 1) * O, sizeof(float) * O);
+                else h_tgt[r] = b.clsT[q.start + t + 1];
+            }
+        }
+    }
+    cudaStream_t st = ctx->stream;
+    B200_CUDA(ctx, cudaMemcpyAsync(lm->pos, h_pos, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+    B200_CUDA(ctx, cudaMemcpyAsync(lm->segs, h_segs, sizeof(AttnSeg) * S, cudaMemcpyHostToDevice, st));
+    B200_CUDA(ctx, cudaMemcpyAsync(lm->rowScale, h_scale, sizeof(float) * N, cudaMemcpyHostToDevice, st));
+    if (c.discrete || c.loss_kind == 0) B200_CUDA(ctx, cudaMemcpyAsync(lm->targets, h_tgt, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+    if (c.discrete) {
+        B200_CUDA(ctx, cudaMemcpyAsync(lm->ids, h_ids, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+        // rows grouped by token id for the deterministic embedding-gradient scatter
+        std::vector<int32_t> sid, soff, perm;
+        sort_rows_by_id(h_ids, N, c.vocab_size, sid, soff, perm);
+        int32_t* h_sort = (int32_t*)(h_segs + lm->maxSeqs);
+        memcpy(h_sort, sid.data(), sizeof(int32_t) * sid.size());
+        memcpy(h_sort + lm->maxRows, soff.data(), sizeof(int32_t) * soff.size());
+        memcpy(h_sort + 2 * (size_t)lm->maxRows + 1, perm.data(), sizeof(int32_t) * perm.size());
+        B200_CUDA(ctx, cudaMemcpyAsync(lm->segId, h_sort, sizeof(int32_t) * sid.size(), cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(lm->segOff, h_sort + lm->maxRows, sizeof(int32_t) * soff.size(), cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(lm->perm, h_sort + 2 * (size_t)lm->maxRows + 1, sizeof(int32_t) * perm.size(), cudaMemcpyHostToDevice, st));
+        lm->nDistinct = sid.size();
+    } else {
+        B200_CUDA(ctx, cudaMemcpyAsync(lm->contIn, h_cont, sizeof(float) * (size_t)N * F, cudaMemcpyHostToDevice, st));
+        if (c.loss_kind == 1) B200_CUDA(ctx, cudaMemcpyAsync(lm->regTgt, h_reg, sizeof(float) * (size_t)N * O, cudaMemcpyHostToDevice, st));
+    }
+    return B200_OK;
+}
+
+// Three products against the per-layer Q/K/V weights.  When the arena places WQ|WK|WV (and the biases) back to back
+// they are one [3d, d] matrix and one GEMM; otherwise (padding between tensors) three GEMMs into column blocks.
+bool qkv_fused(const b200_lm* lm, const LayerOff& L) {
+    int64_t d = lm->cfg.embedding_dim;
+    return L.WK == L.WQ + d * d && L.WV == L.WK + d * d && L.bK == L.bQ + d && L.bV == L.bK + d;
+}
+
+int forward_pass(b200_lm* lm, const Pass& p) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    const int N = p.rows, d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim;
+    const float* P = lm->P;
+    float* x = c.num_layers > 0 ? lm->cache[0].x : lm->xFinal;
+    if (c.discrete) B200_TRY(k_embed(ctx, lm->ids, N, P + lm->lay.in0, d, x));
+    else B200_TRY(linear_fwd(ctx, lm->contIn, N, c.input_feature_dim, P + lm->lay.in0, P + lm->lay.in1, d, x, d));
+    for (int l = 0; l < c.num_layers; l++) {
+        const LayerOff& L = lm->lay.layer[(size_t)l];
+        LayerCache& k = lm->cache[(size_t)l];
+        if (qkv_fused(lm, L)) {
+            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WQ, P + L.bQ, 3 * d, k.qkv, 3 * d));
+        } else {
+            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WQ, P + L.bQ, d, k.qkv, 3 * d));
+            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WK, P + L.bK, d, k.qkv + d, 3 * d));
+            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WV, P + L.bV, d, k.qkv + 2 * d, 3 * d));
+        }
+        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->pos, 0));  // Q and K column blocks
+        Attn a;
+        a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
+        a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
+        a.segs_dev = lm->segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
+        a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum;
+        B200_TRY(attn_forward(ctx, a));
+        B200_TRY(linear_fwd(ctx, k.attnO, N, d, P + L.WO, P + L.bO, d, lm->proj, d));
+        B200_TRY(k_ln_forward(ctx, k.x, lm->proj, P + L.g1, P + L.b1n, N, d, 1e-5f, k.n1, k.mean1, k.var1, nullptr, k.ln1In));
+        {
+            Gemm g;
+            g.M = N; g.N = f; g.K = d; g.A = k.n1; g.lda = d; g.B = P + L.W1; g.ldb = d; g.transB = 1;
+            g.C = k.a1; g.ldc = f; g.bias = P + L.fb1; g.zout = k.z1; g.ldz = f; g.act = c.ffn_activation;
+            B200_TRY(gemm(ctx, g));
+        }
+        B200_TRY(linear_fwd(ctx, k.a1, N, f, P + L.W2, P + L.fb2, d, lm->proj, d));
+        float* nx = (l + 1 < c.num_layers) ? lm->cache[(size_t)l + 1].x : lm->xFinal;
+        B200_TRY(k_ln_forward(ctx, k.n1, lm->proj, P + L.g2, P + L.b2n, N, d, 1e-5f, nx, k.mean2, k.var2, nullptr, k.ln2In));
+    }
+    B200_TRY(linear_fwd(ctx, lm->xFinal, N, d, P + lm->lay.Wout, P + lm->lay.bout, O, lm->logits, O));
+    return B200_OK;
+}
+
+int loss_pass(b200_lm* lm, const Pass& p) {
+    const b200_lm_config& c = lm->cfg;
+    if (c.loss_kind == 0)
+        return k_cross_entropy(lm->ctx, lm->logits, p.rows, c.output_dim, lm->targets, p.rows, lm->rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
+    return k_mse(lm->ctx, lm->logits, p.rows, c.output_dim, lm->regTgt, p.rows, lm->rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
+}
+
+int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    const int N = p.rows, d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim;
+    const float* P = lm->P;
+    float* G = lm->G;
+    float *dX = lm->gbuf[0], *t1 = lm->gbuf[1], *t2 = lm->gbuf[2], *t3 = lm->gbuf[3];
+    // TransformerTrainer.cs:874-879: output projection.
+    B200_TRY(wgrad(ctx, lm->logits, O, lm->xFinal, d, N, O, d, G + lm->lay.Wout, G + lm->lay.bout));
+    B200_TRY(dgrad(ctx, lm->logits, O, P + lm->lay.Wout, N, O, d, dX, 0));
+    if (notify) fire(lm, lm->lay.Wout, lm->lay.total - lm->lay.Wout);
+    for (int l = c.num_layers - 1; l >= 0; l--) {
+        const LayerOff& L = lm->lay.layer[(size_t)l];
+        LayerCache& k = lm->cache[(size_t)l];
+        // LN2 backward (:903-906): dFF -> t1, gamma/beta grads accumulate.
+        B200_TRY(k_ln_backward(ctx, dX, nullptr, k.ln2In, P + L.g2, k.mean2, k.var2, N, d, 1e-5f, t1, G + L.g2, G + L.b2n, 1));
+        // FFN backward (NeuralNetwork.cs:773-884).  delta2 = dFF (output activation None).
+        B200_TRY(wgrad(ctx, t1, d, k.a1, f, N, d, f, G + L.W2, G + L.fb2));
+        {
+            Gemm g;  // delta1 = (delta2 * W2) o act'(z1)
+            g.M = N; g.N = f; g.K = d; g.A = t1; g.lda = d; g.B = P + L.W2; g.ldb = f; g.C = lm->d1; g.ldc = f;
+            g.mulz = k.z1; g.ldmulz = f; g.mulz_act = c.ffn_activation;
+            B200_TRY(gemm(ctx, g));
+        }
+        B200_TRY(wgrad(ctx, lm->d1, f, k.n1, d, N, f, d, G + L.W1, G + L.fb1));
+        {
+            Gemm g;  // dNormed1 = delta1 * W1 + dFF  (:908-909, residual add fused)
+            g.M = N; g.N = d; g.K = f; g.A = lm->d1; g.lda = f; g.B = P + L.W1; g.ldb = d; g.C = t2; g.ldc = d;
+            g.addmat = t1; g.ldadd = d;
+            B200_TRY(gemm(ctx, g));
+        }
+        // LN1 backward (:913-916): dAttnResidual -> t3.
+        B200_TRY(k_ln_backward(ctx, t2, nullptr, k.ln1In, P + L.g1, k.mean1, k.var1, N, d, 1e-5f, t3, G + L.g1, G + L.b1n, 1));
+        // BackpropAttention (:933-987): output projection, attention core, inverse rotary, Q/K/V projections.
+        B200_TRY(wgrad(ctx, t3, d, k.attnO, d, N, d, d, G + L.WO, G + L.bO));
+        B200_TRY(dgrad(ctx, t3, d, P + L.WO, N, d, d, t1, 0));  // dConcatenated (zero-initialised += in the reference)
+        Attn a;
+        a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
+        a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
+        a.segs_dev = lm->segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
+        a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum; a.rowDot = lm->rowDot;
+        a.dO = t1; a.lddo = d; a.dQ = lm->dqkv; a.dK = lm->dqkv + d; a.dV = lm->dqkv + 2 * d; a.lddq = a.lddk = a.lddv = 3 * d;
+        B200_TRY(attn_backward(ctx, a));
+        B200_TRY(k_rope(ctx, lm->dqkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->pos, 1));
+        float* out = t2;  // dX of the layer input = dQKV * Wqkv + dAttnResidual (:919, residual add fused)
+        if (qkv_fused(lm, L)) {
+            B200_TRY(wgrad(ctx, lm->dqkv, 3 * d, k.x, d, N, 3 * d, d, G + L.WQ, G + L.bQ));
+            Gemm g;
+            g.M = N; g.N = d; g.K = 3 * d; g.A = lm->dqkv; g.lda = 3 * d; g.B = P + L.WQ; g.ldb = d; g.C = out; g.ldc = d;
+            g.addmat = t3; g.ldadd = d;
+            B200_TRY(gemm(ctx, g));
+        } else {
+            const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
+            for (int i = 0; i < 3; i++) {
+                B200_TRY(wgrad(ctx, lm->dqkv + i * d, 3 * d, k.x, d, N, d, d, G + Ws[i], G + Bs[i]));
+                Gemm g;
+                g.M = N; g.N = d; g.K = d; g.A = lm->dqkv + i * d; g.lda = 3 * d; g.B = P + Ws[i]; g.ldb = d; g.C = out; g.ldc = d;
+                if (i == 0) { g.addmat = t3; g.ldadd = d; } else g.accumulate = 1;
+                B200_TRY(gemm(ctx, g));
+            }
+        }
+        std::swap(dX, t2);
+        if (notify) {
+            int64_t end = (l + 1 < c.num_layers) ? lm->lay.layer[(size_t)l + 1].WQ : lm->lay.Wout;
+            fire(lm, L.WQ, end - L.WQ);
+        }
+    }
+    // BackpropInput (:887-896)
+    if (c.discrete)
+        B200_TRY(k_embed_scatter(ctx, G + lm->lay.in0, dX, nullptr, lm->segId, lm->segOff, lm->perm, (int)lm->nDistinct, d));
+    else
+        B200_TRY(wgrad(ctx, dX, d, lm->contIn, c.input_feature_dim, N, d, c.input_feature_dim, G + lm->lay.in0, G + lm->lay.in1));
+    if (notify) {
+        int64_t end = c.num_layers > 0 ? lm->lay.layer[0].WQ : lm->lay.Wout;
+        fire(lm, 0, end);
+    }
+    // the swap above rotates local names only; restore the canonical buffer order for the next pass
+    return B200_OK;
+}
+
+// Accumulates gradients of all valid sequences of the batch.  loss_sum = sum over sequences of their mean loss
+// (the reference's totalLoss), valid = number of contributing sequences.
+int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t* valid_count) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    *loss_sum = 0.f;
+    *valid_count = 0;
+    lm->cb_used = 0;
+    lm->t_used = 0;
+    // ---- validity filter and bucketing in order of first appearance of each length (TransformerTrainer.cs:229-245)
+    std::vector<Seq> seqs;
+    std::vector<int> bucketLens;
+    for (int s = 0; s < n_seq; s++) {
+        int start = b.off[s], n = b.off[s + 1] - b.off[s];
+        if (n < 2) continue;
+        bool ok = true;
+        if (c.discrete) {
+            for (int t = 0; t < n && ok; t++) ok = (uint32_t)b.tokens[start + t] < (uint32_t)c.vocab_size;
+        } else {
+            for (int64_t i = 0; i < (int64_t)n * c.input_feature_dim && ok; i++) ok = std::isfinite(b.feats[(size_t)start * c.input_feature_dim + i]);
+            if (ok && c.loss_kind == 1)
+                for (int64_t i = 0; i < (int64_t)n * c.output_dim && ok; i++) ok = std::isfinite(b.regT[(size_t)start * c.output_dim + i]);
+            if (ok && c.loss_kind == 0)
+                for (int t = 0; t < n && ok; t++) ok = (uint32_t)b.clsT[start + t] < (uint32_t)c.output_dim;
+        }
+        if (!ok) continue;
+        if (n - 1 > lm->maxRows) return fail(ctx, B200_ERR_OUT_OF_RANGE, "sequence %d has %d rows, above max_rows_per_pass %d", s, n - 1, lm->maxRows);
+        seqs.push_back(Seq{s, start, n - 1});
+        if (std::find(bucketLens.begin(), bucketLens.end(), n - 1) == bucketLens.end()) bucketLens.push_back(n - 1);
+    }
+    if (seqs.empty()) return B200_OK;
+    std::vector<Seq> ordered;
+    for (int len : bucketLens)
+        for (const Seq& q : seqs)
+            if (q.len == len) ordered.push_back(q);
+    // ---- packed passes
+    std::vector<Pass> passes;
+    Pass cur;
+    for (const Seq& q : ordered) {
+        if (!cur.seqs.empty() && (cur.rows + q.len > lm->maxRows || (int)cur.seqs.size() >= lm->maxSeqs)) {
+            passes.push_back(cur);
+            cur = Pass();
+        }
+        cur.seqs.push_back(q);
+        cur.rows += q.len;
+        cur.maxLen = std::max(cur.maxLen, q.len);
+    }
+    passes.push_back(cur);
+    // per-length running sums for the loss, in the reference's row order
+    std::vector<float> bucketSum(bucketLens.size(), 0.f);
+    std::vector<int> bucketCount(bucketLens.size(), 0);
+    std::vector<float> rowLoss((size_t)lm->maxRows);
+    std::vector<int32_t> rowOk((size_t)lm->maxRows);
+    bool notified = false;
+    for (size_t pi = 0; pi < passes.size(); pi++) {
+        Pass p = passes[pi];
+        const bool last = pi + 1 == passes.size();
+        for (int attempt = 0; attempt < 64 && !p.seqs.empty(); attempt++) {
+            cudaEvent_t e0 = next_event(lm->t_events, lm->t_used), e1 = next_event(lm->t_events, lm->t_used),
+                        e2 = next_event(lm->t_events, lm->t_used), e3 = next_event(lm->t_events, lm->t_used);
+            lm->t_has_bwd.resize(lm->t_used / 4, 0);
+            lm->t_has_bwd[lm->t_used / 4 - 1] = 0;
+            B200_TRY(stage_pass(lm, b, p));
+            cudaEventRecord(e0, ctx->stream);
+            B200_TRY(forward_pass(lm, p));
+            cudaEventRecord(e1, ctx->stream);
+            B200_TRY(loss_pass(lm, p));
+            cudaEventRecord(e2, ctx->stream);
+            B200_CUDA(ctx, cudaMemcpyAsync(rowLoss.data(), lm->rowLoss, sizeof(float) * p.rows, cudaMemcpyDeviceToHost, ctx->stream));
+            B200_CUDA(ctx, cudaMemcpyAsync(rowOk.data(), lm->rowOk, sizeof(int32_t) * p.rows, cudaMemcpyDeviceToHost, ctx->stream));
+            B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            // TransformerTrainer.cs:271-272 / :286-287: a non-finite loss or gradient drops the sequences of that length
+            // (here: of that length within this pass).
+            std::vector<char> lenBad(bucketLens.size(), 0);
+            int r = 0;
+            std::vector<float> passSum(bucketLens.size(), 0.f);
+            for (const Seq& q : p.seqs) {
+                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
+                for (int t = 0; t < q.len; t++, r++) {
+                    passSum[bi] += rowLoss[(size_t)r];
+                    if (!rowOk[(size_t)r]) lenBad[bi] = 1;
+                }
+            }
+            bool anyBad = false, anyGood = false;
+            for (size_t bi = 0; bi < bucketLens.size(); bi++) {
+                if (!std::isfinite(passSum[bi])) lenBad[bi] = 1;
+            }
+            Pass good;
+            for (const Seq& q : p.seqs) {
+                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
+                if (lenBad[bi]) anyBad = true;
+                else {
+                    anyGood = true;
+                    good.seqs.push_back(q);
+                    good.rows += q.len;
+                    good.maxLen = std::max(good.maxLen, q.len);
+                }
+            }
+            float ms;
+            if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) lm->timings[0] += ms;
+            if (cudaEventElapsedTime(&ms, e1, e2) == cudaSuccess) lm->timings[1] += ms;
+            if (!anyGood) break;
+            if (anyBad) {  // rerun the pass with the finite sequences only: its activations must not be mixed with theirs
+                p = good;
+                continue;
+            }
+            r = 0;
+            for (const Seq& q : p.seqs) {
+                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
+                for (int t = 0; t < q.len; t++, r++) bucketSum[bi] += rowLoss[(size_t)r];
+                bucketCount[bi]++;
+            }
+            B200_TRY(backward_pass(lm, p, last && lm->cb != nullptr));
+            cudaEventRecord(e3, ctx->stream);
+            lm->t_has_bwd[lm->t_used / 4 - 1] = 1;
+            if (last && lm->cb) notified = true;
+            break;
+        }
+    }
+    if (lm->cb && !notified) fire(lm, 0, lm->lay.total);
+    float total = 0.f;
+    int valid = 0;
+    for (size_t bi = 0; bi < bucketLens.size(); bi++) {
+        if (bucketCount[bi] == 0) continue;
+        float denom = (float)bucketCount[bi] * bucketLens[bi] * (c.loss_kind == 1 ? c.output_dim : 1);
+        float loss = bucketSum[bi] / denom;       // CPU:2438 / CPU:2489: mean over the bucket's rows
+        total += loss * (float)bucketCount[bi];   // TransformerTrainer.cs:294
+        valid += bucketCount[bi];
+    }
+    *loss_sum = total;
+    *valid_count = valid;
+    return B200_OK;
+}
+
+int collect_backward_time(b200_lm* lm) {
+    // events are laid out in groups of four per attempted pass: forward start, forward end, loss end, backward end
+    for (size_t i = 0; i + 3 < lm->t_used; i += 4) {
+        float ms;
+        if (i / 4 < lm->t_has_bwd.size() && lm->t_has_bwd[i / 4] &&
+            cudaEventElapsedTime(&ms, lm->t_events[i + 2], lm->t_events[i + 3]) == cudaSuccess)
+            lm->timings[2] += ms;
+    }
+    return B200_OK;
+}
+
+int apply_step(b200_lm* lm, int valid, float lr, int use_clip, float thr, int do_step, float* grad_norm) {
+    b200_ctx* ctx = lm->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (grad_norm) *grad_norm = 0.f;
+    if (valid <= 0) return B200_OK;  // TransformerTrainer.cs:309-310
+    if (use_clip && !(thr > 0.f && std::isfinite(thr)))
+        return fail(ctx, B200_ERR_OUT_OF_RANGE, "Gradient clip threshold must be finite and positive.");
+    if (lm->opt == B200_OPT_ADAM && do_step) {
+        if (!lm->M) {
+            B200_CUDA(ctx, cudaMalloc(&lm->M, sizeof(float) * (size_t)lm->lay.total));
+            B200_CUDA(ctx, cudaMalloc(&lm->V, sizeof(float) * (size_t)lm->lay.total));
+            B200_CUDA(ctx, cudaMemsetAsync(lm->M, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
+            B200_CUDA(ctx, cudaMemsetAsync(lm->V, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
+        }
+        lm->step_index++;
+    }
+    cudaEvent_t e0 = next_event(lm->t_events, lm->t_used), e1 = next_event(lm->t_events, lm->t_used);
+    cudaEventRecord(e0, ctx->stream);
+    B200_TRY(k_fused_step(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, 1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1,
+                          lm->beta2, lm->adam_eps, lm->step_index, lm->stepOut));
+    cudaEventRecord(e1, ctx->stream);
+    B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, lm->stepOut, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (grad_norm) *grad_norm = ctx->pinned[0];
+    float ms;
+    if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) lm->timings[3] += ms;
+    lm->t_used -= 2;
+    collect_backward_time(lm);
+    return B200_OK;
+}
+
+int zero_grads(b200_lm* lm) {
+    b200_ctx* ctx = lm->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    for (int i = 0; i < 4; i++) lm->timings[i] = 0.f;
+    B200_CUDA(ctx, cudaMemsetAsync(lm->G, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b200_lm_param_count(const b200_lm_config* cfg) { return config_ok(cfg) ? make_layout(*cfg).total : -1; }
+int32_t b200_lm_tensor_count(const b200_lm_config* cfg) { return config_ok(cfg) ? (cfg->discrete ? 1 : 2) + 16 * cfg->num_layers + 2 : -1; }
+int32_t b200_lm_tensor_info(const b200_lm_config* cfg, int32_t idx, int64_t* off, int32_t* rows, int32_t* cols) {
+    if (!config_ok(cfg) || !off || !rows || !cols) return B200_ERR_INVALID_ARG;
+    Layout o = make_layout(*cfg);
+    int d = cfg->embedding_dim, f = cfg->ffn_dim, n0 = cfg->discrete ? 1 : 2;
+    if (idx < 0) return B200_ERR_OUT_OF_RANGE;
+    if (idx < n0) {
+        if (cfg->discrete) { *off = o.in0; *rows = cfg->vocab_size; *cols = d; }
+        else if (idx == 0) { *off = o.in0; *rows = d; *cols = cfg->input_feature_dim; }
+        else { *off = o.in1; *rows = 1; *cols = d; }
+        return B200_OK;
+    }
+    if (idx < n0 + 16 * cfg->num_layers) {
+        const LayerOff& L = o.layer[(size_t)((idx - n0) / 16)];
+        int t = (idx - n0) % 16;
+        const int64_t offs[16] = {L.WQ, L.WK, L.WV, L.WO, L.bQ, L.bK, L.bV, L.bO, L.g1, L.b1n, L.g2, L.b2n, L.W1, L.fb1, L.W2, L.fb2};
+        const int rws[16] = {d, d, d, d, 1, 1, 1, 1, 1, 1, 1, 1, f, 1, d, 1};
+        const int cls[16] = {d, d, d, d, d, d, d, d, d, d, d, d, d, f, f, d};
+        *off = offs[t]; *rows = rws[t]; *cols = cls[t];
+        return B200_OK;
+    }
+    if (idx == n0 + 16 * cfg->num_layers) { *off = o.Wout; *rows = cfg->output_dim; *cols = d; return B200_OK; }
+    if (idx == n0 + 16 * cfg->num_layers + 1) { *off = o.bout; *rows = 1; *cols = cfg->output_dim; return B200_OK; }
+    return B200_ERR_OUT_OF_RANGE;
+}
+
+int32_t b200_lm_create(b200_ctx* ctx, const b200_lm_config* cfg, float* params_dev, float* grads_dev, int32_t max_rows, b200_lm** out) {
+    if (!ctx || !out) return B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (!config_ok(cfg)) return fail(ctx, B200_ERR_INVALID_ARG, "invalid model configuration");
+    if (max_rows <= 0) return fail(ctx, B200_ERR_INVALID_ARG, "max_rows_per_pass must be positive");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    b200_lm* lm = new b200_lm();
+    lm->ctx = ctx;
+    lm->cfg = *cfg;
+    if (lm->cfg.align_floats < 1) lm->cfg.align_floats = 1;
+    lm->lay = make_layout(lm->cfg);
+    lm->maxRows = max_rows;
+    lm->maxSeqs = std::min(max_rows, 65535);
+    const b200_lm_config& c = lm->cfg;
+    const size_t N = (size_t)max_rows, d = (size_t)c.embedding_dim, f = (size_t)c.ffn_dim, H = (size_t)c.num_heads, O = (size_t)c.output_dim,
+                 F = (size_t)c.input_feature_dim, Lc = (size_t)c.num_layers;
+    auto rnd = [](size_t n) { return (n + 63) & ~(size_t)63; };  // keep every buffer 256-byte aligned
+    size_t perLayer = rnd(N * d) * 5 + rnd(N * 3 * d) + rnd(N * H) * 2 + rnd(N) * 4 + rnd(N * f) * 2;
+    size_t floats = perLayer * Lc + rnd(N * d) /*xFinal*/ + rnd(N * O) /*logits*/ + rnd(N * d) * 5 /*proj, gbuf*/ + rnd(N * 3 * d) + rnd(N * f) +
+                    rnd(N * H) + rnd(N * std::max<size_t>(F, 1)) + rnd(N * O) + rnd(N) * 2 + 64;
+    size_t ints = rnd(N) * 7 + rnd(4 * (size_t)lm->maxSeqs) + 64;
+    auto cleanup = [&](int rc) { b200_lm_destroy(lm); return rc; };
+    cudaError_t e;
+    if (!params_dev) {
+        if ((e = cudaMalloc(&lm->P, sizeof(float) * (size_t)lm->lay.total)) != cudaSuccess)
+            return cleanup(fail(ctx, B200_ERR_CUDA, "parameter arena allocation failed: %s", cudaGetErrorString(e)));
+        lm->ownP = true;
+        cudaMemsetAsync(lm->P, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream);
+    } else lm->P = params_dev;
+    if (!grads_dev) {
+        if ((e = cudaMalloc(&lm->G, sizeof(float) * (size_t)lm->lay.total)) != cudaSuccess)
+            return cleanup(fail(ctx, B200_ERR_CUDA, "gradient arena allocation failed: %s", cudaGetErrorString(e)));
+        lm->ownG = true;
+    } else lm->G = grads_dev;
+    cudaMemsetAsync(lm->G, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream);
+    if ((e = cudaMalloc((void**)&lm->block, sizeof(float) * floats + sizeof(int32_t) * ints)) != cudaSuccess)
+        return cleanup(fail(ctx, B200_ERR_CUDA, "activation cache allocation of %.2f GiB failed: %s",
+                            (sizeof(float) * floats + sizeof(int32_t) * ints) / 1073741824.0, cudaGetErrorString(e)));
+    float* q = (float*)lm->block;
+    auto take = [&](size_t n) { float* r = q; q += rnd(n); return r; };
+    lm->cache.resize(Lc);
+    for (auto& k : lm->cache) {
+        k.x = take(N * d); k.qkv = take(N * 3 * d); k.attnO = take(N * d); k.rowMax = take(N * H); k.rowSum = take(N * H);
+        k.ln1In = take(N * d); k.mean1 = take(N); k.var1 = take(N); k.n1 = take(N * d); k.z1 = take(N * f); k.a1 = take(N * f);
+        k.ln2In = take(N * d); k.mean2 = take(N); k.var2 = take(N);
+    }
+    lm->xFinal = take(N * d); lm->logits = take(N * O); lm->proj = take(N * d);
+    for (int i = 0; i < 4; i++) lm->gbuf[i] = take(N * d);
+    lm->dqkv = take(N * 3 * d); lm->d1 = take(N * f); lm->rowDot = take(N * H);
+    lm->contIn = take(N * std::max<size_t>(F, 1)); lm->regTgt = take(N * O); lm->rowScale = take(N); lm->rowLoss = take(N);
+    lm->stepOut = take(64);
+    int32_t* qi = (int32_t*)q;
+    auto takei = [&](size_t n) { int32_t* r = qi; qi += rnd(n); return r; };
+    lm->rowOk = takei(N); lm->ids = takei(N); lm->targets = takei(N); lm->pos = takei(N); lm->segId = takei(N); lm->segOff = takei(N + 1);
+    lm->perm = takei(N);
+    lm->segs = (AttnSeg*)takei(4 * (size_t)lm->maxSeqs);
+    size_t hInts = 3 * N + 4 * (size_t)lm->maxSeqs + 3 * N + 8;
+    size_t hFloats = N + N * F + N * O + 8;
+    if (cudaMallocHost((void**)&lm->h_int, sizeof(int32_t) * hInts) != cudaSuccess || cudaMallocHost((void**)&lm->h_float, sizeof(float) * hFloats) != cudaSuccess)
+        return cleanup(fail(ctx, B200_ERR_CUDA, "pinned staging allocation failed"));
+    int rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_rows, &lm->rope);
+    if (rc != B200_OK) return cleanup(rc);
+    *out = lm;
+    return B200_OK;
+}
+
+int32_t b200_lm_destroy(b200_lm* lm) {
+    if (!lm) return B200_OK;
+    cudaSetDevice(lm->ctx->device);
+    cudaStreamSynchronize(lm->ctx->stream);
+    if (lm->ownP && lm->P) cudaFree(lm->P);
+    if (lm->ownG && lm->G) cudaFree(lm->G);
+    if (lm->M) cudaFree(lm->M);
+    if (lm->V) cudaFree(lm->V);
+    if (lm->block) cudaFree(lm->block);
+    if (lm->h_int) cudaFreeHost(lm->h_int);
+    if (lm->h_float) cudaFreeHost(lm->h_float);
+    for (cudaEvent_t e : lm->cb_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : lm->t_events) cudaEventDestroy(e);
+    delete lm;
+    return B200_OK;
+}
+
+static int lm_copy(b200_lm* lm, float* host, const float* chost, float* dev, int64_t offset, int64_t count, bool up) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    b200_ctx* ctx = lm->ctx;
+    if ((!host && !chost) || offset < 0 || count < 0 || offset + count > lm->lay.total)
+        return fail(ctx, B200_ERR_OUT_OF_RANGE, "arena range [%lld,%lld) outside [0,%lld)", (long long)offset, (long long)(offset + count), (long long)lm->lay.total);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (up) B200_CUDA(ctx, cudaMemcpyAsync(dev + offset, chost, sizeof(float) * (size_t)count, cudaMemcpyHostToDevice, ctx->stream));
+    else B200_CUDA(ctx, cudaMemcpyAsync(host, dev + offset, sizeof(float) * (size_t)count, cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return B200_OK;
+}
+int32_t b200_lm_upload_params(b200_lm* lm, const float* host, int64_t offset, int64_t count) { return lm_copy(lm, nullptr, host, lm ? lm->P : nullptr, offset, count, true); }
+int32_t b200_lm_download_params(b200_lm* lm, float* host, int64_t offset, int64_t count) { return lm_copy(lm, host, nullptr, lm ? lm->P : nullptr, offset, count, false); }
+int32_t b200_lm_download_grads(b200_lm* lm, float* host, int64_t offset, int64_t count) { return lm_copy(lm, host, nullptr, lm ? lm->G : nullptr, offset, count, false); }
+float* b200_lm_params_device(b200_lm* lm) { return lm ? lm->P : nullptr; }
+float* b200_lm_grads_device(b200_lm* lm) { return lm ? lm->G : nullptr; }
+
+int32_t b200_lm_set_optimizer(b200_lm* lm, int32_t kind, float beta1, float beta2, float eps) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (kind != B200_OPT_SGD && kind != B200_OPT_ADAM) return lm_fail(lm, B200_ERR_INVALID_ARG, "unknown optimizer");
+    lm->opt = kind;
+    if (kind == B200_OPT_ADAM) {
+        if (!(beta1 >= 0.f && beta1 < 1.f && beta2 >= 0.f && beta2 < 1.f && eps > 0.f)) return lm_fail(lm, B200_ERR_INVALID_ARG, "bad Adam hyper-parameters");
+        lm->beta1 = beta1; lm->beta2 = beta2; lm->adam_eps = eps;
+    }
+    return B200_OK;
+}
+
+int32_t b200_lm_set_grad_ready_callback(b200_lm* lm, b200_grad_ready_fn fn, void* user) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    lm->cb = fn;
+    lm->cb_user = user;
+    return B200_OK;
+}
+
+int32_t b200_lm_zero_grads(b200_lm* lm) { return lm ? zero_grads(lm) : B200_ERR_INVALID_ARG; }
+
+int32_t b200_lm_accumulate_discrete(b200_lm* lm, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float* loss_sum, int32_t* valid_count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (!lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes continuous inputs");
+    if (!tokens || !seq_offsets || !loss_sum || !valid_count || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    Batch b;
+    b.tokens = tokens; b.off = seq_offsets;
+    return accumulate(lm, b, n_seq, loss_sum, valid_count);
+}
+
+int32_t b200_lm_accumulate_continuous(b200_lm* lm, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                      const int32_t* seq_offsets, int32_t n_seq, float* loss_sum, int32_t* valid_count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes token ids");
+    if (!features || !seq_offsets || !loss_sum || !valid_count || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    if (lm->cfg.loss_kind == 1 ? !reg_targets : !class_targets) return lm_fail(lm, B200_ERR_INVALID_ARG, "targets missing for the configured loss");
+    Batch b;
+    b.feats = features; b.regT = reg_targets; b.clsT = class_targets; b.off = seq_offsets;
+    return accumulate(lm, b, n_seq, loss_sum, valid_count);
+}
+
+int32_t b200_lm_apply_step(b200_lm* lm, int32_t global_valid_count, float lr, int32_t use_clip, float clip_threshold, int32_t do_step, float* grad_norm) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    return apply_step(lm, global_valid_count, lr, use_clip, clip_threshold, do_step, grad_norm);
+}
+
+int32_t b200_lm_train_step_discrete(b200_lm* lm, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip,
+                                    float clip_threshold, int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    float ls = 0.f, gn = 0.f;
+    int32_t vc = 0;
+    B200_TRY(b200_lm_zero_grads(lm));
+    B200_TRY(b200_lm_accumulate_discrete(lm, tokens, seq_offsets, n_seq, &ls, &vc));
+    B200_TRY(b200_lm_apply_step(lm, vc, lr, use_clip, clip_threshold, do_step, &gn));
+    if (loss) *loss = vc > 0 ? ls / (float)vc : 0.f;
+    if (grad_norm) *grad_norm = gn;
+    if (valid_count) *valid_count = vc;
+    return B200_OK;
+}
+
+int32_t b200_lm_train_step_continuous(b200_lm* lm, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                      const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip, float clip_threshold, int32_t do_step,
+                                      float* loss, float* grad_norm, int32_t* valid_count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    float ls = 0.f, gn = 0.f;
+    int32_t vc = 0;
+    B200_TRY(b200_lm_zero_grads(lm));
+    B200_TRY(b200_lm_accumulate_continuous(lm, features, reg_targets, class_targets, seq_offsets, n_seq, &ls, &vc));
+    B200_TRY(b200_lm_apply_step(lm, vc, lr, use_clip, clip_threshold, do_step, &gn));
+    if (loss) *loss = vc > 0 ? ls / (float)vc : 0.f;
+    if (grad_norm) *grad_norm = gn;
+    if (valid_count) *valid_count = vc;
+    return B200_OK;
+}
+
+int32_t b200_lm_get_timings(b200_lm* lm, float* ms4) {
+    if (!lm || !ms4) return B200_ERR_INVALID_ARG;
+    for (int i = 0; i < 4; i++) ms4[i] = lm->timings[i];
+    return B200_OK;
+}
+
+}  // extern "C"

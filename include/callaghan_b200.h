@@ -1,0 +1,258 @@
+/*
+ * callaghan_b200.h -- C ABI of libcallaghan_b200.so, the sm_100a (B200) training back end that plugs in behind
+ * CallaghanDev.ML's IAccelerationManager (CallaghanDev.ML/AccelerationManagers/IAccelerationManager.cs:13-361).
+ *
+ * Conventions
+ *   - Every entry point returns an int32 status (B200_OK == 0).  b200_last_error() gives the message of the last
+ *     failure on that context.  Nothing throws, nothing traps on the device.
+ *   - Section A ("per-op") functions mirror one IAccelerationManager method each: all pointers are HOST pointers to
+ *     row-major float32 / int32 / uint8 arrays owned by the caller, the call is blocking, and no pointer is retained.
+ *     The accumulate-vs-assign behaviour of each output is the reference's (noted per function).
+ *   - Section B ("resident") functions keep a model's weights, gradients and activation caches on the device and run
+ *     whole train steps; they are what the trainer hooks call.
+ *   - A context is thread-compatible: one call at a time per context; different contexts may be used concurrently.
+ *   - The library never falls back to the CPU: a missing/unsupported device is an error.
+ */
+#ifndef CALLAGHAN_B200_H
+#define CALLAGHAN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+enum {
+    B200_OK = 0,
+    B200_ERR_INVALID_ARG = 1,  /* null pointer, non-positive count: ArgumentNullException / ArgumentException */
+    B200_ERR_SHAPE = 2,        /* dimension mismatch: ArgumentException */
+    B200_ERR_OUT_OF_RANGE = 3, /* row window or token id out of range: ArgumentOutOfRangeException */
+    B200_ERR_CUDA = 4,         /* CUDA runtime/driver error */
+    B200_ERR_TIMEOUT = 6,      /* a bounded device-side wait gave up */
+    B200_ERR_NONFINITE = 7,    /* reserved */
+    B200_ERR_UNSUPPORTED = 8   /* e.g. head dimension above 128 */
+};
+
+/* Activation ids = CallaghanDev.ML.Enums.ActivationType; cost ids = CostFunctionType (Neural Network/Enums). */
+enum { B200_ACT_NONE = 0, B200_ACT_SIGMOID = 1, B200_ACT_TANH = 2, B200_ACT_RELU = 3, B200_ACT_LEAKYRELU = 4, B200_ACT_SWISH = 5 };
+enum { B200_COST_MSE = 0, B200_COST_ZERO_WEIGHTED_MSE = 1, B200_COST_BCE = 2, B200_COST_MAE = 3, B200_COST_CCE = 4, B200_COST_HUBER = 5 };
+/* GEMM engine selection (b200_set_gemm_mode): AUTO = TF32 tcgen05 tiles when every dimension >= 128, FP32 SIMT below. */
+enum { B200_GEMM_AUTO = 0, B200_GEMM_FP32_SIMT = 1, B200_GEMM_TF32_TCGEN05 = 2 };
+enum { B200_OPT_SGD = 0, B200_OPT_ADAM = 1 };
+
+typedef struct b200_ctx b200_ctx;
+typedef struct b200_lm b200_lm;
+typedef struct b200_mlp b200_mlp;
+
+/* ------------------------------------------------------------------------------------------------ context */
+/* Replaces the backend construction in AccelerationFactory.Create (AccelerationManagers/AccelerationFactory.cs:31-45)
+ * and NeuralNetwork.InitAcceleration (Neural Network/NeuralNetwork.cs:37-58).  device = CUDA ordinal. */
+B200_API int32_t b200_create(int32_t device, b200_ctx** out);
+/* IAccelerationManager.Dispose (IAccelerationManager.cs:325). */
+B200_API int32_t b200_destroy(b200_ctx* ctx);
+B200_API const char* b200_last_error(b200_ctx* ctx);
+/* Run all work of this context on a caller-owned cudaStream_t (NULL restores the context's own stream). */
+B200_API int32_t b200_set_stream(b200_ctx* ctx, void* cuda_stream);
+B200_API int32_t b200_set_gemm_mode(b200_ctx* ctx, int32_t mode);
+B200_API int32_t b200_synchronize(b200_ctx* ctx);
+/* Number of kernels this context has launched so far (launch accounting for benchmarks). */
+B200_API int64_t b200_kernel_launches(b200_ctx* ctx);
+/* 1 if the device is compute capability 10.x (tcgen05 path usable), else 0. */
+B200_API int32_t b200_has_tcgen05(b200_ctx* ctx);
+
+/* ------------------------------------------------------------------------------------------------ A. per-op */
+/* IAccelerationManager.MatrixMultiply (IAccelerationManager.cs:20; AccelerationCPU.cs:159-210): C[rowsA,colsB] = A*B. */
+B200_API int32_t b200_MatrixMultiply(b200_ctx*, const float* A, int32_t rowsA, int32_t colsA, const float* B, int32_t rowsB, int32_t colsB, float* C);
+/* MatrixMultiplyTranspose (IAccelerationManager.cs:26): C[rowsA,rowsB] = A*B^T. */
+B200_API int32_t b200_MatrixMultiplyTranspose(b200_ctx*, const float* A, int32_t rowsA, int32_t colsA, const float* B, int32_t rowsB, int32_t colsB, float* C);
+/* BatchDotProductAddBias, both overloads (IAccelerationManager.cs:45,50; AccelerationCPU.cs:342-404):
+ * Y[rowCount,outDim] = X[rowStart..rowStart+rowCount) * W^T + bias. */
+B200_API int32_t b200_BatchDotProductAddBias(b200_ctx*, const float* W, int32_t outDim, int32_t inDim, const float* X, int32_t xRows, int32_t xCols,
+                                             int32_t rowStart, int32_t rowCount, const float* bias, int32_t biasLen, float* Y);
+/* ProjectOutputBatch (IAccelerationManager.cs:259; AccelerationCPU.cs:2694-2715). */
+B200_API int32_t b200_ProjectOutputBatch(b200_ctx*, const float* hidden, int32_t hiddenRows, int32_t embDim, const float* proj, const float* bias,
+                                         int32_t seqLen, int32_t outputDim, float* pred);
+/* MatrixAddInPlace / VectorAccumulate (IAccelerationManager.cs:91,97): target += addend. */
+B200_API int32_t b200_MatrixAddInPlace(b200_ctx*, float* target, const float* addend, int64_t count);
+B200_API int32_t b200_VectorAccumulate(b200_ctx*, float* target, const float* source, int64_t count);
+/* ZeroMatrix / ZeroVector (IAccelerationManager.cs:80,86). */
+B200_API int32_t b200_ZeroMatrix(b200_ctx*, float* matrix, int64_t count);
+B200_API int32_t b200_ZeroVector(b200_ctx*, float* vector, int64_t count);
+
+/* ResidualLayerNormForward (IAccelerationManager.cs:138; AccelerationCPU.cs:1440-1514).  subLayer may be NULL
+ * (= LayerNormForward, IAccelerationManager.cs:127); normalized/residual/means/variances may be NULL when not wanted
+ * (= ResidualLayerNorm / LayerNorm, IAccelerationManager.cs:122,132). */
+B200_API int32_t b200_ResidualLayerNormForward(b200_ctx*, const float* input, const float* subLayer, const float* gamma, const float* beta,
+                                               int32_t rows, int32_t features, float eps, float* output, float* means, float* variances,
+                                               float* normalized, float* residual);
+/* LayerNormBackward (IAccelerationManager.cs:143; AccelerationCPU.cs:1516-1564): all three outputs are assigned. */
+B200_API int32_t b200_LayerNormBackward(b200_ctx*, const float* dOut, const float* normalized, const float* gamma, const float* input,
+                                        const float* mean, const float* variance, int32_t rows, int32_t features, float eps,
+                                        float* dInput, float* dGamma, float* dBeta);
+
+/* ScaledDotProductAttention (IAccelerationManager.cs:167; AccelerationCPU.cs:1797-1956).  mask: NULL or
+ * [queryLen,keyLen] bytes, non-zero = visible.  causal with queryLen != keyLen is B200_ERR_INVALID_ARG. */
+B200_API int32_t b200_ScaledDotProductAttention(b200_ctx*, const float* q, const float* k, const float* v, int32_t queryLen, int32_t keyLen,
+                                                int32_t embDim, int32_t numHeads, const uint8_t* mask, int32_t causal, float* out);
+/* MultiHeadAttentionForward (IAccelerationManager.cs:155): same kernel with an explicit scale. */
+B200_API int32_t b200_MultiHeadAttentionForward(b200_ctx*, const float* q, const float* k, const float* v, int32_t queryLen, int32_t keyLen,
+                                                int32_t embDim, int32_t numHeads, float scale, const uint8_t* mask, float* out);
+/* MultiHeadAttentionBackward, both overloads (IAccelerationManager.cs:161,163; AccelerationCPU.cs:1037-1284). */
+B200_API int32_t b200_MultiHeadAttentionBackward(b200_ctx*, const float* Q, const float* K, const float* V, const float* dConcat, int32_t seqLenQ,
+                                                 int32_t seqLenK, int32_t embDim, int32_t numHeads, float scale, const uint8_t* mask,
+                                                 int32_t useDecoderMask, float* dQ, float* dK, float* dV);
+/* Trainer-side batched attention that today is C# inside TransformerTrainer
+ * (TransformerTrainer.cs:723-809 forward, :989-1121 backward): segment s owns rows [s*segLen,(s+1)*segLen). */
+B200_API int32_t b200_SegmentedAttentionForward(b200_ctx*, const float* Q, const float* K, const float* V, int32_t segLen, int32_t segCount,
+                                                int32_t embDim, int32_t numHeads, int32_t causal, float* out);
+B200_API int32_t b200_SegmentedAttentionBackward(b200_ctx*, const float* Q, const float* K, const float* V, const float* dConcat, int32_t segLen,
+                                                 int32_t segCount, int32_t embDim, int32_t numHeads, float scale, int32_t causal,
+                                                 float* dQ, float* dK, float* dV);
+/* ApplyRotaryPositionEmbeddingInPlace (IAccelerationManager.cs:320; AccelerationCPU.cs:4855-4982); segLen > 0 makes the
+ * position row % segLen (TransformerTrainer.cs:811-848 ApplySegmentedRotaryInPlace). */
+B200_API int32_t b200_ApplyRotaryPositionEmbeddingInPlace(b200_ctx*, float* matrix, int32_t rows, int32_t embDim, int32_t numHeads,
+                                                          float baseTheta, int32_t inverse, int32_t segLen);
+/* ApplyRotaryPositionEmbeddingHeadInPlace (IAccelerationManager.cs:319). */
+B200_API int32_t b200_ApplyRotaryPositionEmbeddingHeadInPlace(b200_ctx*, float* matrix, int32_t rows, int32_t embDim, int32_t startCol,
+                                                              int32_t headDim, float baseTheta, int32_t inverse);
+
+/* ProjectQKV (IAccelerationManager.cs:169; AccelerationCPU.cs:2005-2069). */
+B200_API int32_t b200_ProjectQKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* WQ, const float* bQ, const float* WK,
+                                 const float* bK, const float* WV, const float* bV, int32_t outDim, float* Q, float* K, float* V);
+/* BackpropQKV (IAccelerationManager.cs:171; AccelerationCPU.cs:2071-2182): the six gradients accumulate, dInput is assigned. */
+B200_API int32_t b200_BackpropQKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* dQ, const float* dK, const float* dV,
+                                  int32_t outDim, const float* WQ, const float* WK, const float* WV, float* WQGrad, float* bQGrad,
+                                  float* WKGrad, float* bKGrad, float* WVGrad, float* bVGrad, float* dInput);
+/* BackpropLinearProjection (IAccelerationManager.cs:182; AccelerationCPU.cs:2188-2229): weightGrad, biasGrad AND dInput accumulate. */
+B200_API int32_t b200_BackpropLinearProjection(b200_ctx*, const float* input, const float* dOutput, const float* weights, int32_t seqLen,
+                                               int32_t inDim, int32_t outDim, float* weightGrad, float* biasGrad, float* dInput);
+/* BackpropOutputProjection (IAccelerationManager.cs:184; AccelerationCPU.cs:2231-2273): grads accumulate, dX assigned. */
+B200_API int32_t b200_BackpropOutputProjection(b200_ctx*, const float* dLogits, const float* input, const float* weights, float* weightGrad,
+                                               float* biasGrad, int32_t seqLen, int32_t outputDim, int32_t embDim, float* dX);
+/* BackpropInputProjection, both overloads (IAccelerationManager.cs:190,197; AccelerationCPU.cs:2275-2332). */
+B200_API int32_t b200_BackpropInputProjection(b200_ctx*, const float* dX, int32_t dXRows, int32_t dXCols, const float* continuousInput,
+                                              int32_t contRows, int32_t contCols, int32_t inputRowStart, float* weightGrad, float* biasGrad,
+                                              int32_t seqLen, int32_t embDim, int32_t inputFeatureDim);
+/* EmbedTokenIds, both overloads (IAccelerationManager.cs:275,277; AccelerationCPU.cs:3473-3515).  An id outside
+ * [0,vocab) is B200_ERR_OUT_OF_RANGE, checked on the host before any launch. */
+B200_API int32_t b200_EmbedTokenIds(b200_ctx*, const int32_t* tokenIds, int32_t nIds, int32_t tokenStart, int32_t tokenCount,
+                                    const float* embedding, int32_t vocab, int32_t embDim, float* out);
+/* AccumulateTokenEmbeddingGrad, both overloads (IAccelerationManager.cs:203,205; AccelerationCPU.cs:2334-2370):
+ * embeddingGrad[ids[tokenStart+i],:] += dX[i,:], duplicates summed in row order (deterministic). */
+B200_API int32_t b200_AccumulateTokenEmbeddingGrad(b200_ctx*, float* embeddingGrad, int32_t vocab, const float* dX, const int32_t* tokenIds,
+                                                   int32_t nIds, int32_t tokenStart, int32_t seqLen, int32_t embDim);
+/* CrossEntropyLossAndGradient, both overloads (IAccelerationManager.cs:207,209; AccelerationCPU.cs:2372-2440).
+ * dLogits is [rows,outputDim]; rows at and beyond effectiveLen are zero. */
+B200_API int32_t b200_CrossEntropyLossAndGradient(b200_ctx*, const float* logits, int32_t rows, int32_t outputDim, const int32_t* targets,
+                                                  int32_t nTargets, int32_t targetStart, int32_t effectiveLen, float* loss, float* dLogits);
+/* MSELossAndGradient, both overloads (IAccelerationManager.cs:212,214; AccelerationCPU.cs:2442-2491). */
+B200_API int32_t b200_MSELossAndGradient(b200_ctx*, const float* predictions, int32_t rows, int32_t outputDim, const float* targets,
+                                         int32_t targetRows, int32_t targetStart, int32_t effectiveLen, float* loss, float* dOutput);
+/* MatrixSquaredNorm / VectorSquaredNorm (IAccelerationManager.cs:221,228). */
+B200_API int32_t b200_MatrixSquaredNorm(b200_ctx*, const float* matrix, int64_t count, float* out);
+B200_API int32_t b200_VectorSquaredNorm(b200_ctx*, const float* vector, int64_t count, float* out);
+/* MatrixScaleInPlace / VectorScaleInPlace (IAccelerationManager.cs:235,240). */
+B200_API int32_t b200_MatrixScaleInPlace(b200_ctx*, float* matrix, int64_t count, float scale);
+B200_API int32_t b200_VectorScaleInPlace(b200_ctx*, float* vector, int64_t count, float scale);
+/* MatrixUpdate / VectorUpdate (IAccelerationManager.cs:246,248; AccelerationCPU.cs:2548-2590): w -= lr*g. */
+B200_API int32_t b200_MatrixUpdate(b200_ctx*, float* weights, const float* gradients, int64_t count, float learningRate);
+B200_API int32_t b200_VectorUpdate(b200_ctx*, float* weights, const float* gradients, int64_t count, float learningRate);
+
+/* FFNForwardBatch (IAccelerationManager.cs:165) for the case the reference itself special-cases: the delegate's target
+ * is a NeuralNetwork (AccelerationCPU.cs:1975-1985 -> NeuralNetwork.ForwardPassOnlyBatch, NeuralNetwork.cs:629-668).
+ * The network is passed as nLayers widths/activations (entry 0 = input layer) and, for l = 1..nLayers-1,
+ * weights[l] ([widths[l], widths[l-1]]) and biases[l]; entry 0 of the pointer arrays is ignored. */
+B200_API int32_t b200_FFNForwardBatch(b200_ctx*, const float* input, int32_t rows, int32_t nLayers, const int32_t* widths, const int32_t* activations,
+                                      const float* const* weights, const float* const* biases, float* out);
+/* NeuralNetwork.ComputeInputGradientBatch (NeuralNetwork.cs:773-987), the FFN backward the trainer calls at
+ * TransformerTrainer.cs:923-931.  weightGrads/biasGrads may both be NULL; otherwise they accumulate. */
+B200_API int32_t b200_FFNInputGradientBatch(b200_ctx*, const float* input, const float* dOutput, int32_t rows, int32_t nLayers, const int32_t* widths,
+                                            const int32_t* activations, const float* const* weights, const float* const* biases,
+                                            float* const* weightGrads, float* const* biasGrads, float* dInput);
+
+/* ------------------------------------------------------------------------------------------------ B. resident LM */
+/* Model shape = TransformerConfig (Transformers/MultiTypeTransformer/TransformerConfig.cs:17-103). */
+typedef struct {
+    int32_t vocab_size;        /* VocabSize (discrete models) */
+    int32_t input_feature_dim; /* InputFeatureDim (continuous models) */
+    int32_t output_dim;        /* EffectiveOutputDim */
+    int32_t embedding_dim, num_heads, num_layers, ffn_dim;
+    int32_t ffn_activation;    /* B200_ACT_* of the FFN hidden layer */
+    int32_t discrete;          /* Data.UsesDiscreteTokens */
+    int32_t loss_kind;         /* 0 cross-entropy, 1 MSE (TimeSeriesRegression) */
+    int32_t causal;            /* UseDecoderOnly */
+    int32_t align_floats;      /* tensor offsets in the flat arena are multiples of this (>= 1; 64 recommended) */
+} b200_lm_config;
+
+/* Flat parameter arena.  Tensor order = the reference's weights.bin (LanguageModel.cs:737-765) with each block's FFN
+ * appended to the block: [TokenEmbedding | InputProjection, InputProjectionBias], then per layer WQ WK WV WO bQ bK bV bO
+ * LN1Gamma LN1Beta LN2Gamma LN2Beta W1 b1 W2 b2, then OutputProjection, OutputBias. */
+B200_API int64_t b200_lm_param_count(const b200_lm_config* cfg);
+B200_API int32_t b200_lm_tensor_count(const b200_lm_config* cfg);
+B200_API int32_t b200_lm_tensor_info(const b200_lm_config* cfg, int32_t index, int64_t* offset, int32_t* rows, int32_t* cols);
+
+/* Replaces the construction of TransformerTrainer's state (TransformerTrainer.cs:17-41: model, TransformerGradients,
+ * FFN gradient storage).  params_dev / grads_dev: optional caller-owned DEVICE buffers of b200_lm_param_count floats
+ * (e.g. tensors of a host framework that all-reduces the gradients); NULL lets the library allocate.
+ * max_rows_per_pass bounds the rows (tokens) of one forward/backward pass; larger batches are split. */
+B200_API int32_t b200_lm_create(b200_ctx*, const b200_lm_config* cfg, float* params_dev, float* grads_dev, int32_t max_rows_per_pass, b200_lm** out);
+B200_API int32_t b200_lm_destroy(b200_lm*);
+B200_API int32_t b200_lm_upload_params(b200_lm*, const float* host, int64_t offset, int64_t count);
+B200_API int32_t b200_lm_download_params(b200_lm*, float* host, int64_t offset, int64_t count);
+B200_API int32_t b200_lm_download_grads(b200_lm*, float* host, int64_t offset, int64_t count);
+B200_API float* b200_lm_params_device(b200_lm*);
+B200_API float* b200_lm_grads_device(b200_lm*);
+B200_API int32_t b200_lm_set_optimizer(b200_lm*, int32_t kind, float beta1, float beta2, float eps);
+
+/* TransformerTrainer.TrainBatchDiscrete (TransformerTrainer.cs:217-327) on one batch: sequence s is
+ * tokens[seq_offsets[s] .. seq_offsets[s+1]).  Zeroes the gradients, runs forward + loss + backward for every valid
+ * sequence, scales by 1/validCount, computes the global gradient norm, clips and (do_step != 0) applies the update.
+ * Outputs: *loss = totalLoss/validCount, *grad_norm (before clipping), *valid_count. */
+B200_API int32_t b200_lm_train_step_discrete(b200_lm*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip,
+                                             float clip_threshold, int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
+/* TransformerTrainer.TrainBatchContinuous (TransformerTrainer.cs:337-486): features [rows,F]; regression targets
+ * [rows,O] (loss_kind 1) or class targets [rows] (loss_kind 0); seq_offsets count rows; row t trains against row t+1. */
+B200_API int32_t b200_lm_train_step_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                               const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip, float clip_threshold,
+                                               int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
+
+/* Data-parallel decomposition of the same step (no counterpart in the reference, which is single-device):
+ *   b200_lm_zero_grads -> b200_lm_accumulate_* (this rank's sequences; gradients summed, unscaled)
+ *   -> the host all-reduces the gradient arena, loss sum and valid count -> b200_lm_apply_step on every rank.
+ * The callback, when set, fires on the calling thread during the LAST pass of b200_lm_accumulate_* each time a
+ * contiguous range of the gradient arena [offset, offset+count) has received its final contribution; `event` is a
+ * cudaEvent_t recorded on the compute stream after that contribution (make the communication stream wait on it). */
+typedef void (*b200_grad_ready_fn)(void* user, int64_t offset, int64_t count, void* event);
+B200_API int32_t b200_lm_set_grad_ready_callback(b200_lm*, b200_grad_ready_fn fn, void* user);
+B200_API int32_t b200_lm_zero_grads(b200_lm*);
+B200_API int32_t b200_lm_accumulate_discrete(b200_lm*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float* loss_sum, int32_t* valid_count);
+B200_API int32_t b200_lm_accumulate_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                               const int32_t* seq_offsets, int32_t n_seq, float* loss_sum, int32_t* valid_count);
+B200_API int32_t b200_lm_apply_step(b200_lm*, int32_t global_valid_count, float lr, int32_t use_clip, float clip_threshold, int32_t do_step, float* grad_norm);
+/* Device time of the phases of the last step in milliseconds: [0] forward, [1] loss, [2] backward, [3] step. */
+B200_API int32_t b200_lm_get_timings(b200_lm*, float* ms4);
+
+/* ------------------------------------------------------------------------------------------------ C. resident MLP */
+/* NeuralNetwork.TrainBatch state (NeuralNetwork.cs:420-477 + BatchedAccelerationGPU.cs:12-149): weights stay on the
+ * device across batches.  widths/activations have nLayers entries (entry 0 = input layer, its activation unused). */
+B200_API int32_t b200_mlp_create(b200_ctx*, int32_t nLayers, const int32_t* widths, const int32_t* activations, int32_t cost, float huber_delta,
+                                 float l2_lambda, float clip_threshold, int32_t max_batch, b200_mlp** out);
+B200_API int32_t b200_mlp_destroy(b200_mlp*);
+/* layer = 1..nLayers-1.  download = AccelerationGPUBatch.CopyLayerToCPU (BatchedAccelerationGPU.cs:236-247). */
+B200_API int32_t b200_mlp_upload_layer(b200_mlp*, int32_t layer, const float* weights, const float* biases);
+B200_API int32_t b200_mlp_download_layer(b200_mlp*, int32_t layer, float* weights, float* biases);
+/* NeuralNetwork.LearnBatch (NeuralNetwork.cs:499-520, 542-610): X [B,widths[0]] already input-scaled, Y [B,widths[last]].
+ * in_min/in_max non-NULL applies ScaleInput (NeuralNetwork.cs:121-134) to X on the device first. */
+B200_API int32_t b200_mlp_learn_batch(b200_mlp*, const float* X, const float* Y, int32_t B, float lr, const float* in_min, const float* in_max,
+                                      float* delta_norm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,306 @@
+"""Train-step parity on the GPU through the resident C-ABI entry points: gradients (tensor by tensor) and post-step
+weights of the language-model step and of the MLP batch step against the CPU oracle on identical seeded weights and
+inputs.  FP32 SIMT path: tolerance 1e-5 with the reference's metric |exp-act| <= tol*max(1,|exp|); whole-network
+gradients accumulate rounding through several layers, so the bound is stated per test.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from lmutil import init_params, lm_config, random_walk_batch, token_batch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mgr():
+    from callaghandev.ml_b200 import GEMM_FP32_SIMT, CudaB200AccelerationManager
+
+    m = CudaB200AccelerationManager(0, GEMM_FP32_SIMT)
+    yield m
+    m.Dispose()
+
+
+def _b200_cfg(cfg):
+    from callaghandev.ml_b200 import LMConfig
+
+    c = LMConfig()
+    for name, _ in LMConfig._fields_:
+        setattr(c, name, getattr(cfg, name))
+    return c
+
+
+def _compare_tensors(oracle, cfg, exp, act, tol, what):
+    names = (["emb"] if cfg.discrete else ["inW", "inB"]) + [f"L{l}.{n}" for l in range(cfg.num_layers) for n in
+            ("WQ", "WK", "WV", "WO", "bQ", "bK", "bV", "bO", "g1", "b1", "g2", "b2", "W1", "fb1", "W2", "fb2")] + ["Wout", "bout"]
+    for (off, r, c), name in zip(oracle.lm_tensors(cfg), names):
+        assert_close(exp[off:off + r * c], act[off:off + r * c], tol, f"{what} {name}")
+
+
+def test_layout_matches_oracle(mgr, oracle):
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    for cfg in (lm_config(vocab=200, d=64, H=4, L=2, f=128), lm_config(F=5, O=1, d=32, H=4, L=3, f=64, discrete=False, loss="mse"),
+                lm_config(vocab=13, d=8, H=2, L=1, f=16, align=1)):
+        t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 64)
+        assert t.param_count == oracle.lm_param_count(cfg)
+        assert t.tensors() == oracle.lm_tensors(cfg)
+        t.close()
+
+
+@pytest.mark.parametrize("max_rows", [4096, 70])  # one packed pass, and several passes with gradient accumulation
+def test_config1_discrete_step(mgr, oracle, max_rows):
+    """BASELINE config 1: vocab 200, d 64, 4 heads, 2 layers, ffn 128, batch of 4 sequences of length 2..64,
+    lr 1e-3, clipping at 1.0: one training step compared gradient by gradient and weight by weight."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(1234)
+    cfg = lm_config(vocab=200, d=64, H=4, L=2, f=128, act="Relu")
+    toks, off = token_batch(rng, 32, 200, 2, 64)
+    toks4, off4 = toks[:off[4]], off[:5]
+    P = init_params(oracle, cfg, 7)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), max_rows)
+    # gradients only (no clipping, no update)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off4, tokens=toks4, use_clip=False, do_step=False)
+    t.upload_params(P)
+    al, an, av = t.train_step_discrete(toks4, off4, 1e-3, use_clip=False, do_step=False)
+    assert av == ev == 4
+    assert_close(el, al, 1e-5, "loss"); assert_close(en, an, 2e-5, "grad norm")
+    _compare_tensors(oracle, cfg, ge, t.download_grads(), 2e-5, "grad")
+    assert np.array_equal(t.download_params(), P), "do_step=0 must leave the weights untouched"
+    # the full step
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off4, tokens=toks4, lr=1e-3, use_clip=True, clip_thr=1.0, do_step=True)
+    al, an, av = t.train_step_discrete(toks4, off4, 1e-3, use_clip=True, clip_threshold=1.0, do_step=True)
+    assert_close(el, al, 1e-5, "loss (step)"); assert_close(en, an, 2e-5, "grad norm (step)")
+    _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, "post-step weight")
+    # all 32 sequences as one batch, second step on the updated weights
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=1e-3, use_clip=True, clip_thr=1.0, do_step=True)
+    al, an, av = t.train_step_discrete(toks, off, 1e-3, use_clip=True, clip_threshold=1.0, do_step=True)
+    assert av == ev == 32
+    assert_close(el, al, 2e-5, "loss (32 sequences)")
+    _compare_tensors(oracle, cfg, pe, t.download_params(), 2e-5, "post-step weight (32 sequences)")
+    t.close()
+
+
+def test_step_semantics_and_edge_batches(mgr, oracle):
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(2)
+    cfg = lm_config(vocab=30, d=16, H=2, L=1, f=32, act="Tanh")
+    P = init_params(oracle, cfg, 4)
+    toks, off = token_batch(rng, 5, 30, 2, 12)
+    toks = np.concatenate([toks, [1, 99, 2], [1]]).astype(np.int32)  # out-of-vocabulary id and a length-1 sequence are skipped
+    off = np.concatenate([off, [off[-1] + 3, off[-1] + 4]]).astype(np.int32)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 256)
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=0.1, use_clip=True, clip_thr=0.05)
+    al, an, av = t.train_step_discrete(toks, off, 0.1, True, 0.05, True)
+    assert av == ev == 5 and an > 0.05
+    assert_close(el, al, 1e-5, "loss"); assert_close(en, an, 2e-5, "norm")
+    g = t.download_grads()
+    assert_close(0.05, np.sqrt((g.astype(np.float64) ** 2).sum()), 1e-4, "gradients are left scaled and clipped")
+    _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, "post-step weight")
+    emb = g[:30 * 16].reshape(30, 16)
+    used = set(int(x) for s in range(5) for x in toks[off[s]:off[s + 1] - 1])
+    for r in range(30):
+        assert (np.abs(emb[r]).sum() > 0) == (r in used), "only embedding rows of seen tokens receive gradient"
+    # nothing valid: loss 0, weights untouched (TransformerTrainer.cs:309-310)
+    before = t.download_params()
+    assert t.train_step_discrete(np.array([1], np.int32), np.array([0, 1], np.int32), 0.1) == (0.0, 0.0, 0)
+    assert t.train_step_discrete(np.zeros(0, np.int32), np.array([0], np.int32), 0.1) == (0.0, 0.0, 0)
+    assert np.array_equal(before, t.download_params())
+    # non-finite weights: the step is skipped and gradients are zeroed (TransformerTrainer.cs:271-272, :316-320)
+    bad = before.copy(); bad[oracle.lm_tensors(cfg)[-1][0]] = np.inf  # first output bias
+    t.upload_params(bad)
+    l, n, v = t.train_step_discrete(toks, off, 0.1)
+    assert v == 0 and l == 0.0
+    assert np.array_equal(t.download_params(), bad)
+    assert not t.download_grads().any()
+    t.upload_params(before)
+    with pytest.raises(IndexError):  # ClipGradients rejects a non-positive threshold (TransformerTrainer.cs:1313-1314)
+        t.train_step_discrete(toks, off, 0.1, True, -1.0)
+    t.close()
+
+
+@pytest.mark.parametrize("act", ["Relu", "Leakyrelu", "Swish"])
+def test_config3_continuous_regression_step(mgr, oracle, act):
+    """BASELINE config 3 shape family (features 5 -> d -> 1, MSE, one-step target shift) at a size the oracle finishes
+    in seconds: d 64, 4 heads, 2 layers, ffn 256, 6 sequences of 40 steps."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(5)
+    cfg = lm_config(F=5, O=1, d=64, H=4, L=2, f=256, act=act, discrete=False, loss="mse")
+    x, tg, off = random_walk_batch(rng, 6, 40, 5, 3)
+    P = init_params(oracle, cfg, 9)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 100)  # 3 passes
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, cont=x, reg_targets=tg, lr=0.01, use_clip=True, clip_thr=1.0)
+    al, an, av = t.train_step_continuous(x, off, reg_targets=tg, lr=0.01, use_clip=True, clip_threshold=1.0)
+    assert av == ev == 6
+    assert_close(el, al, 1e-5, "loss"); assert_close(en, an, 3e-5, "norm")
+    _compare_tensors(oracle, cfg, ge, t.download_grads(), 3e-5, "grad")
+    _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, "post-step weight")
+    t.close()
+
+
+def test_continuous_classification_step(mgr, oracle):
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(6)
+    cfg = lm_config(F=3, O=4, d=32, H=2, L=1, f=64, act="Sigmoid", discrete=False, loss="ce", causal=True)
+    x, _, off = random_walk_batch(rng, 4, 17, 3, 1)
+    cls = rng.integers(0, 4, x.shape[0]).astype(np.int32)
+    P = init_params(oracle, cfg, 10)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 512)
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, cont=x, cls_targets=cls, lr=0.01)
+    al, an, av = t.train_step_continuous(x, off, class_targets=cls, lr=0.01)
+    assert av == ev == 4
+    assert_close(el, al, 1e-5, "loss")
+    _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, "post-step weight")
+    t.close()
+
+
+def test_padded_and_unpadded_arena_agree(mgr, oracle):
+    """align_floats=1 (no padding, the three-GEMM Q/K/V path) and align_floats=64 (fused [3d,d] projection)."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(8)
+    toks, off = token_batch(rng, 3, 13, fixed_len=6)
+    for align in (1, 64):
+        cfg = lm_config(vocab=13, d=8, H=2, L=2, f=16, act="Tanh", align=align)
+        P = init_params(oracle, cfg, 3)
+        t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 64)
+        t.upload_params(P)
+        pe, ge = P.copy(), np.zeros_like(P)
+        oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=0.05)
+        t.train_step_discrete(toks, off, 0.05)
+        _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, f"align {align} weight")
+        t.close()
+
+
+def test_adam_extension_against_numpy(mgr, oracle):
+    """Adam is an extension (the reference only has SGD): checked against a numpy Adam applied to the oracle's gradients."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(3)
+    cfg = lm_config(vocab=40, d=32, H=4, L=1, f=64)
+    toks, off = token_batch(rng, 4, 40, 4, 20)
+    P = init_params(oracle, cfg, 11)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 256)
+    t.set_optimizer("adam", 0.9, 0.999, 1e-8)
+    t.upload_params(P)
+    w = P.astype(np.float64); m = np.zeros_like(w); v = np.zeros_like(w)
+    for step in (1, 2, 3):
+        g = np.zeros_like(P)
+        oracle.lm_train_step(cfg, w.astype(np.float32), g, off, tokens=toks, use_clip=True, clip_thr=1.0, do_step=False)
+        g = g.astype(np.float64)
+        m = 0.9 * m + 0.1 * g; v = 0.999 * v + 0.001 * g * g
+        w = w - 3e-4 * (m / (1 - 0.9 ** step)) / (np.sqrt(v / (1 - 0.999 ** step)) + 1e-8)
+        t.train_step_discrete(toks, off, 3e-4, True, 1.0, True)
+    # Adam divides by sqrt(v): where |g| is at rounding level the quotient amplifies it, so compare the bulk tightly
+    got = t.download_params().astype(np.float64)
+    assert np.max(np.abs(got - w)) < 3e-4 * 3 * 1.01 + 1e-6, "no weight may move more than 3 steps of lr"
+    assert np.mean(np.abs(got - w) < 1e-5) > 0.97
+    t.close()
+
+
+def test_run_twice_bit_identical_step(mgr, oracle):
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(12)
+    cfg = lm_config(vocab=100, d=64, H=4, L=2, f=128)
+    toks, off = token_batch(rng, 8, 100, 5, 50, zipf=1.1)
+    P = init_params(oracle, cfg, 1)
+    outs = []
+    for _ in range(2):
+        t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 128)
+        t.upload_params(P)
+        r = t.train_step_discrete(toks, off, 1e-3)
+        outs.append((r, t.download_params(), t.download_grads()))
+        t.close()
+    assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1]) and np.array_equal(outs[0][2], outs[1][2])
+
+
+# ------------------------------------------------------------------------------------------------ MLP batch trainer
+def _mlp_setup(rng, widths):
+    W = [rng.normal(0, np.sqrt(2.0 / widths[l - 1]), (widths[l], widths[l - 1])).astype(np.float32) for l in range(1, len(widths))]
+    B = [rng.normal(0, 0.05, widths[l]).astype(np.float32) for l in range(1, len(widths))]
+    return W, B
+
+
+def test_config2_mlp_batch_step(mgr, oracle):
+    """BASELINE config 2: 784-512-256-10, ReLU hidden, Sigmoid output, MSE, L2 1e-4, batch 256, inputs U[0,1),
+    one-hot targets: one LearnBatch compared weight by weight."""
+    from callaghandev.ml_b200 import B200MlpBatchTrainer
+
+    rng = np.random.default_rng(42)
+    widths, acts = [784, 512, 256, 10], ["Relu", "Relu", "Relu", "Sigmoid"]
+    W, B = _mlp_setup(rng, widths)
+    X = rng.uniform(0, 1, (256, 784)).astype(np.float32)
+    Y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 256)]
+    for thr in (1.0, 1e9):
+        we, be = [w.copy() for w in W], [b.copy() for b in B]
+        en = oracle.mlp_learn_batch(widths, acts, we, be, X, Y, "mse", lr=0.1, lam=1e-4, clip_thr=thr)
+        t = B200MlpBatchTrainer(mgr, widths, acts, "mse", 1.0, 1e-4, thr, 256)
+        for l in range(1, 4):
+            t.upload_layer(l, W[l - 1], B[l - 1])
+        an = t.learn_batch(X, Y, 0.1)
+        assert_close(en, an, 2e-5, "delta norm")
+        for l in range(1, 4):
+            w, b = t.download_layer(l)
+            assert_close(we[l - 1], w, 1e-5, f"W{l}"); assert_close(be[l - 1], b, 1e-5, f"b{l}")
+        t.close()
+
+
+@pytest.mark.parametrize("cost", ["mse", "ZeroWeightedMSE", "mae", "categoricalCrossEntropy", "huberLoss", "binaryCrossEntropy"])
+@pytest.mark.parametrize("act", ["None", "Sigmoid", "Tanh", "Relu", "Leakyrelu"])
+def test_mlp_costs_and_activations(mgr, oracle, cost, act):
+    """The six cost derivatives and five activation derivatives of the batch path (conventions of
+    BatchedAccelerationGPU.cs:262-287 and NeuralNetwork.cs:314-390), two steps, ragged batch, with input scaling."""
+    from callaghandev.ml_b200 import B200MlpBatchTrainer
+
+    rng = np.random.default_rng(sum(map(ord, cost + act)))
+    widths, acts = [20, 33, 7], ["None", act, "Sigmoid"]
+    W, B = _mlp_setup(rng, widths)
+    X = rng.uniform(-2, 3, (37, 20)).astype(np.float32)
+    Y = rng.uniform(0.05, 0.95, (37, 7)).astype(np.float32)  # strictly inside (0,1): BCE divides by y(1-y)
+    if cost == "ZeroWeightedMSE":
+        Y[:, 0] = 0
+    mn, mx = X.min(0), X.max(0)
+    mx[3] = mn[3]  # zero range -> scaled input 0 (NeuralNetwork.cs:131)
+    Xs = oracle.mlp_scale_inputs(X, mn, mx)
+    we, be = [w.copy() for w in W], [b.copy() for b in B]
+    t = B200MlpBatchTrainer(mgr, widths, acts, cost, 0.3, 1e-3, 0.7, 64)
+    for l in (1, 2):
+        t.upload_layer(l, W[l - 1], B[l - 1])
+    for _ in range(2):
+        en = oracle.mlp_learn_batch(widths, acts, we, be, Xs, Y, cost, huber_delta=0.3, lr=0.2, lam=1e-3, clip_thr=0.7)
+        an = t.learn_batch(X, Y, 0.2, mn, mx)
+        assert_close(en, an, 2e-5, "delta norm")
+    for l in (1, 2):
+        w, b = t.download_layer(l)
+        assert_close(we[l - 1], w, 2e-5, f"W{l}"); assert_close(be[l - 1], b, 2e-5, f"b{l}")
+    t.close()
+
+
+def test_mlp_bce_with_one_hot_targets_is_nonfinite_like_the_reference(mgr, oracle):
+    """binaryCrossEntropy divides by y(1-y) (NeuralNetwork.cs:348): one-hot targets give inf/NaN deltas in the reference;
+    the device path reproduces that instead of hiding it."""
+    from callaghandev.ml_b200 import B200MlpBatchTrainer
+
+    rng = np.random.default_rng(1)
+    widths, acts = [4, 3], ["None", "Sigmoid"]
+    W, B = _mlp_setup(rng, widths)
+    X, Y = rng.uniform(0, 1, (5, 4)).astype(np.float32), np.eye(3, dtype=np.float32)[rng.integers(0, 3, 5)]
+    t = B200MlpBatchTrainer(mgr, widths, acts, "binaryCrossEntropy", 1.0, 0.0, 1.0, 8)
+    t.upload_layer(1, W[0], B[0])
+    assert not np.isfinite(t.learn_batch(X, Y, 0.1))
+    we, be = [W[0].copy()], [B[0].copy()]
+    assert not np.isfinite(oracle.mlp_learn_batch(widths, acts, we, be, X, Y, "binaryCrossEntropy", lr=0.1))
+    t.close()
