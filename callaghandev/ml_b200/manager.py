@@ -9,6 +9,7 @@ Exceptions: ValueError <- ArgumentNullException/ArgumentException, IndexError <-
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 
 import numpy as np
 
@@ -60,6 +61,7 @@ class CudaB200AccelerationManager:
             raise L.B200Error(f"b200_create(device={device}) failed with status {rc}: a CUDA device is required (no CPU fallback)")
         self.ctx = h
         self.device = device
+        self._children = weakref.WeakSet()  # resident trainers: they must be destroyed before the context
         self.set_gemm_mode(gemm_mode)
 
     # ------------------------------------------------------------------ plumbing
@@ -83,6 +85,8 @@ class CudaB200AccelerationManager:
 
     def Dispose(self):
         if getattr(self, "ctx", None):
+            for child in list(self._children):
+                child.close()
             self.lib.b200_destroy(self.ctx)
             self.ctx = None
 

@@ -41,6 +41,7 @@ class B200LanguageModelTrainer:
                                             int(max_rows_per_pass), C.byref(h)))
         self.h = h
         self._cb = None
+        manager._children.add(self)
 
     def close(self):
         if getattr(self, "h", None):
@@ -148,6 +149,7 @@ class B200MlpBatchTrainer:
         manager._ck(self.lib.b200_mlp_create(manager.ctx, len(self.widths), _pi(wd), _pi(ac), L.COST[cost] if isinstance(cost, str) else int(cost),
                                              huber_delta, l2_lambda, clip_threshold, int(max_batch), C.byref(h)))
         self.h = h
+        manager._children.add(self)
 
     def close(self):
         if getattr(self, "h", None):

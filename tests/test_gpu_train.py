@@ -126,7 +126,7 @@ def test_step_semantics_and_edge_batches(mgr, oracle):
 
 
 @pytest.mark.parametrize("act", ["Relu", "Leakyrelu", "Swish"])
-def test_config3_continuous_regression_step(mgr, oracle, act):
+def test_config3_continuous_regression_step(mgr, oracle, oracle64, act):
     """BASELINE config 3 shape family (features 5 -> d -> 1, MSE, one-step target shift) at a size the oracle finishes
     in seconds: d 64, 4 heads, 2 layers, ffn 256, 6 sequences of 40 steps."""
     from callaghandev.ml_b200 import B200LanguageModelTrainer
@@ -141,7 +141,12 @@ def test_config3_continuous_regression_step(mgr, oracle, act):
     el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, cont=x, reg_targets=tg, lr=0.01, use_clip=True, clip_thr=1.0)
     al, an, av = t.train_step_continuous(x, off, reg_targets=tg, lr=0.01, use_clip=True, clip_threshold=1.0)
     assert av == ev == 6
-    assert_close(el, al, 1e-5, "loss"); assert_close(en, an, 3e-5, "norm")
+    assert_close(el, al, 1e-5, "loss")
+    # The norm here is ~128 and the float32 oracle adds 1.1 M squares serially, which alone costs ~3e-5 relative
+    # (float32 oracle vs the same code in float64).  The device's tree sum is held to 1e-5 of the float64 value.
+    p64, g64 = P.astype(np.float64), np.zeros(P.size, np.float64)
+    n64 = oracle64.lm_train_step(cfg, p64, g64, off, cont=x, reg_targets=tg, lr=0.01, use_clip=True, clip_thr=1.0)[1]
+    assert_close(n64, an, 1e-5, "norm vs float64 oracle"); assert_close(en, an, 1e-4, "norm vs float32 oracle")
     _compare_tensors(oracle, cfg, ge, t.download_grads(), 3e-5, "grad")
     _compare_tensors(oracle, cfg, pe, t.download_params(), 1e-5, "post-step weight")
     t.close()
