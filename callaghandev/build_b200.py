@@ -1,6 +1,9 @@
-"""Builds libcallaghan_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
+"""Builds callaghandev/ml_b200/libcallaghan_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m callaghandev.ml_b200.build [--force] [--verbose]
+    python -m callaghandev.build_b200 [--force] [--verbose]
+
+Lives beside the package rather than inside it: importing callaghandev.ml_b200 loads the shared library and fails
+when it is missing or stale, which is exactly the situation in which this script has to run.
 """
 from __future__ import annotations
 
@@ -10,7 +13,7 @@ import sys
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
-HERE = Path(__file__).resolve().parent
+HERE = Path(__file__).resolve().parent / "ml_b200"
 CSRC = HERE / "csrc"
 OBJ = HERE / "_obj"
 LIB = HERE / "libcallaghan_b200.so"

@@ -45,6 +45,8 @@ PROTOTYPES = {
     "b200_synchronize": (_i32, [_vp]),
     "b200_kernel_launches": (_i64, [_vp]),
     "b200_has_tcgen05": (_i32, [_vp]),
+    "b200_profile_gemm": (_i32, [_vp, _i32]),
+    "b200_gemm_profile": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200_MatrixMultiply": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _f]),
     "b200_MatrixMultiplyTranspose": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _f]),
     "b200_BatchDotProductAddBias": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _i32, _i32, _f, _i32, _f]),
@@ -97,6 +99,11 @@ PROTOTYPES = {
     "b200_lm_accumulate_discrete": (_i32, [_vp, _i, _i, _i32, _f, _i]),
     "b200_lm_accumulate_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _f, _i]),
     "b200_lm_apply_step": (_i32, [_vp, _i32, _fl, _i32, _fl, _i32, _f]),
+    "b200_lm_batch_create_discrete": (_i32, [_vp, _i, _i, _i32, _pp]),
+    "b200_lm_batch_create_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _pp]),
+    "b200_lm_batch_destroy": (_i32, [_vp]),
+    "b200_lm_accumulate_batch": (_i32, [_vp, _vp, _f, _i]),
+    "b200_lm_train_step_batch": (_i32, [_vp, _vp, _fl, _i32, _fl, _i32, _f, _f, _i]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),
     "b200_mlp_create": (_i32, [_vp, _i32, _i, _i, _i32, _fl, _fl, _fl, _i32, _pp]),
     "b200_mlp_destroy": (_i32, [_vp]),
@@ -114,7 +121,7 @@ def load() -> C.CDLL:
     if _lib is not None:
         return _lib
     if not LIB_PATH.exists():
-        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m callaghandev.ml_b200.build` (needs nvcc). "
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m callaghandev.build_b200` (needs nvcc). "
                           "There is no CPU fallback.")
     lib = C.CDLL(str(LIB_PATH))
     for name, (res, args) in PROTOTYPES.items():

@@ -120,6 +120,7 @@ int32_t b200_destroy(b200_ctx* ctx) {
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
     for (auto& kv : ctx->rope)
         if (kv.second.dev) cudaFree(kv.second.dev);
+    for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return B200_OK;
@@ -145,6 +146,31 @@ int32_t b200_synchronize(b200_ctx* ctx) {
 }
 int64_t b200_kernel_launches(b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
 int32_t b200_has_tcgen05(b200_ctx* ctx) { return ctx && ctx->cc_major == 10 ? 1 : 0; }
+
+int32_t b200_profile_gemm(b200_ctx* ctx, int32_t enable) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->profile = enable ? 1 : 0;
+    ctx->prof_used = 0;
+    ctx->prof_flops.clear();
+    ctx->prof_engine.clear();
+    return B200_OK;
+}
+
+int32_t b200_gemm_profile(b200_ctx* ctx, int32_t engine, int64_t* launches, double* flops, double* ms) {
+    if (!ctx || !launches || !flops || !ms) return B200_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    *launches = 0; *flops = 0; *ms = 0;
+    for (size_t i = 0; i < ctx->prof_flops.size(); i++) {
+        if (ctx->prof_engine[i] != engine) continue;
+        float t = 0.f;
+        B200_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]));
+        *launches += 1; *flops += ctx->prof_flops[i]; *ms += t;
+    }
+    return B200_OK;
+}
 
 // ------------------------------------------------------------------------------------------------ tensor primitives
 int32_t b200_MatrixMultiply(b200_ctx* ctx, const float* A, int32_t rowsA, int32_t colsA, const float* B, int32_t rowsB, int32_t colsB, float* C) {

@@ -35,6 +35,12 @@ struct b200_ctx {
     float* pinned = nullptr;  // 4 KiB pinned staging for scalars
     std::map<std::pair<int, uint32_t>, RopeTable> rope;  // key: (headDim, bits of baseTheta)
     void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
+    // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
+    int profile = 0;
+    std::vector<cudaEvent_t> prof_events;
+    size_t prof_used = 0;
+    std::vector<double> prof_flops;   // per launch
+    std::vector<int> prof_engine;     // per launch: 0 SIMT, 1 tcgen05
 };
 
 namespace b200 {

@@ -109,13 +109,34 @@ int gemm_simt(b200_ctx* ctx, const Gemm& g) {
     return B200_OK;
 }
 
-int gemm(b200_ctx* ctx, const Gemm& g) {
-    if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) return gemm_tcgen05(ctx, g);
+static int gemm_dispatch(b200_ctx* ctx, const Gemm& g, int* engine) {
+    if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) {
+        *engine = 1;
+        return gemm_tcgen05(ctx, g);
+    }
     if (ctx->gemm_mode == B200_GEMM_TF32_TCGEN05 && g.M >= 128 && g.N >= 128 && g.K >= 128)
         return fail(ctx, B200_ERR_UNSUPPORTED, "TF32 tcgen05 GEMM requested but shape/alignment/device does not qualify (M=%d N=%d K=%d)", g.M, g.N, g.K);
+    *engine = 0;
     return gemm_simt(ctx, g);
 }
 
+int gemm(b200_ctx* ctx, const Gemm& g) {
+    int engine = 0;
+    if (!ctx->profile) return gemm_dispatch(ctx, g, &engine);
+    while (ctx->prof_events.size() < ctx->prof_used + 2) {
+        cudaEvent_t e;
+        B200_CUDA(ctx, cudaEventCreate(&e));
+        ctx->prof_events.push_back(e);
+    }
+    cudaEvent_t e0 = ctx->prof_events[ctx->prof_used], e1 = ctx->prof_events[ctx->prof_used + 1];
+    B200_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
+    B200_TRY(gemm_dispatch(ctx, g, &engine));
+    B200_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
+    ctx->prof_used += 2;
+    ctx->prof_flops.push_back(2.0 * g.M * g.N * g.K);
+    ctx->prof_engine.push_back(engine);
+    return B200_OK;
+}
 
 int linear_fwd(b200_ctx* ctx, const float* X, int rows, int inDim, const float* W, const float* bias, int outDim, float* Y, int ldy) {
     Gemm g;

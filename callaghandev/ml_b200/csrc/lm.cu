@@ -72,6 +72,25 @@ struct LayerCache {
 
 struct Seq { int index, start, len; };  // len = input length (sequence length - 1)
 
+// Device-resident inputs of one packed pass.
+struct PassDev {
+    int32_t *ids = nullptr, *targets = nullptr, *pos = nullptr, *segId = nullptr, *segOff = nullptr, *perm = nullptr;
+    AttnSeg* segs = nullptr;
+    float *rowScale = nullptr, *contIn = nullptr, *regTgt = nullptr;
+    size_t nDistinct = 0;  // distinct token ids of the pass (segments of the embedding-gradient scatter)
+};
+struct Pass {
+    std::vector<Seq> seqs;
+    int rows = 0, maxLen = 0;
+};
+struct Batch {  // host views of the caller's batch
+    const int32_t* tokens = nullptr;
+    const float* feats = nullptr;
+    const float* regT = nullptr;
+    const int32_t* clsT = nullptr;
+    const int32_t* off = nullptr;
+};
+
 }  // namespace
 
 struct b200_lm {
@@ -87,13 +106,13 @@ struct b200_lm {
     char* block = nullptr;
     std::vector<LayerCache> cache;
     float *xFinal = nullptr, *logits = nullptr, *proj = nullptr, *gbuf[4] = {nullptr, nullptr, nullptr, nullptr}, *dqkv = nullptr, *d1 = nullptr,
-          *rowDot = nullptr, *contIn = nullptr, *regTgt = nullptr, *rowScale = nullptr, *rowLoss = nullptr, *stepOut = nullptr;
-    int32_t *rowOk = nullptr, *ids = nullptr, *targets = nullptr, *pos = nullptr, *segId = nullptr, *segOff = nullptr, *perm = nullptr;
-    AttnSeg* segs = nullptr;
+          *rowDot = nullptr, *rowLoss = nullptr, *stepOut = nullptr;
+    int32_t* rowOk = nullptr;
+    PassDev own;  // the trainer's own staging buffers (one pass)
+    PassDev cur;  // inputs of the pass being processed: `own`, or a slice of a prepared batch
     // pinned host staging
     int32_t* h_int = nullptr;
     float* h_float = nullptr;
-    size_t nDistinct = 0;  // distinct token ids of the staged pass
     std::vector<char> t_has_bwd;  // per group of four timing events: was the backward-end event recorded
     b200_grad_ready_fn cb = nullptr;
     void* cb_user = nullptr;
@@ -103,6 +122,18 @@ struct b200_lm {
     size_t t_used = 0;
     float timings[4] = {0, 0, 0, 0};
     const float* rope = nullptr;
+};
+
+// A batch whose inputs have been planned, packed and copied to the device once; it can be trained on repeatedly
+// (epochs over a resident dataset) without touching host memory again.
+struct b200_lm_batch {
+    b200_lm* lm = nullptr;
+    std::vector<int32_t> tokens, off, clsT;  // host copies (needed only if a pass must be re-packed after a non-finite loss)
+    std::vector<float> feats, regT;
+    int n_seq = 0;
+    char* block = nullptr;
+    std::vector<PassDev> dev;
+    void* plan = nullptr;  // Plan*
 };
 
 namespace {
@@ -126,20 +157,8 @@ void fire(b200_lm* lm, int64_t off, int64_t count) {
 }
 
 // ---- one packed pass ---------------------------------------------------------------------------------------------
-struct Pass {
-    std::vector<Seq> seqs;
-    int rows = 0, maxLen = 0;
-};
 
-struct Batch {  // host views of the caller's batch
-    const int32_t* tokens = nullptr;
-    const float* feats = nullptr;
-    const float* regT = nullptr;
-    const int32_t* clsT = nullptr;
-    const int32_t* off = nullptr;
-};
-
-int stage_pass(b200_lm* lm, const Batch& b, const Pass& p) {
+int stage_pass(b200_lm* lm, const Batch& b, const Pass& p, PassDev& dst) {
     b200_ctx* ctx = lm->ctx;
     const b200_lm_config& c = lm->cfg;
     const int N = p.rows, S = (int)p.seqs.size(), F = c.input_feature_dim, O = c.output_dim;
@@ -169,12 +188,12 @@ int stage_pass(b200_lm* lm, const Batch& b, const Pass& p) {
         }
     }
     cudaStream_t st = ctx->stream;
-    B200_CUDA(ctx, cudaMemcpyAsync(lm->pos, h_pos, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
-    B200_CUDA(ctx, cudaMemcpyAsync(lm->segs, h_segs, sizeof(AttnSeg) * S, cudaMemcpyHostToDevice, st));
-    B200_CUDA(ctx, cudaMemcpyAsync(lm->rowScale, h_scale, sizeof(float) * N, cudaMemcpyHostToDevice, st));
-    if (c.discrete || c.loss_kind == 0) B200_CUDA(ctx, cudaMemcpyAsync(lm->targets, h_tgt, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+    B200_CUDA(ctx, cudaMemcpyAsync(dst.pos, h_pos, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+    B200_CUDA(ctx, cudaMemcpyAsync(dst.segs, h_segs, sizeof(AttnSeg) * S, cudaMemcpyHostToDevice, st));
+    B200_CUDA(ctx, cudaMemcpyAsync(dst.rowScale, h_scale, sizeof(float) * N, cudaMemcpyHostToDevice, st));
+    if (c.discrete || c.loss_kind == 0) B200_CUDA(ctx, cudaMemcpyAsync(dst.targets, h_tgt, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
     if (c.discrete) {
-        B200_CUDA(ctx, cudaMemcpyAsync(lm->ids, h_ids, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(dst.ids, h_ids, sizeof(int32_t) * N, cudaMemcpyHostToDevice, st));
         // rows grouped by token id for the deterministic embedding-gradient scatter
         std::vector<int32_t> sid, soff, perm;
         sort_rows_by_id(h_ids, N, c.vocab_size, sid, soff, perm);
@@ -182,13 +201,13 @@ int stage_pass(b200_lm* lm, const Batch& b, const Pass& p) {
         memcpy(h_sort, sid.data(), sizeof(int32_t) * sid.size());
         memcpy(h_sort + lm->maxRows, soff.data(), sizeof(int32_t) * soff.size());
         memcpy(h_sort + 2 * (size_t)lm->maxRows + 1, perm.data(), sizeof(int32_t) * perm.size());
-        B200_CUDA(ctx, cudaMemcpyAsync(lm->segId, h_sort, sizeof(int32_t) * sid.size(), cudaMemcpyHostToDevice, st));
-        B200_CUDA(ctx, cudaMemcpyAsync(lm->segOff, h_sort + lm->maxRows, sizeof(int32_t) * soff.size(), cudaMemcpyHostToDevice, st));
-        B200_CUDA(ctx, cudaMemcpyAsync(lm->perm, h_sort + 2 * (size_t)lm->maxRows + 1, sizeof(int32_t) * perm.size(), cudaMemcpyHostToDevice, st));
-        lm->nDistinct = sid.size();
+        B200_CUDA(ctx, cudaMemcpyAsync(dst.segId, h_sort, sizeof(int32_t) * sid.size(), cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(dst.segOff, h_sort + lm->maxRows, sizeof(int32_t) * soff.size(), cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(dst.perm, h_sort + 2 * (size_t)lm->maxRows + 1, sizeof(int32_t) * perm.size(), cudaMemcpyHostToDevice, st));
+        dst.nDistinct = sid.size();
     } else {
-        B200_CUDA(ctx, cudaMemcpyAsync(lm->contIn, h_cont, sizeof(float) * (size_t)N * F, cudaMemcpyHostToDevice, st));
-        if (c.loss_kind == 1) B200_CUDA(ctx, cudaMemcpyAsync(lm->regTgt, h_reg, sizeof(float) * (size_t)N * O, cudaMemcpyHostToDevice, st));
+        B200_CUDA(ctx, cudaMemcpyAsync(dst.contIn, h_cont, sizeof(float) * (size_t)N * F, cudaMemcpyHostToDevice, st));
+        if (c.loss_kind == 1) B200_CUDA(ctx, cudaMemcpyAsync(dst.regTgt, h_reg, sizeof(float) * (size_t)N * O, cudaMemcpyHostToDevice, st));
     }
     return B200_OK;
 }
@@ -206,8 +225,8 @@ int forward_pass(b200_lm* lm, const Pass& p) {
     const int N = p.rows, d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim;
     const float* P = lm->P;
     float* x = c.num_layers > 0 ? lm->cache[0].x : lm->xFinal;
-    if (c.discrete) B200_TRY(k_embed(ctx, lm->ids, N, P + lm->lay.in0, d, x));
-    else B200_TRY(linear_fwd(ctx, lm->contIn, N, c.input_feature_dim, P + lm->lay.in0, P + lm->lay.in1, d, x, d));
+    if (c.discrete) B200_TRY(k_embed(ctx, lm->cur.ids, N, P + lm->lay.in0, d, x));
+    else B200_TRY(linear_fwd(ctx, lm->cur.contIn, N, c.input_feature_dim, P + lm->lay.in0, P + lm->lay.in1, d, x, d));
     for (int l = 0; l < c.num_layers; l++) {
         const LayerOff& L = lm->lay.layer[(size_t)l];
         LayerCache& k = lm->cache[(size_t)l];
@@ -218,11 +237,11 @@ int forward_pass(b200_lm* lm, const Pass& p) {
             B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WK, P + L.bK, d, k.qkv + d, 3 * d));
             B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WV, P + L.bV, d, k.qkv + 2 * d, 3 * d));
         }
-        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->pos, 0));  // Q and K column blocks
+        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 0));  // Q and K column blocks
         Attn a;
         a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
         a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
-        a.segs_dev = lm->segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
+        a.segs_dev = lm->cur.segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
         a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum;
         B200_TRY(attn_forward(ctx, a));
         B200_TRY(linear_fwd(ctx, k.attnO, N, d, P + L.WO, P + L.bO, d, lm->proj, d));
@@ -244,8 +263,8 @@ int forward_pass(b200_lm* lm, const Pass& p) {
 int loss_pass(b200_lm* lm, const Pass& p) {
     const b200_lm_config& c = lm->cfg;
     if (c.loss_kind == 0)
-        return k_cross_entropy(lm->ctx, lm->logits, p.rows, c.output_dim, lm->targets, p.rows, lm->rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
-    return k_mse(lm->ctx, lm->logits, p.rows, c.output_dim, lm->regTgt, p.rows, lm->rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
+        return k_cross_entropy(lm->ctx, lm->logits, p.rows, c.output_dim, lm->cur.targets, p.rows, lm->cur.rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
+    return k_mse(lm->ctx, lm->logits, p.rows, c.output_dim, lm->cur.regTgt, p.rows, lm->cur.rowScale, 0.f, lm->logits, lm->rowLoss, lm->rowOk);
 }
 
 int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
@@ -287,11 +306,11 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         Attn a;
         a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
         a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
-        a.segs_dev = lm->segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
+        a.segs_dev = lm->cur.segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
         a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum; a.rowDot = lm->rowDot;
         a.dO = t1; a.lddo = d; a.dQ = lm->dqkv; a.dK = lm->dqkv + d; a.dV = lm->dqkv + 2 * d; a.lddq = a.lddk = a.lddv = 3 * d;
         B200_TRY(attn_backward(ctx, a));
-        B200_TRY(k_rope(ctx, lm->dqkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->pos, 1));
+        B200_TRY(k_rope(ctx, lm->dqkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 1));
         float* out = t2;  // dX of the layer input = dQKV * Wqkv + dAttnResidual (:919, residual add fused)
         if (qkv_fused(lm, L)) {
             B200_TRY(wgrad(ctx, lm->dqkv, 3 * d, k.x, d, N, 3 * d, d, G + L.WQ, G + L.bQ));
@@ -317,9 +336,9 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
     }
     // BackpropInput (:887-896)
     if (c.discrete)
-        B200_TRY(k_embed_scatter(ctx, G + lm->lay.in0, dX, nullptr, lm->segId, lm->segOff, lm->perm, (int)lm->nDistinct, d));
+        B200_TRY(k_embed_scatter(ctx, G + lm->lay.in0, dX, nullptr, lm->cur.segId, lm->cur.segOff, lm->cur.perm, (int)lm->cur.nDistinct, d));
     else
-        B200_TRY(wgrad(ctx, dX, d, lm->contIn, c.input_feature_dim, N, d, c.input_feature_dim, G + lm->lay.in0, G + lm->lay.in1));
+        B200_TRY(wgrad(ctx, dX, d, lm->cur.contIn, c.input_feature_dim, N, d, c.input_feature_dim, G + lm->lay.in0, G + lm->lay.in1));
     if (notify) {
         int64_t end = c.num_layers > 0 ? lm->lay.layer[0].WQ : lm->lay.Wout;
         fire(lm, 0, end);
@@ -328,25 +347,22 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
     return B200_OK;
 }
 
-// Accumulates gradients of all valid sequences of the batch.  loss_sum = sum over sequences of their mean loss
-// (the reference's totalLoss), valid = number of contributing sequences.
-int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t* valid_count) {
+// The plan of a batch: which sequences are trained, the distinct lengths in order of first appearance (the
+// reference's buckets, TransformerTrainer.cs:229-245) and the packed passes.
+struct Plan {
+    std::vector<int> bucketLens;
+    std::vector<Pass> passes;
+};
+
+int plan_batch(b200_lm* lm, const Batch& b, int n_seq, Plan& plan) {
     b200_ctx* ctx = lm->ctx;
     const b200_lm_config& c = lm->cfg;
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    B200_CUDA(ctx, cudaSetDevice(ctx->device));
-    *loss_sum = 0.f;
-    *valid_count = 0;
-    lm->cb_used = 0;
-    lm->t_used = 0;
-    // ---- validity filter and bucketing in order of first appearance of each length (TransformerTrainer.cs:229-245)
     std::vector<Seq> seqs;
-    std::vector<int> bucketLens;
     for (int s = 0; s < n_seq; s++) {
         int start = b.off[s], n = b.off[s + 1] - b.off[s];
         if (n < 2) continue;
         bool ok = true;
-        if (c.discrete) {
+        if (c.discrete) {  // TransformerTrainer.cs:1467-1478 TokensAreValid
             for (int t = 0; t < n && ok; t++) ok = (uint32_t)b.tokens[start + t] < (uint32_t)c.vocab_size;
         } else {
             for (int64_t i = 0; i < (int64_t)n * c.input_feature_dim && ok; i++) ok = std::isfinite(b.feats[(size_t)start * c.input_feature_dim + i]);
@@ -358,26 +374,42 @@ int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t*
         if (!ok) continue;
         if (n - 1 > lm->maxRows) return fail(ctx, B200_ERR_OUT_OF_RANGE, "sequence %d has %d rows, above max_rows_per_pass %d", s, n - 1, lm->maxRows);
         seqs.push_back(Seq{s, start, n - 1});
-        if (std::find(bucketLens.begin(), bucketLens.end(), n - 1) == bucketLens.end()) bucketLens.push_back(n - 1);
+        if (std::find(plan.bucketLens.begin(), plan.bucketLens.end(), n - 1) == plan.bucketLens.end()) plan.bucketLens.push_back(n - 1);
     }
     if (seqs.empty()) return B200_OK;
-    std::vector<Seq> ordered;
-    for (int len : bucketLens)
-        for (const Seq& q : seqs)
-            if (q.len == len) ordered.push_back(q);
-    // ---- packed passes
-    std::vector<Pass> passes;
     Pass cur;
-    for (const Seq& q : ordered) {
-        if (!cur.seqs.empty() && (cur.rows + q.len > lm->maxRows || (int)cur.seqs.size() >= lm->maxSeqs)) {
-            passes.push_back(cur);
-            cur = Pass();
+    for (int len : plan.bucketLens)
+        for (const Seq& q : seqs) {
+            if (q.len != len) continue;
+            if (!cur.seqs.empty() && (cur.rows + q.len > lm->maxRows || (int)cur.seqs.size() >= lm->maxSeqs)) {
+                plan.passes.push_back(cur);
+                cur = Pass();
+            }
+            cur.seqs.push_back(q);
+            cur.rows += q.len;
+            cur.maxLen = std::max(cur.maxLen, q.len);
         }
-        cur.seqs.push_back(q);
-        cur.rows += q.len;
-        cur.maxLen = std::max(cur.maxLen, q.len);
+    plan.passes.push_back(cur);
+    return B200_OK;
+}
+
+// Accumulates gradients of all planned sequences.  loss_sum = sum over sequences of their mean loss (the reference's
+// totalLoss), valid = number of contributing sequences.  `staged`, when given, holds the device-resident inputs of
+// every pass (a prepared batch); otherwise each pass is staged from the host arrays in `b`.
+int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<PassDev>* staged, float* loss_sum, int32_t* valid_count) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    *loss_sum = 0.f;
+    *valid_count = 0;
+    lm->cb_used = 0;
+    lm->t_used = 0;
+    const std::vector<int>& bucketLens = plan.bucketLens;
+    const std::vector<Pass>& passes = plan.passes;
+    if (passes.empty()) {
+        if (lm->cb) fire(lm, 0, lm->lay.total);
+        return B200_OK;
     }
-    passes.push_back(cur);
+    auto bucket_of = [&](int len) { return (size_t)(std::find(bucketLens.begin(), bucketLens.end(), len) - bucketLens.begin()); };
     // per-length running sums for the loss, in the reference's row order
     std::vector<float> bucketSum(bucketLens.size(), 0.f);
     std::vector<int> bucketCount(bucketLens.size(), 0);
@@ -392,7 +424,12 @@ int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t*
                         e2 = next_event(lm->t_events, lm->t_used), e3 = next_event(lm->t_events, lm->t_used);
             lm->t_has_bwd.resize(lm->t_used / 4, 0);
             lm->t_has_bwd[lm->t_used / 4 - 1] = 0;
-            B200_TRY(stage_pass(lm, b, p));
+            if (staged && attempt == 0) {
+                lm->cur = (*staged)[pi];
+            } else {
+                B200_TRY(stage_pass(lm, b, p, lm->own));
+                lm->cur = lm->own;
+            }
             cudaEventRecord(e0, ctx->stream);
             B200_TRY(forward_pass(lm, p));
             cudaEventRecord(e1, ctx->stream);
@@ -404,41 +441,36 @@ int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t*
             // TransformerTrainer.cs:271-272 / :286-287: a non-finite loss or gradient drops the sequences of that length
             // (here: of that length within this pass).
             std::vector<char> lenBad(bucketLens.size(), 0);
-            int r = 0;
             std::vector<float> passSum(bucketLens.size(), 0.f);
+            int r = 0;
             for (const Seq& q : p.seqs) {
-                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
+                size_t bi = bucket_of(q.len);
                 for (int t = 0; t < q.len; t++, r++) {
                     passSum[bi] += rowLoss[(size_t)r];
                     if (!rowOk[(size_t)r]) lenBad[bi] = 1;
                 }
             }
-            bool anyBad = false, anyGood = false;
-            for (size_t bi = 0; bi < bucketLens.size(); bi++) {
+            for (size_t bi = 0; bi < bucketLens.size(); bi++)
                 if (!std::isfinite(passSum[bi])) lenBad[bi] = 1;
-            }
+            bool anyBad = false;
             Pass good;
             for (const Seq& q : p.seqs) {
-                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
-                if (lenBad[bi]) anyBad = true;
-                else {
-                    anyGood = true;
-                    good.seqs.push_back(q);
-                    good.rows += q.len;
-                    good.maxLen = std::max(good.maxLen, q.len);
-                }
+                if (lenBad[bucket_of(q.len)]) { anyBad = true; continue; }
+                good.seqs.push_back(q);
+                good.rows += q.len;
+                good.maxLen = std::max(good.maxLen, q.len);
             }
             float ms;
             if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) lm->timings[0] += ms;
             if (cudaEventElapsedTime(&ms, e1, e2) == cudaSuccess) lm->timings[1] += ms;
-            if (!anyGood) break;
-            if (anyBad) {  // rerun the pass with the finite sequences only: its activations must not be mixed with theirs
+            if (good.seqs.empty()) break;
+            if (anyBad) {  // rerun the pass with the finite sequences only: their activations must not mix with the others'
                 p = good;
                 continue;
             }
             r = 0;
             for (const Seq& q : p.seqs) {
-                size_t bi = std::find(bucketLens.begin(), bucketLens.end(), q.len) - bucketLens.begin();
+                size_t bi = bucket_of(q.len);
                 for (int t = 0; t < q.len; t++, r++) bucketSum[bi] += rowLoss[(size_t)r];
                 bucketCount[bi]++;
             }
@@ -462,6 +494,17 @@ int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t*
     *loss_sum = total;
     *valid_count = valid;
     return B200_OK;
+}
+
+int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t* valid_count) {
+    b200_ctx* ctx = lm->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    *loss_sum = 0.f;
+    *valid_count = 0;
+    Plan plan;
+    B200_TRY(plan_batch(lm, b, n_seq, plan));
+    return run_plan(lm, b, plan, nullptr, loss_sum, valid_count);
 }
 
 int collect_backward_time(b200_lm* lm) {
@@ -597,13 +640,13 @@ int32_t b200_lm_create(b200_ctx* ctx, const b200_lm_config* cfg, float* params_d
     lm->xFinal = take(N * d); lm->logits = take(N * O); lm->proj = take(N * d);
     for (int i = 0; i < 4; i++) lm->gbuf[i] = take(N * d);
     lm->dqkv = take(N * 3 * d); lm->d1 = take(N * f); lm->rowDot = take(N * H);
-    lm->contIn = take(N * std::max<size_t>(F, 1)); lm->regTgt = take(N * O); lm->rowScale = take(N); lm->rowLoss = take(N);
+    lm->own.contIn = take(N * std::max<size_t>(F, 1)); lm->own.regTgt = take(N * O); lm->own.rowScale = take(N); lm->rowLoss = take(N);
     lm->stepOut = take(64);
     int32_t* qi = (int32_t*)q;
     auto takei = [&](size_t n) { int32_t* r = qi; qi += rnd(n); return r; };
-    lm->rowOk = takei(N); lm->ids = takei(N); lm->targets = takei(N); lm->pos = takei(N); lm->segId = takei(N); lm->segOff = takei(N + 1);
-    lm->perm = takei(N);
-    lm->segs = (AttnSeg*)takei(4 * (size_t)lm->maxSeqs);
+    lm->rowOk = takei(N); lm->own.ids = takei(N); lm->own.targets = takei(N); lm->own.pos = takei(N); lm->own.segId = takei(N); lm->own.segOff = takei(N + 1);
+    lm->own.perm = takei(N);
+    lm->own.segs = (AttnSeg*)takei(4 * (size_t)lm->maxSeqs);
     size_t hInts = 3 * N + 4 * (size_t)lm->maxSeqs + 3 * N + 8;
     size_t hFloats = N + N * F + N * O + 8;
     if (cudaMallocHost((void**)&lm->h_int, sizeof(int32_t) * hInts) != cudaSuccess || cudaMallocHost((void**)&lm->h_float, sizeof(float) * hFloats) != cudaSuccess)
@@ -716,6 +759,114 @@ int32_t b200_lm_train_step_continuous(b200_lm* lm, const float* features, const 
     int32_t vc = 0;
     B200_TRY(b200_lm_zero_grads(lm));
     B200_TRY(b200_lm_accumulate_continuous(lm, features, reg_targets, class_targets, seq_offsets, n_seq, &ls, &vc));
+    B200_TRY(b200_lm_apply_step(lm, vc, lr, use_clip, clip_threshold, do_step, &gn));
+    if (loss) *loss = vc > 0 ? ls / (float)vc : 0.f;
+    if (grad_norm) *grad_norm = gn;
+    if (valid_count) *valid_count = vc;
+    return B200_OK;
+}
+
+static int batch_finish(b200_lm* lm, b200_lm_batch* bt, b200_lm_batch** out) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    Batch hb;
+    hb.tokens = bt->tokens.data(); hb.feats = bt->feats.data(); hb.regT = bt->regT.data(); hb.clsT = bt->clsT.data(); hb.off = bt->off.data();
+    Plan* plan = new Plan();
+    bt->plan = plan;
+    int rc = plan_batch(lm, hb, bt->n_seq, *plan);
+    if (rc != B200_OK) return rc;
+    auto rnd = [](size_t n) { return (n + 63) & ~(size_t)63; };
+    const size_t F = (size_t)c.input_feature_dim, O = (size_t)c.output_dim;
+    size_t words = 64;
+    for (const Pass& p : plan->passes) {
+        size_t N = (size_t)p.rows, S = p.seqs.size();
+        words += rnd(N) * 6 + rnd(N + 1) + rnd(4 * S) + rnd(N * std::max<size_t>(F, 1)) + rnd(N * O);
+    }
+    if (!plan->passes.empty()) {
+        cudaError_t e = cudaMalloc((void**)&bt->block, words * 4);
+        if (e != cudaSuccess) return fail(ctx, B200_ERR_CUDA, "prepared batch allocation of %zu bytes failed: %s", words * 4, cudaGetErrorString(e));
+    }
+    int32_t* q = (int32_t*)bt->block;
+    auto take = [&](size_t n) { int32_t* r = q; q += rnd(n); return r; };
+    for (const Pass& p : plan->passes) {
+        size_t N = (size_t)p.rows, S = p.seqs.size();
+        PassDev d;
+        d.ids = take(N); d.targets = take(N); d.pos = take(N); d.segId = take(N); d.segOff = take(N + 1); d.perm = take(N);
+        d.segs = (AttnSeg*)take(4 * S);
+        d.rowScale = (float*)take(N); d.contIn = (float*)take(N * std::max<size_t>(F, 1)); d.regTgt = (float*)take(N * O);
+        rc = stage_pass(lm, hb, p, d);
+        if (rc != B200_OK) return rc;
+        B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the pinned staging area is reused by the next pass
+        bt->dev.push_back(d);
+    }
+    *out = bt;
+    return B200_OK;
+}
+
+int32_t b200_lm_batch_create_discrete(b200_lm* lm, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out) {
+    if (!lm || !out) return B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (!lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes continuous inputs");
+    if (!tokens || !seq_offsets || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    b200_lm_batch* bt = new b200_lm_batch();
+    bt->lm = lm; bt->n_seq = n_seq;
+    bt->off.assign(seq_offsets, seq_offsets + n_seq + 1);
+    bt->tokens.assign(tokens, tokens + seq_offsets[n_seq]);
+    int rc = batch_finish(lm, bt, out);
+    if (rc != B200_OK) b200_lm_batch_destroy(bt);
+    return rc;
+}
+
+int32_t b200_lm_batch_create_continuous(b200_lm* lm, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                        const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out) {
+    if (!lm || !out) return B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes token ids");
+    if (!features || !seq_offsets || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    if (lm->cfg.loss_kind == 1 ? !reg_targets : !class_targets) return lm_fail(lm, B200_ERR_INVALID_ARG, "targets missing for the configured loss");
+    b200_lm_batch* bt = new b200_lm_batch();
+    bt->lm = lm; bt->n_seq = n_seq;
+    bt->off.assign(seq_offsets, seq_offsets + n_seq + 1);
+    size_t rows = (size_t)seq_offsets[n_seq];
+    bt->feats.assign(features, features + rows * lm->cfg.input_feature_dim);
+    if (reg_targets && lm->cfg.loss_kind == 1) bt->regT.assign(reg_targets, reg_targets + rows * lm->cfg.output_dim);
+    if (class_targets && lm->cfg.loss_kind == 0) bt->clsT.assign(class_targets, class_targets + rows);
+    int rc = batch_finish(lm, bt, out);
+    if (rc != B200_OK) b200_lm_batch_destroy(bt);
+    return rc;
+}
+
+int32_t b200_lm_batch_destroy(b200_lm_batch* bt) {
+    if (!bt) return B200_OK;
+    if (bt->lm) {
+        cudaSetDevice(bt->lm->ctx->device);
+        cudaStreamSynchronize(bt->lm->ctx->stream);
+    }
+    if (bt->block) cudaFree(bt->block);
+    delete (Plan*)bt->plan;
+    delete bt;
+    return B200_OK;
+}
+
+int32_t b200_lm_accumulate_batch(b200_lm* lm, b200_lm_batch* bt, float* loss_sum, int32_t* valid_count) {
+    if (!lm || !bt || bt->lm != lm || !loss_sum || !valid_count) return B200_ERR_INVALID_ARG;
+    b200_ctx* ctx = lm->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    Batch hb;
+    hb.tokens = bt->tokens.data(); hb.feats = bt->feats.data(); hb.regT = bt->regT.data(); hb.clsT = bt->clsT.data(); hb.off = bt->off.data();
+    return run_plan(lm, hb, *(Plan*)bt->plan, &bt->dev, loss_sum, valid_count);
+}
+
+int32_t b200_lm_train_step_batch(b200_lm* lm, b200_lm_batch* bt, float lr, int32_t use_clip, float clip_threshold, int32_t do_step, float* loss,
+                                 float* grad_norm, int32_t* valid_count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    float ls = 0.f, gn = 0.f;
+    int32_t vc = 0;
+    B200_TRY(b200_lm_zero_grads(lm));
+    B200_TRY(b200_lm_accumulate_batch(lm, bt, &ls, &vc));
     B200_TRY(b200_lm_apply_step(lm, vc, lr, use_clip, clip_threshold, do_step, &gn));
     if (loss) *loss = vc > 0 ? ls / (float)vc : 0.f;
     if (grad_norm) *grad_norm = gn;

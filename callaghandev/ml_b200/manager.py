@@ -80,6 +80,15 @@ class CudaB200AccelerationManager:
     def kernel_launches(self) -> int:
         return int(self.lib.b200_kernel_launches(self.ctx))
 
+    def profile_gemm(self, enable: bool):
+        self._ck(self.lib.b200_profile_gemm(self.ctx, int(bool(enable))))
+
+    def gemm_profile(self, engine: int):
+        """(launches, algorithmic FLOPs, device milliseconds) of the GEMM launches of one engine since profiling was enabled."""
+        n, fl, ms = C.c_int64(0), C.c_double(0), C.c_double(0)
+        self._ck(self.lib.b200_gemm_profile(self.ctx, int(engine), C.byref(n), C.byref(fl), C.byref(ms)))
+        return n.value, fl.value, ms.value
+
     def has_tcgen05(self) -> bool:
         return bool(self.lib.b200_has_tcgen05(self.ctx))
 

@@ -107,6 +107,36 @@ class B200LanguageModelTrainer:
                                                             clip_threshold, int(bool(do_step)), C.byref(loss), C.byref(norm), C.byref(valid)))
         return loss.value, norm.value, valid.value
 
+    # ---- device-resident batches
+    def prepare_discrete(self, tokens, seq_offsets):
+        """Plan, pack and copy a batch to the device once; returns a handle for train_step_batch / accumulate_batch."""
+        t, o = _i(tokens), _i(seq_offsets)
+        h = C.c_void_p()
+        self.mgr._ck(self.lib.b200_lm_batch_create_discrete(self.h, _pi(t), _pi(o), len(o) - 1, C.byref(h)))
+        return h
+
+    def prepare_continuous(self, features, seq_offsets, reg_targets=None, class_targets=None):
+        x, o = _f(features), _i(seq_offsets)
+        r = None if reg_targets is None else _f(reg_targets)
+        k = None if class_targets is None else _i(class_targets)
+        h = C.c_void_p()
+        self.mgr._ck(self.lib.b200_lm_batch_create_continuous(self.h, _pf(x), _pf(r), None if k is None else _pi(k), _pi(o), len(o) - 1, C.byref(h)))
+        return h
+
+    def release_batch(self, batch):
+        self.lib.b200_lm_batch_destroy(batch)
+
+    def train_step_batch(self, batch, lr, use_clip=True, clip_threshold=1.0, do_step=True):
+        loss, norm, valid = C.c_float(0), C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_train_step_batch(self.h, batch, lr, int(bool(use_clip)), clip_threshold, int(bool(do_step)),
+                                                       C.byref(loss), C.byref(norm), C.byref(valid)))
+        return loss.value, norm.value, valid.value
+
+    def accumulate_batch(self, batch):
+        ls, vc = C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_accumulate_batch(self.h, batch, C.byref(ls), C.byref(vc)))
+        return ls.value, vc.value
+
     # ---- data-parallel decomposition
     def zero_grads(self):
         self.mgr._ck(self.lib.b200_lm_zero_grads(self.h))
@@ -242,22 +272,39 @@ class DataParallelLMTrainer:
             self.dist.broadcast(self.params, src=0, group=self.pg)
         torch.cuda.synchronize(self.device)
 
-    def train_step_discrete(self, tokens, seq_offsets, lr, use_clip=True, clip_threshold=1.0, do_step=True):
-        """tokens/seq_offsets describe the GLOBAL batch; this rank trains its shard."""
-        torch = self.torch
+    def shard(self, tokens, seq_offsets):
+        """This rank's contiguous slice of a GLOBAL batch, as (tokens, offsets) re-based to zero."""
         off = np.asarray(seq_offsets, np.int32)
         lo, hi = split_sequences(len(off) - 1, self.rank, self.world)
-        loc_off = (off[lo:hi + 1] - off[lo]).astype(np.int32)
-        loc_tok = np.asarray(tokens, np.int32)[off[lo]:off[hi]]
-        self._pending.clear()
-        self.lm.zero_grads()
-        ls, vc = self.lm.accumulate_discrete(loc_tok, loc_off) if hi > lo else (0.0, 0)
+        return np.ascontiguousarray(np.asarray(tokens, np.int32)[off[lo]:off[hi]]), (off[lo:hi + 1] - off[lo]).astype(np.int32)
+
+    def prepare_discrete(self, tokens, seq_offsets):
+        """Copy this rank's shard of the global batch to the device once; returns a handle for train_step_prepared."""
+        t, o = self.shard(tokens, seq_offsets)
+        return self.lm.prepare_discrete(t, o) if len(o) > 1 else None
+
+    def _finish(self, ls, vc, had_local, lr, use_clip, clip_threshold, do_step):
         if self.world > 1:
-            if hi == lo:  # nothing local: still contribute (zeros) to every bucket
+            if not had_local:  # nothing local: still contribute (zeros) to every bucket
                 self._on_ready(0, self.lm.param_count, 0)
-            for w in self._pending:
-                w.wait()
+            with self.torch.cuda.stream(self.compute):  # Work.wait() orders the *current* stream after the collective
+                for w in self._pending:
+                    w.wait()
             self.compute.wait_stream(self.comm)
             ls, vc = reduce_host_scalars(self.dist, ls, vc, self.device)
         norm = self.lm.apply_step(vc, lr, use_clip, clip_threshold, do_step)
         return (ls / vc if vc else 0.0), norm, vc
+
+    def train_step_prepared(self, batch, lr, use_clip=True, clip_threshold=1.0, do_step=True):
+        self._pending.clear()
+        self.lm.zero_grads()
+        ls, vc = self.lm.accumulate_batch(batch) if batch is not None else (0.0, 0)
+        return self._finish(ls, vc, batch is not None, lr, use_clip, clip_threshold, do_step)
+
+    def train_step_discrete(self, tokens, seq_offsets, lr, use_clip=True, clip_threshold=1.0, do_step=True):
+        """tokens/seq_offsets describe the GLOBAL batch in host memory; this rank trains its shard."""
+        t, o = self.shard(tokens, seq_offsets)
+        self._pending.clear()
+        self.lm.zero_grads()
+        ls, vc = self.lm.accumulate_discrete(t, o) if len(o) > 1 else (0.0, 0)
+        return self._finish(ls, vc, len(o) > 1, lr, use_clip, clip_threshold, do_step)

@@ -49,6 +49,7 @@ enum { B200_OPT_SGD = 0, B200_OPT_ADAM = 1 };
 typedef struct b200_ctx b200_ctx;
 typedef struct b200_lm b200_lm;
 typedef struct b200_mlp b200_mlp;
+typedef struct b200_lm_batch b200_lm_batch;
 
 /* ------------------------------------------------------------------------------------------------ context */
 /* Replaces the backend construction in AccelerationFactory.Create (AccelerationManagers/AccelerationFactory.cs:31-45)
@@ -63,6 +64,11 @@ B200_API int32_t b200_set_gemm_mode(b200_ctx* ctx, int32_t mode);
 B200_API int32_t b200_synchronize(b200_ctx* ctx);
 /* Number of kernels this context has launched so far (launch accounting for benchmarks). */
 B200_API int64_t b200_kernel_launches(b200_ctx* ctx);
+/* Per-launch GEMM timing for roofline reports: while enabled, a CUDA-event pair brackets every GEMM launch on the
+ * context's stream.  b200_gemm_profile sums, for one engine (0 = FP32 SIMT, 1 = TF32 tcgen05), the launches, their
+ * algorithmic FLOPs (2*M*N*K) and their device time since the last b200_profile_gemm call. */
+B200_API int32_t b200_profile_gemm(b200_ctx* ctx, int32_t enable);
+B200_API int32_t b200_gemm_profile(b200_ctx* ctx, int32_t engine, int64_t* launches, double* flops, double* ms);
 /* 1 if the device is compute capability 10.x (tcgen05 path usable), else 0. */
 B200_API int32_t b200_has_tcgen05(b200_ctx* ctx);
 
@@ -221,6 +227,17 @@ B200_API int32_t b200_lm_train_step_discrete(b200_lm*, const int32_t* tokens, co
 B200_API int32_t b200_lm_train_step_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
                                                const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip, float clip_threshold,
                                                int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
+
+/* Device-resident batches (no counterpart in the reference, whose trainers re-read managed arrays every step): the
+ * batch is validated, bucketed, packed into passes and copied to the device ONCE; training on it afterwards moves no
+ * input bytes from the host.  Semantics of b200_lm_train_step_batch = b200_lm_train_step_discrete/continuous. */
+B200_API int32_t b200_lm_batch_create_discrete(b200_lm*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out);
+B200_API int32_t b200_lm_batch_create_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                                 const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out);
+B200_API int32_t b200_lm_batch_destroy(b200_lm_batch*);
+B200_API int32_t b200_lm_accumulate_batch(b200_lm*, b200_lm_batch*, float* loss_sum, int32_t* valid_count);
+B200_API int32_t b200_lm_train_step_batch(b200_lm*, b200_lm_batch*, float lr, int32_t use_clip, float clip_threshold, int32_t do_step,
+                                          float* loss, float* grad_norm, int32_t* valid_count);
 
 /* Data-parallel decomposition of the same step (no counterpart in the reference, which is single-device):
  *   b200_lm_zero_grads -> b200_lm_accumulate_* (this rank's sequences; gradients summed, unscaled)

@@ -27,12 +27,14 @@ def lm_config(vocab=0, F=0, O=None, d=64, H=4, L=2, f=128, act="Relu", discrete=
     return c
 
 
-def init_params(oracle, cfg, seed=0, dtype=np.float32):
-    """Flat arena with seeded weights; padding between tensors stays zero."""
+def init_params(oracle, cfg, seed=0, dtype=np.float32, tensors=None, total=None):
+    """Flat arena with seeded weights; padding between tensors stays zero.  The arena layout comes from the oracle, or
+    from an explicit (tensors, total) pair (e.g. the device library's own b200_lm_tensor_info) when oracle is None."""
     rng = np.random.default_rng(seed)
-    total = oracle.lm_param_count(cfg)
+    if tensors is None:
+        total = oracle.lm_param_count(cfg)
+        tensors = oracle.lm_tensors(cfg)
     P = np.zeros(total, dtype)
-    tensors = oracle.lm_tensors(cfg)
     d, f = cfg.embedding_dim, cfg.ffn_dim
     n0 = 1 if cfg.discrete else 2
     for idx, (off, r, c) in enumerate(tensors):

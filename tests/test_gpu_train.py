@@ -309,3 +309,23 @@ def test_mlp_bce_with_one_hot_targets_is_nonfinite_like_the_reference(mgr, oracl
     we, be = [W[0].copy()], [B[0].copy()]
     assert not np.isfinite(oracle.mlp_learn_batch(widths, acts, we, be, X, Y, "binaryCrossEntropy", lr=0.1))
     t.close()
+
+
+def test_prepared_batch_equals_host_path(mgr, oracle):
+    """A batch copied to the device once (b200_lm_batch_*) trains bit-identically to the host-buffer entry point."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(21)
+    cfg = lm_config(vocab=120, d=64, H=4, L=2, f=128)
+    toks, off = token_batch(rng, 9, 120, 2, 40, zipf=1.1)
+    toks = np.concatenate([toks, [1]]).astype(np.int32); off = np.concatenate([off, [off[-1] + 1]]).astype(np.int32)  # one invalid sequence
+    P = init_params(oracle, cfg, 2)
+    a, b = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 96), B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 96)
+    a.upload_params(P); b.upload_params(P)
+    h = b.prepare_discrete(toks, off)
+    for _ in range(3):
+        ra, rb = a.train_step_discrete(toks, off, 1e-2), b.train_step_batch(h, 1e-2)
+        assert ra == rb and ra[2] == 9
+    assert np.array_equal(a.download_params(), b.download_params())
+    b.release_batch(h)
+    a.close(); b.close()
