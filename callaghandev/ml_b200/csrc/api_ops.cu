@@ -73,7 +73,7 @@ struct Scope {
     }
     int sync() {
         B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        return B200_OK;
+        return check_device_status(ctx);
     }
 };
 
@@ -118,6 +118,7 @@ int32_t b200_destroy(b200_ctx* ctx) {
     if (ctx->pool) cudaFree(ctx->pool);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
     for (auto& kv : ctx->rope)
         if (kv.second.dev) cudaFree(kv.second.dev);
     for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
@@ -142,7 +143,7 @@ int32_t b200_set_gemm_mode(b200_ctx* ctx, int32_t mode) {
 int32_t b200_synchronize(b200_ctx* ctx) {
     if (!ctx) return B200_ERR_INVALID_ARG;
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return B200_OK;
+    return check_device_status(ctx);
 }
 int64_t b200_kernel_launches(b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
 int32_t b200_has_tcgen05(b200_ctx* ctx) { return ctx && ctx->cc_major == 10 ? 1 : 0; }

@@ -35,6 +35,8 @@ struct b200_ctx {
     float* pinned = nullptr;  // 4 KiB pinned staging for scalars
     std::map<std::pair<int, uint32_t>, RopeTable> rope;  // key: (headDim, bits of baseTheta)
     void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
+    int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
+    int* status_dev = nullptr;
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;
@@ -68,6 +70,8 @@ int fail(b200_ctx* ctx, int code, const char* fmt, ...);
                               __FILE__, __LINE__);                                                              \
     } while (0)
 
+// B200_ERR_TIMEOUT if a kernel of this context reported that a bounded device-side wait expired (call after a sync).
+int check_device_status(b200_ctx* ctx);
 // Ensure ctx->ws holds at least n floats (contents are not preserved).
 int ensure_ws(b200_ctx* ctx, size_t n);
 // cos/sin table for rotary embeddings covering positions [0, rows).

@@ -20,6 +20,14 @@ int fail(b200_ctx* ctx, int code, const char* fmt, ...) {
     return code;
 }
 
+int check_device_status(b200_ctx* ctx) {
+    if (ctx->status_host && *ctx->status_host != 0) {
+        int code = *ctx->status_host;
+        return fail(ctx, B200_ERR_TIMEOUT, "a bounded device-side wait expired in the tcgen05 GEMM (role %d: 1 producer, 2 MMA issuer, 3 epilogue)", code);
+    }
+    return B200_OK;
+}
+
 int ensure_ws(b200_ctx* ctx, size_t n) {
     if (ctx->ws_floats >= n) return B200_OK;
     // The old block may still be in use by enqueued kernels: drain the stream before replacing it.

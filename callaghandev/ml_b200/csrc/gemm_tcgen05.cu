@@ -1,6 +1,320 @@
-// Placeholder until the tensor-core engine lands: nothing is eligible, so every GEMM takes the FP32 SIMT kernel.
+// TF32 tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in tensor memory (TMEM), operands staged in
+// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), an mbarrier pipeline, and the fused
+// epilogue read back from TMEM with tcgen05.ld.
+//
+//   CTA tile 128 x BN (BN = 128), K step 32 floats (= one 128-byte swizzle row) per pipeline stage, 4 UMMAs
+//   (M128 x N128 x K8) per stage.  192 threads: warp 0 = TMA producer (one elected lane), warp 1 = TMEM allocator and
+//   MMA issuer (one elected lane), warps 2-5 = epilogue (each owns the 32 TMEM lanes its warp id modulo 4 selects).
+//   Three stages of 32 KiB keep a CTA under 100 KiB so two CTAs share an SM: one runs its epilogue while the other
+//   keeps the tensor pipe busy.
+//
+// All four operand layouts are supported without a transpose pass: a K-contiguous operand is one TMA box per stage
+// and a K-major UMMA descriptor; an M/N-contiguous operand (dX = dY W uses W as [K,N]; dW = dY^T X uses both
+// operands as [K,M] / [K,N]) is loaded as 32-column boxes and described as MN-major.  TMA converts FP32 to TF32 with
+// round-to-nearest on the way in (tensor-map data type TFLOAT32); accumulation is FP32.
+//
+// Every wait on an mbarrier is bounded by a clock budget: on expiry the kernel raises a status word in host-mapped
+// memory, drains the copies it still has in flight (bounded again), frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.h"
+#include "gemm_epilogue.cuh"
+
 namespace b200 {
-bool gemm_tcgen05_eligible(b200_ctx*, const Gemm&) { return false; }
-int gemm_tcgen05(b200_ctx* ctx, const Gemm&) { return fail(ctx, B200_ERR_UNSUPPORTED, "tcgen05 GEMM not built"); }
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *status, a word in host-mapped memory) when the clock budget runs out or
+// another role of this kernel has already failed.  The status word is only touched on the slow path.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* status, int code) {
+    for (int i = 0; i < 64; i++)
+        if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; it++) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 255u) == 0) {
+            if (*status != 0) return false;
+            if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
+                *status = code;
+                __threadfence_system();
+                return false;
+            }
+        }
+        __nanosleep(32);
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+// UMMA shared-memory descriptor: start address, leading/stride byte offsets (16-byte units), descriptor version 1,
+// layout type 2 = 128-byte swizzle with 16-byte atoms (K-major operands) or 1 = 128-byte swizzle with 32-byte atoms
+// (the only layout tcgen05.mma.kind::tf32 accepts for an M/N-contiguous operand: 32-byte chunks XOR (row mod 4)).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TcParams {
+    int M, N, K;
+    int a_mn_major, b_mn_major;  // 0: K contiguous (one box per stage); 1: M/N contiguous (32-column boxes)
+    int* status;                 // host-mapped status word
+};
+
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                                               TcParams p, Epilogue ep) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles must start on 1024-byte boundaries
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    const uint32_t tiles_s = smem_u32(tiles);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum_bar = smem_u32(bars + 2 * STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int kblocks = (p.K + BK - 1) / BK;
+    volatile int* status = p.status;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM: BN fp32 accumulator columns x 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t par = ((kb / STAGES) & 1) ^ 1;  // first pass over the ring finds every slot empty
+                ok = mbar_wait(empty0 + 8 * s, par, status, 1);
+                if (!ok) break;
+                const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
+                mbar_expect_tx(bar, STAGE_BYTES);
+                const int k0 = kb * BK;
+                if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
+                else
+                    for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * (BK * 128), &mapA, bar, m0 + 32 * c, k0);
+                if (!p.b_mn_major) tma_load_2d(b_dst, &mapB, bar, k0, n0);
+                else
+                    for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
+                issued = kb + 1;
+            }
+            if (!ok) {
+                // failure path: wait (bounded) until the copies already issued have landed before the CTA may exit
+                for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; kb++) {
+                    const long long t0 = clock64();
+                    while (!mbar_test(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ MMA issuer
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major: rows 128 B apart, 8-row groups 1024 B apart (SBO), 32 B per K=8 step inside the swizzle row.
+            // MN-major: 32-column chunks BK*128 B apart (LBO), K rows 128 B apart in groups of 4 rows, groups 512 B
+            //           apart (SBO); one K=8 step is two groups = 1024 B.
+            const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+            const uint32_t a_sbo = p.a_mn_major ? 512 : 1024, b_sbo = p.b_mn_major ? 512 : 1024;
+            const uint32_t a_lay = p.a_mn_major ? 1 : 2, b_lay = p.b_mn_major ? 1 : 2;
+            const uint32_t a_step = p.a_mn_major ? 1024 : 32, b_step = p.b_mn_major ? 1024 : 32;
+            bool ok = true;
+            for (int kb = 0; kb < kblocks; kb++) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, status, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_s = tiles_s + s * STAGE_BYTES, b_s = a_s + A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; kk++) {
+                    const uint64_t ad = umma_desc(a_s + kk * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t bd = umma_desc(b_s + kk * b_step, b_lbo, b_sbo, b_lay);
+                    umma_tf32(tmem_base, ad, bd, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+            }
+            umma_commit(accum_bar);  // accumulator complete (also issued on the failure path so nobody waits forever)
+        }
+    } else {
+        // ---------------------------------------------------------------------- epilogue (warps 2..5)
+        bool ok = mbar_wait(accum_bar, 0, status, 3);
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: the whole warp takes the same path
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int q = warp & 3;  // this warp may touch TMEM lanes [32q, 32q+32)
+            // All MMAs have completed, so the operand stages are free: each warp transposes its 32x32 chunks through
+            // a padded slice of them, which turns "one row per thread" into "one row per warp instruction" and makes
+            // every global access of the epilogue a full 128-byte line.
+            float* stage = reinterpret_cast<float*>(tiles) + q * (32 * 33);
+            float alpha = ep.alpha;
+            if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= p.N) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+#pragma unroll
+                for (int j = 0; j < 32; j++) stage[lane * 33 + j] = __uint_as_float(r[j]);
+                __syncwarp();
+                const int n = n0 + c0 + lane;
+                if (n < p.N) {
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr++) {
+                        const int m = m0 + 32 * q + rr;
+                        if (m < p.M) epilogue_store(ep, m, n, stage[rr * 33 + lane], alpha);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int resolve_encode(b200_ctx* ctx) {
+    if (ctx->tmap_encode) return B200_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    B200_CUDA(ctx, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) return fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    ctx->tmap_encode = fn;
+    return B200_OK;
+}
+
+// 2-D FP32 tensor [outer, inner] with row pitch ld floats; box = [boxOuter, 32] floats (128 B inner), 128-byte swizzle
+// (16-byte atoms for a K-contiguous operand, 32-byte atoms for an M/N-contiguous one, matching the UMMA layout types),
+// out-of-range elements read as zero, FP32 -> TF32 conversion (round to nearest) on load.
+int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxOuter, bool mn_major) {
+    cuuint64_t gdim[2] = {inner, outer};
+    cuuint64_t gstride[1] = {ld * sizeof(float)};
+    cuuint32_t box[2] = {32, boxOuter};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((EncodeTiledFn)ctx->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void*)base, gdim, gstride, box, estr,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %llu outer %llu ld %llu)", (int)r,
+                                       (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)ld);
+    return B200_OK;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
+    if (ctx->cc_major != 10) return false;
+    if (g.M < 128 || g.N < 128 || g.K < 128) return false;
+    if ((g.lda & 3) || (g.ldb & 3)) return false;
+    if (((uintptr_t)g.A | (uintptr_t)g.B) & 15) return false;
+    return true;
+}
+
+int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
+    if (!gemm_tcgen05_eligible(ctx, g)) return fail(ctx, B200_ERR_UNSUPPORTED, "shape does not qualify for the tcgen05 GEMM");
+    B200_TRY(resolve_encode(ctx));
+    if (!ctx->status_host) {
+        B200_CUDA(ctx, cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped));
+        *ctx->status_host = 0;
+        B200_CUDA(ctx, cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    }
+    CUtensorMap mapA, mapB;
+    // A: stored [M,K] (K contiguous) or [K,M] (M contiguous).  B: stored [N,K] (transB, K contiguous) or [K,N].
+    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BM, false));
+    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
+    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BN, false));
+    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
+    TcParams p;
+    p.M = g.M; p.N = g.N; p.K = g.K;
+    p.a_mn_major = g.transA ? 1 : 0;
+    p.b_mn_major = g.transB ? 0 : 1;
+    p.status = ctx->status_dev;
+    Epilogue e;
+    e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
+    e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
+    e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda;
+    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
+    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 }  // namespace b200

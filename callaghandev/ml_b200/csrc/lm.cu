@@ -542,6 +542,7 @@ int apply_step(b200_lm* lm, int valid, float lr, int use_clip, float thr, int do
     cudaEventRecord(e1, ctx->stream);
     B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, lm->stepOut, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    B200_TRY(check_device_status(ctx));
     if (grad_norm) *grad_norm = ctx->pinned[0];
     float ms;
     if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) lm->timings[3] += ms;

@@ -136,6 +136,7 @@ int32_t b200_mlp_learn_batch(b200_mlp* m, const float* X, const float* Y, int32_
     }
     B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, m->scaleNorm, 2 * sizeof(float), cudaMemcpyDeviceToHost, st));
     B200_CUDA(ctx, cudaStreamSynchronize(st));
+    B200_TRY(check_device_status(ctx));
     if (delta_norm) *delta_norm = ctx->pinned[1];
     return B200_OK;
 }

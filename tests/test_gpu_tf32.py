@@ -1,0 +1,154 @@
+"""The TF32 tensor-core path (tcgen05/TMEM GEMM fed by TMA) on the GPU.
+
+Two bars:
+  * against the CPU oracle (FP32), the reference's metric |exp-act| <= 2e-3*max(1,|exp|): the stated tolerance of the
+    TF32 path, on inputs of realistic magnitude (the parity-test generators, seeded network weights);
+  * against a numpy emulation of the same arithmetic (operands rounded to TF32 with round-to-nearest-even, products
+    summed exactly): <= 2e-5, which shows the kernel itself (layouts, pipeline, K tails, ragged tiles, epilogues) is
+    exact up to FP32 accumulation order, independent of how coarse TF32 is.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from lmutil import init_params, lm_config, token_batch
+from oracle import pt_matrix, pt_vector
+
+pytestmark = pytest.mark.gpu
+TF32_TOL = 2e-3
+
+
+def tf32(x):
+    """Round FP32 to TF32 (10 explicit mantissa bits), nearest-even, as the TMA load does."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    b = (b + 0xFFF + ((b >> 13) & 1)) & 0xFFFFE000
+    return b.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+@pytest.fixture(scope="module")
+def mgr():
+    from callaghandev.ml_b200 import GEMM_TF32_TCGEN05, CudaB200AccelerationManager
+
+    m = CudaB200AccelerationManager(0, GEMM_TF32_TCGEN05)
+    if not m.has_tcgen05():
+        pytest.skip("device is not compute capability 10.x")
+    yield m
+    m.Dispose()
+
+
+# TMA needs 16-byte row pitches: every leading dimension is a multiple of 4 floats; row counts are free.
+SHAPES = [(128, 128, 128), (256, 512, 384), (200, 136, 328), (132, 140, 260), (1000, 300, 260), (132, 4100, 128), (2048, 160, 1024)]
+
+
+@pytest.mark.parametrize("M,K,N", SHAPES)
+def test_gemm_all_layouts(mgr, oracle, M, K, N):
+    """NN, NT (forward), and the two backward contractions dX = dY W (B is [K,N]) and dW = dY^T X (both operands [K,*])."""
+    A, B = pt_matrix(M, K, 3), pt_matrix(K, N, 4)
+    emu = tf32(A) @ tf32(B)
+    out = mgr.MatrixMultiply(A, B)
+    assert_close(emu, out, 2e-5, "NN vs TF32 emulation"); assert_close(oracle.MatrixMultiply(A, B), out, TF32_TOL, "NN vs oracle")
+    Bt = np.ascontiguousarray(B.T)
+    out = mgr.MatrixMultiplyTranspose(A, Bt)
+    assert_close(emu, out, 2e-5, "NT vs TF32 emulation")
+    # BackpropLinearProjection with rows=K: Wg[N,M] += dY^T x (both MN-major), dIn[K,M] += dY W (B MN-major); start non-zero
+    x, dy, W = pt_matrix(K, M, 5), pt_matrix(K, N, 6), pt_matrix(N, M, 7)
+    wg0, bg0, di0 = pt_matrix(N, M, 8), pt_vector(N, 9), pt_matrix(K, M, 10)
+    wg, bg, di = wg0.copy(), bg0.copy(), di0.copy()
+    mgr.BackpropLinearProjection(x, dy, W, wg, bg, di)
+    assert_close(wg0 + tf32(dy).T @ tf32(x), wg, 2e-5, "dW vs TF32 emulation")
+    assert_close(di0 + tf32(dy) @ tf32(W), di, 2e-5, "dX vs TF32 emulation")
+    we, be, de = wg0.copy(), bg0.copy(), di0.copy()
+    oracle.BackpropLinearProjection(x, dy, W, we, be, de)
+    assert_close(we, wg, TF32_TOL, "dW vs oracle"); assert_close(de, di, TF32_TOL, "dX vs oracle"); assert_close(be, bg, 1e-5, "bias grad (FP32 column sum)")
+
+
+def test_fused_epilogues(mgr, oracle):
+    rng = np.random.default_rng(1)
+    W, X, b = pt_matrix(384, 256, 1), pt_matrix(300, 256, 2), pt_vector(384, 3)
+    assert_close(tf32(X) @ tf32(W).T + b, mgr.BatchDotProductAddBias(W, X, b), 2e-5, "bias epilogue")
+    assert_close(oracle.BatchDotProductAddBias(W, X, b, 17, 200), mgr.BatchDotProductAddBias(W, X, b, 17, 200), TF32_TOL, "row window")
+    widths = [256, 512, 256]
+    for act in ("Relu", "Swish", "Tanh"):
+        acts = ["None", act, "None"]
+        # A pre-activation that lands within TF32 rounding of a ReLU kink flips its derivative between the two
+        # precisions; that is a property of reduced precision, not of the kernel.  Keep |z| away from zero here
+        # (small weights, biases of magnitude >= 0.5) so that the comparison measures the arithmetic.
+        Ws = [rng.normal(0, 0.01, (512, 256)).astype(np.float32), rng.normal(0, 0.04, (256, 512)).astype(np.float32)]
+        Bs = [(np.where(rng.random(512) < 0.5, -1.0, 1.0) * (0.5 + np.abs(rng.normal(0, 0.3, 512)))).astype(np.float32),
+              rng.normal(0, 0.1, 256).astype(np.float32)]
+        x, dO = rng.normal(0, 1, (333, 256)).astype(np.float32), rng.normal(0, 0.1, (333, 256)).astype(np.float32)
+        assert_close(oracle.FFNForwardBatch(x, widths, acts, Ws, Bs), mgr.FFNForwardBatch(x, widths, acts, Ws, Bs), TF32_TOL, "FFN forward " + act)
+        ge = [np.zeros((512, 256), np.float32), np.zeros((256, 512), np.float32)], [np.zeros(512, np.float32), np.zeros(256, np.float32)]
+        ga = [t.copy() for t in ge[0]], [t.copy() for t in ge[1]]
+        assert_close(oracle.FFNInputGradientBatch(x, dO, widths, acts, Ws, Bs, *ge), mgr.FFNInputGradientBatch(x, dO, widths, acts, Ws, Bs, *ga), TF32_TOL, "FFN dInput " + act)
+        for ee, aa in zip(ge[0] + ge[1], ga[0] + ga[1]):
+            assert_close(ee, aa, TF32_TOL, "FFN gradients " + act)
+    x = pt_matrix(192, 128, 142)
+    wq, wk, wv = (pt_matrix(128, 128, 143 + i) for i in range(3))
+    bq, bk, bv = (pt_vector(128, 146 + i) for i in range(3))
+    for ee, aa in zip(oracle.ProjectQKV(x, wq, bq, wk, bk, wv, bv), mgr.ProjectQKV(x, wq, bq, wk, bk, wv, bv)):
+        assert_close(ee, aa, TF32_TOL, "ProjectQKV (AccelerationManagerParityTests.cs:1202-1218 shapes)")
+
+
+def test_unqualified_shapes_fall_back_to_simt_in_auto_mode(mgr, oracle):
+    from callaghandev.ml_b200 import GEMM_AUTO, CudaB200AccelerationManager
+
+    m = CudaB200AccelerationManager(0, GEMM_AUTO)
+    a, b = pt_matrix(64, 200, 1), pt_matrix(200, 300, 2)  # M < 128: FP32 SIMT engine, 1e-5 parity
+    assert_close(oracle.MatrixMultiply(a, b), m.MatrixMultiply(a, b), 1e-5, "below the tensor-core threshold")
+    a, b = pt_matrix(131, 129, 1), pt_matrix(129, 130, 2)  # row pitches not multiples of 16 bytes: TMA cannot address them
+    assert_close(oracle.MatrixMultiply(a, b), m.MatrixMultiply(a, b), 1e-5, "unaligned leading dimensions")
+    m.Dispose()
+    with pytest.raises(NotImplementedError):  # forcing the tensor-core engine on such a shape is an error, not a silent fallback
+        mgr.MatrixMultiply(a, b)
+
+
+def test_lm_step_on_tensor_cores(oracle):
+    """One train step of a d=128 model (every GEMM dimension >= 128 except none) in AUTO mode: gradients and post-step
+    weights within the TF32 tolerance of the CPU oracle."""
+    from callaghandev.ml_b200 import GEMM_AUTO, B200LanguageModelTrainer, CudaB200AccelerationManager, LMConfig
+
+    rng = np.random.default_rng(77)
+    cfg = lm_config(vocab=300, d=128, H=4, L=2, f=512, act="Relu")
+    c = LMConfig()
+    for name, _ in LMConfig._fields_:
+        setattr(c, name, getattr(cfg, name))
+    toks, off = token_batch(rng, 6, 300, 40, 90, zipf=1.1)
+    P = init_params(oracle, cfg, 5)
+    m = CudaB200AccelerationManager(0, GEMM_AUTO)
+    t = B200LanguageModelTrainer(m, c, 1024)
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=1e-2, use_clip=True, clip_thr=1.0)
+    m.profile_gemm(True)
+    al, an, av = t.train_step_discrete(toks, off, 1e-2, True, 1.0, True)
+    n_tc = m.gemm_profile(1)[0]
+    m.profile_gemm(False)
+    assert n_tc > 0, "the tensor-core engine must actually have run"
+    assert av == ev
+    assert_close(el, al, TF32_TOL, "loss"); assert_close(en, an, TF32_TOL, "grad norm")
+    assert_close(ge, t.download_grads(), TF32_TOL, "gradients"); assert_close(pe, t.download_params(), TF32_TOL, "post-step weights")
+    t.close(); m.Dispose()
+
+
+def test_mlp_config2_on_tensor_cores(oracle):
+    from callaghandev.ml_b200 import GEMM_AUTO, B200MlpBatchTrainer, CudaB200AccelerationManager
+
+    rng = np.random.default_rng(42)
+    widths, acts = [784, 512, 256, 10], ["Relu", "Relu", "Relu", "Sigmoid"]
+    W = [rng.normal(0, np.sqrt(2.0 / widths[l - 1]), (widths[l], widths[l - 1])).astype(np.float32) for l in range(1, 4)]
+    B = [rng.normal(0, 0.05, widths[l]).astype(np.float32) for l in range(1, 4)]
+    X = rng.uniform(0, 1, (256, 784)).astype(np.float32)
+    Y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 256)]
+    we, be = [w.copy() for w in W], [b.copy() for b in B]
+    en = oracle.mlp_learn_batch(widths, acts, we, be, X, Y, "mse", lr=0.1, lam=1e-4, clip_thr=1.0)
+    m = CudaB200AccelerationManager(0, GEMM_AUTO)
+    t = B200MlpBatchTrainer(m, widths, acts, "mse", 1.0, 1e-4, 1.0, 256)
+    for l in range(1, 4):
+        t.upload_layer(l, W[l - 1], B[l - 1])
+    an = t.learn_batch(X, Y, 0.1)
+    assert_close(en, an, TF32_TOL, "delta norm")
+    for l in range(1, 4):
+        w, b = t.download_layer(l)
+        assert_close(we[l - 1], w, TF32_TOL, f"W{l}"); assert_close(be[l - 1], b, TF32_TOL, f"b{l}")
+    t.close(); m.Dispose()
