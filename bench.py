@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample (0 disables)")
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (sequences)")
+    ap.add_argument("--gemm-csv", default="", help="write the per-shape GEMM timing table of the timed region to this file")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.batch:
@@ -238,6 +239,8 @@ def main():
     dev_ms, wall_ms, out = timed(step_resident, args.steps)
     launches = tr.mgr.kernel_launches() - l0
     prof = {e: tr.mgr.gemm_profile(e) for e in (0, 1)}
+    if args.gemm_csv and rank == 0:
+        Path(args.gemm_csv).write_text(tr.mgr.gemm_profile_csv())
     tr.mgr.profile_gemm(False)
     clocks = sampler.stop() if rank == 0 else None
     step_host()  # one untimed call so that the host path is warm as well

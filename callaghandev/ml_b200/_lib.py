@@ -46,6 +46,7 @@ PROTOTYPES = {
     "b200_kernel_launches": (_i64, [_vp]),
     "b200_has_tcgen05": (_i32, [_vp]),
     "b200_profile_gemm": (_i32, [_vp, _i32]),
+    "b200_gemm_profile_csv": (_i64, [_vp, C.c_char_p, _i64]),
     "b200_gemm_profile": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200_MatrixMultiply": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _f]),
     "b200_MatrixMultiplyTranspose": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _f]),

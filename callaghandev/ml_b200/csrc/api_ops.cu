@@ -155,7 +155,35 @@ int32_t b200_profile_gemm(b200_ctx* ctx, int32_t enable) {
     ctx->prof_used = 0;
     ctx->prof_flops.clear();
     ctx->prof_engine.clear();
+    ctx->prof_shape.clear();
     return B200_OK;
+}
+
+int64_t b200_gemm_profile_csv(b200_ctx* ctx, char* buf, int64_t cap) {
+    if (!ctx || !buf || cap <= 0) return -1;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return -1;
+    struct Agg { int64_t n = 0; double ms = 0, flops = 0; };
+    std::map<std::vector<int>, Agg> agg;
+    for (size_t i = 0; i < ctx->prof_flops.size(); i++) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]) != cudaSuccess) continue;
+        const auto& sh = ctx->prof_shape[i];
+        Agg& a = agg[{ctx->prof_engine[i], sh.M, sh.N, sh.K, sh.tA, sh.tB}];
+        a.n++; a.ms += t; a.flops += ctx->prof_flops[i];
+    }
+    std::string out = "engine,M,N,K,transA,transB,launches,total_ms,tflops\n";
+    char line[256];
+    for (auto& kv : agg) {
+        snprintf(line, sizeof(line), "%d,%d,%d,%d,%d,%d,%lld,%.4f,%.2f\n", kv.first[0], kv.first[1], kv.first[2], kv.first[3], kv.first[4], kv.first[5],
+                 (long long)kv.second.n, kv.second.ms, kv.second.ms > 0 ? kv.second.flops / (kv.second.ms * 1e-3) / 1e12 : 0.0);
+        out += line;
+    }
+    int64_t n = (int64_t)out.size() < cap - 1 ? (int64_t)out.size() : cap - 1;
+    memcpy(buf, out.data(), (size_t)n);
+    buf[n] = 0;
+    return n;
 }
 
 int32_t b200_gemm_profile(b200_ctx* ctx, int32_t engine, int64_t* launches, double* flops, double* ms) {

@@ -43,6 +43,8 @@ struct b200_ctx {
     size_t prof_used = 0;
     std::vector<double> prof_flops;   // per launch
     std::vector<int> prof_engine;     // per launch: 0 SIMT, 1 tcgen05
+    struct ProfShape { int M, N, K, tA, tB; };
+    std::vector<ProfShape> prof_shape;  // per launch
 };
 
 namespace b200 {
@@ -171,7 +173,11 @@ struct Attn {
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr; int lddq = 0, lddk = 0, lddv = 0;
     float* rowDot = nullptr;  // [totalQ, numHeads] scratch: sum_k dO*O
 };
-int attn_forward(b200_ctx*, const Attn& a);
+int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-core kernels when attn_tc_eligible
+// TF32 mma.sync engine (head dimension <= 64, context not in FP32 mode)
+bool attn_tc_eligible(b200_ctx*, const Attn& a);
+int attn_forward_tc(b200_ctx*, const Attn& a);
+int attn_backward_tc(b200_ctx*, const Attn& a);
 int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from the forward
 
 // ------------------------------------------------------------------------------------------------ parameter step

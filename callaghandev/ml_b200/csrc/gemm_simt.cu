@@ -135,6 +135,7 @@ int gemm(b200_ctx* ctx, const Gemm& g) {
     ctx->prof_used += 2;
     ctx->prof_flops.push_back(2.0 * g.M * g.N * g.K);
     ctx->prof_engine.push_back(engine);
+    ctx->prof_shape.push_back(b200_ctx::ProfShape{g.M, g.N, g.K, g.transA, g.transB});
     return B200_OK;
 }
 

@@ -115,6 +115,19 @@ struct TcParams {
     int* status;                 // host-mapped status word
 };
 
+// Epilogue kinds.  GENERIC handles every field of Epilogue element by element.  The other three are the shapes the
+// transformer step uses, written as 128-bit row operations (requirements checked on the host: N and every leading
+// dimension a multiple of 4, 16-byte aligned bases):
+//   LINEAR: v = alpha*acc (+bias) (+addmat); C = v or C += v
+//   ACT   : z = acc + bias -> zout; C = act(z)                       (FFN hidden layer forward)
+//   MULZ  : C = acc * act'(mulz)                                     (FFN hidden delta)
+enum { EPI_GENERIC = 0, EPI_LINEAR = 1, EPI_ACT = 2, EPI_MULZ = 3 };
+constexpr int EPI_STRIDE = 132;  // floats per staged row: 16-byte aligned and conflict-free for 128-bit accesses
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+
+template <int EPI>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                                TcParams p, Epilogue ep) {
     extern __shared__ uint8_t smem_raw[];
@@ -212,29 +225,81 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int q = warp & 3;  // this warp may touch TMEM lanes [32q, 32q+32)
-            // All MMAs have completed, so the operand stages are free: each warp transposes its 32x32 chunks through
-            // a padded slice of them, which turns "one row per thread" into "one row per warp instruction" and makes
-            // every global access of the epilogue a full 128-byte line.
-            float* stage = reinterpret_cast<float*>(tiles) + q * (32 * 33);
             float alpha = ep.alpha;
             if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+            // All MMAs have completed, so the operand stages are free: each warp transposes its accumulator rows
+            // through a padded slice of them, which turns "one row per thread" (the TMEM load shape) into "one row
+            // per warp instruction" and makes every global access of the epilogue a full line.
+            if (EPI == EPI_GENERIC) {
+                float* stage = reinterpret_cast<float*>(tiles) + q * (32 * 33);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= p.N) break;
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
 #pragma unroll
-                for (int j = 0; j < 32; j++) stage[lane * 33 + j] = __uint_as_float(r[j]);
-                __syncwarp();
-                const int n = n0 + c0 + lane;
-                if (n < p.N) {
+                    for (int j = 0; j < 32; j++) stage[lane * 33 + j] = __uint_as_float(r[j]);
+                    __syncwarp();
+                    const int n = n0 + c0 + lane;
+                    if (n < p.N) {
 #pragma unroll 4
-                    for (int rr = 0; rr < 32; rr++) {
-                        const int m = m0 + 32 * q + rr;
-                        if (m < p.M) epilogue_store(ep, m, n, stage[rr * 33 + lane], alpha);
+                        for (int rr = 0; rr < 32; rr++) {
+                            const int m = m0 + 32 * q + rr;
+                            if (m < p.M) epilogue_store(ep, m, n, stage[rr * 33 + lane], alpha);
+                        }
                     }
+                    __syncwarp();
+                }
+            } else {
+                float* stage = reinterpret_cast<float*>(tiles) + q * (32 * EPI_STRIDE);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        st4(stage + lane * EPI_STRIDE + c0 + j,
+                            make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
                 }
                 __syncwarp();
+                const int n = n0 + 4 * lane;  // this lane's four columns of every row
+                if (n < p.N) {                // N is a multiple of 4 on this path
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
+                    const int rows = min(32, p.M - (m0 + 32 * q));
+#pragma unroll 4
+                    for (int rr = 0; rr < rows; rr++) {
+                        const size_t m = (size_t)(m0 + 32 * q + rr);
+                        float4 v = ld4(stage + rr * EPI_STRIDE + 4 * lane);
+                        if (EPI == EPI_LINEAR) {
+                            v.x = alpha * v.x + b4.x; v.y = alpha * v.y + b4.y; v.z = alpha * v.z + b4.z; v.w = alpha * v.w + b4.w;
+                            if (ep.addmat) {
+                                const float4 a4 = ld4(ep.addmat + m * ep.ldadd + n);
+                                v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w;
+                            }
+                            float* c = ep.C + m * ep.ldc + n;
+                            if (ep.accumulate) {
+                                const float4 c4 = ld4(c);
+                                v.x += c4.x; v.y += c4.y; v.z += c4.z; v.w += c4.w;
+                            }
+                            st4(c, v);
+                        } else if (EPI == EPI_ACT) {
+                            v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                            st4(ep.zout + m * ep.ldz + n, v);
+                            float d;
+                            ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
+                            ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
+                            st4(ep.C + m * ep.ldc + n, v);
+                        } else {  // EPI_MULZ
+                            const float4 z4 = ld4(ep.mulz + m * ep.ldmulz + n);
+                            float a, dx, dy, dz, dw;
+                            ffn_act_der(z4.x, ep.mulz_act, a, dx); ffn_act_der(z4.y, ep.mulz_act, a, dy);
+                            ffn_act_der(z4.z, ep.mulz_act, a, dz); ffn_act_der(z4.w, ep.mulz_act, a, dw);
+                            v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
+                            st4(ep.C + m * ep.ldc + n, v);
+                        }
+                    }
+                }
             }
         }
     }
@@ -293,7 +358,10 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
         B200_CUDA(ctx, cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped));
         *ctx->status_host = 0;
         B200_CUDA(ctx, cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_MULZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     }
     CUtensorMap mapA, mapB;
     // A: stored [M,K] (K contiguous) or [K,M] (M contiguous).  B: stored [N,K] (transB, K contiguous) or [K,N].
@@ -312,7 +380,26 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda;
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
-    gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+    // pick the epilogue kind
+    auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    const bool plain_act = g.act == B200_ACT_NONE && !g.dout && !g.zout;
+    const bool no_sgd = g.sgd_lr == 0.f && !g.mulmat;
+    const bool vec_c = (g.N % 4 == 0) && (g.ldc % 4 == 0) && a16(g.C) && (!g.bias || a16(g.bias));
+    int kind = EPI_GENERIC;
+    if (vec_c && no_sgd) {
+        if (plain_act && !g.mulz && (!g.addmat || (g.ldadd % 4 == 0 && a16(g.addmat)))) kind = EPI_LINEAR;
+        else if (g.zout && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
+                 g.ldz % 4 == 0 && a16(g.zout))
+            kind = EPI_ACT;
+        else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
+            kind = EPI_MULZ;
+    }
+    switch (kind) {
+        case EPI_LINEAR: gemm_tcgen05_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_ACT: gemm_tcgen05_kernel<EPI_ACT><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_MULZ: gemm_tcgen05_kernel<EPI_MULZ><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        default: gemm_tcgen05_kernel<EPI_GENERIC><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+    }
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -89,6 +89,11 @@ class CudaB200AccelerationManager:
         self._ck(self.lib.b200_gemm_profile(self.ctx, int(engine), C.byref(n), C.byref(fl), C.byref(ms)))
         return n.value, fl.value, ms.value
 
+    def gemm_profile_csv(self) -> str:
+        buf = C.create_string_buffer(1 << 20)
+        n = self.lib.b200_gemm_profile_csv(self.ctx, buf, len(buf))
+        return buf.raw[:max(n, 0)].decode()
+
     def has_tcgen05(self) -> bool:
         return bool(self.lib.b200_has_tcgen05(self.ctx))
 

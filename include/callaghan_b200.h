@@ -69,6 +69,8 @@ B200_API int64_t b200_kernel_launches(b200_ctx* ctx);
  * algorithmic FLOPs (2*M*N*K) and their device time since the last b200_profile_gemm call. */
 B200_API int32_t b200_profile_gemm(b200_ctx* ctx, int32_t enable);
 B200_API int32_t b200_gemm_profile(b200_ctx* ctx, int32_t engine, int64_t* launches, double* flops, double* ms);
+/* The same data grouped by (engine, M, N, K, transA, transB) as CSV text; returns the number of bytes written. */
+B200_API int64_t b200_gemm_profile_csv(b200_ctx* ctx, char* buf, int64_t capacity);
 /* 1 if the device is compute capability 10.x (tcgen05 path usable), else 0. */
 B200_API int32_t b200_has_tcgen05(b200_ctx* ctx);
 
