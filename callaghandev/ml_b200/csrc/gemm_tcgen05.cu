@@ -28,6 +28,7 @@ constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
 constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
+constexpr int GROUP_M = 16;
 constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -113,6 +114,8 @@ struct TcParams {
     int M, N, K;
     int a_mn_major, b_mn_major;  // 0: K contiguous (one box per stage); 1: M/N contiguous (32-column boxes)
     int* status;                 // host-mapped status word
+    int kb_per_split;            // K blocks handled by one blockIdx.y (split-K); all of them when gridDim.y == 1
+    long long split_stride;      // elements between the partial outputs of consecutive splits
 };
 
 // Epilogue kinds.  GENERIC handles every field of Epilogue element by element.  The other three are the shapes the
@@ -138,8 +141,20 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     const uint32_t tiles_s = smem_u32(tiles);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum_bar = smem_u32(bars + 2 * STAGES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int kblocks = (p.K + BK - 1) / BK;
+    // Tile order: bands of GROUP_M row-tiles are walked column by column, so the CTAs resident at one time share a few
+    // A bands and B panels through L2 instead of streaming the whole B operand once per row-tile.
+    int m0, n0;
+    {
+        const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+        const int per_group = GROUP_M * tiles_n;
+        const int group = blockIdx.x / per_group, first_m = group * GROUP_M;
+        const int gm = min(tiles_m - first_m, GROUP_M);
+        const int r = blockIdx.x - group * per_group;
+        m0 = (first_m + r % gm) * BM;
+        n0 = (r / gm) * BN;
+    }
+    const int kb_begin = blockIdx.y * p.kb_per_split;
+    const int kblocks = min((p.K + BK - 1) / BK - kb_begin, p.kb_per_split);  // K blocks of this split
     volatile int* status = p.status;
 
     if (threadIdx.x == 0) {
@@ -172,7 +187,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
                 if (!ok) break;
                 const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
                 mbar_expect_tx(bar, STAGE_BYTES);
-                const int k0 = kb * BK;
+                const int k0 = (kb_begin + kb) * BK;
                 if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
                 else
                     for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * (BK * 128), &mapA, bar, m0 + 32 * c, k0);
@@ -267,36 +282,46 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
                     float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
                     const int rows = min(32, p.M - (m0 + 32 * q));
-#pragma unroll 4
-                    for (int rr = 0; rr < rows; rr++) {
-                        const size_t m = (size_t)(m0 + 32 * q + rr);
-                        float4 v = ld4(stage + rr * EPI_STRIDE + 4 * lane);
-                        if (EPI == EPI_LINEAR) {
-                            v.x = alpha * v.x + b4.x; v.y = alpha * v.y + b4.y; v.z = alpha * v.z + b4.z; v.w = alpha * v.w + b4.w;
-                            if (ep.addmat) {
-                                const float4 a4 = ld4(ep.addmat + m * ep.ldadd + n);
-                                v.x += a4.x; v.y += a4.y; v.z += a4.z; v.w += a4.w;
+                    // 8 rows per batch: all global loads of the batch are issued before any of them is consumed
+#pragma unroll 1
+                    for (int r0 = 0; r0 < rows; r0 += 8) {
+                        float4 ext[8], ext2[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const size_t m = (size_t)(m0 + 32 * q + r0 + i);
+                            ext[i] = ext2[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (r0 + i < rows) {
+                                if (EPI == EPI_LINEAR) {
+                                    if (ep.accumulate) ext[i] = ld4(ep.C + m * ep.ldc + n);
+                                    if (ep.addmat) ext2[i] = ld4(ep.addmat + m * ep.ldadd + n);
+                                } else if (EPI == EPI_MULZ) {
+                                    ext[i] = ld4(ep.mulz + m * ep.ldmulz + n);
+                                }
                             }
-                            float* c = ep.C + m * ep.ldc + n;
-                            if (ep.accumulate) {
-                                const float4 c4 = ld4(c);
-                                v.x += c4.x; v.y += c4.y; v.z += c4.z; v.w += c4.w;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            if (r0 + i >= rows) break;
+                            const size_t m = (size_t)(m0 + 32 * q + r0 + i);
+                            float4 v = ld4(stage + (r0 + i) * EPI_STRIDE + 4 * lane);
+                            if (EPI == EPI_LINEAR) {
+                                v.x = alpha * v.x + b4.x + ext[i].x + ext2[i].x; v.y = alpha * v.y + b4.y + ext[i].y + ext2[i].y;
+                                v.z = alpha * v.z + b4.z + ext[i].z + ext2[i].z; v.w = alpha * v.w + b4.w + ext[i].w + ext2[i].w;
+                                st4(ep.C + (size_t)blockIdx.y * p.split_stride + m * ep.ldc + n, v);
+                            } else if (EPI == EPI_ACT) {
+                                v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                                st4(ep.zout + m * ep.ldz + n, v);
+                                float d;
+                                ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
+                                ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
+                                st4(ep.C + m * ep.ldc + n, v);
+                            } else {  // EPI_MULZ
+                                float a, dx, dy, dz, dw;
+                                ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
+                                ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                                v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
+                                st4(ep.C + m * ep.ldc + n, v);
                             }
-                            st4(c, v);
-                        } else if (EPI == EPI_ACT) {
-                            v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
-                            st4(ep.zout + m * ep.ldz + n, v);
-                            float d;
-                            ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
-                            ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
-                            st4(ep.C + m * ep.ldc + n, v);
-                        } else {  // EPI_MULZ
-                            const float4 z4 = ld4(ep.mulz + m * ep.ldmulz + n);
-                            float a, dx, dy, dz, dw;
-                            ffn_act_der(z4.x, ep.mulz_act, a, dx); ffn_act_der(z4.y, ep.mulz_act, a, dy);
-                            ffn_act_der(z4.z, ep.mulz_act, a, dz); ffn_act_der(z4.w, ep.mulz_act, a, dw);
-                            v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
-                            st4(ep.C + m * ep.ldc + n, v);
                         }
                     }
                 }
@@ -308,6 +333,32 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+// C[m,n] (+)= alpha * sum_s partial[s][m,n], splits added in index order (N a multiple of 4).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, float* __restrict__ C, int ldc, float alpha,
+                                     const float* __restrict__ alpha_dev, int accumulate) {
+    const int64_t n4 = (int64_t)M * N / 4, plane = (int64_t)M * N;
+    if (alpha_dev) alpha *= alpha_dev[0];
+    const bool vecC = (ldc % 4 == 0) && (((uintptr_t)C & 15) == 0);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 s = ld4(partial + 4 * i);
+        for (int k = 1; k < splits; k++) {
+            const float4 v = ld4(partial + k * plane + 4 * i);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const int64_t e = 4 * i;
+        const int m = (int)(e / N), n = (int)(e - (int64_t)m * N);
+        float* c = C + (size_t)m * ldc + n;
+        if (vecC) {
+            float4 o = accumulate ? ld4(c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            o.x += alpha * s.x; o.y += alpha * s.y; o.z += alpha * s.z; o.w += alpha * s.w;
+            st4(c, o);
+        } else {
+            c[0] = (accumulate ? c[0] : 0.f) + alpha * s.x; c[1] = (accumulate ? c[1] : 0.f) + alpha * s.y;
+            c[2] = (accumulate ? c[2] : 0.f) + alpha * s.z; c[3] = (accumulate ? c[3] : 0.f) + alpha * s.w;
+        }
     }
 }
 
@@ -374,12 +425,40 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     p.a_mn_major = g.transA ? 1 : 0;
     p.b_mn_major = g.transB ? 0 : 1;
     p.status = ctx->status_dev;
+    const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
+    const int kblocks_total = (g.K + BK - 1) / BK;
+    p.kb_per_split = kblocks_total;
+    p.split_stride = 0;
+    // Split-K for the weight-gradient shape (few output tiles, very long K): partial products go to a workspace and a
+    // second kernel adds them to C in split order, so the result does not depend on scheduling.
+    int splits = 1;
+    const bool plain = g.act == B200_ACT_NONE && !g.dout && !g.zout && !g.mulz && !g.mulmat && !g.addmat && !g.bias && g.sgd_lr == 0.f;
+    if (plain && tiles < 2 * ctx->sm_count && kblocks_total >= 256 && (g.N % 4 == 0)) {
+        splits = (2 * ctx->sm_count + tiles - 1) / tiles;
+        if (splits > 8) splits = 8;
+        while (splits > 1 && (kblocks_total + splits - 1) / splits < 64) splits--;
+        p.kb_per_split = (kblocks_total + splits - 1) / splits;
+        splits = (kblocks_total + p.kb_per_split - 1) / p.kb_per_split;  // every split owns at least one K block
+    }
     Epilogue e;
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda;
-    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM);
+    dim3 grid((unsigned)tiles, (unsigned)splits);
+    if (splits > 1) {
+        B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));
+        p.split_stride = (long long)g.M * g.N;
+        e.C = ctx->ws; e.ldc = g.N; e.accumulate = 0; e.alpha = 1.f; e.alpha_dev = nullptr;
+        gemm_tcgen05_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+        B200_LAUNCH_CHECK(ctx);
+        const int64_t count = (int64_t)g.M * g.N;
+        int blocks = (int)((count / 4 + 255) / 256);
+        if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+        splitk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->ws, splits, g.M, g.N, g.C, g.ldc, g.alpha, g.alpha_dev, g.accumulate);
+        B200_LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     // pick the epilogue kind
     auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     const bool plain_act = g.act == B200_ACT_NONE && !g.dout && !g.zout;
