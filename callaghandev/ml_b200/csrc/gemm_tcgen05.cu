@@ -1,5 +1,5 @@
 // TF32 tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in tensor memory (TMEM), operands staged in
-// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast), an mbarrier pipeline, and the fused
+// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, every CTA loads its own tiles), an mbarrier pipeline, and the fused
 // epilogue read back from TMEM with tcgen05.ld.
 //
 //   CTA tile 128 x BN (BN = 128), K step 32 floats (= one 128-byte swizzle row) per pipeline stage, 4 UMMAs
