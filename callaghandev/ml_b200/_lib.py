@@ -58,6 +58,7 @@ PROTOTYPES = {
     "b200_ZeroVector": (_i32, [_vp, _f, _i64]),
     "b200_ResidualLayerNormForward": (_i32, [_vp, _f, _f, _f, _f, _i32, _i32, _fl, _f, _f, _f, _f, _f]),
     "b200_LayerNormBackward": (_i32, [_vp, _f, _f, _f, _f, _f, _f, _i32, _i32, _fl, _f, _f, _f]),
+    "b200_LayerNormBackward_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _fl, _vp, _vp, _vp]),
     "b200_ScaledDotProductAttention": (_i32, [_vp, _f, _f, _f, _i32, _i32, _i32, _i32, _b, _i32, _f]),
     "b200_MultiHeadAttentionForward": (_i32, [_vp, _f, _f, _f, _i32, _i32, _i32, _i32, _fl, _b, _f]),
     "b200_MultiHeadAttentionBackward": (_i32, [_vp, _f, _f, _f, _f, _i32, _i32, _i32, _i32, _fl, _b, _i32, _f, _f, _f]),

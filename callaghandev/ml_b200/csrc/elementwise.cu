@@ -611,6 +611,75 @@ int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const f
     return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ LayerNorm backward without any allocation
+// Scratch for b200_LayerNormBackward_noalloc: the per-block dGamma/dBeta partial rows of the two-stage column
+// reduction.  It is part of the library image, so every GPU that loads the library holds these 2.3 MiB until the
+// process exits; in exchange the entry point below never asks the driver (or any allocator) for memory.
+constexpr int NOALLOC_LN_MAX_FEATURES = 1024;  // widest row the entry point accepts
+constexpr int NOALLOC_LN_MAX_PARTS = 296;      // partial rows (blocks) the scratch has room for
+static __device__ __align__(256) float g_noalloc_ln_scratch[NOALLOC_LN_MAX_PARTS * 2 * NOALLOC_LN_MAX_FEATURES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ln_ptr[NOALLOC_MAX_DEVICES];  // device address of the scratch, per device ordinal (0 = not set up yet)
+static std::mutex g_noalloc_mu;
+
+}  // namespace b200
+
+extern "C" int32_t b200_LayerNormBackward_noalloc(void* cuda_stream, const float* dOut, const float* input, const float* gamma, const float* mean,
+                                                  const float* variance, int32_t rows, int32_t features, float eps, float* dInput, float* dGamma,
+                                                  float* dBeta) {
+    using namespace b200;
+    auto reject = [](int code, const char* why) {
+        fprintf(stderr, "b200_LayerNormBackward_noalloc: %s\n", why);
+        return code;
+    };
+    if (!dOut || !input || !gamma || !mean || !variance || !dInput || !dGamma || !dBeta) return reject(B200_ERR_INVALID_ARG, "null device pointer");
+    if (rows <= 0 || features <= 0) return reject(B200_ERR_INVALID_ARG, "rows and features must be positive");
+    if (features > NOALLOC_LN_MAX_FEATURES)
+        return reject(B200_ERR_OUT_OF_RANGE, "features exceeds the built-in scratch (maximum 1024 columns); use b200_LayerNormBackward");
+    if (features % 4 != 0) return reject(B200_ERR_UNSUPPORTED, "features must be a multiple of 4");
+    if (!aligned16(dOut) || !aligned16(input) || !aligned16(gamma) || !aligned16(dInput))
+        return reject(B200_ERR_UNSUPPORTED, "dOut, input, gamma and dInput must be 16-byte aligned");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return reject(B200_ERR_CUDA, "no current CUDA device");
+    float* scratch = nullptr;
+    {
+        // Set-up, once per device, with that device current: in host code the array's name is only a stand-in for
+        // the device object, so its device address has to be asked for before a kernel can be given it.
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (!g_noalloc_ln_ptr[dev]) {
+            float* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_ln_scratch);
+            if (e != cudaSuccess || !p) {
+                fprintf(stderr, "b200_LayerNormBackward_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+                return B200_ERR_CUDA;
+            }
+            g_noalloc_ln_ptr[dev] = p;
+        }
+        scratch = g_noalloc_ln_ptr[dev];
+    }
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const int warps = 4;
+    int grid = (rows + warps - 1) / warps;
+    if (grid > NOALLOC_LN_MAX_PARTS) grid = NOALLOC_LN_MAX_PARTS;
+    const size_t smem = (size_t)warps * 2 * features * sizeof(float);
+    // Every partial row the second kernel reads (grid of them) is written in full by the first one, so nothing in the
+    // scratch has to start at zero and nothing left by an earlier call can leak into this one.
+    ln_bwd_vec_kernel<false><<<grid, warps * 32, smem, st>>>(dOut, nullptr, input, gamma, mean, variance, rows, features, eps, dInput, scratch);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) {
+        ln_bwd_final_kernel<<<(2 * features + 255) / 256, 256, 0, st>>>(scratch, grid, features, dGamma, dBeta, 0);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        fprintf(stderr, "b200_LayerNormBackward_noalloc: kernel launch failed: %s\n", cudaGetErrorString(e));
+        return B200_ERR_CUDA;
+    }
+    return B200_OK;
+}
+
+namespace b200 {
+
 // ------------------------------------------------------------------------------------------------ losses
 // One block per row; the row lives in registers (up to 32 values per thread), so logits are read once and the
 // gradient written once even when it overwrites the logits.

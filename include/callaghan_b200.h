@@ -104,6 +104,22 @@ B200_API int32_t b200_LayerNormBackward(b200_ctx*, const float* dOut, const floa
                                         const float* mean, const float* variance, int32_t rows, int32_t features, float eps,
                                         float* dInput, float* dGamma, float* dBeta);
 
+/* No counterpart in the reference.  LayerNormBackward for callers that must not cause a device allocation while they
+ * run: a host framework that has handed all device memory to its own pool, or a training loop that cannot afford the
+ * device-wide synchronisation and possible out-of-memory failure of a driver allocation in the middle of a step.
+ * Every pointer is a DEVICE pointer supplied by the caller (inputs and the three outputs, which are assigned as in
+ * b200_LayerNormBackward); the call enqueues two kernels on cuda_stream (NULL = default stream) and returns without
+ * synchronising.  It takes no context and calls neither cudaMalloc/cudaFree nor any allocating routine: the scratch of
+ * the column reduction is a fixed array inside the library (2.3 MiB per GPU, held until the process exits).
+ * Limits: features <= 1024 and a multiple of 4 (otherwise B200_ERR_OUT_OF_RANGE / B200_ERR_UNSUPPORTED with a message on
+ * stderr); dOut, input, gamma, dInput 16-byte aligned.  The first call on each device looks up the scratch's device
+ * address; make that first call before starting any stream capture.  All calls share the one scratch array, so two
+ * calls that can overlap on the GPU (different streams without an ordering between them) race: keep calls on one
+ * device ordered.  Nothing in the scratch needs clearing between calls. */
+B200_API int32_t b200_LayerNormBackward_noalloc(void* cuda_stream, const float* dOut, const float* input, const float* gamma, const float* mean,
+                                                const float* variance, int32_t rows, int32_t features, float eps, float* dInput,
+                                                float* dGamma, float* dBeta);
+
 /* ScaledDotProductAttention (IAccelerationManager.cs:167; AccelerationCPU.cs:1797-1956).  mask: NULL or
  * [queryLen,keyLen] bytes, non-zero = visible.  causal with queryLen != keyLen is B200_ERR_INVALID_ARG. */
 B200_API int32_t b200_ScaledDotProductAttention(b200_ctx*, const float* q, const float* k, const float* v, int32_t queryLen, int32_t keyLen,
