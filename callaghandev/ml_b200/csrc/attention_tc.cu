@@ -42,6 +42,19 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x; -inf gives +0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Four 8x4-word blocks of a row-major tile in one instruction: lane l supplies the address of row (l%8) of block (l/8);
+// every lane receives word (l%4) of row (l/4) of each block, which is exactly the B fragment (k = l%4, n = l/4) of a
+// tile stored [n][k].
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const uint32_t* p) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 // Stage rows [rowStart, rowStart+64) x columns [colOff, colOff+hd) of a [rows, ld] matrix as TF32 words, zero-padded to
 // 64 x HD, with row stride STRIDE.
 template <int HD, int STRIDE>
@@ -84,15 +97,19 @@ __device__ __forceinline__ void load_a_frags(const uint32_t* __restrict__ tile, 
     }
 }
 
-// c[nt] (16 rows x 64 staged rows of Bt) += A(16 x HD) * Bt(64 x HD)^T
+// c[nt] (16 rows x 64 staged rows of Bt) += A(16 x HD) * Bt(64 x HD)^T.  B fragments come four at a time (two K steps).
 template <int HD, int STRIDE>
 __device__ __forceinline__ void mma_a_bt(const uint32_t (&a)[HD / 8][4], const uint32_t* __restrict__ Bt, int g, int t, float (&c)[8][4]) {
+    const int lane = g * 4 + t;
+    const uint32_t* base = Bt + (lane & 7) * STRIDE + 4 * (lane >> 3);
 #pragma unroll
     for (int nt = 0; nt < 8; nt++) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 8; ks++) {
-            uint32_t b0 = Bt[(nt * 8 + g) * STRIDE + ks * 8 + t], b1 = Bt[(nt * 8 + g) * STRIDE + ks * 8 + t + 4];
-            mma_tf32(c[nt], a[ks][0], a[ks][1], a[ks][2], a[ks][3], b0, b1);
+        for (int ks = 0; ks < HD / 8; ks += 2) {
+            uint32_t b[4];
+            ldsm_x4(b, base + nt * 8 * STRIDE + ks * 8);
+            mma_tf32(c[nt], a[ks][0], a[ks][1], a[ks][2], a[ks][3], b[0], b[1]);
+            mma_tf32(c[nt], a[ks + 1][0], a[ks + 1][1], a[ks + 1][2], a[ks + 1][3], b[2], b[3]);
         }
     }
 }
@@ -144,6 +161,8 @@ __global__ void __launch_bounds__(TC_THREADS) attn_fwd_tc_kernel(TcAttnArgs a, i
         for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
         mma_a_bt<HD, ST>(qa, Ks, g, t, s);
         uint32_t p[8][4];
+        // a tile that no mask, sequence end or causal diagonal touches needs no per-element visibility test (warp-uniform)
+        const bool full = !a.mask && k0 + 64 <= sg.kLen && q0 + warp * 16 + 16 <= sg.qLen && (!a.causal || k0 + 63 <= q0 + warp * 16);
 #pragma unroll
         for (int h = 0; h < 2; h++) {  // the two rows (g, g+8) this thread holds
             const int qi = q0 + warp * 16 + g + 8 * h;
@@ -153,21 +172,22 @@ __global__ void __launch_bounds__(TC_THREADS) attn_fwd_tc_kernel(TcAttnArgs a, i
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     const int kj = k0 + nt * 8 + 2 * t + e;
-                    float v = tc_visible(a, sg, qi, kj) ? s[nt][2 * h + e] * sl2 : -INFINITY;  // scores in log2 units
+                    float v = (full || tc_visible(a, sg, qi, kj)) ? s[nt][2 * h + e] * sl2 : -INFINITY;  // scores in log2 units
                     s[nt][2 * h + e] = v;
                     mx = fmaxf(mx, v);
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_i[h], mx);
-            const float corr = (m_i[h] == -INFINITY) ? 0.f : exp2f(m_i[h] - m_new);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // keeps (-inf) - (-inf) out of the exponent
+            const float corr = fast_exp2(m_i[h] - m_safe);
             float rs = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 8; nt++)
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     const float v = s[nt][2 * h + e];
-                    const float pv = (v == -INFINITY) ? 0.f : exp2f(v - m_new);
+                    const float pv = fast_exp2(v - m_safe);
                     rs += pv;
                     p[nt][2 * h + e] = to_tf32(pv);
                 }
@@ -213,6 +233,7 @@ __device__ __forceinline__ void recompute_tc(const TcAttnArgs& a, const AttnSeg&
     mma_a_bt<HD, STK>(qa, Ks, g, t, s);
     mma_a_bt<HD, STK>(da, Vs, g, t, dp);
     const float sl2 = a.scale * LOG2E;
+    const bool full = !a.mask && k0 + 64 <= sg.kLen && qbase + 16 <= sg.qLen && (!a.causal || k0 + 63 <= qbase);
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int qi = qbase + g + 8 * h;
@@ -223,7 +244,7 @@ __device__ __forceinline__ void recompute_tc(const TcAttnArgs& a, const AttnSeg&
             for (int e = 0; e < 2; e++) {
                 const int kj = k0 + nt * 8 + 2 * t + e;
                 float pv = 0.f;
-                if (ilrow[h] > 0.f && tc_visible(a, sg, qi, kj)) pv = exp2f(s[nt][2 * h + e] * sl2 - m2) * ilrow[h];
+                if (full || tc_visible(a, sg, qi, kj)) pv = fast_exp2(s[nt][2 * h + e] * sl2 - m2) * ilrow[h];  // ilrow = 0 for rows with no visible key
                 s[nt][2 * h + e] = pv;                                              // P
                 dp[nt][2 * h + e] = pv * (dp[nt][2 * h + e] - drow[h]) * a.scale;  // dS
             }
@@ -378,6 +399,203 @@ __global__ void __launch_bounds__(TC_THREADS) attn_bwd_dkv_tc_kernel(TcAttnArgs 
     }
 }
 
+// ------------------------------------------------------------------------------------------------ pipelined variants
+// When the producer of Q, K, V and dO has already rounded them to TF32 (the resident trainer does: the Q/K/V projection
+// and rotary kernels and the attention-output dX GEMM round on store), tiles need no conversion and are copied with
+// cp.async into a two-deep ring, so the copy of tile i+1 overlaps the MMAs on tile i.
+__device__ __forceinline__ void cp16(uint32_t* dst, const float* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int HD, int STRIDE>
+__device__ __forceinline__ void copy_tile_async(uint32_t* __restrict__ dst, const float* __restrict__ src, int ld, int rowStart, int nValid,
+                                                int colOff, int hd) {
+    for (int idx = threadIdx.x; idx < 64 * (HD / 4); idx += TC_THREADS) {
+        const int r = idx / (HD / 4), c = (idx - r * (HD / 4)) * 4;
+        const bool ok = r < nValid && c < hd;
+        cp16(dst + r * STRIDE + c, ok ? src + (size_t)(rowStart + r) * ld + colOff + c : src, ok);
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS) attn_fwd_tc_pipe_kernel(TcAttnArgs a) {
+    constexpr int ST = HD + 4, TILE = 64 * ST;
+    extern __shared__ __align__(16) uint32_t smu[];
+    uint32_t* Qs = smu;
+    uint32_t* KV = Qs + TILE;  // ring: [buf][K | V]
+    const AttnSeg sg = a.segs[blockIdx.z];
+    const int q0 = blockIdx.x * 64;
+    if (q0 >= sg.qLen) return;
+    const int head = blockIdx.y, colOff = head * a.headDim, hd = a.headDim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kEnd = a.causal ? min(sg.kLen, q0 + 64) : sg.kLen;
+    const int nTiles = (kEnd + 63) / 64;
+    copy_tile_async<HD, ST>(Qs, a.Q, a.ldq, sg.qStart + q0, min(64, sg.qLen - q0), colOff, hd);
+    if (nTiles > 0) {
+        copy_tile_async<HD, ST>(KV, a.K, a.ldk, sg.kStart, min(64, sg.kLen), colOff, hd);
+        copy_tile_async<HD, ST>(KV + TILE, a.V, a.ldv, sg.kStart, min(64, sg.kLen), colOff, hd);
+    }
+    cp_commit();
+    float m_i[2] = {-INFINITY, -INFINITY}, l_i[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qa[HD / 8][4];
+    const float sl2 = a.scale * LOG2E;
+    for (int it = 0; it < nTiles; it++) {
+        const int k0 = it * 64;
+        uint32_t* Ks = KV + (it & 1) * 2 * TILE;
+        uint32_t* Vs = Ks + TILE;
+        if (it + 1 < nTiles) {  // prefetch the next tile into the other buffer (its last readers passed the barrier below)
+            uint32_t* Kn = KV + ((it + 1) & 1) * 2 * TILE;
+            copy_tile_async<HD, ST>(Kn, a.K, a.ldk, sg.kStart + k0 + 64, min(64, sg.kLen - k0 - 64), colOff, hd);
+            copy_tile_async<HD, ST>(Kn + TILE, a.V, a.ldv, sg.kStart + k0 + 64, min(64, sg.kLen - k0 - 64), colOff, hd);
+            cp_commit();
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) load_a_frags<HD, ST>(Qs, warp * 16, g, t, qa);
+        float s[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        mma_a_bt<HD, ST>(qa, Ks, g, t, s);
+        uint32_t p[8][4];
+        // a tile that no mask, sequence end or causal diagonal touches needs no per-element visibility test (warp-uniform)
+        const bool full = !a.mask && k0 + 64 <= sg.kLen && q0 + warp * 16 + 16 <= sg.qLen && (!a.causal || k0 + 63 <= q0 + warp * 16);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int qi = q0 + warp * 16 + g + 8 * h;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int kj = k0 + nt * 8 + 2 * t + e;
+                    float v = (full || tc_visible(a, sg, qi, kj)) ? s[nt][2 * h + e] * sl2 : -INFINITY;  // scores in log2 units
+                    s[nt][2 * h + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_i[h], mx);
+            const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;  // keeps (-inf) - (-inf) out of the exponent
+            const float corr = fast_exp2(m_i[h] - m_safe);
+            float rs = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float v = s[nt][2 * h + e];
+                    const float pv = fast_exp2(v - m_safe);
+                    rs += pv;
+                    p[nt][2 * h + e] = to_tf32(pv);
+                }
+            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            l_i[h] = l_i[h] * corr + rs;
+            m_i[h] = m_new;
+#pragma unroll
+            for (int i = 0; i < HD / 8; i++) { o[i][2 * h] *= corr; o[i][2 * h + 1] *= corr; }
+        }
+        mma_c_b<HD, ST>(p, Vs, g, t, o);
+        __syncthreads();  // everyone is done with this buffer before the next iteration's prefetch overwrites it
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int qi = q0 + warp * 16 + g + 8 * h;
+        if (qi >= sg.qLen) continue;
+        const float inv = l_i[h] > 0.f ? 1.0f / l_i[h] : 0.f;
+        const size_t row = (size_t)(sg.qStart + qi);
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            const int c = i * 8 + 2 * t;  // hd is a multiple of 4 on this path, so c+1 < hd whenever c < hd
+            if (c < hd) *reinterpret_cast<float2*>(a.Oout + row * a.ldo + colOff + c) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        }
+        if (t == 0 && a.rowMax) {
+            a.rowMax[row * a.numHeads + head] = m_i[h] == -INFINITY ? -INFINITY : m_i[h] / LOG2E;
+            a.rowSum[row * a.numHeads + head] = l_i[h];
+        }
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS) attn_bwd_dq_tc_pipe_kernel(TcAttnArgs a) {
+    constexpr int ST = HD + 4, TILE = 64 * ST;
+    extern __shared__ __align__(16) uint32_t smu[];
+    uint32_t* Qs = smu;
+    uint32_t* dOs = Qs + TILE;
+    uint32_t* KV = dOs + TILE;
+    const AttnSeg sg = a.segs[blockIdx.z];
+    const int q0 = blockIdx.x * 64;
+    if (q0 >= sg.qLen) return;
+    const int head = blockIdx.y, colOff = head * a.headDim, hd = a.headDim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kEnd = a.causal ? min(sg.kLen, q0 + 64) : sg.kLen;
+    const int nTiles = (kEnd + 63) / 64;
+    copy_tile_async<HD, ST>(Qs, a.Q, a.ldq, sg.qStart + q0, min(64, sg.qLen - q0), colOff, hd);
+    copy_tile_async<HD, ST>(dOs, a.dO, a.lddo, sg.qStart + q0, min(64, sg.qLen - q0), colOff, hd);
+    if (nTiles > 0) {
+        copy_tile_async<HD, ST>(KV, a.K, a.ldk, sg.kStart, min(64, sg.kLen), colOff, hd);
+        copy_tile_async<HD, ST>(KV + TILE, a.V, a.ldv, sg.kStart, min(64, sg.kLen), colOff, hd);
+    }
+    cp_commit();
+    float mrow[2], ilrow[2], drow[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) row_stats(a, sg, q0 + warp * 16 + g + 8 * h, head, mrow[h], ilrow[h], drow[h]);
+    float dq[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f;
+    uint32_t qa[HD / 8][4], da[HD / 8][4];
+    for (int it = 0; it < nTiles; it++) {
+        const int k0 = it * 64;
+        uint32_t* Ks = KV + (it & 1) * 2 * TILE;
+        uint32_t* Vs = Ks + TILE;
+        if (it + 1 < nTiles) {
+            uint32_t* Kn = KV + ((it + 1) & 1) * 2 * TILE;
+            copy_tile_async<HD, ST>(Kn, a.K, a.ldk, sg.kStart + k0 + 64, min(64, sg.kLen - k0 - 64), colOff, hd);
+            copy_tile_async<HD, ST>(Kn + TILE, a.V, a.ldv, sg.kStart + k0 + 64, min(64, sg.kLen - k0 - 64), colOff, hd);
+            cp_commit();
+            cp_wait<1>();
+        } else {
+            cp_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) {
+            load_a_frags<HD, ST>(Qs, warp * 16, g, t, qa);
+            load_a_frags<HD, ST>(dOs, warp * 16, g, t, da);
+        }
+        float s[8][4], ds[8][4];
+        recompute_tc<HD, ST>(a, sg, qa, da, Ks, Vs, mrow, ilrow, drow, q0 + warp * 16, k0, g, t, s, ds);
+        uint32_t dsu[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) dsu[nt][e] = to_tf32(ds[nt][e]);
+        mma_c_b<HD, ST>(dsu, Ks, g, t, dq);
+        __syncthreads();
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int qi = q0 + warp * 16 + g + 8 * h;
+        if (qi >= sg.qLen) continue;
+        const size_t row = (size_t)(sg.qStart + qi);
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            const int c = i * 8 + 2 * t;
+            if (c < hd) *reinterpret_cast<float2*>(a.dQ + row * a.lddq + colOff + c) = make_float2(dq[i][2 * h], dq[i][2 * h + 1]);
+        }
+    }
+}
+
 __global__ void attn_rowdot_tc_kernel(const float* __restrict__ dO, int lddo, const float* __restrict__ O, int ldo, int rows, int numHeads, int hd,
                                       float* __restrict__ rowDot) {
     int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -415,6 +633,17 @@ int launch_fwd_tc(b200_ctx* ctx, const Attn& t) {
         configured = true;
     }
     dim3 grid((t.maxQLen + 63) / 64, t.numHeads, t.nSeg);
+    if (t.pre_rounded && vec_ok(t, false) && (t.ldo % 2 == 0) && (((uintptr_t)t.O & 7) == 0)) {
+        constexpr size_t smem_pipe = (size_t)5 * 64 * (HD + 4) * 4;
+        static bool configured_pipe = false;
+        if (!configured_pipe) {
+            B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_tc_pipe_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pipe));
+            configured_pipe = true;
+        }
+        attn_fwd_tc_pipe_kernel<HD><<<grid, TC_THREADS, smem_pipe, ctx->stream>>>(make_tc_args(t));
+        B200_LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     attn_fwd_tc_kernel<HD><<<grid, TC_THREADS, smem, ctx->stream>>>(make_tc_args(t), vec_ok(t, false) ? 1 : 0);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -439,6 +668,17 @@ int launch_bwd_tc(b200_ctx* ctx, const Attn& t) {
     attn_bwd_dkv_tc_kernel<HD><<<gk, TC_THREADS, smem_dkv, ctx->stream>>>(a, vec);
     B200_LAUNCH_CHECK(ctx);
     dim3 gq((t.maxQLen + 63) / 64, t.numHeads, t.nSeg);
+    if (t.pre_rounded && vec && (t.lddq % 2 == 0) && (((uintptr_t)t.dQ & 7) == 0)) {
+        constexpr size_t smem_pipe = (size_t)6 * 64 * (HD + 4) * 4;
+        static bool configured_pipe = false;
+        if (!configured_pipe) {
+            B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dq_tc_pipe_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pipe));
+            configured_pipe = true;
+        }
+        attn_bwd_dq_tc_pipe_kernel<HD><<<gq, TC_THREADS, smem_pipe, ctx->stream>>>(a);
+        B200_LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     attn_bwd_dq_tc_kernel<HD><<<gq, TC_THREADS, smem_dq, ctx->stream>>>(a, vec);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;

@@ -101,6 +101,7 @@ struct Gemm {
     const float* mulmat = nullptr; int ldmul = 0;
     const float* addmat = nullptr; int ldadd = 0;
     float sgd_lr = 0.f, sgd_lambda = 0.f;
+    int round_tf32 = 0;  // store the result rounded to TF32 (round-to-nearest): its only consumer is a TF32 tensor-core kernel
 };
 int gemm(b200_ctx* ctx, const Gemm& g);            // picks the engine from ctx->gemm_mode and the shape
 int gemm_simt(b200_ctx* ctx, const Gemm& g);       // FP32 SIMT, any shape
@@ -133,7 +134,7 @@ int k_embed_scatter(b200_ctx*, float* eg, const float* dXa, const float* dXb, co
 // Rotary embedding in place on `count` row-major matrices sharing one launch: matrix m = base + m*matStride, rows x ld,
 // heads are numHeads slices of headDim columns starting at startCol.  pos_dev (per row) or row index when NULL.
 int k_rope(b200_ctx*, float* base, int64_t matStride, int count, int rows, int ld, int startCol, int numHeads, int headDim,
-           const float* table, const int32_t* pos_dev, int inverse);
+           const float* table, const int32_t* pos_dev, int inverse, int round_tf32 = 0);
 // Residual + LayerNorm forward.  sub, mean, var, normalized, residual may be null.
 int k_ln_forward(b200_ctx*, const float* x, const float* sub, const float* gamma, const float* beta, int rows, int d, float eps,
                  float* out, float* mean, float* var, float* normalized, float* residual);
@@ -172,6 +173,7 @@ struct Attn {
     const float* dO = nullptr; int lddo = 0;
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr; int lddq = 0, lddk = 0, lddv = 0;
     float* rowDot = nullptr;  // [totalQ, numHeads] scratch: sum_k dO*O
+    int pre_rounded = 0;      // Q, K, V (and dO) already hold TF32-rounded values: tiles can be copied asynchronously as they are
 };
 int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-core kernels when attn_tc_eligible
 // TF32 mma.sync engine (head dimension <= 64, context not in FP32 mode)

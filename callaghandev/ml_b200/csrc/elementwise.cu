@@ -263,7 +263,7 @@ int k_embed_scatter(b200_ctx* ctx, float* eg, const float* a, const float* b, co
 
 // ------------------------------------------------------------------------------------------------ rotary embedding
 __global__ void rope_kernel(float* __restrict__ base, int64_t matStride, int count, int rows, int ld, int startCol, int numHeads,
-                            int headDim, const float2* __restrict__ table, const int32_t* __restrict__ pos, int inverse) {
+                            int headDim, const float2* __restrict__ table, const int32_t* __restrict__ pos, int inverse, int round_tf32) {
     int pairs = headDim >> 1;
     int64_t perMat = (int64_t)rows * numHeads * pairs;
     int64_t total = perMat * count;
@@ -281,11 +281,17 @@ __global__ void rope_kernel(float* __restrict__ base, int64_t matStride, int cou
         float2 y;
         y.x = x.x * cs.x - x.y * sn;
         y.y = x.x * sn + x.y * cs.x;
+        if (round_tf32) {
+            uint32_t u0, u1;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y.x));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y.y));
+            y.x = __uint_as_float(u0); y.y = __uint_as_float(u1);
+        }
         *ptr = y;
     }
 }
 __global__ void rope_kernel_scalar(float* __restrict__ base, int64_t matStride, int count, int rows, int ld, int startCol, int numHeads,
-                                   int headDim, const float* __restrict__ table, const int32_t* __restrict__ pos, int inverse) {
+                                   int headDim, const float* __restrict__ table, const int32_t* __restrict__ pos, int inverse, int round_tf32) {
     int pairs = headDim >> 1;
     int64_t perMat = (int64_t)rows * numHeads * pairs;
     int64_t total = perMat * count;
@@ -300,21 +306,28 @@ __global__ void rope_kernel_scalar(float* __restrict__ base, int64_t matStride, 
         if (inverse) sn = -sn;
         float* ptr = base + m * matStride + (size_t)row * ld + startCol + h * headDim + 2 * p;
         float x0 = ptr[0], x1 = ptr[1];
-        ptr[0] = x0 * c - x1 * sn;
-        ptr[1] = x0 * sn + x1 * c;
+        float y0 = x0 * c - x1 * sn, y1 = x0 * sn + x1 * c;
+        if (round_tf32) {
+            uint32_t u0, u1;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y0));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y1));
+            y0 = __uint_as_float(u0); y1 = __uint_as_float(u1);
+        }
+        ptr[0] = y0;
+        ptr[1] = y1;
     }
 }
 int k_rope(b200_ctx* ctx, float* base, int64_t matStride, int count, int rows, int ld, int startCol, int numHeads, int headDim,
-           const float* table, const int32_t* pos, int inverse) {
+           const float* table, const int32_t* pos, int inverse, int round_tf32) {
     int64_t total = (int64_t)count * rows * numHeads * (headDim / 2);
     if (total <= 0) return B200_OK;
     int g = grid_for(total, 256, 148 * 16);
     bool vec = ((uintptr_t)base % 8 == 0) && (matStride % 2 == 0) && (ld % 2 == 0) && (startCol % 2 == 0) && (headDim % 2 == 0);
     if (vec)
         rope_kernel<<<g, 256, 0, ctx->stream>>>(base, matStride, count, rows, ld, startCol, numHeads, headDim,
-                                                reinterpret_cast<const float2*>(table), pos, inverse);
+                                                reinterpret_cast<const float2*>(table), pos, inverse, round_tf32);
     else
-        rope_kernel_scalar<<<g, 256, 0, ctx->stream>>>(base, matStride, count, rows, ld, startCol, numHeads, headDim, table, pos, inverse);
+        rope_kernel_scalar<<<g, 256, 0, ctx->stream>>>(base, matStride, count, rows, ld, startCol, numHeads, headDim, table, pos, inverse, round_tf32);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -17,7 +17,14 @@ struct Epilogue {
     const float* mulmat; int ldmul;
     const float* addmat; int ldadd;
     float sgd_lr, sgd_lambda;
+    int round_tf32;
 };
+
+__device__ __forceinline__ float tf32_round(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
 
 __device__ __forceinline__ void epilogue_store(const Epilogue& e, int m, int n, float acc, float alpha) {
     float v = alpha * acc;
@@ -42,9 +49,10 @@ __device__ __forceinline__ void epilogue_store(const Epilogue& e, int m, int n, 
         float w = *c;
         *c = w - e.sgd_lr * (v + e.sgd_lambda * w);
     } else if (e.accumulate) {
-        *c += v;
+        v += *c;
+        *c = e.round_tf32 ? tf32_round(v) : v;
     } else {
-        *c = v;
+        *c = e.round_tf32 ? tf32_round(v) : v;
     }
 }
 

@@ -307,6 +307,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
                             if (EPI == EPI_LINEAR) {
                                 v.x = alpha * v.x + b4.x + ext[i].x + ext2[i].x; v.y = alpha * v.y + b4.y + ext[i].y + ext2[i].y;
                                 v.z = alpha * v.z + b4.z + ext[i].z + ext2[i].z; v.w = alpha * v.w + b4.w + ext[i].w + ext2[i].w;
+                                if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
                                 st4(ep.C + (size_t)blockIdx.y * p.split_stride + m * ep.ldc + n, v);
                             } else if (EPI == EPI_ACT) {
                                 v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
@@ -432,7 +433,7 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     // Split-K for the weight-gradient shape (few output tiles, very long K): partial products go to a workspace and a
     // second kernel adds them to C in split order, so the result does not depend on scheduling.
     int splits = 1;
-    const bool plain = g.act == B200_ACT_NONE && !g.dout && !g.zout && !g.mulz && !g.mulmat && !g.addmat && !g.bias && g.sgd_lr == 0.f;
+    const bool plain = g.act == B200_ACT_NONE && !g.dout && !g.zout && !g.mulz && !g.mulmat && !g.addmat && !g.bias && g.sgd_lr == 0.f && !g.round_tf32;
     if (plain && tiles < 2 * ctx->sm_count && kblocks_total >= 256 && (g.N % 4 == 0)) {
         splits = (2 * ctx->sm_count + tiles - 1) / tiles;
         if (splits > 8) splits = 8;
@@ -444,7 +445,7 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
-    e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda;
+    e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     dim3 grid((unsigned)tiles, (unsigned)splits);
     if (splits > 1) {
         B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));

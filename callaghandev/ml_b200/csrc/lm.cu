@@ -219,6 +219,14 @@ bool qkv_fused(const b200_lm* lm, const LayerOff& L) {
     return L.WK == L.WQ + d * d && L.WV == L.WK + d * d && L.bK == L.bQ + d && L.bV == L.bK + d;
 }
 
+// In TF32 mode the attention kernels run on tensor cores; their operands are rounded to TF32 where they are produced
+// (Q/K/V projection epilogue, rotary kernel, attention-output dX epilogue) so that tiles can be copied as they are.
+bool tf32_attention(const b200_lm* lm) {
+    const b200_ctx* ctx = lm->ctx;
+    const int hd = lm->cfg.embedding_dim / lm->cfg.num_heads;
+    return ctx->gemm_mode != B200_GEMM_FP32_SIMT && ctx->cc_major >= 8 && hd >= 8 && hd <= 64;
+}
+
 int forward_pass(b200_lm* lm, const Pass& p) {
     b200_ctx* ctx = lm->ctx;
     const b200_lm_config& c = lm->cfg;
@@ -230,19 +238,23 @@ int forward_pass(b200_lm* lm, const Pass& p) {
     for (int l = 0; l < c.num_layers; l++) {
         const LayerOff& L = lm->lay.layer[(size_t)l];
         LayerCache& k = lm->cache[(size_t)l];
-        if (qkv_fused(lm, L)) {
-            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WQ, P + L.bQ, 3 * d, k.qkv, 3 * d));
-        } else {
-            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WQ, P + L.bQ, d, k.qkv, 3 * d));
-            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WK, P + L.bK, d, k.qkv + d, 3 * d));
-            B200_TRY(linear_fwd(ctx, k.x, N, d, P + L.WV, P + L.bV, d, k.qkv + 2 * d, 3 * d));
+        const int rnd = tf32_attention(lm) ? 1 : 0;
+        {
+            const int nParts = qkv_fused(lm, L) ? 1 : 3;
+            const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
+            for (int i = 0; i < nParts; i++) {
+                Gemm g;
+                g.M = N; g.N = nParts == 1 ? 3 * d : d; g.K = d; g.A = k.x; g.lda = d; g.B = P + Ws[i]; g.ldb = d; g.transB = 1;
+                g.C = k.qkv + i * d; g.ldc = 3 * d; g.bias = P + Bs[i]; g.round_tf32 = rnd;
+                B200_TRY(gemm(ctx, g));
+            }
         }
-        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 0));  // Q and K column blocks
+        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 0, rnd));  // Q and K column blocks
         Attn a;
         a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
         a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
         a.segs_dev = lm->cur.segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
-        a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum;
+        a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum; a.pre_rounded = rnd;
         B200_TRY(attn_forward(ctx, a));
         B200_TRY(linear_fwd(ctx, k.attnO, N, d, P + L.WO, P + L.bO, d, lm->proj, d));
         B200_TRY(k_ln_forward(ctx, k.x, lm->proj, P + L.g1, P + L.b1n, N, d, 1e-5f, k.n1, k.mean1, k.var1, nullptr, k.ln1In));
@@ -302,13 +314,19 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         B200_TRY(k_ln_backward(ctx, t2, nullptr, k.ln1In, P + L.g1, k.mean1, k.var1, N, d, 1e-5f, t3, G + L.g1, G + L.b1n, 1));
         // BackpropAttention (:933-987): output projection, attention core, inverse rotary, Q/K/V projections.
         B200_TRY(wgrad(ctx, t3, d, k.attnO, d, N, d, d, G + L.WO, G + L.bO));
-        B200_TRY(dgrad(ctx, t3, d, P + L.WO, N, d, d, t1, 0));  // dConcatenated (zero-initialised += in the reference)
+        {
+            Gemm g;  // dConcatenated = dAttnResidual * WO (zero-initialised += in the reference)
+            g.M = N; g.N = d; g.K = d; g.A = t3; g.lda = d; g.B = P + L.WO; g.ldb = d; g.C = t1; g.ldc = d;
+            g.round_tf32 = tf32_attention(lm) ? 1 : 0;
+            B200_TRY(gemm(ctx, g));
+        }
         Attn a;
         a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
         a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
         a.segs_dev = lm->cur.segs; a.nSeg = (int)p.seqs.size(); a.maxQLen = a.maxKLen = p.maxLen; a.totalQ = a.totalK = N;
         a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum; a.rowDot = lm->rowDot;
         a.dO = t1; a.lddo = d; a.dQ = lm->dqkv; a.dK = lm->dqkv + d; a.dV = lm->dqkv + 2 * d; a.lddq = a.lddk = a.lddv = 3 * d;
+        a.pre_rounded = tf32_attention(lm) ? 1 : 0;
         B200_TRY(attn_backward(ctx, a));
         B200_TRY(k_rope(ctx, lm->dqkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 1));
         float* out = t2;  // dX of the layer input = dQKV * Wqkv + dAttnResidual (:919, residual add fused)

@@ -105,17 +105,18 @@ def test_unqualified_shapes_fall_back_to_simt_in_auto_mode(mgr, oracle):
         mgr.MatrixMultiply(a, b)
 
 
-def test_lm_step_on_tensor_cores(oracle):
-    """One train step of a d=128 model (every GEMM dimension >= 128 except none) in AUTO mode: gradients and post-step
-    weights within the TF32 tolerance of the CPU oracle."""
+@pytest.mark.parametrize("d,H,L,f", [(128, 4, 2, 512), (256, 4, 1, 512), (128, 8, 1, 256)])  # head dims 32, 64, 16
+def test_lm_step_on_tensor_cores(oracle, d, H, L, f):
+    """One train step in AUTO mode (TF32 GEMMs, TF32 attention with operands rounded where they are produced and
+    copied asynchronously): gradients and post-step weights within the TF32 tolerance of the CPU oracle."""
     from callaghandev.ml_b200 import GEMM_AUTO, B200LanguageModelTrainer, CudaB200AccelerationManager, LMConfig
 
     rng = np.random.default_rng(77)
-    cfg = lm_config(vocab=300, d=128, H=4, L=2, f=512, act="Relu")
+    cfg = lm_config(vocab=300, d=d, H=H, L=L, f=f, act="Relu")
     c = LMConfig()
     for name, _ in LMConfig._fields_:
         setattr(c, name, getattr(cfg, name))
-    toks, off = token_batch(rng, 6, 300, 40, 90, zipf=1.1)
+    toks, off = token_batch(rng, 6, 300, 40, 200, zipf=1.1)
     P = init_params(oracle, cfg, 5)
     m = CudaB200AccelerationManager(0, GEMM_AUTO)
     t = B200LanguageModelTrainer(m, c, 1024)
