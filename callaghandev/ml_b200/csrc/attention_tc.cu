@@ -691,6 +691,7 @@ bool attn_tc_eligible(b200_ctx* ctx, const Attn& t) {
 }
 
 int attn_forward_tc(b200_ctx* ctx, const Attn& t) {
+    if (attn_umma_eligible(ctx, t)) return attn_forward_umma(ctx, t);
     if (t.headDim <= 16) return launch_fwd_tc<16>(ctx, t);
     if (t.headDim <= 32) return launch_fwd_tc<32>(ctx, t);
     return launch_fwd_tc<64>(ctx, t);

@@ -37,6 +37,7 @@ struct b200_ctx {
     void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
+    int gemm_tc_configured = 0, attn_umma_configured = 0;  // dynamic shared memory attributes set
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;
@@ -180,6 +181,9 @@ int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-c
 bool attn_tc_eligible(b200_ctx*, const Attn& a);
 int attn_forward_tc(b200_ctx*, const Attn& a);
 int attn_backward_tc(b200_ctx*, const Attn& a);
+// tcgen05 engine (head dimension 64, no explicit mask, sm_100a, context not in FP32 mode)
+bool attn_umma_eligible(b200_ctx*, const Attn& a);
+int attn_forward_umma(b200_ctx*, const Attn& a);
 int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from the forward
 
 // ------------------------------------------------------------------------------------------------ parameter step

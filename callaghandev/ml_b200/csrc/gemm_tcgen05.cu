@@ -15,9 +15,7 @@
 //
 // Every wait on an mbarrier is bounded by a clock budget: on expiry the kernel raises a status word in host-mapped
 // memory, drains the copies it still has in flight (bounded again), frees its TMEM and returns.
-#include <cuda.h>
-
-#include "common.h"
+#include "tcgen05.cuh"
 #include "gemm_epilogue.cuh"
 
 namespace b200 {
@@ -29,86 +27,6 @@ constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTE
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 16;
-constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (and raises *status, a word in host-mapped memory) when the clock budget runs out or
-// another role of this kernel has already failed.  The status word is only touched on the slow path.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* status, int code) {
-    for (int i = 0; i < 64; i++)
-        if (mbar_test(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 1;; it++) {
-        if (mbar_test(bar, parity)) return true;
-        if ((it & 255u) == 0) {
-            if (*status != 0) return false;
-            if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
-                *status = code;
-                __threadfence_system();
-                return false;
-            }
-        }
-        __nanosleep(32);
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                 "l"(map), "r"(bar), "r"(c0), "r"(c1)
-                 : "memory");
-}
-
-// UMMA shared-memory descriptor: start address, leading/stride byte offsets (16-byte units), descriptor version 1,
-// layout type 2 = 128-byte swizzle with 16-byte atoms (K-major operands) or 1 = 128-byte swizzle with 32-byte atoms
-// (the only layout tcgen05.mma.kind::tf32 accepts for an M/N-contiguous operand: 32-byte chunks XOR (row mod 4)).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)layout << 61;
-    return d;
-}
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-          "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 struct TcParams {
     int M, N, K;
@@ -363,6 +281,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
 }
 
+}  // namespace
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -376,9 +296,6 @@ int resolve_encode(b200_ctx* ctx) {
     return B200_OK;
 }
 
-// 2-D FP32 tensor [outer, inner] with row pitch ld floats; box = [boxOuter, 32] floats (128 B inner), 128-byte swizzle
-// (16-byte atoms for a K-contiguous operand, 32-byte atoms for an M/N-contiguous one, matching the UMMA layout types),
-// out-of-range elements read as zero, FP32 -> TF32 conversion (round to nearest) on load.
 int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxOuter, bool mn_major) {
     cuuint64_t gdim[2] = {inner, outer};
     cuuint64_t gstride[1] = {ld * sizeof(float)};
@@ -393,7 +310,13 @@ int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner,
     return B200_OK;
 }
 
-}  // namespace
+int ensure_status(b200_ctx* ctx) {
+    if (ctx->status_host) return B200_OK;
+    B200_CUDA(ctx, cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped));
+    *ctx->status_host = 0;
+    B200_CUDA(ctx, cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
+    return B200_OK;
+}
 
 bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
     if (ctx->cc_major != 10) return false;
@@ -406,10 +329,9 @@ bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
 int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     if (!gemm_tcgen05_eligible(ctx, g)) return fail(ctx, B200_ERR_UNSUPPORTED, "shape does not qualify for the tcgen05 GEMM");
     B200_TRY(resolve_encode(ctx));
-    if (!ctx->status_host) {
-        B200_CUDA(ctx, cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped));
-        *ctx->status_host = 0;
-        B200_CUDA(ctx, cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
+    B200_TRY(ensure_status(ctx));
+    if (!ctx->gemm_tc_configured) {
+        ctx->gemm_tc_configured = 1;
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

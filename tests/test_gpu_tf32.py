@@ -170,6 +170,29 @@ def test_tensor_core_attention(mgr, oracle, L, S, d, H):
             assert_close(ee, aa, TF32_TOL, "backward d" + n)
 
 
+@pytest.mark.parametrize("L,S,H", [(128, 2, 2), (300, 3, 4), (385, 2, 1), (640, 1, 2)])
+def test_tcgen05_attention_head_dim_64(mgr, oracle, L, S, H):
+    """Head dimension 64 without an explicit mask runs on tcgen05: several key tiles per query tile, ragged last
+    tiles, segments that start at rows which are not multiples of the tile."""
+    d = 64 * H
+    Q, K, V, dO = (pt_matrix(L * S, d, s) * 4 for s in (11, 12, 13, 14))
+    scale = 1 / np.sqrt(64)
+    for causal in (True, False):
+        assert_close(oracle.SegmentedAttentionForward(Q, K, V, L, S, H, causal), mgr.SegmentedAttentionForward(Q, K, V, L, S, H, causal), TF32_TOL,
+                     f"forward causal={causal}")
+        e = oracle.SegmentedAttentionBackward(Q, K, V, dO, L, S, H, scale, causal)
+        a = mgr.SegmentedAttentionBackward(Q, K, V, dO, L, S, H, scale, causal)
+        for ee, aa, n in zip(e, a, "QKV"):
+            assert_close(ee, aa, TF32_TOL, f"backward d{n} causal={causal}")
+
+
+def test_tcgen05_attention_more_keys_than_queries(mgr, oracle):
+    q, k, v, do = pt_matrix(200, 128, 1) * 3, pt_matrix(333, 128, 2) * 3, pt_matrix(333, 128, 3), pt_matrix(200, 128, 4)
+    assert_close(oracle.ScaledDotProductAttention(q, k, v, 2), mgr.ScaledDotProductAttention(q, k, v, 2), TF32_TOL, "cross lengths")
+    for ee, aa, n in zip(oracle.MultiHeadAttentionBackward(q, k, v, do, 2, 0.125), mgr.MultiHeadAttentionBackward(q, k, v, do, 2, 0.125), "QKV"):
+        assert_close(ee, aa, TF32_TOL, "cross lengths backward d" + n)
+
+
 def test_tensor_core_attention_masks(mgr, oracle):
     q, k, v, do = pt_matrix(70, 64, 1), pt_matrix(90, 64, 2), pt_matrix(90, 64, 3), pt_matrix(70, 64, 4)
     rng = np.random.default_rng(0)
