@@ -697,6 +697,7 @@ int attn_forward_tc(b200_ctx* ctx, const Attn& t) {
     return launch_fwd_tc<64>(ctx, t);
 }
 int attn_backward_tc(b200_ctx* ctx, const Attn& t) {
+    if (attn_umma_bwd_eligible(ctx, t)) return attn_backward_umma(ctx, t);
     if (t.headDim <= 16) return launch_bwd_tc<16>(ctx, t);
     if (t.headDim <= 32) return launch_bwd_tc<32>(ctx, t);
     return launch_bwd_tc<64>(ctx, t);

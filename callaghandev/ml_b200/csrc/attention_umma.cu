@@ -268,6 +268,443 @@ __global__ void __launch_bounds__(U_THREADS) attn_fwd_umma_kernel(const __grid_c
     }
 }
 
+// ------------------------------------------------------------------------------------------------------ backward
+// Two deterministic passes, as in the other engines (dQ per query tile, dK/dV per key tile; no atomics).  The softmax
+// statistics are known, so the element-wise step has no row reduction and is split over eight warps (lane quarter x
+// column half).  The inner tiles are 64 wide and S/dP are double-buffered in TMEM: the MMA warp issues the S and dP
+// products of tile j+1 while the element-wise warps turn tile j into P and dS, then issues the products that consume
+// them.  An operand that is needed both K-contiguous (for S / dP) and N-contiguous (for dQ, dK, dV) is loaded twice,
+// once per shared-memory image; the second read comes from L2.
+constexpr int B_THREADS = 64 + 256;
+constexpr int A128 = 128 * 128, T128 = 2 * A128;  // atom column / tile with 128 rows
+constexpr int A64 = 64 * 128, T64 = 2 * A64;      // atom column / tile with 64 rows
+constexpr int DQ_STAGE = 3 * T64, DQ_SMEM = 2 * T128 + 2 * DQ_STAGE + 1024 + 256;
+constexpr int DKV_STAGE = 4 * T64, DKV_SMEM = 2 * T128 + 2 * DKV_STAGE + 1024 + 256 + 2 * 3 * 64 * 4;
+constexpr int BWD_TMEM_COLS = 512;
+
+__device__ __forceinline__ uint64_t kdesc(uint32_t tile, int kk, int atom) { return umma_desc(tile + (kk >> 2) * atom + (kk & 3) * 32, 16, 1024, 2); }
+__device__ __forceinline__ uint64_t ndesc(uint32_t tile, int kk, int atom) { return umma_desc(tile + kk * 1024, atom, 512, 1); }
+// Named barrier of the 256 element-wise threads, and the same barrier with an OR vote (true when any thread passes true).
+__device__ __forceinline__ void ew_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ bool ew_barrier_or(bool pred) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(r)
+                 : "r"((uint32_t)pred)
+                 : "memory");
+    return r != 0;
+}
+
+struct UBwdArgs {
+    float *dQ, *dK, *dV;
+    int lddq, lddk, lddv;
+    const float *rowMax, *rowSum, *rowDot;
+    const AttnSeg* segs;
+    int numHeads, causal;
+    float scale;
+    int* status;
+};
+
+// Store a [128 x 64] result staged in shared memory (row stride OUT_STRIDE) with whole-row 128-bit accesses; 256 threads.
+__device__ __forceinline__ void store_rows(const float* stage, float* dst, int ld, int rowBase, int nRows, int colBase, int tid) {
+    const int c4 = (tid & 15) * 4;
+#pragma unroll 2
+    for (int r = tid >> 4; r < 128; r += 16)
+        if (r < nRows) *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
+}
+
+__global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
+                                                                const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                                                                const __grid_constant__ CUtensorMap mapKn, UBwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const AttnSeg sg = a.segs[blockIdx.z];
+    const int head = blockIdx.y;
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * 128;
+    if (q0 >= sg.qLen) return;
+    const int kEnd = a.causal ? min(sg.kLen, q0 + 128) : sg.kLen;
+    const int nkt = (kEnd + 63) / 64;
+    if (nkt == 0) {
+        for (int idx = threadIdx.x; idx < 128 * 16; idx += B_THREADS) {
+            const int r = idx >> 4, c = (idx & 15) * 4;
+            if (q0 + r < sg.qLen) *reinterpret_cast<float4*>(a.dQ + (size_t)(sg.qStart + q0 + r) * a.lddq + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + 2 * DQ_STAGE);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128, st0 = dOs + T128;  // stage s: K (K-major), V (K-major), K (N-major)
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t qdo_full = bar0, kv_full = bar0 + 8, kv_empty = bar0 + 24, sdp_full = bar0 + 40, ds_full = bar0 + 56, dq_full = bar0 + 72;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* status = a.status;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 10; i++) mbar_init(bar0 + 8 * i, (i == 7 || i == 8) ? 256 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = *tmem_slot;
+    constexpr uint32_t DQ_COL = 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int col = head * UHD;
+            mbar_expect_tx(qdo_full, 2 * T128);
+            tma_load_2d(Qs, &mapQ, qdo_full, col, sg.qStart + q0);
+            tma_load_2d(Qs + A128, &mapQ, qdo_full, col + 32, sg.qStart + q0);
+            tma_load_2d(dOs, &mapdO, qdo_full, col, sg.qStart + q0);
+            tma_load_2d(dOs + A128, &mapdO, qdo_full, col + 32, sg.qStart + q0);
+            bool ok = true;
+            int issued = 0;
+            for (int j = 0; j < nkt; j++) {
+                const int s = j & 1, row = sg.kStart + j * 64;
+                ok = mbar_wait(kv_empty + 8 * s, ((j >> 1) & 1) ^ 1, status, 21);
+                if (!ok) break;
+                const uint32_t base = st0 + s * DQ_STAGE, bar = kv_full + 8 * s;
+                mbar_expect_tx(bar, DQ_STAGE);
+                tma_load_2d(base, &mapK, bar, col, row);
+                tma_load_2d(base + A64, &mapK, bar, col + 32, row);
+                tma_load_2d(base + T64, &mapV, bar, col, row);
+                tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
+                tma_load_2d(base + 2 * T64, &mapKn, bar, col, row);
+                tma_load_2d(base + 2 * T64 + A64, &mapKn, bar, col + 32, row);
+                issued = j + 1;
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (!mbar_test(qdo_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int j = max(0, issued - 2); j < issued; j++)
+                    while (!mbar_test(kv_full + 8 * (j & 1), (j >> 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
+            auto issue_sdp = [&](int j) {
+                const int s = j & 1;
+                const uint32_t base = st0 + s * DQ_STAGE;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128, kdesc(Qs, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128 + 64, kdesc(dOs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                umma_commit(sdp_full + 8 * s);
+            };
+            bool ok = mbar_wait(qdo_full, 0, status, 22);
+            if (ok) ok = mbar_wait(kv_full, 0, status, 23);
+            if (ok) {
+                tc_fence_after();
+                issue_sdp(0);
+            }
+            for (int j = 0; j < nkt && ok; j++) {
+                if (j + 1 < nkt) {
+                    ok = mbar_wait(kv_full + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, status, 24);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_sdp(j + 1);
+                }
+                const int s = j & 1;
+                ok = mbar_wait(ds_full + 8 * s, (j >> 1) & 1, status, 25);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t kn = st0 + s * DQ_STAGE + 2 * T64;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + s * 128 + kk * 8, ndesc(kn, kk, A64), idN, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(kv_empty + 8 * s);
+            }
+            umma_commit(dq_full);
+        }
+    } else {
+        const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half;
+        const int row = 32 * quarter + lane, qi = q0 + row;
+        const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
+        const float sl2 = a.scale * LOG2E_F;
+        float m2 = 0.f, il = 0.f, D = 0.f;
+        if (qi < sg.qLen) {
+            const size_t idx = (size_t)(sg.qStart + qi) * a.numHeads + head;
+            const float m = a.rowMax[idx], l = a.rowSum[idx];
+            if (l > 0.f && m != -INFINITY) { il = 1.f / l; m2 = m * LOG2E_F; }
+            D = a.rowDot[idx];
+        }
+        const int lim = il > 0.f ? (a.causal ? min(sg.kLen, qi + 1) : sg.kLen) : 0;  // keys [0, lim) are visible to this row
+        bool ok = true;
+        for (int j = 0; j < nkt; j++) {
+            const int s = j & 1;
+            ok = mbar_wait(sdp_full + 8 * s, (j >> 1) & 1, status, 26);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int nvis = lim - j * 64 - c0;  // columns [0, nvis) of this warp's 32 are visible
+            uint32_t sr[32], pr[32];
+            tmem_ld32_nowait(tlane + s * 128 + c0, sr);
+            tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                float v = fmaf(__uint_as_float(sr[i]), sl2, -m2);
+                if (i >= nvis) v = -INFINITY;
+                const float p = ex2(v) * il;
+                sr[i] = rna_tf32(p * (__uint_as_float(pr[i]) - D));
+            }
+            tmem_st32(tlane + s * 128 + c0, sr);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(ds_full + 8 * s);
+        }
+        if (ok) {
+            ok = mbar_wait(dq_full, 0, status, 27);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            float* stage = reinterpret_cast<float*>(tiles);  // every MMA has completed: the operand tiles are free
+            uint32_t r[32];
+            tmem_ld32(tlane + DQ_COL + c0, r);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(stage + row * OUT_STRIDE + c0 + i) =
+                    make_float4(__uint_as_float(r[i]) * a.scale, __uint_as_float(r[i + 1]) * a.scale, __uint_as_float(r[i + 2]) * a.scale,
+                                __uint_as_float(r[i + 3]) * a.scale);
+        }
+        ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
+        if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(BWD_TMEM_COLS) : "memory");
+    }
+}
+
+// dK / dV for 128 keys (one key per TMEM lane) against the query tiles (64 rows each) that can see them:
+//   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T (element-wise, per-column statistics from shared memory)
+//   dV += P^T dO,  dK += dS^T Q   (A from TMEM, Q / dO as N-contiguous shared-memory operands)
+__global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                                                                 const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
+                                                                 const __grid_constant__ CUtensorMap mapQn, const __grid_constant__ CUtensorMap mapdOn,
+                                                                 UBwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const AttnSeg sg = a.segs[blockIdx.z];
+    const int head = blockIdx.y;
+    const int k0 = blockIdx.x * 128;  // under a causal mask the first key tiles see the most queries
+    if (k0 >= sg.kLen) return;
+    const int qtBegin = a.causal ? k0 / 64 : 0, qtEnd = (sg.qLen + 63) / 64;
+    const int nqt = qtEnd - qtBegin;
+    if (nqt <= 0) {  // keys no query can see
+        for (int idx = threadIdx.x; idx < 128 * 16; idx += B_THREADS) {
+            const int r = idx >> 4, c = (idx & 15) * 4;
+            if (k0 + r < sg.kLen) {
+                *reinterpret_cast<float4*>(a.dK + (size_t)(sg.kStart + k0 + r) * a.lddk + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(a.dV + (size_t)(sg.kStart + k0 + r) * a.lddv + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        return;
+    }
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + 2 * DKV_STAGE);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    float* stats = reinterpret_cast<float*>(bars + 12);  // [2 stages][m2 | il | D][64]
+    const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128, st0 = Vs + T128;  // stage s: Q, dO (K-major), Q, dO (N-major)
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t kv_full = bar0, q_full = bar0 + 8, q_empty = bar0 + 24, sdp_full = bar0 + 40, ds_full = bar0 + 56, acc_full = bar0 + 72;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* status = a.status;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 10; i++) mbar_init(bar0 + 8 * i, (i == 7 || i == 8) ? 256 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = *tmem_slot;
+    constexpr uint32_t DV_COL = 256, DK_COL = 320;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int col = head * UHD;
+            mbar_expect_tx(kv_full, 2 * T128);
+            tma_load_2d(Ks, &mapK, kv_full, col, sg.kStart + k0);
+            tma_load_2d(Ks + A128, &mapK, kv_full, col + 32, sg.kStart + k0);
+            tma_load_2d(Vs, &mapV, kv_full, col, sg.kStart + k0);
+            tma_load_2d(Vs + A128, &mapV, kv_full, col + 32, sg.kStart + k0);
+            bool ok = true;
+            int issued = 0;
+            for (int i = 0; i < nqt; i++) {
+                const int s = i & 1, row = sg.qStart + (qtBegin + i) * 64;
+                ok = mbar_wait(q_empty + 8 * s, ((i >> 1) & 1) ^ 1, status, 31);
+                if (!ok) break;
+                const uint32_t base = st0 + s * DKV_STAGE, bar = q_full + 8 * s;
+                mbar_expect_tx(bar, DKV_STAGE);
+                tma_load_2d(base, &mapQ, bar, col, row);
+                tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
+                tma_load_2d(base + T64, &mapdO, bar, col, row);
+                tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
+                tma_load_2d(base + 2 * T64, &mapQn, bar, col, row);
+                tma_load_2d(base + 2 * T64 + A64, &mapQn, bar, col + 32, row);
+                tma_load_2d(base + 3 * T64, &mapdOn, bar, col, row);
+                tma_load_2d(base + 3 * T64 + A64, &mapdOn, bar, col + 32, row);
+                issued = i + 1;
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (!mbar_test(kv_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int i = max(0, issued - 2); i < issued; i++)
+                    while (!mbar_test(q_full + 8 * (i & 1), (i >> 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
+            auto issue_sdp = [&](int i) {
+                const int s = i & 1;
+                const uint32_t base = st0 + s * DKV_STAGE;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128, kdesc(Ks, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128 + 64, kdesc(Vs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                umma_commit(sdp_full + 8 * s);
+            };
+            bool ok = mbar_wait(kv_full, 0, status, 32);
+            if (ok) ok = mbar_wait(q_full, 0, status, 33);
+            if (ok) {
+                tc_fence_after();
+                issue_sdp(0);
+            }
+            for (int i = 0; i < nqt && ok; i++) {
+                if (i + 1 < nqt) {
+                    ok = mbar_wait(q_full + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, status, 34);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_sdp(i + 1);
+                }
+                const int s = i & 1;
+                ok = mbar_wait(ds_full + 8 * s, (i >> 1) & 1, status, 35);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t qn = st0 + s * DKV_STAGE + 2 * T64, don = qn + T64;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + s * 128 + kk * 8, ndesc(don, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + s * 128 + 64 + kk * 8, ndesc(qn, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(q_empty + 8 * s);
+            }
+            umma_commit(acc_full);
+        }
+    } else {
+        const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half, tid = threadIdx.x - 64;
+        const int row = 32 * quarter + lane, kj = k0 + row;
+        const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
+        const float sl2 = a.scale * LOG2E_F;
+        bool ok = true;
+        for (int i = 0; i < nqt; i++) {
+            const int s = i & 1, qbase = (qtBegin + i) * 64;
+            float* st = stats + s * 192;
+            if (tid < 64) {  // statistics of this tile's 64 query rows
+                float m2 = 0.f, il = 0.f, D = 0.f;
+                const int q = qbase + tid;
+                if (q < sg.qLen) {
+                    const size_t idx = (size_t)(sg.qStart + q) * a.numHeads + head;
+                    const float m = a.rowMax[idx], l = a.rowSum[idx];
+                    if (l > 0.f && m != -INFINITY) { il = 1.f / l; m2 = m * LOG2E_F; }
+                    D = a.rowDot[idx];
+                }
+                st[tid] = m2; st[64 + tid] = il; st[128 + tid] = D;
+            }
+            ok = mbar_wait(sdp_full + 8 * s, (i >> 1) & 1, status, 36);
+            if (ew_barrier_or(!ok)) {  // publishes the statistics; a failed wait anywhere stops all 256 threads together
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            // visible columns of this warp's 32: query index >= key index (causal), query inside the segment, key inside it
+            int cmin = a.causal ? kj - qbase - c0 : 0, cmax = sg.qLen - qbase - c0;
+            if (kj >= sg.kLen) cmax = 0;
+            uint32_t sr[32], pr[32];
+            tmem_ld32_nowait(tlane + s * 128 + c0, sr);
+            tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+                const float4 m4 = *reinterpret_cast<const float4*>(st + c0 + c), i4 = *reinterpret_cast<const float4*>(st + 64 + c0 + c),
+                             d4 = *reinterpret_cast<const float4*>(st + 128 + c0 + c);
+                const float mm[4] = {m4.x, m4.y, m4.z, m4.w}, ii[4] = {i4.x, i4.y, i4.z, i4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float v = fmaf(__uint_as_float(sr[c + e]), sl2, -mm[e]);
+                    if (c + e < cmin || c + e >= cmax || ii[e] == 0.f) v = -INFINITY;
+                    const float p = ex2(v) * ii[e];
+                    sr[c + e] = rna_tf32(p);
+                    pr[c + e] = rna_tf32(p * (__uint_as_float(pr[c + e]) - dd[e]));
+                }
+            }
+            tmem_st32(tlane + s * 128 + c0, sr);
+            tmem_st32(tlane + s * 128 + 64 + c0, pr);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(ds_full + 8 * s);
+        }
+        if (ok) {
+            ok = mbar_wait(acc_full, 0, status, 37);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        float* stageV = reinterpret_cast<float*>(tiles);                 // every MMA has completed: K and V tiles are free
+        float* stageK = reinterpret_cast<float*>(tiles + 36864);
+        if (ok) {
+            tc_fence_after();
+            uint32_t r[32];
+            tmem_ld32(tlane + DV_COL + c0, r);
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+                *reinterpret_cast<float4*>(stageV + row * OUT_STRIDE + c0 + c) =
+                    make_float4(__uint_as_float(r[c]), __uint_as_float(r[c + 1]), __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+            tmem_ld32(tlane + DK_COL + c0, r);
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+                *reinterpret_cast<float4*>(stageK + row * OUT_STRIDE + c0 + c) =
+                    make_float4(__uint_as_float(r[c]) * a.scale, __uint_as_float(r[c + 1]) * a.scale, __uint_as_float(r[c + 2]) * a.scale,
+                                __uint_as_float(r[c + 3]) * a.scale);
+        }
+        ew_barrier();
+        if (ok) {
+            const int nRows = min(128, sg.kLen - k0);
+            store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
+            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(BWD_TMEM_COLS) : "memory");
+    }
+}
+
+// rowDot[row, head] = sum_c dO[row, head*64 + c] * O[row, head*64 + c]; one warp per (row, head)
+__global__ void attn_rowdot_umma_kernel(const float* __restrict__ dO, int lddo, const float* __restrict__ O, int ldo, int rows, int numHeads,
+                                        float* __restrict__ rowDot) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (w >= rows * numHeads) return;
+    const int row = w / numHeads, head = w - row * numHeads;
+    const float2 x = *reinterpret_cast<const float2*>(dO + (size_t)row * lddo + head * UHD + 2 * lane);
+    const float2 y = *reinterpret_cast<const float2*>(O + (size_t)row * ldo + head * UHD + 2 * lane);
+    const float s = warp_sum(x.x * y.x + x.y * y.y);
+    if (lane == 0) rowDot[w] = s;
+}
+
 bool umma_enabled() {
     static int v = -1;
     if (v < 0) {
@@ -285,13 +722,59 @@ bool attn_umma_eligible(b200_ctx* ctx, const Attn& t) {
            t.maxQLen >= 128 && t.totalQ >= 128 && t.totalK >= 128 && ok(t.Q, t.ldq) && ok(t.K, t.ldk) && ok(t.V, t.ldv) && ok(t.O, t.ldo);
 }
 
-int attn_forward_umma(b200_ctx* ctx, const Attn& t) {
+namespace {
+int configure(b200_ctx* ctx) {
     B200_TRY(resolve_encode(ctx));
     B200_TRY(ensure_status(ctx));
     if (!ctx->attn_umma_configured) {
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(attn_dq_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(attn_dkv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DKV_SMEM));
         ctx->attn_umma_configured = 1;
     }
+    return B200_OK;
+}
+}  // namespace
+
+bool attn_umma_bwd_eligible(b200_ctx* ctx, const Attn& t) {
+    auto ok = [](const void* p, int ld) { return p && (((uintptr_t)p) & 15) == 0 && (ld & 3) == 0; };
+    return attn_umma_eligible(ctx, t) && t.maxKLen >= 128 && t.rowDot && ok(t.dO, t.lddo) && ok(t.dQ, t.lddq) && ok(t.dK, t.lddk) && ok(t.dV, t.lddv);
+}
+
+int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
+    B200_TRY(configure(ctx));
+    const uint64_t cols = (uint64_t)t.numHeads * UHD;
+    const uint64_t nq = (uint64_t)t.totalQ, nk = (uint64_t)t.totalK;
+    CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64, qn64, don64, kn64;
+    B200_TRY(make_map(ctx, &q128, t.Q, cols, nq, (uint64_t)t.ldq, 128, false));
+    B200_TRY(make_map(ctx, &do128, t.dO, cols, nq, (uint64_t)t.lddo, 128, false));
+    B200_TRY(make_map(ctx, &k128, t.K, cols, nk, (uint64_t)t.ldk, 128, false));
+    B200_TRY(make_map(ctx, &v128, t.V, cols, nk, (uint64_t)t.ldv, 128, false));
+    B200_TRY(make_map(ctx, &q64, t.Q, cols, nq, (uint64_t)t.ldq, 64, false));
+    B200_TRY(make_map(ctx, &do64, t.dO, cols, nq, (uint64_t)t.lddo, 64, false));
+    B200_TRY(make_map(ctx, &k64, t.K, cols, nk, (uint64_t)t.ldk, 64, false));
+    B200_TRY(make_map(ctx, &v64, t.V, cols, nk, (uint64_t)t.ldv, 64, false));
+    B200_TRY(make_map(ctx, &qn64, t.Q, cols, nq, (uint64_t)t.ldq, 64, true));
+    B200_TRY(make_map(ctx, &don64, t.dO, cols, nq, (uint64_t)t.lddo, 64, true));
+    B200_TRY(make_map(ctx, &kn64, t.K, cols, nk, (uint64_t)t.ldk, 64, true));
+    UBwdArgs a;
+    a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
+    a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
+    a.scale = t.scale; a.status = ctx->status_dev;
+    const int warps = t.totalQ * t.numHeads;
+    attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
+    B200_LAUNCH_CHECK(ctx);
+    dim3 gk((t.maxKLen + 127) / 128, t.numHeads, t.nSeg);
+    attn_dkv_umma_kernel<<<gk, B_THREADS, DKV_SMEM, ctx->stream>>>(k128, v128, q64, do64, qn64, don64, a);
+    B200_LAUNCH_CHECK(ctx);
+    dim3 gq((t.maxQLen + 127) / 128, t.numHeads, t.nSeg);
+    attn_dq_umma_kernel<<<gq, B_THREADS, DQ_SMEM, ctx->stream>>>(q128, do128, k64, v64, kn64, a);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int attn_forward_umma(b200_ctx* ctx, const Attn& t) {
+    B200_TRY(configure(ctx));
     const uint64_t cols = (uint64_t)t.numHeads * UHD;
     CUtensorMap mq, mk, mv;
     B200_TRY(make_map(ctx, &mq, t.Q, cols, (uint64_t)t.totalQ, (uint64_t)t.ldq, 128, false));

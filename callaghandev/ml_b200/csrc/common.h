@@ -184,6 +184,8 @@ int attn_backward_tc(b200_ctx*, const Attn& a);
 // tcgen05 engine (head dimension 64, no explicit mask, sm_100a, context not in FP32 mode)
 bool attn_umma_eligible(b200_ctx*, const Attn& a);
 int attn_forward_umma(b200_ctx*, const Attn& a);
+bool attn_umma_bwd_eligible(b200_ctx*, const Attn& a);
+int attn_backward_umma(b200_ctx*, const Attn& a);
 int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from the forward
 
 // ------------------------------------------------------------------------------------------------ parameter step
