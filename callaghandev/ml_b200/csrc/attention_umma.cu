@@ -55,13 +55,11 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x; -inf gives +0
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t rna_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return u;
-}
+// Round to TF32 (nearest, ties away from zero) with integer instructions: the conversion instruction shares the
+// transcendental pipe with ex2, which is the scarce resource of the element-wise step.
+__device__ __forceinline__ uint32_t rna_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 
-__global__ void __launch_bounds__(U_THREADS) attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+__global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                                                                  const __grid_constant__ CUtensorMap mapV, UArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const AttnSeg sg = a.segs[blockIdx.z];
@@ -179,37 +177,42 @@ __global__ void __launch_bounds__(U_THREADS) attn_fwd_umma_kernel(const __grid_c
             const int k0 = j * UK;
             const bool full = k0 + UK <= sg.kLen && (!a.causal || k0 + UK - 1 <= q0 + 32 * quarter);  // warp-uniform
             const int nvis = lim - k0;  // columns [0, nvis) of this tile are visible
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < UK; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tlane + S_COL + c, r);
-                if (full) {
+            // the whole score row of this tile in registers: one TMEM read, four independent max / sum chains
+            uint32_t r[4][32];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
-                } else {
+            for (int c = 0; c < 4; c++) tmem_ld32_nowait(tlane + S_COL + 32 * c, r[c]);
+            tmem_ld_wait();
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (full) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, (c + i < nvis) ? __uint_as_float(r[i]) : -INFINITY);
-                }
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        if (32 * c + i >= nvis) r[c][i] = 0xff800000u;  // -inf
+                        mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+                    }
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = fmaxf(m, mx * sl2);  // scale > 0, so the maximum commutes with the scaling
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = ex2(m - m_safe);
-            float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < UK; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tlane + S_COL + c, r);
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
-                    float v = fmaf(__uint_as_float(r[i]), sl2, -m_safe);
-                    if (!full && c + i >= nvis) v = -INFINITY;
-                    const float p = ex2(v);
-                    rs += p;
-                    r[i] = rna_tf32(p);
+                    const float p = ex2(fmaf(__uint_as_float(r[c][i]), sl2, -m_safe));  // masked entries are -inf: p = 0
+                    rs4[i & 3] += p;
+                    r[c][i] = rna_tf32(p);
                 }
-                tmem_st32(tlane + S_COL + c, r);
+                tmem_st32(tlane + S_COL + 32 * c, r[c]);
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l = l * corr + rs;
             m = m_new;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // S(j) complete implies P V(j-1) complete: O is stable
@@ -278,8 +281,13 @@ __global__ void __launch_bounds__(U_THREADS) attn_fwd_umma_kernel(const __grid_c
 constexpr int B_THREADS = 64 + 256;
 constexpr int A128 = 128 * 128, T128 = 2 * A128;  // atom column / tile with 128 rows
 constexpr int A64 = 64 * 128, T64 = 2 * A64;      // atom column / tile with 64 rows
-constexpr int DQ_STAGE = 3 * T64, DQ_SMEM = 2 * T128 + 2 * DQ_STAGE + 1024 + 256;
-constexpr int DKV_STAGE = 4 * T64, DKV_SMEM = 2 * T128 + 2 * DKV_STAGE + 1024 + 256 + 2 * 3 * 64 * 4;
+// Streamed operands live in two rings per kernel, because their consumers differ: the K-contiguous images feed the
+// S / dP products and are free as soon as those complete, the N-contiguous images feed the products that follow the
+// element-wise step.  Three slots let the loads run two to three tiles ahead of the MMA warp.
+constexpr int RING_K = 3;                                      // slots of {two K-contiguous 64-row tiles} (32 KiB each)
+constexpr int DQ_RING_N = 3, DKV_RING_N = 2;                   // slots of N-contiguous tiles: 16 KiB (dQ) / 32 KiB (dK,dV)
+constexpr int DQ_SMEM = 2 * T128 + RING_K * 2 * T64 + DQ_RING_N * T64 + 1024 + 256;
+constexpr int DKV_SMEM = 2 * T128 + RING_K * 2 * T64 + DKV_RING_N * 2 * T64 + 1024 + 256 + 2 * 3 * 64 * 4;
 constexpr int BWD_TMEM_COLS = 512;
 
 __device__ __forceinline__ uint64_t kdesc(uint32_t tile, int kk, int atom) { return umma_desc(tile + (kk >> 2) * atom + (kk & 3) * 32, 16, 1024, 2); }
@@ -331,16 +339,19 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         return;
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + 2 * DQ_STAGE);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
-    const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128, st0 = dOs + T128;  // stage s: K (K-major), V (K-major), K (N-major)
+    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DQ_RING_N * T64);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 18);
+    const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128;
+    const uint32_t ringK = dOs + T128;                 // slot: K tile then V tile, both K-contiguous
+    const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: K tile, N-contiguous
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t qdo_full = bar0, kv_full = bar0 + 8, kv_empty = bar0 + 24, sdp_full = bar0 + 40, ds_full = bar0 + 56, dq_full = bar0 + 72;
+    const uint32_t qdo_full = bar0, kk_full = bar0 + 8, kk_empty = bar0 + 32, kn_full = bar0 + 56, kn_empty = bar0 + 80, sdp_full = bar0 + 104,
+                   ds_full = bar0 + 120, dq_full = bar0 + 136;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 10; i++) mbar_init(bar0 + 8 * i, (i == 7 || i == 8) ? 256 : 1);
+        for (int i = 0; i < 18; i++) mbar_init(bar0 + 8 * i, (i == 15 || i == 16) ? 256 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -363,61 +374,72 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             tma_load_2d(dOs, &mapdO, qdo_full, col, sg.qStart + q0);
             tma_load_2d(dOs + A128, &mapdO, qdo_full, col + 32, sg.qStart + q0);
             bool ok = true;
-            int issued = 0;
-            for (int j = 0; j < nkt; j++) {
-                const int s = j & 1, row = sg.kStart + j * 64;
-                ok = mbar_wait(kv_empty + 8 * s, ((j >> 1) & 1) ^ 1, status, 21);
-                if (!ok) break;
-                const uint32_t base = st0 + s * DQ_STAGE, bar = kv_full + 8 * s;
-                mbar_expect_tx(bar, DQ_STAGE);
-                tma_load_2d(base, &mapK, bar, col, row);
-                tma_load_2d(base + A64, &mapK, bar, col + 32, row);
-                tma_load_2d(base + T64, &mapV, bar, col, row);
-                tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
-                tma_load_2d(base + 2 * T64, &mapKn, bar, col, row);
-                tma_load_2d(base + 2 * T64 + A64, &mapKn, bar, col + 32, row);
-                issued = j + 1;
+            int nk = 0, nn = 0;  // next tile to load into each ring
+            while (nk < nkt || nn < nkt) {
+                if (nk < nkt && nk < nn + RING_K) {
+                    const int s = nk % RING_K, row = sg.kStart + nk * 64;
+                    ok = mbar_wait(kk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 21);
+                    if (!ok) break;
+                    const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
+                    mbar_expect_tx(bar, 2 * T64);
+                    tma_load_2d(base, &mapK, bar, col, row);
+                    tma_load_2d(base + A64, &mapK, bar, col + 32, row);
+                    tma_load_2d(base + T64, &mapV, bar, col, row);
+                    tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
+                    nk++;
+                } else {
+                    const int s = nn % DQ_RING_N, row = sg.kStart + nn * 64;
+                    ok = mbar_wait(kn_empty + 8 * s, ((nn / DQ_RING_N) & 1) ^ 1, status, 28);
+                    if (!ok) break;
+                    const uint32_t base = ringN + s * T64, bar = kn_full + 8 * s;
+                    mbar_expect_tx(bar, T64);
+                    tma_load_2d(base, &mapKn, bar, col, row);
+                    tma_load_2d(base + A64, &mapKn, bar, col + 32, row);
+                    nn++;
+                }
             }
-            if (!ok) {
+            if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
                 while (!mbar_test(qdo_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int j = max(0, issued - 2); j < issued; j++)
-                    while (!mbar_test(kv_full + 8 * (j & 1), (j >> 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int j = max(0, nk - RING_K); j < nk; j++)
+                    while (!mbar_test(kk_full + 8 * (j % RING_K), (j / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int j = max(0, nn - DQ_RING_N); j < nn; j++)
+                    while (!mbar_test(kn_full + 8 * (j % DQ_RING_N), (j / DQ_RING_N) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            auto issue_sdp = [&](int j) {
-                const int s = j & 1;
-                const uint32_t base = st0 + s * DQ_STAGE;
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128, kdesc(Qs, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128 + 64, kdesc(dOs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
-                umma_commit(sdp_full + 8 * s);
-            };
             bool ok = mbar_wait(qdo_full, 0, status, 22);
-            if (ok) ok = mbar_wait(kv_full, 0, status, 23);
-            if (ok) {
+            auto issue_sdp = [&](int j) {  // S(j) and dP(j) into TMEM buffer j&1; frees the K-contiguous slot when they complete
+                const int s = j % RING_K, b = j & 1;
+                ok = mbar_wait(kk_full + 8 * s, (j / RING_K) & 1, status, 23);
+                if (!ok) return;
                 tc_fence_after();
-                issue_sdp(0);
-            }
+                const uint32_t base = ringK + s * 2 * T64;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128, kdesc(Qs, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128 + 64, kdesc(dOs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                umma_commit(kk_empty + 8 * s);
+                umma_commit(sdp_full + 8 * b);
+            };
+            if (ok) issue_sdp(0);
             for (int j = 0; j < nkt && ok; j++) {
                 if (j + 1 < nkt) {
-                    ok = mbar_wait(kv_full + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, status, 24);
-                    if (!ok) break;
-                    tc_fence_after();
                     issue_sdp(j + 1);
+                    if (!ok) break;
                 }
-                const int s = j & 1;
-                ok = mbar_wait(ds_full + 8 * s, (j >> 1) & 1, status, 25);
+                const int s = j % DQ_RING_N, b = j & 1;
+                ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 24);
+                if (!ok) break;
+                ok = mbar_wait(ds_full + 8 * b, (j >> 1) & 1, status, 25);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t kn = st0 + s * DQ_STAGE + 2 * T64;
+                const uint32_t kn = ringN + s * T64;
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + s * 128 + kk * 8, ndesc(kn, kk, A64), idN, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(kv_empty + 8 * s);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, ndesc(kn, kk, A64), idN, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(kn_empty + 8 * s);
             }
             umma_commit(dq_full);
         }
@@ -509,17 +531,20 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
         return;
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + 2 * DKV_STAGE);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
-    float* stats = reinterpret_cast<float*>(bars + 12);  // [2 stages][m2 | il | D][64]
-    const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128, st0 = Vs + T128;  // stage s: Q, dO (K-major), Q, dO (N-major)
+    uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DKV_RING_N * 2 * T64);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+    float* stats = reinterpret_cast<float*>(bars + 18);  // [2 buffers][m2 | il | D][64]
+    const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128;
+    const uint32_t ringK = Vs + T128;                  // slot: Q tile then dO tile, both K-contiguous
+    const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: Q tile then dO tile, both N-contiguous
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t kv_full = bar0, q_full = bar0 + 8, q_empty = bar0 + 24, sdp_full = bar0 + 40, ds_full = bar0 + 56, acc_full = bar0 + 72;
+    const uint32_t kv_full = bar0, qk_full = bar0 + 8, qk_empty = bar0 + 32, qn_full = bar0 + 56, qn_empty = bar0 + 72, sdp_full = bar0 + 88,
+                   ds_full = bar0 + 104, acc_full = bar0 + 120;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 10; i++) mbar_init(bar0 + 8 * i, (i == 7 || i == 8) ? 256 : 1);
+        for (int i = 0; i < 16; i++) mbar_init(bar0 + 8 * i, (i == 13 || i == 14) ? 256 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -542,65 +567,76 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             tma_load_2d(Vs, &mapV, kv_full, col, sg.kStart + k0);
             tma_load_2d(Vs + A128, &mapV, kv_full, col + 32, sg.kStart + k0);
             bool ok = true;
-            int issued = 0;
-            for (int i = 0; i < nqt; i++) {
-                const int s = i & 1, row = sg.qStart + (qtBegin + i) * 64;
-                ok = mbar_wait(q_empty + 8 * s, ((i >> 1) & 1) ^ 1, status, 31);
-                if (!ok) break;
-                const uint32_t base = st0 + s * DKV_STAGE, bar = q_full + 8 * s;
-                mbar_expect_tx(bar, DKV_STAGE);
-                tma_load_2d(base, &mapQ, bar, col, row);
-                tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
-                tma_load_2d(base + T64, &mapdO, bar, col, row);
-                tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
-                tma_load_2d(base + 2 * T64, &mapQn, bar, col, row);
-                tma_load_2d(base + 2 * T64 + A64, &mapQn, bar, col + 32, row);
-                tma_load_2d(base + 3 * T64, &mapdOn, bar, col, row);
-                tma_load_2d(base + 3 * T64 + A64, &mapdOn, bar, col + 32, row);
-                issued = i + 1;
+            int nk = 0, nn = 0;  // next tile to load into each ring
+            while (nk < nqt || nn < nqt) {
+                if (nk < nqt && nk < nn + RING_K) {
+                    const int s = nk % RING_K, row = sg.qStart + (qtBegin + nk) * 64;
+                    ok = mbar_wait(qk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 31);
+                    if (!ok) break;
+                    const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
+                    mbar_expect_tx(bar, 2 * T64);
+                    tma_load_2d(base, &mapQ, bar, col, row);
+                    tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
+                    tma_load_2d(base + T64, &mapdO, bar, col, row);
+                    tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
+                    nk++;
+                } else {
+                    const int s = nn % DKV_RING_N, row = sg.qStart + (qtBegin + nn) * 64;
+                    ok = mbar_wait(qn_empty + 8 * s, ((nn / DKV_RING_N) & 1) ^ 1, status, 38);
+                    if (!ok) break;
+                    const uint32_t base = ringN + s * 2 * T64, bar = qn_full + 8 * s;
+                    mbar_expect_tx(bar, 2 * T64);
+                    tma_load_2d(base, &mapQn, bar, col, row);
+                    tma_load_2d(base + A64, &mapQn, bar, col + 32, row);
+                    tma_load_2d(base + T64, &mapdOn, bar, col, row);
+                    tma_load_2d(base + T64 + A64, &mapdOn, bar, col + 32, row);
+                    nn++;
+                }
             }
-            if (!ok) {
+            if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
                 while (!mbar_test(kv_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int i = max(0, issued - 2); i < issued; i++)
-                    while (!mbar_test(q_full + 8 * (i & 1), (i >> 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int i = max(0, nk - RING_K); i < nk; i++)
+                    while (!mbar_test(qk_full + 8 * (i % RING_K), (i / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (int i = max(0, nn - DKV_RING_N); i < nn; i++)
+                    while (!mbar_test(qn_full + 8 * (i % DKV_RING_N), (i / DKV_RING_N) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            auto issue_sdp = [&](int i) {
-                const int s = i & 1;
-                const uint32_t base = st0 + s * DKV_STAGE;
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128, kdesc(Ks, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + s * 128 + 64, kdesc(Vs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
-                umma_commit(sdp_full + 8 * s);
-            };
             bool ok = mbar_wait(kv_full, 0, status, 32);
-            if (ok) ok = mbar_wait(q_full, 0, status, 33);
-            if (ok) {
+            auto issue_sdp = [&](int i) {  // S^T(i) and dP^T(i) into TMEM buffer i&1; frees the K-contiguous slot when they complete
+                const int s = i % RING_K, b = i & 1;
+                ok = mbar_wait(qk_full + 8 * s, (i / RING_K) & 1, status, 33);
+                if (!ok) return;
                 tc_fence_after();
-                issue_sdp(0);
-            }
+                const uint32_t base = ringK + s * 2 * T64;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128, kdesc(Ks, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128 + 64, kdesc(Vs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                umma_commit(qk_empty + 8 * s);
+                umma_commit(sdp_full + 8 * b);
+            };
+            if (ok) issue_sdp(0);
             for (int i = 0; i < nqt && ok; i++) {
                 if (i + 1 < nqt) {
-                    ok = mbar_wait(q_full + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, status, 34);
-                    if (!ok) break;
-                    tc_fence_after();
                     issue_sdp(i + 1);
+                    if (!ok) break;
                 }
-                const int s = i & 1;
-                ok = mbar_wait(ds_full + 8 * s, (i >> 1) & 1, status, 35);
+                const int s = i % DKV_RING_N, b = i & 1;
+                ok = mbar_wait(qn_full + 8 * s, (i / DKV_RING_N) & 1, status, 34);
+                if (!ok) break;
+                ok = mbar_wait(ds_full + 8 * b, (i >> 1) & 1, status, 35);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t qn = st0 + s * DKV_STAGE + 2 * T64, don = qn + T64;
+                const uint32_t qn = ringN + s * 2 * T64, don = qn + T64;
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + s * 128 + kk * 8, ndesc(don, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + b * 128 + kk * 8, ndesc(don, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + s * 128 + 64 + kk * 8, ndesc(qn, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(q_empty + 8 * s);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, ndesc(qn, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(qn_empty + 8 * s);
             }
             umma_commit(acc_full);
         }

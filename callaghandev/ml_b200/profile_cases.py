@@ -1,0 +1,64 @@
+"""Small, self-contained launches of the hot kernels, sized for a profiler capture (a few hundred MB on the device,
+a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>`` with case one of
+
+  attention   segmented causal attention forward + backward, 8 sequences x 1024 tokens, 16 heads of 64
+  gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
+  layernorm   LayerNorm forward + backward on 32768 x 1024
+"""
+import sys
+
+import numpy as np
+
+from . import CudaB200AccelerationManager, GEMM_AUTO
+
+
+def attention(m, rng):
+    L, S, d, H = 1024, 8, 1024, 16
+    Q, K, V, dO = (rng.normal(0, 1, (L * S, d)).astype(np.float32) for _ in range(4))
+    out = None
+    for _ in range(2):
+        m.SegmentedAttentionForward(Q, K, V, L, S, H, True)
+        out = m.SegmentedAttentionBackward(Q, K, V, dO, L, S, H, 0.125, True)
+    return float(np.abs(out[0]).mean())
+
+
+def gemm(m, rng):
+    rows, inp, out = 8192, 1024, 4096
+    x = rng.normal(0, 1, (rows, inp)).astype(np.float32)
+    W = rng.normal(0, 0.02, (out, inp)).astype(np.float32)
+    b = np.zeros(out, np.float32)
+    dy = rng.normal(0, 1, (rows, out)).astype(np.float32)
+    y = m.BatchDotProductAddBias(W, x, b)
+    wg, bg, di = np.zeros_like(W), np.zeros_like(b), np.zeros_like(x)
+    for _ in range(2):
+        m.BackpropLinearProjection(x, dy, W, wg, bg, di)
+    return float(np.abs(wg).mean()) + float(np.abs(y).mean())
+
+
+def layernorm(m, rng):
+    rows, f = 32768, 1024
+    x = rng.normal(0, 1, (rows, f)).astype(np.float32)
+    g, b = np.ones(f, np.float32), np.zeros(f, np.float32)
+    dOut = rng.normal(0, 1, (rows, f)).astype(np.float32)
+    r = None
+    for _ in range(2):
+        out, mean, var, normalized = m.LayerNormForward(x, g, b)
+        r = m.LayerNormBackward(dOut, normalized, g, x, mean, var)
+    return float(np.abs(r[0]).mean())
+
+
+CASES = {"attention": attention, "gemm": gemm, "layernorm": layernorm}
+
+
+def main(argv):
+    if len(argv) != 2 or argv[1] not in CASES:
+        print(__doc__)
+        return 2
+    m = CudaB200AccelerationManager(0, GEMM_AUTO)
+    print(argv[1], "ok", CASES[argv[1]](m, np.random.default_rng(0)))
+    m.Dispose()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv))
