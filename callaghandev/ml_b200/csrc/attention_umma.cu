@@ -45,6 +45,10 @@ struct UArgs {
 __device__ __forceinline__ uint32_t idesc_tf32(uint32_t M, uint32_t N, uint32_t a_mn, uint32_t b_mn) {
     return (1u << 4) | (2u << 7) | (2u << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
+// Descriptors are built once per kernel; inside the loops a K step or a ring slot is a constant added to the address
+// field (the MMA warp is a single thread, so every instruction it spends on descriptor arithmetic delays the pipe).
+__host__ __device__ constexpr uint64_t koff(int kk, int atom) { return (uint64_t)(((kk >> 2) * atom + (kk & 3) * 32) >> 4); }
+__host__ __device__ constexpr uint64_t noff(int kk) { return (uint64_t)((kk * 1024) >> 4); }
 // K-contiguous 128 x 64 tile (two swizzle atoms side by side): descriptor of K step kk (8 floats = 32 bytes)
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile, int kk) { return umma_desc(tile + (kk >> 2) * U_ATOM + (kk & 3) * 32, 16, 1024, 2); }
 // N-contiguous [128 K rows][64 N] tile stored as two 32-column chunks: descriptor of K step kk (8 rows = 1024 bytes)
@@ -139,13 +143,14 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         if (lane == 0) {
             // ---------------------------------------------------------------------------------- MMA issuer
             const uint32_t idS = idesc_tf32(UQ, UK, 0, 0), idO = idesc_tf32(UQ, UHD, 0, 1);
+            const uint64_t dQ0 = kmajor_desc(Qs, 0), dK0 = kmajor_desc(Ks, 0), dV0 = nmajor_desc(Vs, 0);
             bool ok = mbar_wait(q_full, 0, status, 13);
             for (int j = 0; j < nkt && ok; j++) {
                 ok = mbar_wait(k_full, j & 1, status, 14);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < UHD / 8; kk++) umma_tf32(tmem_base + S_COL, kmajor_desc(Qs, kk), kmajor_desc(Ks, kk), idS, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < UHD / 8; kk++) umma_tf32(tmem_base + S_COL, dQ0 + koff(kk, U_ATOM), dK0 + koff(kk, U_ATOM), idS, kk > 0 ? 1u : 0u);
                 umma_commit(k_empty);
                 umma_commit(s_full);
                 ok = mbar_wait(p_full, j & 1, status, 15);
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < UK / 8; kk++)
-                    umma_tf32_ta(tmem_base + O_COL, tmem_base + S_COL + kk * 8, nmajor_desc(Vs, kk), idO, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_tf32_ta(tmem_base + O_COL, tmem_base + S_COL + kk * 8, dV0 + noff(kk), idO, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(v_empty);
             }
             umma_commit(o_full);
@@ -170,7 +175,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nkt; j++) {
-            ok = mbar_wait(s_full, j & 1, status, 17);
+            ok = mbar_wait_warp(s_full, j & 1, status, 17);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             mbar_arrive(p_full);
         }
         if (ok) {
-            ok = mbar_wait(o_full, 0, status, 18);
+            ok = mbar_wait_warp(o_full, 0, status, 18);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
@@ -276,9 +281,10 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
 // statistics are known, so the element-wise step has no row reduction and is split over eight warps (lane quarter x
 // column half).  The inner tiles are 64 wide and S/dP are double-buffered in TMEM: the MMA warp issues the S and dP
 // products of tile j+1 while the element-wise warps turn tile j into P and dS, then issues the products that consume
-// them.  An operand that is needed both K-contiguous (for S / dP) and N-contiguous (for dQ, dK, dV) is loaded twice,
-// once per shared-memory image; the second read comes from L2.
-constexpr int B_THREADS = 64 + 256;
+// them.  These kernels are bound by the L2 -> shared-memory traffic of the streamed tiles (FP32 storage, 64-wide
+// heads), so an operand that is needed both K-contiguous (for S / dP) and N-contiguous (for dQ, dK, dV) is loaded
+// once, K-contiguous, and four extra warps rewrite it into the N-contiguous swizzle image inside shared memory.
+constexpr int B_THREADS = 64 + 256 + 128;  // producer, MMA issuer, 8 element-wise warps, 4 re-swizzle warps
 constexpr int A128 = 128 * 128, T128 = 2 * A128;  // atom column / tile with 128 rows
 constexpr int A64 = 64 * 128, T64 = 2 * A64;      // atom column / tile with 64 rows
 // Streamed operands live in two rings per kernel, because their consumers differ: the K-contiguous images feed the
@@ -303,6 +309,40 @@ __device__ __forceinline__ bool ew_barrier_or(bool pred) {
     return r != 0;
 }
 
+// Copy a [64 x 64] FP32 tile (two 32-column atoms of 64 rows x 128 bytes) from the K-contiguous image (16-byte chunks
+// XOR row%8, what TMA SWIZZLE_128B writes) to the N-contiguous image (32-byte chunks XOR row%4, what the UMMA layout
+// "128-byte swizzle, 32-byte atoms" reads).  128 threads, eight 16-byte chunks each, conflict-free on both sides.
+__device__ __forceinline__ void reswizzle_tile(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int t) {
+#pragma unroll
+    for (int it = 0; it < 8; it++) {
+        const int idx = it * 128 + t;
+        const int atom = idx >> 9, r = (idx >> 3) & 63, q = idx & 7;
+        const uint4 v = *reinterpret_cast<const uint4*>(src + atom * A64 + r * 128 + ((q ^ (r & 7)) << 4));
+        *reinterpret_cast<uint4*>(dst + atom * A64 + r * 128 + ((((q >> 1) ^ (r & 3)) << 5) | ((q & 1) << 4))) = v;
+    }
+}
+
+#ifdef B200_ATTN_TRACE
+// Development aid: clock64() time stamps of the first CTA's roles, [role][tile][event].
+__device__ long long g_attn_trace[4 * 32 * 8];
+#define TR(role, tile, ev) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) g_attn_trace[((role) * 32 + (tile)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define TR(role, tile, ev) do { } while (0)
+#endif
+
+// Copy one row of a K-contiguous swizzle atom (32 floats, already TF32) into TMEM columns [col, col+32) of the calling
+// thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand read from
+// shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
+__device__ __forceinline__ void row_to_tmem(const uint8_t* atom, int row, uint32_t taddr) {
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+        const uint4 v = *reinterpret_cast<const uint4*>(atom + row * 128 + ((c ^ (row & 7)) << 4));
+        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+    }
+    tmem_st32(taddr, r);
+}
+
 struct UBwdArgs {
     float *dQ, *dK, *dV;
     int lddq, lddk, lddv;
@@ -323,7 +363,7 @@ __device__ __forceinline__ void store_rows(const float* stage, float* dst, int l
 
 __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
                                                                 const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
-                                                                const __grid_constant__ CUtensorMap mapKn, UBwdArgs a) {
+                                                                UBwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const AttnSeg sg = a.segs[blockIdx.z];
     const int head = blockIdx.y;
@@ -340,18 +380,19 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DQ_RING_N * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 18);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 19);
     const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128;
     const uint32_t ringK = dOs + T128;                 // slot: K tile then V tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: K tile, N-contiguous
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t qdo_full = bar0, kk_full = bar0 + 8, kk_empty = bar0 + 32, kn_full = bar0 + 56, kn_empty = bar0 + 80, sdp_full = bar0 + 104,
-                   ds_full = bar0 + 120, dq_full = bar0 + 136;
+                   ds_full = bar0 + 120, dq_full = bar0 + 136, a_ready = bar0 + 144;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 18; i++) mbar_init(bar0 + 8 * i, (i == 15 || i == 16) ? 256 : 1);
+        for (int i = 0; i < 19; i++)  // a_ready: 256; kk_empty: MMA commit + 128 re-swizzle readers; kn_full: 128 re-swizzle writers; ds_full: 256
+            mbar_init(bar0 + 8 * i, (i == 15 || i == 16 || i == 18) ? 256 : (i >= 4 && i <= 6) ? 129 : (i >= 7 && i <= 9) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -363,7 +404,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = *tmem_slot;
-    constexpr uint32_t DQ_COL = 256;
+    constexpr uint32_t DQ_COL = 256, QA_COL = 320, DOA_COL = 384;  // Q and dO live in TMEM as A operands
 
     if (warp == 0) {
         if (lane == 0) {
@@ -374,55 +415,50 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             tma_load_2d(dOs, &mapdO, qdo_full, col, sg.qStart + q0);
             tma_load_2d(dOs + A128, &mapdO, qdo_full, col + 32, sg.qStart + q0);
             bool ok = true;
-            int nk = 0, nn = 0;  // next tile to load into each ring
-            while (nk < nkt || nn < nkt) {
-                if (nk < nkt && nk < nn + RING_K) {
-                    const int s = nk % RING_K, row = sg.kStart + nk * 64;
-                    ok = mbar_wait(kk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 21);
-                    if (!ok) break;
-                    const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
-                    mbar_expect_tx(bar, 2 * T64);
-                    tma_load_2d(base, &mapK, bar, col, row);
-                    tma_load_2d(base + A64, &mapK, bar, col + 32, row);
-                    tma_load_2d(base + T64, &mapV, bar, col, row);
-                    tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
-                    nk++;
-                } else {
-                    const int s = nn % DQ_RING_N, row = sg.kStart + nn * 64;
-                    ok = mbar_wait(kn_empty + 8 * s, ((nn / DQ_RING_N) & 1) ^ 1, status, 28);
-                    if (!ok) break;
-                    const uint32_t base = ringN + s * T64, bar = kn_full + 8 * s;
-                    mbar_expect_tx(bar, T64);
-                    tma_load_2d(base, &mapKn, bar, col, row);
-                    tma_load_2d(base + A64, &mapKn, bar, col + 32, row);
-                    nn++;
-                }
+            int nk = 0;
+            for (; nk < nkt; nk++) {
+                const int s = nk % RING_K, row = sg.kStart + nk * 64;
+                ok = mbar_wait(kk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 21);
+                if (!ok) break;
+                TR(0, nk, 0);
+                const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
+                mbar_expect_tx(bar, 2 * T64);
+                tma_load_2d(base, &mapK, bar, col, row);
+                tma_load_2d(base + A64, &mapK, bar, col + 32, row);
+                tma_load_2d(base + T64, &mapV, bar, col, row);
+                tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
                 while (!mbar_test(qdo_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
                 for (int j = max(0, nk - RING_K); j < nk; j++)
                     while (!mbar_test(kk_full + 8 * (j % RING_K), (j / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int j = max(0, nn - DQ_RING_N); j < nn; j++)
-                    while (!mbar_test(kn_full + 8 * (j % DQ_RING_N), (j / DQ_RING_N) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            bool ok = mbar_wait(qdo_full, 0, status, 22);
+            const uint64_t dRK0 = kdesc(ringK, 0, A64), dRN0 = ndesc(ringN, 0, A64);
+            bool ok = mbar_wait(a_ready, 0, status, 22);
+            tc_fence_after();
             auto issue_sdp = [&](int j) {  // S(j) and dP(j) into TMEM buffer j&1; frees the K-contiguous slot when they complete
                 const int s = j % RING_K, b = j & 1;
+                TR(1, j, 0);
                 ok = mbar_wait(kk_full + 8 * s, (j / RING_K) & 1, status, 23);
                 if (!ok) return;
+                TR(1, j, 1);
                 tc_fence_after();
-                const uint32_t base = ringK + s * 2 * T64;
+                const uint64_t dk = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dv = dk + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128, kdesc(Qs, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + QA_COL + kk * 8, dk + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                TR(0, j, 1);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128 + 64, kdesc(dOs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + DOA_COL + kk * 8, dv + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                TR(0, j, 2);
                 umma_commit(kk_empty + 8 * s);
+                TR(0, j, 3);
                 umma_commit(sdp_full + 8 * b);
+                TR(1, j, 2);
             };
             if (ok) issue_sdp(0);
             for (int j = 0; j < nkt && ok; j++) {
@@ -433,17 +469,24 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 const int s = j % DQ_RING_N, b = j & 1;
                 ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 24);
                 if (!ok) break;
+                TR(1, j, 3);
                 ok = mbar_wait(ds_full + 8 * b, (j >> 1) & 1, status, 25);
                 if (!ok) break;
+                TR(1, j, 4);
                 tc_fence_after();
-                const uint32_t kn = ringN + s * T64;
+                const uint64_t dn = dRN0 + (uint64_t)(s * (T64 >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, ndesc(kn, kk, A64), idN, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 4; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
+                TR(0, j, 4);
+#pragma unroll
+                for (int kk = 4; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, 1u);
+                TR(0, j, 5);
                 umma_commit(kn_empty + 8 * s);
+                TR(1, j, 5);
             }
             umma_commit(dq_full);
         }
-    } else {
+    } else if (warp < 10) {
         const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half;
         const int row = 32 * quarter + lane, qi = q0 + row;
         const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
@@ -456,18 +499,28 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             D = a.rowDot[idx];
         }
         const int lim = il > 0.f ? (a.causal ? min(sg.kLen, qi + 1) : sg.kLen) : 0;  // keys [0, lim) are visible to this row
-        bool ok = true;
+        bool ok = mbar_wait_warp(qdo_full, 0, status, 20);
+        if (__all_sync(0xffffffffu, ok)) {  // move this thread's half rows of Q and dO into TMEM
+            row_to_tmem(tiles + half * A128, row, tlane + QA_COL + c0);
+            row_to_tmem(tiles + T128 + half * A128, row, tlane + DOA_COL + c0);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(a_ready);
+        }
         for (int j = 0; j < nkt; j++) {
             const int s = j & 1;
-            ok = mbar_wait(sdp_full + 8 * s, (j >> 1) & 1, status, 26);
+            if (threadIdx.x == 64) TR(2, j, 0);
+            ok = mbar_wait_warp(sdp_full + 8 * s, (j >> 1) & 1, status, 26);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (threadIdx.x == 64) TR(2, j, 1);
             tc_fence_after();
             const int nvis = lim - j * 64 - c0;  // columns [0, nvis) of this warp's 32 are visible
             uint32_t sr[32], pr[32];
             tmem_ld32_nowait(tlane + s * 128 + c0, sr);
             tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
             tmem_ld_wait();
+            if (threadIdx.x == 64) TR(2, j, 2);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
                 float v = fmaf(__uint_as_float(sr[i]), sl2, -m2);
@@ -476,12 +529,14 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 sr[i] = rna_tf32(p * (__uint_as_float(pr[i]) - D));
             }
             tmem_st32(tlane + s * 128 + c0, sr);
+            if (threadIdx.x == 64) TR(2, j, 3);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(ds_full + 8 * s);
+            if (threadIdx.x == 64) TR(2, j, 4);
         }
         if (ok) {
-            ok = mbar_wait(dq_full, 0, status, 27);
+            ok = mbar_wait_warp(dq_full, 0, status, 27);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
@@ -497,6 +552,23 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         }
         ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
         if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64);
+    } else {
+        // ------------------------------------------------------------------------------ re-swizzle warps: K -> N-contiguous image
+        const int t = threadIdx.x - 320;
+        uint8_t* ringK_p = tiles + 2 * T128;
+        uint8_t* ringN_p = ringK_p + RING_K * 2 * T64;
+        for (int j = 0; j < nkt; j++) {
+            const int sk = j % RING_K, sn = j % DQ_RING_N;
+            if (!mbar_wait_warp(kk_full + 8 * sk, (j / RING_K) & 1, status, 29)) break;
+            if (t == 0) TR(3, j, 0);
+            if (!mbar_wait_warp(kn_empty + 8 * sn, ((j / DQ_RING_N) & 1) ^ 1, status, 30)) break;
+            if (t == 0) TR(3, j, 1);
+            reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * T64, t);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+            mbar_arrive(kn_full + 8 * sn);
+            mbar_arrive(kk_empty + 8 * sk);
+            if (t == 0) TR(3, j, 2);
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -511,7 +583,6 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
 //   dV += P^T dO,  dK += dS^T Q   (A from TMEM, Q / dO as N-contiguous shared-memory operands)
 __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                                                                  const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
-                                                                 const __grid_constant__ CUtensorMap mapQn, const __grid_constant__ CUtensorMap mapdOn,
                                                                  UBwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const AttnSeg sg = a.segs[blockIdx.z];
@@ -532,19 +603,20 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DKV_RING_N * 2 * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
     float* stats = reinterpret_cast<float*>(bars + 18);  // [2 buffers][m2 | il | D][64]
     const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128;
     const uint32_t ringK = Vs + T128;                  // slot: Q tile then dO tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: Q tile then dO tile, both N-contiguous
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t kv_full = bar0, qk_full = bar0 + 8, qk_empty = bar0 + 32, qn_full = bar0 + 56, qn_empty = bar0 + 72, sdp_full = bar0 + 88,
-                   ds_full = bar0 + 104, acc_full = bar0 + 120;
+                   ds_full = bar0 + 104, acc_full = bar0 + 120, a_ready = bar0 + 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 16; i++) mbar_init(bar0 + 8 * i, (i == 13 || i == 14) ? 256 : 1);
+        for (int i = 0; i < 17; i++)  // a_ready: 256; qk_empty: MMA commit + 128 re-swizzle readers; qn_full: 128 re-swizzle writers; ds_full: 256
+            mbar_init(bar0 + 8 * i, (i == 13 || i == 14 || i == 16) ? 256 : (i >= 4 && i <= 6) ? 129 : (i == 7 || i == 8) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -556,7 +628,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = *tmem_slot;
-    constexpr uint32_t DV_COL = 256, DK_COL = 320;
+    constexpr uint32_t DV_COL = 256, DK_COL = 320, KA_COL = 384, VA_COL = 448;  // K and V live in TMEM as A operands
 
     if (warp == 0) {
         if (lane == 0) {
@@ -567,55 +639,41 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             tma_load_2d(Vs, &mapV, kv_full, col, sg.kStart + k0);
             tma_load_2d(Vs + A128, &mapV, kv_full, col + 32, sg.kStart + k0);
             bool ok = true;
-            int nk = 0, nn = 0;  // next tile to load into each ring
-            while (nk < nqt || nn < nqt) {
-                if (nk < nqt && nk < nn + RING_K) {
-                    const int s = nk % RING_K, row = sg.qStart + (qtBegin + nk) * 64;
-                    ok = mbar_wait(qk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 31);
-                    if (!ok) break;
-                    const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
-                    mbar_expect_tx(bar, 2 * T64);
-                    tma_load_2d(base, &mapQ, bar, col, row);
-                    tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
-                    tma_load_2d(base + T64, &mapdO, bar, col, row);
-                    tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
-                    nk++;
-                } else {
-                    const int s = nn % DKV_RING_N, row = sg.qStart + (qtBegin + nn) * 64;
-                    ok = mbar_wait(qn_empty + 8 * s, ((nn / DKV_RING_N) & 1) ^ 1, status, 38);
-                    if (!ok) break;
-                    const uint32_t base = ringN + s * 2 * T64, bar = qn_full + 8 * s;
-                    mbar_expect_tx(bar, 2 * T64);
-                    tma_load_2d(base, &mapQn, bar, col, row);
-                    tma_load_2d(base + A64, &mapQn, bar, col + 32, row);
-                    tma_load_2d(base + T64, &mapdOn, bar, col, row);
-                    tma_load_2d(base + T64 + A64, &mapdOn, bar, col + 32, row);
-                    nn++;
-                }
+            int nk = 0;
+            for (; nk < nqt; nk++) {
+                const int s = nk % RING_K, row = sg.qStart + (qtBegin + nk) * 64;
+                ok = mbar_wait(qk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 31);
+                if (!ok) break;
+                const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
+                mbar_expect_tx(bar, 2 * T64);
+                tma_load_2d(base, &mapQ, bar, col, row);
+                tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
+                tma_load_2d(base + T64, &mapdO, bar, col, row);
+                tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
                 while (!mbar_test(kv_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
                 for (int i = max(0, nk - RING_K); i < nk; i++)
                     while (!mbar_test(qk_full + 8 * (i % RING_K), (i / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int i = max(0, nn - DKV_RING_N); i < nn; i++)
-                    while (!mbar_test(qn_full + 8 * (i % DKV_RING_N), (i / DKV_RING_N) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            bool ok = mbar_wait(kv_full, 0, status, 32);
+            const uint64_t dRK0 = kdesc(ringK, 0, A64), dRN0 = ndesc(ringN, 0, A64);
+            bool ok = mbar_wait(a_ready, 0, status, 32);
+            tc_fence_after();
             auto issue_sdp = [&](int i) {  // S^T(i) and dP^T(i) into TMEM buffer i&1; frees the K-contiguous slot when they complete
                 const int s = i % RING_K, b = i & 1;
                 ok = mbar_wait(qk_full + 8 * s, (i / RING_K) & 1, status, 33);
                 if (!ok) return;
                 tc_fence_after();
-                const uint32_t base = ringK + s * 2 * T64;
+                const uint64_t dq = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dd = dq + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128, kdesc(Ks, kk, A128), kdesc(base, kk, A64), idS, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + KA_COL + kk * 8, dq + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32(tm + b * 128 + 64, kdesc(Vs, kk, A128), kdesc(base + T64, kk, A64), idS, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + VA_COL + kk * 8, dd + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
                 umma_commit(qk_empty + 8 * s);
                 umma_commit(sdp_full + 8 * b);
             };
@@ -631,21 +689,28 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
                 ok = mbar_wait(ds_full + 8 * b, (i >> 1) & 1, status, 35);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t qn = ringN + s * 2 * T64, don = qn + T64;
+                const uint64_t dqn = dRN0 + (uint64_t)(s * ((2 * T64) >> 4)), ddn = dqn + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + b * 128 + kk * 8, ndesc(don, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + b * 128 + kk * 8, ddn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, ndesc(qn, kk, A64), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, dqn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(qn_empty + 8 * s);
             }
             umma_commit(acc_full);
         }
-    } else {
+    } else if (warp < 10) {
         const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half, tid = threadIdx.x - 64;
         const int row = 32 * quarter + lane, kj = k0 + row;
         const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
         const float sl2 = a.scale * LOG2E_F;
-        bool ok = true;
+        bool ok = mbar_wait_warp(kv_full, 0, status, 30);
+        if (__all_sync(0xffffffffu, ok)) {  // move this thread's half rows of K and V into TMEM
+            row_to_tmem(tiles + half * A128, row, tlane + KA_COL + c0);
+            row_to_tmem(tiles + T128 + half * A128, row, tlane + VA_COL + c0);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(a_ready);
+        }
         for (int i = 0; i < nqt; i++) {
             const int s = i & 1, qbase = (qtBegin + i) * 64;
             float* st = stats + s * 192;
@@ -660,7 +725,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
                 }
                 st[tid] = m2; st[64 + tid] = il; st[128 + tid] = D;
             }
-            ok = mbar_wait(sdp_full + 8 * s, (i >> 1) & 1, status, 36);
+            ok = mbar_wait_warp(sdp_full + 8 * s, (i >> 1) & 1, status, 36);
             if (ew_barrier_or(!ok)) {  // publishes the statistics; a failed wait anywhere stops all 256 threads together
                 ok = false;
                 break;
@@ -694,7 +759,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             mbar_arrive(ds_full + 8 * s);
         }
         if (ok) {
-            ok = mbar_wait(acc_full, 0, status, 37);
+            ok = mbar_wait_warp(acc_full, 0, status, 37);
             ok = __all_sync(0xffffffffu, ok);
         }
         float* stageV = reinterpret_cast<float*>(tiles);                 // every MMA has completed: K and V tiles are free
@@ -719,6 +784,21 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             const int nRows = min(128, sg.kLen - k0);
             store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
             store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid);
+        }
+    } else {
+        // ------------------------------------------------------------------------------ re-swizzle warps: Q, dO -> N-contiguous images
+        const int t = threadIdx.x - 320;
+        uint8_t* ringK_p = tiles + 2 * T128;
+        uint8_t* ringN_p = ringK_p + RING_K * 2 * T64;
+        for (int i = 0; i < nqt; i++) {
+            const int sk = i % RING_K, sn = i % DKV_RING_N;
+            if (!mbar_wait_warp(qk_full + 8 * sk, (i / RING_K) & 1, status, 39)) break;
+            if (!mbar_wait_warp(qn_empty + 8 * sn, ((i / DKV_RING_N) & 1) ^ 1, status, 40)) break;
+            reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * 2 * T64, t);
+            reswizzle_tile(ringK_p + sk * 2 * T64 + T64, ringN_p + sn * 2 * T64 + T64, t);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+            mbar_arrive(qn_full + 8 * sn);
+            mbar_arrive(qk_empty + 8 * sk);
         }
     }
     tc_fence_before();
@@ -781,7 +861,7 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     B200_TRY(configure(ctx));
     const uint64_t cols = (uint64_t)t.numHeads * UHD;
     const uint64_t nq = (uint64_t)t.totalQ, nk = (uint64_t)t.totalK;
-    CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64, qn64, don64, kn64;
+    CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
     B200_TRY(make_map(ctx, &q128, t.Q, cols, nq, (uint64_t)t.ldq, 128, false));
     B200_TRY(make_map(ctx, &do128, t.dO, cols, nq, (uint64_t)t.lddo, 128, false));
     B200_TRY(make_map(ctx, &k128, t.K, cols, nk, (uint64_t)t.ldk, 128, false));
@@ -790,9 +870,6 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     B200_TRY(make_map(ctx, &do64, t.dO, cols, nq, (uint64_t)t.lddo, 64, false));
     B200_TRY(make_map(ctx, &k64, t.K, cols, nk, (uint64_t)t.ldk, 64, false));
     B200_TRY(make_map(ctx, &v64, t.V, cols, nk, (uint64_t)t.ldv, 64, false));
-    B200_TRY(make_map(ctx, &qn64, t.Q, cols, nq, (uint64_t)t.ldq, 64, true));
-    B200_TRY(make_map(ctx, &don64, t.dO, cols, nq, (uint64_t)t.lddo, 64, true));
-    B200_TRY(make_map(ctx, &kn64, t.K, cols, nk, (uint64_t)t.ldk, 64, true));
     UBwdArgs a;
     a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
     a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
@@ -801,10 +878,10 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
     B200_LAUNCH_CHECK(ctx);
     dim3 gk((t.maxKLen + 127) / 128, t.numHeads, t.nSeg);
-    attn_dkv_umma_kernel<<<gk, B_THREADS, DKV_SMEM, ctx->stream>>>(k128, v128, q64, do64, qn64, don64, a);
+    attn_dkv_umma_kernel<<<gk, B_THREADS, DKV_SMEM, ctx->stream>>>(k128, v128, q64, do64, a);
     B200_LAUNCH_CHECK(ctx);
     dim3 gq((t.maxQLen + 127) / 128, t.numHeads, t.nSeg);
-    attn_dq_umma_kernel<<<gq, B_THREADS, DQ_SMEM, ctx->stream>>>(q128, do128, k64, v64, kn64, a);
+    attn_dq_umma_kernel<<<gq, B_THREADS, DQ_SMEM, ctx->stream>>>(q128, do128, k64, v64, a);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -826,3 +903,9 @@ int attn_forward_umma(b200_ctx* ctx, const Attn& t) {
 }
 
 }  // namespace b200
+
+#ifdef B200_ATTN_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_debug_attn_trace(long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, b200::g_attn_trace, sizeof(long long) * (size_t)n);
+}
+#endif
