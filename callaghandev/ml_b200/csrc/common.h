@@ -37,7 +37,8 @@ struct b200_ctx {
     void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
-    int gemm_tc_configured = 0, attn_umma_configured = 0;  // dynamic shared memory attributes set
+    int gemm_tc_configured = 0, attn_umma_configured = 0;
+    int gemm_tile_n = 0;  // 0 = choose; 128 forces the narrow tcgen05 tile (set from B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;

@@ -15,6 +15,8 @@
 //
 // Every wait on an mbarrier is bounded by a clock budget: on expiry the kernel raises a status word in host-mapped
 // memory, drains the copies it still has in flight (bounded again), frees its TMEM and returns.
+#include <cstdlib>
+
 #include "tcgen05.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -22,9 +24,18 @@ namespace b200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
-constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int BM = 128, BK = 32;
+constexpr int A_BYTES = BM * BK * 4;
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 132 * 4;  // epilogue staging: 4 warps x 32 rows x EPI_STRIDE floats
+// Tile configurations: 128 x 128 with three stages (two CTAs per SM), or 128 x 256 with four stages (one CTA per SM).
+// A TF32 MMA with operands in shared memory reads (128 + N) x 32 bytes per K step of 8; at N = 128 that already equals
+// the shared-memory bandwidth of the SM, and the TMA writes of the next stage come on top, so the wide tile (which
+// reads 25% less shared memory per flop) is preferred whenever N allows it.
+template <int BN_> struct TileCfg {
+    static constexpr int STAGES = BN_ == 256 ? 3 : 4;
+    static constexpr int B_BYTES = BN_ * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 16;
 
@@ -32,8 +43,9 @@ struct TcParams {
     int M, N, K;
     int a_mn_major, b_mn_major;  // 0: K contiguous (one box per stage); 1: M/N contiguous (32-column boxes)
     int* status;                 // host-mapped status word
-    int kb_per_split;            // K blocks handled by one blockIdx.y (split-K); all of them when gridDim.y == 1
+    int kb_per_split;            // K blocks handled by one work item (split-K); all of them without a split
     long long split_stride;      // elements between the partial outputs of consecutive splits
+    int items;                   // work items of the persistent schedule: C tiles x K splits
 };
 
 // Epilogue kinds.  GENERIC handles every field of Epilogue element by element.  The other three are the shapes the
@@ -48,31 +60,42 @@ constexpr int EPI_STRIDE = 132;  // floats per staged row: 16-byte aligned and c
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 
-template <int EPI>
-__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+// Decode a work item (tile of C, K split) of the persistent schedule.  Tiles: bands of GROUP_M row-tiles are walked
+// column by column, so the CTAs working at one time share a few A bands and B panels through L2 instead of streaming
+// the whole B operand once per row-tile.
+template <int BN>
+__device__ __forceinline__ void decode_item(const TcParams& p, int item, int& m0, int& n0, int& split) {
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+    const int tiles = tiles_m * tiles_n;
+    split = item / tiles;
+    const int tile = item - split * tiles;
+    const int per_group = GROUP_M * tiles_n;
+    const int group = tile / per_group, first_m = group * GROUP_M;
+    const int gm = min(tiles_m - first_m, GROUP_M);
+    const int r = tile - group * per_group;
+    m0 = (first_m + r % gm) * BM;
+    n0 = (r / gm) * BN;
+}
+
+// Persistent kernel: one CTA per SM walks work items blockIdx.x, blockIdx.x + gridDim.x, ...  The operand ring and
+// the two TMEM accumulators are shared by consecutive items, so the producer keeps loading and the MMA warp keeps
+// issuing across item boundaries while the epilogue warps drain the previous accumulator.
+template <int EPI, int BN>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                                TcParams p, Epilogue ep) {
+    constexpr int STAGES = TileCfg<BN>::STAGES, STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles must start on 1024-byte boundaries
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(tiles + STAGES * STAGE_BYTES);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    float* epi_stage = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES);  // 4 warps x 32 rows x EPI_STRIDE floats
+    uint64_t* bars = (uint64_t*)(tiles + STAGES * STAGE_BYTES + EPI_STAGE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     const uint32_t tiles_s = smem_u32(tiles);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum_bar = smem_u32(bars + 2 * STAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), acc_full0 = smem_u32(bars + 2 * STAGES),
+                   acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Tile order: bands of GROUP_M row-tiles are walked column by column, so the CTAs resident at one time share a few
-    // A bands and B panels through L2 instead of streaming the whole B operand once per row-tile.
-    int m0, n0;
-    {
-        const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-        const int per_group = GROUP_M * tiles_n;
-        const int group = blockIdx.x / per_group, first_m = group * GROUP_M;
-        const int gm = min(tiles_m - first_m, GROUP_M);
-        const int r = blockIdx.x - group * per_group;
-        m0 = (first_m + r % gm) * BM;
-        n0 = (r / gm) * BN;
-    }
-    const int kb_begin = blockIdx.y * p.kb_per_split;
-    const int kblocks = min((p.K + BK - 1) / BK - kb_begin, p.kb_per_split);  // K blocks of this split
+    const int kblocks_total = (p.K + BK - 1) / BK;
+    const int n_items = p.items;
     volatile int* status = p.status;
 
     if (threadIdx.x == 0) {
@@ -80,12 +103,261 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM: two accumulators of BN fp32 columns x 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            int kc = 0;  // K blocks loaded so far, over all items: ring position and phase
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                int m0, n0, split;
+                decode_item<BN>(p, item, m0, n0, split);
+                const int kb_begin = split * p.kb_per_split;
+                const int kblocks = min(kblocks_total - kb_begin, p.kb_per_split);
+                for (int kb = 0; kb < kblocks; kb++, kc++) {
+                    const int s = kc % STAGES;
+                    ok = mbar_wait(empty0 + 8 * s, ((kc / STAGES) & 1) ^ 1, status, 1);  // first pass over the ring finds every slot empty
+                    if (!ok) break;
+                    const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    const int k0 = (kb_begin + kb) * BK;
+                    if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
+                    else
+                        for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * (BK * 128), &mapA, bar, m0 + 32 * c, k0);
+                    if (!p.b_mn_major) tma_load_2d(b_dst, &mapB, bar, k0, n0);
+                    else
+                        for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
+                }
+            }
+            if (!ok) {
+                // failure path: wait (bounded) until the copies already issued have landed before the CTA may exit
+                for (int k = (kc > STAGES ? kc - STAGES : 0); k < kc; k++) {
+                    const long long t0 = clock64();
+                    while (!mbar_test(full0 + 8 * (k % STAGES), (k / STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ MMA issuer
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major: rows 128 B apart, 8-row groups 1024 B apart (SBO), 32 B per K=8 step inside the swizzle row.
+            // MN-major: 32-column chunks BK*128 B apart (LBO), K rows 128 B apart in groups of 4 rows, groups 512 B
+            //           apart (SBO); one K=8 step is two groups = 1024 B.
+            // The descriptors of stage 0 are built once; a stage or a K step only adds to the address field.
+            const uint64_t a_d0 = umma_desc(tiles_s, p.a_mn_major ? BK * 128 : 16, p.a_mn_major ? 512 : 1024, p.a_mn_major ? 1 : 2);
+            const uint64_t b_d0 = umma_desc(tiles_s + A_BYTES, p.b_mn_major ? BK * 128 : 16, p.b_mn_major ? 512 : 1024, p.b_mn_major ? 1 : 2);
+            const uint64_t a_step = p.a_mn_major ? (1024 >> 4) : (32 >> 4), b_step = p.b_mn_major ? (1024 >> 4) : (32 >> 4);
+            int kc = 0, it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, it++) {
+                int m0, n0, split;
+                decode_item<BN>(p, item, m0, n0, split);
+                const int kblocks = min(kblocks_total - split * p.kb_per_split, p.kb_per_split);
+                const int buf = it & 1;
+                ok = mbar_wait(acc_empty0 + 8 * buf, ((it >> 1) & 1) ^ 1, status, 4);  // the epilogue has drained this accumulator
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < kblocks; kb++, kc++) {
+                    const int s = kc % STAGES;
+                    ok = mbar_wait(full0 + 8 * s, (kc / STAGES) & 1, status, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t so = (uint64_t)(s * (STAGE_BYTES >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 8; kk++) umma_tf32(acc, a_d0 + so + kk * a_step, b_d0 + so + kk * b_step, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                }
+                umma_commit(acc_full0 + 8 * buf);  // accumulator complete (also issued on the failure path so nobody waits forever)
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------------- epilogue (warps 2..5)
+        const int q = warp & 3;  // this warp may touch TMEM lanes [32q, 32q+32)
+        float alpha = ep.alpha;
+        if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+        int it = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, it++) {
+            int m0, n0, split;
+            decode_item<BN>(p, item, m0, n0, split);
+            const int buf = it & 1;
+            const uint32_t acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(32 * q) << 16);
+            if (!mbar_wait_warp(acc_full0 + 8 * buf, (it >> 1) & 1, status, 3)) break;  // tcgen05.ld is warp-collective: the warp decides together
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // Each warp transposes its accumulator rows through its own padded staging slice, which turns "one row per
+            // thread" (the TMEM load shape) into "one row per warp instruction" and makes every global access of the
+            // epilogue a full line.  The accumulator is handed back to the MMA warp as soon as it has been read.
+            if (EPI == EPI_GENERIC) {
+                float* stage = epi_stage + q * (32 * EPI_STRIDE);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 < p.N) {
+                        uint32_t r[32];
+                        tmem_ld32(acc + (uint32_t)c0, r);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) stage[lane * 33 + j] = __uint_as_float(r[j]);
+                    }
+                    if (c0 + 32 >= BN) {  // last chunk read: release the accumulator
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+                    }
+                    __syncwarp();
+                    const int n = n0 + c0 + lane;
+                    if (n0 + c0 < p.N && n < p.N) {
+#pragma unroll 4
+                        for (int rr = 0; rr < 32; rr++) {
+                            const int m = m0 + 32 * q + rr;
+                            if (m < p.M) epilogue_store(ep, m, n, stage[rr * 33 + lane], alpha);
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else {
+                float* stage = epi_stage + q * (32 * EPI_STRIDE);
+#pragma unroll 1
+                for (int h0 = 0; h0 < BN; h0 += 128) {  // 128 accumulator columns at a time
+                    __syncwarp();
+                    if (n0 + h0 < p.N) {
+#pragma unroll 1
+                        for (int c0 = 0; c0 < 128; c0 += 32) {
+                            uint32_t r[32];
+                            tmem_ld32(acc + (uint32_t)(h0 + c0), r);
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                st4(stage + lane * EPI_STRIDE + c0 + j,
+                                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+                        }
+                    }
+                    if (h0 + 128 >= BN) {  // last columns read: release the accumulator
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+                    }
+                    __syncwarp();
+                    const int n = n0 + h0 + 4 * lane;  // this lane's four columns of every row
+                    if (n0 + h0 < p.N && n < p.N) {    // N is a multiple of 4 on this path
+                        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
+                        const int rows = min(32, p.M - (m0 + 32 * q));
+                        // 8 rows per batch: all global loads of the batch are issued before any of them is consumed
+#pragma unroll 1
+                        for (int r0 = 0; r0 < rows; r0 += 8) {
+                            float4 ext[8], ext2[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const size_t m = (size_t)(m0 + 32 * q + r0 + i);
+                                ext[i] = ext2[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (r0 + i < rows) {
+                                    if (EPI == EPI_LINEAR) {
+                                        if (ep.accumulate) ext[i] = ld4(ep.C + m * ep.ldc + n);
+                                        if (ep.addmat) ext2[i] = ld4(ep.addmat + m * ep.ldadd + n);
+                                    } else if (EPI == EPI_MULZ) {
+                                        ext[i] = ld4(ep.mulz + m * ep.ldmulz + n);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                if (r0 + i >= rows) break;
+                                const size_t m = (size_t)(m0 + 32 * q + r0 + i);
+                                float4 v = ld4(stage + (r0 + i) * EPI_STRIDE + 4 * lane);
+                                if (EPI == EPI_LINEAR) {
+                                    v.x = alpha * v.x + b4.x + ext[i].x + ext2[i].x; v.y = alpha * v.y + b4.y + ext[i].y + ext2[i].y;
+                                    v.z = alpha * v.z + b4.z + ext[i].z + ext2[i].z; v.w = alpha * v.w + b4.w + ext[i].w + ext2[i].w;
+                                    if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+                                    st4(ep.C + (size_t)split * p.split_stride + m * ep.ldc + n, v);
+                                } else if (EPI == EPI_ACT) {
+                                    v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                                    st4(ep.zout + m * ep.ldz + n, v);
+                                    float d;
+                                    ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
+                                    ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
+                                    st4(ep.C + m * ep.ldc + n, v);
+                                } else {  // EPI_MULZ
+                                    float a, dx, dy, dz, dw;
+                                    ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
+                                    ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                                    v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
+                                    st4(ep.C + m * ep.ldc + n, v);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ one tile per CTA
+// 128 x 128 tile, three stages of 32 KiB, two CTAs per SM (one runs its epilogue while the other keeps the tensor pipe
+// busy).  Used for split-K and for long K, where it measures faster than the persistent kernel above.
+constexpr int T_BN = 128, T_STAGES = 3;
+constexpr int T_B_BYTES = T_BN * BK * 4, T_STAGE_BYTES = A_BYTES + T_B_BYTES;
+constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+template <int EPI>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                                               TcParams p, Epilogue ep) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles must start on 1024-byte boundaries
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + T_STAGES * T_STAGE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * T_STAGES + 1);
+    const uint32_t tiles_s = smem_u32(tiles);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + T_STAGES), accum_bar = smem_u32(bars + 2 * T_STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Tile order: bands of GROUP_M row-tiles are walked column by column, so the CTAs resident at one time share a few
+    // A bands and B panels through L2 instead of streaming the whole B operand once per row-tile.
+    int m0, n0;
+    {
+        const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + T_BN - 1) / T_BN;
+        const int per_group = GROUP_M * tiles_n;
+        const int group = blockIdx.x / per_group, first_m = group * GROUP_M;
+        const int gm = min(tiles_m - first_m, GROUP_M);
+        const int r = blockIdx.x - group * per_group;
+        m0 = (first_m + r % gm) * BM;
+        n0 = (r / gm) * T_BN;
+    }
+    const int kb_begin = blockIdx.y * p.kb_per_split;
+    const int kblocks = min((p.K + BK - 1) / BK - kb_begin, p.kb_per_split);  // K blocks of this split
+    volatile int* status = p.status;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T_STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM: BN fp32 accumulator columns x 128 lanes
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    if (warp == 1) {  // TMEM: T_BN fp32 accumulator columns x 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(T_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -99,26 +371,26 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             int issued = 0;
             bool ok = true;
             for (int kb = 0; kb < kblocks && ok; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t par = ((kb / STAGES) & 1) ^ 1;  // first pass over the ring finds every slot empty
+                const int s = kb % T_STAGES;
+                const uint32_t par = ((kb / T_STAGES) & 1) ^ 1;  // first pass over the ring finds every slot empty
                 ok = mbar_wait(empty0 + 8 * s, par, status, 1);
                 if (!ok) break;
-                const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
-                mbar_expect_tx(bar, STAGE_BYTES);
+                const uint32_t a_dst = tiles_s + s * T_STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
+                mbar_expect_tx(bar, T_STAGE_BYTES);
                 const int k0 = (kb_begin + kb) * BK;
                 if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
                 else
                     for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * (BK * 128), &mapA, bar, m0 + 32 * c, k0);
                 if (!p.b_mn_major) tma_load_2d(b_dst, &mapB, bar, k0, n0);
                 else
-                    for (int c = 0; c < BN / 32; c++) tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
+                    for (int c = 0; c < T_BN / 32; c++) tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
                 issued = kb + 1;
             }
             if (!ok) {
                 // failure path: wait (bounded) until the copies already issued have landed before the CTA may exit
-                for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; kb++) {
+                for (int kb = (issued > T_STAGES ? issued - T_STAGES : 0); kb < issued; kb++) {
                     const long long t0 = clock64();
-                    while (!mbar_test(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                    while (!mbar_test(full0 + 8 * (kb % T_STAGES), (kb / T_STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
                 }
             }
         }
@@ -126,7 +398,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
         if (lane == 0) {
             // ------------------------------------------------------------------ MMA issuer
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
-                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                                   ((uint32_t)(T_BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             // K-major: rows 128 B apart, 8-row groups 1024 B apart (SBO), 32 B per K=8 step inside the swizzle row.
             // MN-major: 32-column chunks BK*128 B apart (LBO), K rows 128 B apart in groups of 4 rows, groups 512 B
             //           apart (SBO); one K=8 step is two groups = 1024 B.
@@ -136,11 +408,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             const uint32_t a_step = p.a_mn_major ? 1024 : 32, b_step = p.b_mn_major ? 1024 : 32;
             bool ok = true;
             for (int kb = 0; kb < kblocks; kb++) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(full0 + 8 * s, (kb / STAGES) & 1, status, 2);
+                const int s = kb % T_STAGES;
+                ok = mbar_wait(full0 + 8 * s, (kb / T_STAGES) & 1, status, 2);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_s = tiles_s + s * STAGE_BYTES, b_s = a_s + A_BYTES;
+                const uint32_t a_s = tiles_s + s * T_STAGE_BYTES, b_s = a_s + A_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; kk++) {
                     const uint64_t ad = umma_desc(a_s + kk * a_step, a_lbo, a_sbo, a_lay);
@@ -166,7 +438,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             if (EPI == EPI_GENERIC) {
                 float* stage = reinterpret_cast<float*>(tiles) + q * (32 * 33);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = 0; c0 < T_BN; c0 += 32) {
                     if (n0 + c0 >= p.N) break;
                     uint32_t r[32];
                     tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
@@ -186,7 +458,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             } else {
                 float* stage = reinterpret_cast<float*>(tiles) + q * (32 * EPI_STRIDE);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = 0; c0 < T_BN; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
 #pragma unroll
@@ -251,7 +523,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(T_BN) : "memory");
     }
 }
 
@@ -326,16 +598,95 @@ bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
     return true;
 }
 
-int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
-    if (!gemm_tcgen05_eligible(ctx, g)) return fail(ctx, B200_ERR_UNSUPPORTED, "shape does not qualify for the tcgen05 GEMM");
-    B200_TRY(resolve_encode(ctx));
-    B200_TRY(ensure_status(ctx));
+namespace {
+template <int BN>
+int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
+    constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
+    static bool configured = false;  // per tile width; the attribute belongs to the function, not the context
+    if (!configured) {
+        configured = true;
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_GENERIC, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_ACT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_MULZ, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    }
+    CUtensorMap mapA, mapB;
+    // A: stored [M,K] (K contiguous) or [K,M] (M contiguous).  B: stored [N,K] (transB, K contiguous) or [K,N].
+    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BM, false));
+    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
+    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BN, false));
+    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
+    TcParams p;
+    p.M = g.M; p.N = g.N; p.K = g.K;
+    p.a_mn_major = g.transA ? 1 : 0;
+    p.b_mn_major = g.transB ? 0 : 1;
+    p.status = ctx->status_dev;
+    const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
+    const int kblocks_total = (g.K + BK - 1) / BK;
+    p.kb_per_split = kblocks_total;
+    p.split_stride = 0;
+    // Split-K for the weight-gradient shape (few output tiles, very long K): partial products go to a workspace and a
+    // second kernel adds them to C in split order, so the result does not depend on scheduling.
+    int splits = 1;
+    const bool plain = g.act == B200_ACT_NONE && !g.dout && !g.zout && !g.mulz && !g.mulmat && !g.addmat && !g.bias && g.sgd_lr == 0.f && !g.round_tf32;
+    if (plain && tiles < 2 * ctx->sm_count && kblocks_total >= 256 && (g.N % 4 == 0)) {
+        splits = (2 * ctx->sm_count + tiles - 1) / tiles;
+        if (splits > 8) splits = 8;
+        while (splits > 1 && (kblocks_total + splits - 1) / splits < 64) splits--;
+        p.kb_per_split = (kblocks_total + splits - 1) / splits;
+        splits = (kblocks_total + p.kb_per_split - 1) / p.kb_per_split;  // every split owns at least one K block
+    }
+    Epilogue e;
+    e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
+    e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
+    e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
+    p.items = tiles * splits;
+    const unsigned grid = (unsigned)(p.items < ctx->sm_count ? p.items : ctx->sm_count);  // persistent: one CTA per SM
+    if (splits > 1) {
+        B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));
+        p.split_stride = (long long)g.M * g.N;
+        e.C = ctx->ws; e.ldc = g.N; e.accumulate = 0; e.alpha = 1.f; e.alpha_dev = nullptr;
+        gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+        B200_LAUNCH_CHECK(ctx);
+        const int64_t count = (int64_t)g.M * g.N;
+        int blocks = (int)((count / 4 + 255) / 256);
+        if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+        splitk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->ws, splits, g.M, g.N, g.C, g.ldc, g.alpha, g.alpha_dev, g.accumulate);
+        B200_LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
+    // pick the epilogue kind
+    auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    const bool plain_act = g.act == B200_ACT_NONE && !g.dout && !g.zout;
+    const bool no_sgd = g.sgd_lr == 0.f && !g.mulmat;
+    const bool vec_c = (g.N % 4 == 0) && (g.ldc % 4 == 0) && a16(g.C) && (!g.bias || a16(g.bias));
+    int kind = EPI_GENERIC;
+    if (vec_c && no_sgd) {
+        if (plain_act && !g.mulz && (!g.addmat || (g.ldadd % 4 == 0 && a16(g.addmat)))) kind = EPI_LINEAR;
+        else if (g.zout && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
+                 g.ldz % 4 == 0 && a16(g.zout))
+            kind = EPI_ACT;
+        else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
+            kind = EPI_MULZ;
+    }
+    switch (kind) {
+        case EPI_LINEAR: gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_ACT: gemm_tcgen05_persistent_kernel<EPI_ACT, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_MULZ: gemm_tcgen05_persistent_kernel<EPI_MULZ, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        default: gemm_tcgen05_persistent_kernel<EPI_GENERIC, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+    }
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
+    constexpr int BN = T_BN, SMEM_BYTES = T_SMEM_BYTES;
     if (!ctx->gemm_tc_configured) {
         ctx->gemm_tc_configured = 1;
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI_MULZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_tile_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_tile_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_tile_kernel<EPI_ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_tile_kernel<EPI_MULZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     }
     CUtensorMap mapA, mapB;
     // A: stored [M,K] (K contiguous) or [K,M] (M contiguous).  B: stored [N,K] (transB, K contiguous) or [K,N].
@@ -373,7 +724,7 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
         B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));
         p.split_stride = (long long)g.M * g.N;
         e.C = ctx->ws; e.ldc = g.N; e.accumulate = 0; e.alpha = 1.f; e.alpha_dev = nullptr;
-        gemm_tcgen05_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+        gemm_tcgen05_tile_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
         B200_LAUNCH_CHECK(ctx);
         const int64_t count = (int64_t)g.M * g.N;
         int blocks = (int)((count / 4 + 255) / 256);
@@ -397,13 +748,31 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
             kind = EPI_MULZ;
     }
     switch (kind) {
-        case EPI_LINEAR: gemm_tcgen05_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        case EPI_ACT: gemm_tcgen05_kernel<EPI_ACT><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        case EPI_MULZ: gemm_tcgen05_kernel<EPI_MULZ><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        default: gemm_tcgen05_kernel<EPI_GENERIC><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_LINEAR: gemm_tcgen05_tile_kernel<EPI_LINEAR><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_ACT: gemm_tcgen05_tile_kernel<EPI_ACT><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_MULZ: gemm_tcgen05_tile_kernel<EPI_MULZ><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        default: gemm_tcgen05_tile_kernel<EPI_GENERIC><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
     }
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
+}
+
+
+}  // namespace
+
+int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
+    if (!gemm_tcgen05_eligible(ctx, g)) return fail(ctx, B200_ERR_UNSUPPORTED, "shape does not qualify for the tcgen05 GEMM");
+    B200_TRY(resolve_encode(ctx));
+    B200_TRY(ensure_status(ctx));
+    // Short K (where the epilogue and the pipeline fill are a large share of a tile): persistent kernel, wide tile
+    // when N allows.  Longer K and split-K: one tile per CTA -- there the persistent kernel, with a single CTA's
+    // three or four stages in flight per SM, measured slower and erratic (its CTAs advance in lock step and queue up
+    // on the same L2 lines), while two independent CTAs per SM drift apart and keep six stages in flight.
+    const int mode = ctx->gemm_tile_n;  // 0 = choose; 1 = always one tile per CTA; 128 / 256 = always persistent with that width
+    if (mode == 128) return gemm_tcgen05_persistent<128>(ctx, g);
+    if (mode == 256 && g.N >= 256) return gemm_tcgen05_persistent<256>(ctx, g);
+    if (mode == 0 && g.K <= 1024) return g.N >= 256 ? gemm_tcgen05_persistent<256>(ctx, g) : gemm_tcgen05_persistent<128>(ctx, g);
+    return gemm_tcgen05_tile(ctx, g);
 }
 
 }  // namespace b200
