@@ -393,14 +393,22 @@ int attn_forward(b200_ctx* ctx, const Attn& t) {
     if (t.headDim <= 128) return launch_fwd<128>(ctx, t);
     return fail(ctx, B200_ERR_UNSUPPORTED, "attention head dimension %d exceeds 128", t.headDim);
 }
-int attn_backward(b200_ctx* ctx, const Attn& t) {
-    if (t.nSeg <= 0 || t.numHeads <= 0) return B200_OK;
+static int attn_backward_engine(b200_ctx* ctx, const Attn& t) {
     if (attn_tc_eligible(ctx, t)) return attn_backward_tc(ctx, t);
     if (t.headDim <= 16) return launch_bwd<16>(ctx, t);
     if (t.headDim <= 32) return launch_bwd<32>(ctx, t);
     if (t.headDim <= 64) return launch_bwd<64>(ctx, t);
     if (t.headDim <= 128) return launch_bwd<128>(ctx, t);
     return fail(ctx, B200_ERR_UNSUPPORTED, "attention head dimension %d exceeds 128", t.headDim);
+}
+int attn_backward(b200_ctx* ctx, const Attn& t) {
+    if (t.nSeg <= 0 || t.numHeads <= 0) return B200_OK;
+    if (!t.rope_table || (attn_tc_eligible(ctx, t) && attn_umma_bwd_eligible(ctx, t))) return attn_backward_engine(ctx, t);  // fused, or nothing to rotate
+    Attn u = t;
+    u.rope_table = nullptr;
+    B200_TRY(attn_backward_engine(ctx, u));
+    B200_TRY(k_rope(ctx, t.dQ, 0, 1, t.totalQ, t.lddq, 0, t.numHeads, t.headDim, t.rope_table, t.rope_pos, 1, 0));
+    return k_rope(ctx, t.dK, 0, 1, t.totalK, t.lddk, 0, t.numHeads, t.headDim, t.rope_table, t.rope_pos, 1, 0);
 }
 
 }  // namespace b200

@@ -351,14 +351,26 @@ struct UBwdArgs {
     int numHeads, causal;
     float scale;
     int* status;
+    const float* rope_table; const int32_t* rope_pos;  // inverse rotary rotation of dQ and dK on the way out (or null)
 };
 
 // Store a [128 x 64] result staged in shared memory (row stride OUT_STRIDE) with whole-row 128-bit accesses; 256 threads.
-__device__ __forceinline__ void store_rows(const float* stage, float* dst, int ld, int rowBase, int nRows, int colBase, int tid) {
+__device__ __forceinline__ void store_rows(const float* stage, float* dst, int ld, int rowBase, int nRows, int colBase, int tid,
+                                           const float* rope_table = nullptr, const int32_t* rope_pos = nullptr) {
     const int c4 = (tid & 15) * 4;
 #pragma unroll 2
     for (int r = tid >> 4; r < 128; r += 16)
-        if (r < nRows) *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
+        if (r < nRows) {
+            float4 v = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
+            if (rope_table) {  // gradient of a rotation = rotation by the opposite angle
+                const int pos = rope_pos ? rope_pos[rowBase + r] : rowBase + r;
+                const float4 cs = *reinterpret_cast<const float4*>(rope_table + ((size_t)pos * (UHD / 2) + (c4 >> 1)) * 2);
+                const float x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
+                v.x = x0 * cs.x + x1 * cs.y; v.y = x1 * cs.x - x0 * cs.y;
+                v.z = x2 * cs.z + x3 * cs.w; v.w = x3 * cs.z - x2 * cs.w;
+            }
+            *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = v;
+        }
 }
 
 __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
@@ -551,7 +563,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                                 __uint_as_float(r[i + 3]) * a.scale);
         }
         ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
-        if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64);
+        if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64, a.rope_table, a.rope_pos);
     } else {
         // ------------------------------------------------------------------------------ re-swizzle warps: K -> N-contiguous image
         const int t = threadIdx.x - 320;
@@ -783,7 +795,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
         if (ok) {
             const int nRows = min(128, sg.kLen - k0);
             store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
-            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid);
+            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid, a.rope_table, a.rope_pos);
         }
     } else {
         // ------------------------------------------------------------------------------ re-swizzle warps: Q, dO -> N-contiguous images
@@ -873,7 +885,7 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     UBwdArgs a;
     a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
     a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
-    a.scale = t.scale; a.status = ctx->status_dev;
+    a.scale = t.scale; a.status = ctx->status_dev; a.rope_table = t.rope_table; a.rope_pos = t.rope_pos;
     const int warps = t.totalQ * t.numHeads;
     attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
     B200_LAUNCH_CHECK(ctx);

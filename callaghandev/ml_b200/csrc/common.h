@@ -104,11 +104,16 @@ struct Gemm {
     const float* addmat = nullptr; int ldadd = 0;
     float sgd_lr = 0.f, sgd_lambda = 0.f;
     int round_tf32 = 0;  // store the result rounded to TF32 (round-to-nearest): its only consumer is a TF32 tensor-core kernel
+    // Rotary position embedding applied to the result (after the bias) for columns [0, rope_cols): column pair
+    // (2i, 2i+1) of every head of width rope_head_dim is rotated by table[pos[row]][i] = (cos, sin).  Fused into the
+    // tcgen05 epilogue when the shape allows, otherwise run as a separate kernel after the GEMM.
+    const float* rope_table = nullptr; const int32_t* rope_pos = nullptr; int rope_cols = 0, rope_head_dim = 0;
 };
 int gemm(b200_ctx* ctx, const Gemm& g);            // picks the engine from ctx->gemm_mode and the shape
 int gemm_simt(b200_ctx* ctx, const Gemm& g);       // FP32 SIMT, any shape
 int gemm_tcgen05(b200_ctx* ctx, const Gemm& g);    // TF32 tcgen05/TMEM/TMA; B200_ERR_UNSUPPORTED if the shape does not qualify
 bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g);
+bool gemm_tcgen05_fuses_rope(b200_ctx* ctx, const Gemm& g);  // the rope_* fields would be applied inside the tcgen05 epilogue
 // Y[rows,outDim] (leading dim ldy) = X[rows,inDim] * W[outDim,inDim]^T + bias
 int linear_fwd(b200_ctx* ctx, const float* X, int rows, int inDim, const float* W, const float* bias, int outDim, float* Y, int ldy);
 // Wg[outDim,inDim] += dY^T X ; bg[outDim] += column sums of dY
@@ -176,6 +181,9 @@ struct Attn {
     float *dQ = nullptr, *dK = nullptr, *dV = nullptr; int lddq = 0, lddk = 0, lddv = 0;
     float* rowDot = nullptr;  // [totalQ, numHeads] scratch: sum_k dO*O
     int pre_rounded = 0;      // Q, K, V (and dO) already hold TF32-rounded values: tiles can be copied asynchronously as they are
+    // backward only: inverse rotary rotation of dQ and dK (table[pos[row]][i] = (cos, sin)), fused into the stores of
+    // the tcgen05 engine, a separate kernel behind the other engines
+    const float* rope_table = nullptr; const int32_t* rope_pos = nullptr;
 };
 int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-core kernels when attn_tc_eligible
 // TF32 mma.sync engine (head dimension <= 64, context not in FP32 mode)

@@ -18,12 +18,26 @@ struct Epilogue {
     const float* addmat; int ldadd;
     float sgd_lr, sgd_lambda;
     int round_tf32;
+    const float* rope_table; const int32_t* rope_pos; int rope_cols, rope_hd;
 };
 
 __device__ __forceinline__ float tf32_round(float x) {
     uint32_t u;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
     return __uint_as_float(u);
+}
+
+// Rotary embedding in the 128-bit epilogue: a lane owns columns n..n+3 (two pairs inside one head) of row m.
+// rope_cs fetches (cos0, sin0, cos1, sin1) for them -- issued with the other operand loads of a row batch, so its
+// latency is overlapped -- and rope_rotate applies the rotation.
+__device__ __forceinline__ float4 rope_cs(const Epilogue& e, int m, int n) {
+    const int pos = e.rope_pos ? e.rope_pos[m] : m;
+    return *reinterpret_cast<const float4*>(e.rope_table + ((size_t)pos * (e.rope_hd >> 1) + ((n % e.rope_hd) >> 1)) * 2);
+}
+__device__ __forceinline__ void rope_rotate(const float4& cs, float4& v) {
+    const float x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
+    v.x = x0 * cs.x - x1 * cs.y; v.y = x0 * cs.y + x1 * cs.x;
+    v.z = x2 * cs.z - x3 * cs.w; v.w = x2 * cs.w + x3 * cs.z;
 }
 
 __device__ __forceinline__ void epilogue_store(const Epilogue& e, int m, int n, float acc, float alpha) {

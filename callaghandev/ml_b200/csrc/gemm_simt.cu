@@ -91,6 +91,7 @@ static Epilogue make_epilogue(const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
+    e.rope_table = nullptr; e.rope_pos = nullptr; e.rope_cols = 0; e.rope_hd = 0;  // the rotation is a separate kernel behind this engine
     return e;
 }
 
@@ -109,7 +110,16 @@ int gemm_simt(b200_ctx* ctx, const Gemm& g) {
     return B200_OK;
 }
 
-static int gemm_dispatch(b200_ctx* ctx, const Gemm& g, int* engine) {
+static int gemm_dispatch(b200_ctx* ctx, const Gemm& g0, int* engine) {
+    Gemm g = g0;
+    const bool rope_after = g.rope_table && !(ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_fuses_rope(ctx, g));
+    if (rope_after) {  // not fusable here: plain GEMM, then the rotation as its own kernel (TF32 rounding moves there too)
+        g.rope_table = nullptr;
+        g.round_tf32 = 0;
+        B200_TRY(gemm_dispatch(ctx, g, engine));
+        const int heads = g0.rope_cols / g0.rope_head_dim;
+        return k_rope(ctx, g0.C, 0, 1, g0.M, g0.ldc, 0, heads, g0.rope_head_dim, g0.rope_table, g0.rope_pos, 0, g0.round_tf32);
+    }
     if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) {
         *engine = 1;
         return gemm_tcgen05(ctx, g);

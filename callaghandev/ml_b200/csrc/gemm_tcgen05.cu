@@ -26,13 +26,16 @@ namespace {
 
 constexpr int BM = 128, BK = 32;
 constexpr int A_BYTES = BM * BK * 4;
-constexpr int EPI_STAGE_BYTES = 4 * 32 * 132 * 4;  // epilogue staging: 4 warps x 32 rows x EPI_STRIDE floats
+constexpr int EPI_STRIDE64 = 68;                        // floats per staged row of 64 columns: 16-byte aligned, conflict-free 128-bit accesses
+constexpr int EPI_STAGE_BYTES = 8 * 32 * EPI_STRIDE64 * 4;  // persistent kernel: up to 8 epilogue warps x 32 rows x 64 columns
 // Tile configurations: 128 x 128 with three stages (two CTAs per SM), or 128 x 256 with four stages (one CTA per SM).
 // A TF32 MMA with operands in shared memory reads (128 + N) x 32 bytes per K step of 8; at N = 128 that already equals
 // the shared-memory bandwidth of the SM, and the TMA writes of the next stage come on top, so the wide tile (which
 // reads 25% less shared memory per flop) is preferred whenever N allows it.
 template <int BN_> struct TileCfg {
     static constexpr int STAGES = BN_ == 256 ? 3 : 4;
+    static constexpr int EPI_WARPS = BN_ / 32;                 // one warp per (lane quarter, 128-column half)
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int B_BYTES = BN_ * BK * 4, STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -81,13 +84,13 @@ __device__ __forceinline__ void decode_item(const TcParams& p, int item, int& m0
 // the two TMEM accumulators are shared by consecutive items, so the producer keeps loading and the MMA warp keeps
 // issuing across item boundaries while the epilogue warps drain the previous accumulator.
 template <int EPI, int BN>
-__global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+__global__ void __launch_bounds__(TileCfg<BN>::THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                                TcParams p, Epilogue ep) {
     constexpr int STAGES = TileCfg<BN>::STAGES, STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzled tiles must start on 1024-byte boundaries
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* epi_stage = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES);  // 4 warps x 32 rows x EPI_STRIDE floats
+    float* epi_stage = reinterpret_cast<float*>(tiles + STAGES * STAGE_BYTES);  // one 32 x 64 staging slice per epilogue warp
     uint64_t* bars = (uint64_t*)(tiles + STAGES * STAGE_BYTES + EPI_STAGE_BYTES);
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     const uint32_t tiles_s = smem_u32(tiles);
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full0 + 8 * b, 1);
-            mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+            mbar_init(acc_empty0 + 8 * b, TileCfg<BN>::EPI_WARPS);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -189,39 +192,43 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
             }
         }
     } else {
-        // ---------------------------------------------------------------------- epilogue (warps 2..5)
-        const int q = warp & 3;  // this warp may touch TMEM lanes [32q, 32q+32)
+        // ---------------------------------------------------------------------- epilogue (warps 2 .. 2+EW-1)
+        // A warp owns 32 accumulator rows (the TMEM lanes its warp id modulo 4 selects) and 128 of the tile's columns:
+        // with the wide tile two warps share a lane quarter, one per column half.
+        const int q = warp & 3, ew = warp - 2;
+        const int colBase = (ew >> 2) * 128;
         float alpha = ep.alpha;
         if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+        float* stage = epi_stage + ew * (32 * EPI_STRIDE64);
         int it = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, it++) {
             int m0, n0, split;
             decode_item<BN>(p, item, m0, n0, split);
             const int buf = it & 1;
-            const uint32_t acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(32 * q) << 16);
+            const uint32_t acc = tmem_base + (uint32_t)(buf * BN + colBase) + ((uint32_t)(32 * q) << 16);
             if (!mbar_wait_warp(acc_full0 + 8 * buf, (it >> 1) & 1, status, 3)) break;  // tcgen05.ld is warp-collective: the warp decides together
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // Each warp transposes its accumulator rows through its own padded staging slice, which turns "one row per
-            // thread" (the TMEM load shape) into "one row per warp instruction" and makes every global access of the
-            // epilogue a full line.  The accumulator is handed back to the MMA warp as soon as it has been read.
+            // thread" (the TMEM load shape) into "one row per half warp" and makes every global access of the epilogue
+            // a full line.  The accumulator is handed back to the MMA warp as soon as this warp has read its part.
             if (EPI == EPI_GENERIC) {
-                float* stage = epi_stage + q * (32 * EPI_STRIDE);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (n0 + c0 < p.N) {
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    const bool live = n0 + colBase + c0 < p.N;  // warp-uniform
+                    if (live) {
                         uint32_t r[32];
                         tmem_ld32(acc + (uint32_t)c0, r);
 #pragma unroll
                         for (int j = 0; j < 32; j++) stage[lane * 33 + j] = __uint_as_float(r[j]);
                     }
-                    if (c0 + 32 >= BN) {  // last chunk read: release the accumulator
+                    if (c0 == 96) {  // last chunk read: release the accumulator
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
                     }
                     __syncwarp();
-                    const int n = n0 + c0 + lane;
-                    if (n0 + c0 < p.N && n < p.N) {
+                    const int n = n0 + colBase + c0 + lane;
+                    if (live && n < p.N) {
 #pragma unroll 4
                         for (int rr = 0; rr < 32; rr++) {
                             const int m = m0 + 32 * q + rr;
@@ -231,44 +238,50 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
                     __syncwarp();
                 }
             } else {
-                float* stage = epi_stage + q * (32 * EPI_STRIDE);
+                const int rsub = lane >> 4, l16 = lane & 15;
 #pragma unroll 1
-                for (int h0 = 0; h0 < BN; h0 += 128) {  // 128 accumulator columns at a time
+                for (int c0 = 0; c0 < 128; c0 += 64) {  // 64 accumulator columns per pass
+                    const bool live = n0 + colBase + c0 < p.N;  // warp-uniform (N is a multiple of 4, tiles start at multiples of 128)
                     __syncwarp();
-                    if (n0 + h0 < p.N) {
-#pragma unroll 1
-                        for (int c0 = 0; c0 < 128; c0 += 32) {
-                            uint32_t r[32];
-                            tmem_ld32(acc + (uint32_t)(h0 + c0), r);
+                    if (live) {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld32_nowait(acc + (uint32_t)c0, r0);
+                        tmem_ld32_nowait(acc + (uint32_t)(c0 + 32), r1);
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                st4(stage + lane * EPI_STRIDE + c0 + j,
-                                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+                        for (int j = 0; j < 32; j += 4) {
+                            st4(stage + lane * EPI_STRIDE64 + j,
+                                make_float4(__uint_as_float(r0[j]), __uint_as_float(r0[j + 1]), __uint_as_float(r0[j + 2]), __uint_as_float(r0[j + 3])));
+                            st4(stage + lane * EPI_STRIDE64 + 32 + j,
+                                make_float4(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1]), __uint_as_float(r1[j + 2]), __uint_as_float(r1[j + 3])));
                         }
                     }
-                    if (h0 + 128 >= BN) {  // last columns read: release the accumulator
+                    if (c0 == 64) {  // last columns read: release the accumulator
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
                     }
                     __syncwarp();
-                    const int n = n0 + h0 + 4 * lane;  // this lane's four columns of every row
-                    if (n0 + h0 < p.N && n < p.N) {    // N is a multiple of 4 on this path
+                    const int n = n0 + colBase + c0 + 4 * l16;  // this lane's four columns; lanes 16..31 take the odd rows
+                    if (live && n < p.N) {
                         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
+                        const bool rope = EPI == EPI_LINEAR && ep.rope_table && n < ep.rope_cols;
                         const int rows = min(32, p.M - (m0 + 32 * q));
-                        // 8 rows per batch: all global loads of the batch are issued before any of them is consumed
+                        // 16 rows (8 per half warp) per batch: all global loads of the batch are issued before any is consumed
 #pragma unroll 1
-                        for (int r0 = 0; r0 < rows; r0 += 8) {
+                        for (int rb = 0; rb < rows; rb += 16) {
                             float4 ext[8], ext2[8];
 #pragma unroll
                             for (int i = 0; i < 8; i++) {
-                                const size_t m = (size_t)(m0 + 32 * q + r0 + i);
+                                const int rr = rb + 2 * i + rsub;
+                                const size_t m = (size_t)(m0 + 32 * q + rr);
                                 ext[i] = ext2[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (r0 + i < rows) {
+                                if (rr < rows) {
                                     if (EPI == EPI_LINEAR) {
                                         if (ep.accumulate) ext[i] = ld4(ep.C + m * ep.ldc + n);
                                         if (ep.addmat) ext2[i] = ld4(ep.addmat + m * ep.ldadd + n);
+                                        else if (rope) ext2[i] = rope_cs(ep, (int)m, n);  // (cos, sin) of this lane's two column pairs
                                     } else if (EPI == EPI_MULZ) {
                                         ext[i] = ld4(ep.mulz + m * ep.ldmulz + n);
                                     }
@@ -276,12 +289,15 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
                             }
 #pragma unroll
                             for (int i = 0; i < 8; i++) {
-                                if (r0 + i >= rows) break;
-                                const size_t m = (size_t)(m0 + 32 * q + r0 + i);
-                                float4 v = ld4(stage + (r0 + i) * EPI_STRIDE + 4 * lane);
+                                const int rr = rb + 2 * i + rsub;
+                                if (rr >= rows) continue;
+                                const size_t m = (size_t)(m0 + 32 * q + rr);
+                                float4 v = ld4(stage + rr * EPI_STRIDE64 + 4 * l16);
                                 if (EPI == EPI_LINEAR) {
-                                    v.x = alpha * v.x + b4.x + ext[i].x + ext2[i].x; v.y = alpha * v.y + b4.y + ext[i].y + ext2[i].y;
-                                    v.z = alpha * v.z + b4.z + ext[i].z + ext2[i].z; v.w = alpha * v.w + b4.w + ext[i].w + ext2[i].w;
+                                    v.x = alpha * v.x + b4.x + ext[i].x; v.y = alpha * v.y + b4.y + ext[i].y;
+                                    v.z = alpha * v.z + b4.z + ext[i].z; v.w = alpha * v.w + b4.w + ext[i].w;
+                                    if (rope) rope_rotate(ext2[i], v);
+                                    else { v.x += ext2[i].x; v.y += ext2[i].y; v.z += ext2[i].z; v.w += ext2[i].w; }
                                     if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
                                     st4(ep.C + (size_t)split * p.split_stride + m * ep.ldc + n, v);
                                 } else if (EPI == EPI_ACT) {
@@ -471,6 +487,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
                 if (n < p.N) {                // N is a multiple of 4 on this path
                     float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
+                    const bool rope = EPI == EPI_LINEAR && ep.rope_table && n < ep.rope_cols;
                     const int rows = min(32, p.M - (m0 + 32 * q));
                     // 8 rows per batch: all global loads of the batch are issued before any of them is consumed
 #pragma unroll 1
@@ -484,6 +501,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
                                 if (EPI == EPI_LINEAR) {
                                     if (ep.accumulate) ext[i] = ld4(ep.C + m * ep.ldc + n);
                                     if (ep.addmat) ext2[i] = ld4(ep.addmat + m * ep.ldadd + n);
+                                    else if (rope) ext2[i] = rope_cs(ep, (int)m, n);  // (cos, sin) of this lane's two column pairs
                                 } else if (EPI == EPI_MULZ) {
                                     ext[i] = ld4(ep.mulz + m * ep.ldmulz + n);
                                 }
@@ -495,8 +513,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
                             const size_t m = (size_t)(m0 + 32 * q + r0 + i);
                             float4 v = ld4(stage + (r0 + i) * EPI_STRIDE + 4 * lane);
                             if (EPI == EPI_LINEAR) {
-                                v.x = alpha * v.x + b4.x + ext[i].x + ext2[i].x; v.y = alpha * v.y + b4.y + ext[i].y + ext2[i].y;
-                                v.z = alpha * v.z + b4.z + ext[i].z + ext2[i].z; v.w = alpha * v.w + b4.w + ext[i].w + ext2[i].w;
+                                v.x = alpha * v.x + b4.x + ext[i].x; v.y = alpha * v.y + b4.y + ext[i].y;
+                                v.z = alpha * v.z + b4.z + ext[i].z; v.w = alpha * v.w + b4.w + ext[i].w;
+                                if (rope) rope_rotate(ext2[i], v);
+                                else { v.x += ext2[i].x; v.y += ext2[i].y; v.z += ext2[i].z; v.w += ext2[i].w; }
                                 if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
                                 st4(ep.C + (size_t)blockIdx.y * p.split_stride + m * ep.ldc + n, v);
                             } else if (EPI == EPI_ACT) {
@@ -641,13 +661,14 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
+    e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     p.items = tiles * splits;
     const unsigned grid = (unsigned)(p.items < ctx->sm_count ? p.items : ctx->sm_count);  // persistent: one CTA per SM
     if (splits > 1) {
         B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));
         p.split_stride = (long long)g.M * g.N;
         e.C = ctx->ws; e.ldc = g.N; e.accumulate = 0; e.alpha = 1.f; e.alpha_dev = nullptr;
-        gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
+        gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, TileCfg<BN>::THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e);
         B200_LAUNCH_CHECK(ctx);
         const int64_t count = (int64_t)g.M * g.N;
         int blocks = (int)((count / 4 + 255) / 256);
@@ -671,10 +692,10 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
             kind = EPI_MULZ;
     }
     switch (kind) {
-        case EPI_LINEAR: gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        case EPI_ACT: gemm_tcgen05_persistent_kernel<EPI_ACT, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        case EPI_MULZ: gemm_tcgen05_persistent_kernel<EPI_MULZ, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
-        default: gemm_tcgen05_persistent_kernel<EPI_GENERIC, BN><<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_LINEAR: gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN><<<grid, TileCfg<BN>::THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_ACT: gemm_tcgen05_persistent_kernel<EPI_ACT, BN><<<grid, TileCfg<BN>::THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        case EPI_MULZ: gemm_tcgen05_persistent_kernel<EPI_MULZ, BN><<<grid, TileCfg<BN>::THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
+        default: gemm_tcgen05_persistent_kernel<EPI_GENERIC, BN><<<grid, TileCfg<BN>::THREADS, SMEM_BYTES, ctx->stream>>>(mapA, mapB, p, e); break;
     }
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -707,10 +728,21 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     // second kernel adds them to C in split order, so the result does not depend on scheduling.
     int splits = 1;
     const bool plain = g.act == B200_ACT_NONE && !g.dout && !g.zout && !g.mulz && !g.mulmat && !g.addmat && !g.bias && g.sgd_lr == 0.f && !g.round_tf32;
-    if (plain && tiles < 2 * ctx->sm_count && kblocks_total >= 256 && (g.N % 4 == 0)) {
-        splits = (2 * ctx->sm_count + tiles - 1) / tiles;
-        if (splits > 8) splits = 8;
-        while (splits > 1 && (kblocks_total + splits - 1) / splits < 64) splits--;
+    if (plain && tiles < 4 * ctx->sm_count && kblocks_total >= 256 && (g.N % 4 == 0)) {
+        // Cost model in units of one K block on one SM: the SM that receives the most work items sets the time
+        // (items are spread evenly over SMs, two resident at a time), every item pays a fixed fill + epilogue cost,
+        // and every split adds one more pass over the output in the reduction.
+        const double fixed = 16.0, reduce_per_split = (double)g.M * g.N * 8.0 / 5.0e12 / 0.26e-6;
+        double best = 1e30;
+        for (int sp = 1; sp <= 12; sp++) {
+            const int kbs = (kblocks_total + sp - 1) / sp;
+            if (sp > 1 && kbs < 48) break;
+            const int per_sm = (tiles * sp + ctx->sm_count - 1) / ctx->sm_count;
+            // items run two at a time on an SM and share its tensor pipe; an item that runs alone reaches about 65%
+            const double item = kbs + fixed;
+            const double cost = (per_sm / 2) * 2 * item + (per_sm & 1 ? item / 0.65 : 0.0) + (sp > 1 ? (sp + 0.5) * reduce_per_split : 0.0);
+            if (cost < best) { best = cost; splits = sp; }
+        }
         p.kb_per_split = (kblocks_total + splits - 1) / splits;
         splits = (kblocks_total + p.kb_per_split - 1) / p.kb_per_split;  // every split owns at least one K block
     }
@@ -719,6 +751,7 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
+    e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     dim3 grid((unsigned)tiles, (unsigned)splits);
     if (splits > 1) {
         B200_TRY(ensure_ws(ctx, (size_t)splits * g.M * g.N));
@@ -759,6 +792,14 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
 
 
 }  // namespace
+
+// The rotation is part of the 128-bit LINEAR epilogue only, and never of a split-K launch (a bias keeps the split off).
+bool gemm_tcgen05_fuses_rope(b200_ctx* ctx, const Gemm& g) {
+    auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    return gemm_tcgen05_eligible(ctx, g) && g.rope_table && g.bias && a16(g.bias) && a16(g.rope_table) && g.rope_head_dim % 4 == 0 &&
+           g.rope_cols % g.rope_head_dim == 0 && g.N % 4 == 0 && g.ldc % 4 == 0 && a16(g.C) && g.act == B200_ACT_NONE && !g.dout && !g.zout &&
+           !g.mulz && !g.mulmat && g.sgd_lr == 0.f && !g.accumulate && !g.addmat;
+}
 
 int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     if (!gemm_tcgen05_eligible(ctx, g)) return fail(ctx, B200_ERR_UNSUPPORTED, "shape does not qualify for the tcgen05 GEMM");

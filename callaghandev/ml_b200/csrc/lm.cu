@@ -246,10 +246,13 @@ int forward_pass(b200_lm* lm, const Pass& p) {
                 Gemm g;
                 g.M = N; g.N = nParts == 1 ? 3 * d : d; g.K = d; g.A = k.x; g.lda = d; g.B = P + Ws[i]; g.ldb = d; g.transB = 1;
                 g.C = k.qkv + i * d; g.ldc = 3 * d; g.bias = P + Bs[i]; g.round_tf32 = rnd;
+                // rotary embedding of the Q and K column blocks, inside the epilogue where the engine allows
+                g.rope_table = lm->rope; g.rope_pos = lm->cur.pos; g.rope_head_dim = hd;
+                g.rope_cols = nParts == 1 ? 2 * d : (i < 2 ? d : 0);
+                if (g.rope_cols == 0) g.rope_table = nullptr;
                 B200_TRY(gemm(ctx, g));
             }
         }
-        B200_TRY(k_rope(ctx, k.qkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 0, rnd));  // Q and K column blocks
         Attn a;
         a.Q = k.qkv; a.K = k.qkv + d; a.V = k.qkv + 2 * d; a.ldq = a.ldk = a.ldv = 3 * d;
         a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = c.causal;
@@ -327,8 +330,8 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         a.O = k.attnO; a.ldo = d; a.rowMax = k.rowMax; a.rowSum = k.rowSum; a.rowDot = lm->rowDot;
         a.dO = t1; a.lddo = d; a.dQ = lm->dqkv; a.dK = lm->dqkv + d; a.dV = lm->dqkv + 2 * d; a.lddq = a.lddk = a.lddv = 3 * d;
         a.pre_rounded = tf32_attention(lm) ? 1 : 0;
+        a.rope_table = lm->rope; a.rope_pos = lm->cur.pos;  // inverse rotation of dQ and dK
         B200_TRY(attn_backward(ctx, a));
-        B200_TRY(k_rope(ctx, lm->dqkv, d, 2, N, 3 * d, 0, H, hd, lm->rope, lm->cur.pos, 1));
         float* out = t2;  // dX of the layer input = dQKV * Wqkv + dAttnResidual (:919, residual add fused)
         if (qkv_fused(lm, L)) {
             B200_TRY(wgrad(ctx, lm->dqkv, 3 * d, k.x, d, N, 3 * d, d, G + L.WQ, G + L.bQ));
