@@ -193,18 +193,57 @@ __global__ void colsum_final_kernel(const float* __restrict__ partial, int chunk
     for (int k = 0; k < chunks; k++) s += partial[(size_t)k * cols + c];
     out[c] = accumulate ? out[c] + s : s;
 }
+// 128-bit variant: grid (colTiles of 128 columns, chunks), block (32, 8): thread (x,y) sums rows y, y+8, ... of its chunk
+// for columns tile*128 + 4x .. +3, four rows in flight per thread.
+__global__ void __launch_bounds__(256) colsum_partial_vec_kernel(const float* __restrict__ x, int rows, int cols, int ld, int rowsPerChunk,
+                                                                 float* __restrict__ partial) {
+    __shared__ float4 sm[8][33];
+    const int c = blockIdx.x * 128 + threadIdx.x * 4;
+    const int r0 = blockIdx.y * rowsPerChunk, r1 = min(rows, r0 + rowsPerChunk);
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
+    if (c < cols) {
+        const float* base = x + c;
+        int r = r0 + threadIdx.y;
+        for (; r + 24 < r1; r += 32) {
+            const float4 a = *reinterpret_cast<const float4*>(base + (size_t)r * ld), b = *reinterpret_cast<const float4*>(base + (size_t)(r + 8) * ld),
+                         cc = *reinterpret_cast<const float4*>(base + (size_t)(r + 16) * ld), d = *reinterpret_cast<const float4*>(base + (size_t)(r + 24) * ld);
+            s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+            s1.x += b.x; s1.y += b.y; s1.z += b.z; s1.w += b.w;
+            s2.x += cc.x; s2.y += cc.y; s2.z += cc.z; s2.w += cc.w;
+            s3.x += d.x; s3.y += d.y; s3.z += d.z; s3.w += d.w;
+        }
+        for (; r < r1; r += 8) {
+            const float4 a = *reinterpret_cast<const float4*>(base + (size_t)r * ld);
+            s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+        }
+    }
+    sm[threadIdx.y][threadIdx.x] = make_float4((s0.x + s1.x) + (s2.x + s3.x), (s0.y + s1.y) + (s2.y + s3.y), (s0.z + s1.z) + (s2.z + s3.z),
+                                               (s0.w + s1.w) + (s2.w + s3.w));
+    __syncthreads();
+    if (threadIdx.y == 0 && c < cols) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int y = 0; y < 8; y++) {
+            const float4 v = sm[y][threadIdx.x];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        *reinterpret_cast<float4*>(partial + (size_t)blockIdx.y * cols + c) = t;
+    }
+}
 int k_colsum(b200_ctx* ctx, const float* x, int rows, int cols, int ld, float* out, int accumulate) {
     if (cols <= 0) return B200_OK;
-    int colTiles = (cols + 31) / 32;
+    const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && aligned16(x);
+    int colTiles = vec ? (cols + 127) / 128 : (cols + 31) / 32;
     int chunks = (148 * 8 + colTiles - 1) / colTiles;
-    if (chunks > 64) chunks = 64;
+    if (chunks > (vec ? 256 : 64)) chunks = vec ? 256 : 64;
     int maxChunks = (rows + 63) / 64;
     if (maxChunks < 1) maxChunks = 1;
     if (chunks > maxChunks) chunks = maxChunks;
     int rowsPerChunk = (rows + chunks - 1) / chunks;
     if (rowsPerChunk < 1) rowsPerChunk = 1;
     B200_TRY(ensure_ws(ctx, (size_t)chunks * cols));
-    colsum_partial_kernel<<<dim3(colTiles, chunks), dim3(32, 8), 0, ctx->stream>>>(x, rows, cols, ld, rowsPerChunk, ctx->ws);
+    if (vec) colsum_partial_vec_kernel<<<dim3(colTiles, chunks), dim3(32, 8), 0, ctx->stream>>>(x, rows, cols, ld, rowsPerChunk, ctx->ws);
+    else colsum_partial_kernel<<<dim3(colTiles, chunks), dim3(32, 8), 0, ctx->stream>>>(x, rows, cols, ld, rowsPerChunk, ctx->ws);
     B200_LAUNCH_CHECK(ctx);
     colsum_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, chunks, cols, out, accumulate);
     B200_LAUNCH_CHECK(ctx);
@@ -446,21 +485,23 @@ int k_ln_forward(b200_ctx* ctx, const float* x, const float* sub, const float* g
 // order (deterministic).  dx = dNorm*invStd + (2/n)*dVar*(x-mean) + dMean/n with
 // dVar = -0.5*invStd^3*sum(dNorm*(x-mean)), dMean = -invStd*sum(dNorm)  (the reference's formulation).
 template <bool HAS_B>
-__global__ void __launch_bounds__(128) ln_bwd_vec_kernel(const float* __restrict__ dOutA, const float* __restrict__ dOutB,
-                                                         const float* __restrict__ x, const float* __restrict__ gamma,
-                                                         const float* __restrict__ mean, const float* __restrict__ var, int rows,
-                                                         int d, float eps, float* __restrict__ dx, float* __restrict__ partial) {
+__global__ void __launch_bounds__(128, 4) ln_bwd_vec_kernel(const float* __restrict__ dOutA, const float* __restrict__ dOutB,
+                                                            const float* __restrict__ x, const float* __restrict__ gamma,
+                                                            const float* __restrict__ mean, const float* __restrict__ var, int rows,
+                                                            int d, float eps, float* __restrict__ dx, float* __restrict__ partial) {
+    // The dGamma/dBeta partial sums of a warp live in its own shared-memory slice (every lane owns its columns, so
+    // there is nothing to synchronise) instead of 64 registers per thread: the kernel is bound by how many rows are in
+    // flight per SM, and the registers it does not hold become resident warps.
     extern __shared__ float sm[];  // [warps][2*d]
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     int d4 = d >> 2;
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    float4 gam[LN_MAXV], dg[LN_MAXV], db[LN_MAXV];
+    float4* smg = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d);
+    float4* smb = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d + d);
 #pragma unroll
     for (int i = 0; i < LN_MAXV; i++) {
         int c = lane + 32 * i;
-        gam[i] = c < d4 ? g4[c] : make_float4(0, 0, 0, 0);
-        dg[i] = make_float4(0, 0, 0, 0);
-        db[i] = make_float4(0, 0, 0, 0);
+        if (c < d4) { smg[c] = make_float4(0, 0, 0, 0); smb[c] = make_float4(0, 0, 0, 0); }
     }
     float invN = 1.0f / d;
     for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
@@ -470,20 +511,32 @@ __global__ void __launch_bounds__(128) ln_bwd_vec_kernel(const float* __restrict
         float mu = mean[row];
         float inv = 1.0f / sqrtf(var[row] + eps);
         float4 dn[LN_MAXV], xm[LN_MAXV];
+#pragma unroll
+        for (int i = 0; i < LN_MAXV; i++) {  // all loads of the row first
+            int c = lane + 32 * i;
+            if (c < d4) {
+                float4 o = a4[c];
+                if (HAS_B) { float4 p = b4[c]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+                dn[i] = o;
+                xm[i] = x4[c];
+            }
+        }
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int i = 0; i < LN_MAXV; i++) {
             int c = lane + 32 * i;
             if (c < d4) {
-                float4 o = a4[c];
-                if (HAS_B) { float4 p = b4[c]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
-                float4 xv = x4[c];
+                const float4 o = dn[i];
+                float4 xv = xm[i];
                 xv.x -= mu; xv.y -= mu; xv.z -= mu; xv.w -= mu;
                 xm[i] = xv;
-                dg[i].x += o.x * (xv.x * inv); dg[i].y += o.y * (xv.y * inv); dg[i].z += o.z * (xv.z * inv); dg[i].w += o.w * (xv.w * inv);
-                db[i].x += o.x; db[i].y += o.y; db[i].z += o.z; db[i].w += o.w;
+                float4 g = smg[c], bb = smb[c];
+                g.x += o.x * (xv.x * inv); g.y += o.y * (xv.y * inv); g.z += o.z * (xv.z * inv); g.w += o.w * (xv.w * inv);
+                bb.x += o.x; bb.y += o.y; bb.z += o.z; bb.w += o.w;
+                smg[c] = g; smb[c] = bb;
+                const float4 gm = __ldg(g4 + c);
                 float4 n;
-                n.x = o.x * gam[i].x; n.y = o.y * gam[i].y; n.z = o.z * gam[i].z; n.w = o.w * gam[i].w;
+                n.x = o.x * gm.x; n.y = o.y * gm.y; n.z = o.z * gm.z; n.w = o.w * gm.w;
                 dn[i] = n;
                 s1 += (n.x * xv.x + n.y * xv.y) + (n.z * xv.z + n.w * xv.w);
                 s2 += (n.x + n.y) + (n.z + n.w);
@@ -505,13 +558,6 @@ __global__ void __launch_bounds__(128) ln_bwd_vec_kernel(const float* __restrict
                 reinterpret_cast<float4*>(dx + (size_t)row * d)[c] = r;
             }
         }
-    }
-    float4* smg = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d);
-    float4* smb = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d + d);
-#pragma unroll
-    for (int i = 0; i < LN_MAXV; i++) {
-        int c = lane + 32 * i;
-        if (c < d4) { smg[c] = dg[i]; smb[c] = db[i]; }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {

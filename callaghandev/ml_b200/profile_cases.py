@@ -4,6 +4,7 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
   attention   segmented causal attention forward + backward, 8 sequences x 1024 tokens, 16 heads of 64
   gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
   layernorm   LayerNorm forward + backward on 32768 x 1024
+  crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
 """
 import sys
 
@@ -47,7 +48,17 @@ def layernorm(m, rng):
     return float(np.abs(r[0]).mean())
 
 
-CASES = {"attention": attention, "gemm": gemm, "layernorm": layernorm}
+def crossentropy(m, rng):
+    rows, vocab = 4096, 32000
+    logits = rng.normal(0, 1, (rows, vocab)).astype(np.float32)
+    targets = rng.integers(0, vocab, rows).astype(np.int32)
+    r = None
+    for _ in range(2):
+        r = m.CrossEntropyLossAndGradient(logits, targets, rows)
+    return float(r[0])
+
+
+CASES = {"attention": attention, "gemm": gemm, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):
