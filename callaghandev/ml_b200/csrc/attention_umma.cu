@@ -59,9 +59,56 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x; -inf gives +0
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Packed FP32 pairs (one instruction for two lanes of arithmetic): the element-wise step is bound by instruction issue.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+// Round-to-nearest into the TF32 mantissa by adding half an ulp; the MMA ignores the 13 low bits that remain.
+__device__ __forceinline__ uint32_t rna_tf32_add(float x) { return __float_as_uint(x) + 0x1000u; }
+
 // Round to TF32 (nearest, ties away from zero) with integer instructions: the conversion instruction shares the
 // transcendental pipe with ex2, which is the scarce resource of the element-wise step.
 __device__ __forceinline__ uint32_t rna_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
+
+#ifdef B200_ATTN_TRACE
+// Development aid: clock64() time stamps of the first CTA's roles, [role][tile][event].
+__device__ long long g_attn_trace[4 * 32 * 8];
+#define TR(role, tile, ev) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) g_attn_trace[((role) * 32 + (tile)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define TR(role, tile, ev) do { } while (0)
+#endif
+
+// Copy one row of a K-contiguous swizzle atom (32 floats, already TF32) into TMEM columns [col, col+32) of the calling
+// thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand read from
+// shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
+__device__ __forceinline__ void row_to_tmem(const uint8_t* atom, int row, uint32_t taddr) {
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+        const uint4 v = *reinterpret_cast<const uint4*>(atom + row * 128 + ((c ^ (row & 7)) << 4));
+        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+    }
+    tmem_st32(taddr, r);
+}
 
 __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                                                                  const __grid_constant__ CUtensorMap mapV, UArgs a) {
@@ -148,20 +195,24 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             for (int j = 0; j < nkt && ok; j++) {
                 ok = mbar_wait(k_full, j & 1, status, 14);
                 if (!ok) break;
+                TR(1, j, 0);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < UHD / 8; kk++) umma_tf32(tmem_base + S_COL, dQ0 + koff(kk, U_ATOM), dK0 + koff(kk, U_ATOM), idS, kk > 0 ? 1u : 0u);
                 umma_commit(k_empty);
                 umma_commit(s_full);
+                TR(1, j, 1);
                 ok = mbar_wait(p_full, j & 1, status, 15);
                 if (!ok) break;
                 ok = mbar_wait(v_full, j & 1, status, 16);
                 if (!ok) break;
+                TR(1, j, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < UK / 8; kk++)
                     umma_tf32_ta(tmem_base + O_COL, tmem_base + S_COL + kk * 8, dV0 + noff(kk), idO, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(v_empty);
+                TR(1, j, 3);
             }
             umma_commit(o_full);
         }
@@ -178,6 +229,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             ok = mbar_wait_warp(s_full, j & 1, status, 17);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (threadIdx.x == 64) TR(2, j, 0);
             tc_fence_after();
             const int k0 = j * UK;
             const bool full = k0 + UK <= sg.kLen && (!a.causal || k0 + UK - 1 <= q0 + 32 * quarter);  // warp-uniform
@@ -187,6 +239,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld32_nowait(tlane + S_COL + 32 * c, r[c]);
             tmem_ld_wait();
+            if (threadIdx.x == 64) TR(2, j, 1);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full) {
 #pragma unroll
@@ -218,6 +271,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
                 tmem_st32(tlane + S_COL + 32 * c, r[c]);
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            if (threadIdx.x == 64) TR(2, j, 2);
             l = l * corr + rs;
             m = m_new;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // S(j) complete implies P V(j-1) complete: O is stable
@@ -233,6 +287,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full);
+            if (threadIdx.x == 64) TR(2, j, 3);
         }
         if (ok) {
             ok = mbar_wait_warp(o_full, 0, status, 18);
@@ -279,12 +334,13 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
 // ------------------------------------------------------------------------------------------------------ backward
 // Two deterministic passes, as in the other engines (dQ per query tile, dK/dV per key tile; no atomics).  The softmax
 // statistics are known, so the element-wise step has no row reduction and is split over eight warps (lane quarter x
-// column half).  The inner tiles are 64 wide and S/dP are double-buffered in TMEM: the MMA warp issues the S and dP
-// products of tile j+1 while the element-wise warps turn tile j into P and dS, then issues the products that consume
-// them.  These kernels are bound by the L2 -> shared-memory traffic of the streamed tiles (FP32 storage, 64-wide
+// column half).  The inner tiles are 64 wide and S/dP are double-buffered in TMEM.  Two threads issue MMAs: one
+// the S and dP products (running up to two tiles ahead), the other the products that consume P and dS -- a single
+// thread issues a narrow TF32 MMA only every ~50 cycles (more when its scheduler is busy with the element-wise
+// warps), which is slower than the tensor pipe executes them.  These kernels are bound by the L2 -> shared-memory traffic of the streamed tiles (FP32 storage, 64-wide
 // heads), so an operand that is needed both K-contiguous (for S / dP) and N-contiguous (for dQ, dK, dV) is loaded
 // once, K-contiguous, and four extra warps rewrite it into the N-contiguous swizzle image inside shared memory.
-constexpr int B_THREADS = 64 + 256 + 128;  // producer, MMA issuer, 8 element-wise warps, 4 re-swizzle warps
+constexpr int B_THREADS = 64 + 256 + 128 + 32;  // producer, first MMA issuer, 8 element-wise warps, 4 re-swizzle warps, second MMA issuer
 constexpr int A128 = 128 * 128, T128 = 2 * A128;  // atom column / tile with 128 rows
 constexpr int A64 = 64 * 128, T64 = 2 * A64;      // atom column / tile with 64 rows
 // Streamed operands live in two rings per kernel, because their consumers differ: the K-contiguous images feed the
@@ -320,27 +376,6 @@ __device__ __forceinline__ void reswizzle_tile(const uint8_t* __restrict__ src, 
         const uint4 v = *reinterpret_cast<const uint4*>(src + atom * A64 + r * 128 + ((q ^ (r & 7)) << 4));
         *reinterpret_cast<uint4*>(dst + atom * A64 + r * 128 + ((((q >> 1) ^ (r & 3)) << 5) | ((q & 1) << 4))) = v;
     }
-}
-
-#ifdef B200_ATTN_TRACE
-// Development aid: clock64() time stamps of the first CTA's roles, [role][tile][event].
-__device__ long long g_attn_trace[4 * 32 * 8];
-#define TR(role, tile, ev) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) g_attn_trace[((role) * 32 + (tile)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define TR(role, tile, ev) do { } while (0)
-#endif
-
-// Copy one row of a K-contiguous swizzle atom (32 floats, already TF32) into TMEM columns [col, col+32) of the calling
-// thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand read from
-// shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
-__device__ __forceinline__ void row_to_tmem(const uint8_t* atom, int row, uint32_t taddr) {
-    uint32_t r[32];
-#pragma unroll
-    for (int c = 0; c < 8; c++) {
-        const uint4 v = *reinterpret_cast<const uint4*>(atom + row * 128 + ((c ^ (row & 7)) << 4));
-        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
-    }
-    tmem_st32(taddr, r);
 }
 
 struct UBwdArgs {
@@ -392,18 +427,18 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DQ_RING_N * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 19);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
     const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128;
     const uint32_t ringK = dOs + T128;                 // slot: K tile then V tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: K tile, N-contiguous
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t qdo_full = bar0, kk_full = bar0 + 8, kk_empty = bar0 + 32, kn_full = bar0 + 56, kn_empty = bar0 + 80, sdp_full = bar0 + 104,
-                   ds_full = bar0 + 120, dq_full = bar0 + 136, a_ready = bar0 + 144;
+                   ds_full = bar0 + 120, dq_full = bar0 + 136, a_ready = bar0 + 144, buf_free = bar0 + 152;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 19; i++)  // a_ready: 256; kk_empty: MMA commit + 128 re-swizzle readers; kn_full: 128 re-swizzle writers; ds_full: 256
+        for (int i = 0; i < 21; i++)  // a_ready: 256; kk_empty: MMA commit + 128 re-swizzle readers; kn_full: 128 re-swizzle writers; ds_full: 256
             mbar_init(bar0 + 8 * i, (i == 15 || i == 16 || i == 18) ? 256 : (i >= 4 && i <= 6) ? 129 : (i >= 7 && i <= 9) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -449,37 +484,39 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            const uint64_t dRK0 = kdesc(ringK, 0, A64), dRN0 = ndesc(ringN, 0, A64);
+            const uint32_t idS = idesc_tf32(128, 64, 0, 0);
+            const uint64_t dRK0 = kdesc(ringK, 0, A64);
+            // ---------------------------------------------------------------- first issuer: S(j) and dP(j) into TMEM buffer j&1
             bool ok = mbar_wait(a_ready, 0, status, 22);
             tc_fence_after();
-            auto issue_sdp = [&](int j) {  // S(j) and dP(j) into TMEM buffer j&1; frees the K-contiguous slot when they complete
+            for (int j = 0; j < nkt && ok; j++) {
                 const int s = j % RING_K, b = j & 1;
                 TR(1, j, 0);
                 ok = mbar_wait(kk_full + 8 * s, (j / RING_K) & 1, status, 23);
-                if (!ok) return;
+                if (!ok) break;
+                ok = mbar_wait(buf_free + 8 * b, ((j >> 1) & 1) ^ 1, status, 24);  // dQ(j-2) has consumed the buffer (free at first use)
+                if (!ok) break;
                 TR(1, j, 1);
                 tc_fence_after();
                 const uint64_t dk = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dv = dk + (uint64_t)(T64 >> 4);
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + QA_COL + kk * 8, dk + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
-                TR(0, j, 1);
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + DOA_COL + kk * 8, dv + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
-                TR(0, j, 2);
                 umma_commit(kk_empty + 8 * s);
-                TR(0, j, 3);
                 umma_commit(sdp_full + 8 * b);
                 TR(1, j, 2);
-            };
-            if (ok) issue_sdp(0);
+            }
+        }
+    } else if (warp == 14) {
+        if (lane == 0) {
+            // ---------------------------------------------------------------- second issuer: dQ += dS(j) K(j)
+            const uint32_t idN = idesc_tf32(128, 64, 0, 1);
+            const uint64_t dRN0 = ndesc(ringN, 0, A64);
+            bool ok = true;
             for (int j = 0; j < nkt && ok; j++) {
-                if (j + 1 < nkt) {
-                    issue_sdp(j + 1);
-                    if (!ok) break;
-                }
                 const int s = j % DQ_RING_N, b = j & 1;
-                ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 24);
+                ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 25);
                 if (!ok) break;
                 TR(1, j, 3);
                 ok = mbar_wait(ds_full + 8 * b, (j >> 1) & 1, status, 25);
@@ -488,12 +525,9 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 tc_fence_after();
                 const uint64_t dn = dRN0 + (uint64_t)(s * (T64 >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
-                TR(0, j, 4);
-#pragma unroll
-                for (int kk = 4; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, 1u);
-                TR(0, j, 5);
+                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(kn_empty + 8 * s);
+                umma_commit(buf_free + 8 * b);
                 TR(1, j, 5);
             }
             umma_commit(dq_full);
@@ -503,14 +537,18 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         const int row = 32 * quarter + lane, qi = q0 + row;
         const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
         const float sl2 = a.scale * LOG2E_F;
-        float m2 = 0.f, il = 0.f, D = 0.f;
+        // P = 2^(s*sl2 - m2l) with m2l = rowMax*log2(e) + log2(rowSum): the normalisation rides in the exponent.
+        // Rows without any visible key (or outside the segment) get m2l = +inf, i.e. P = 0.
+        float m2l = INFINITY, D = 0.f;
+        bool live = false;
         if (qi < sg.qLen) {
             const size_t idx = (size_t)(sg.qStart + qi) * a.numHeads + head;
             const float m = a.rowMax[idx], l = a.rowSum[idx];
-            if (l > 0.f && m != -INFINITY) { il = 1.f / l; m2 = m * LOG2E_F; }
+            if (l > 0.f && m != -INFINITY) { m2l = fmaf(m, LOG2E_F, log2f(l)); live = true; }
             D = a.rowDot[idx];
         }
-        const int lim = il > 0.f ? (a.causal ? min(sg.kLen, qi + 1) : sg.kLen) : 0;  // keys [0, lim) are visible to this row
+        const int lim = live ? (a.causal ? min(sg.kLen, qi + 1) : sg.kLen) : 0;  // keys [0, lim) are visible to this row
+        const float2 sl22 = make_float2(sl2, sl2), nm2 = make_float2(-m2l, -m2l), nD2 = make_float2(-D, -D);
         bool ok = mbar_wait_warp(qdo_full, 0, status, 20);
         if (__all_sync(0xffffffffu, ok)) {  // move this thread's half rows of Q and dO into TMEM
             row_to_tmem(tiles + half * A128, row, tlane + QA_COL + c0);
@@ -533,12 +571,18 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
             tmem_ld_wait();
             if (threadIdx.x == 64) TR(2, j, 2);
+            const bool fullw = __all_sync(0xffffffffu, nvis >= 32);  // no masking anywhere in this warp's slice
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                float v = fmaf(__uint_as_float(sr[i]), sl2, -m2);
-                if (i >= nvis) v = -INFINITY;
-                const float p = ex2(v) * il;
-                sr[i] = rna_tf32(p * (__uint_as_float(pr[i]) - D));
+            for (int i = 0; i < 32; i += 2) {
+                float2 v = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sl22, nm2);
+                if (!fullw) {
+                    if (i >= nvis) v.x = -INFINITY;
+                    if (i + 1 >= nvis) v.y = -INFINITY;
+                }
+                const float2 pp = make_float2(ex2(v.x), ex2(v.y));
+                const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), nD2));
+                sr[i] = rna_tf32_add(ds.x);
+                sr[i + 1] = rna_tf32_add(ds.y);
             }
             tmem_st32(tlane + s * 128 + c0, sr);
             if (threadIdx.x == 64) TR(2, j, 3);
@@ -564,7 +608,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         }
         ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
         if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64, a.rope_table, a.rope_pos);
-    } else {
+    } else if (warp < 14) {
         // ------------------------------------------------------------------------------ re-swizzle warps: K -> N-contiguous image
         const int t = threadIdx.x - 320;
         uint8_t* ringK_p = tiles + 2 * T128;
@@ -615,19 +659,19 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
     }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DKV_RING_N * 2 * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
-    float* stats = reinterpret_cast<float*>(bars + 18);  // [2 buffers][m2 | il | D][64]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 19);
+    float* stats = reinterpret_cast<float*>(bars + 20);  // [2 buffers][-(m2 + log2 l) | -D][64] (stride 192 floats)
     const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128;
     const uint32_t ringK = Vs + T128;                  // slot: Q tile then dO tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: Q tile then dO tile, both N-contiguous
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t kv_full = bar0, qk_full = bar0 + 8, qk_empty = bar0 + 32, qn_full = bar0 + 56, qn_empty = bar0 + 72, sdp_full = bar0 + 88,
-                   ds_full = bar0 + 104, acc_full = bar0 + 120, a_ready = bar0 + 128;
+                   ds_full = bar0 + 104, acc_full = bar0 + 120, a_ready = bar0 + 128, buf_free = bar0 + 136;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 17; i++)  // a_ready: 256; qk_empty: MMA commit + 128 re-swizzle readers; qn_full: 128 re-swizzle writers; ds_full: 256
+        for (int i = 0; i < 19; i++)  // a_ready: 256; qk_empty: MMA commit + 128 re-swizzle readers; qn_full: 128 re-swizzle writers; ds_full: 256
             mbar_init(bar0 + 8 * i, (i == 13 || i == 14 || i == 16) ? 256 : (i >= 4 && i <= 6) ? 129 : (i == 7 || i == 8) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -672,14 +716,17 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idS = idesc_tf32(128, 64, 0, 0), idN = idesc_tf32(128, 64, 0, 1);
-            const uint64_t dRK0 = kdesc(ringK, 0, A64), dRN0 = ndesc(ringN, 0, A64);
+            const uint32_t idS = idesc_tf32(128, 64, 0, 0);
+            const uint64_t dRK0 = kdesc(ringK, 0, A64);
+            // ---------------------------------------------------------------- first issuer: S^T(i) and dP^T(i) into TMEM buffer i&1
             bool ok = mbar_wait(a_ready, 0, status, 32);
             tc_fence_after();
-            auto issue_sdp = [&](int i) {  // S^T(i) and dP^T(i) into TMEM buffer i&1; frees the K-contiguous slot when they complete
+            for (int i = 0; i < nqt && ok; i++) {
                 const int s = i % RING_K, b = i & 1;
                 ok = mbar_wait(qk_full + 8 * s, (i / RING_K) & 1, status, 33);
-                if (!ok) return;
+                if (!ok) break;
+                ok = mbar_wait(buf_free + 8 * b, ((i >> 1) & 1) ^ 1, status, 34);  // dV, dK of tile i-2 have consumed the buffer
+                if (!ok) break;
                 tc_fence_after();
                 const uint64_t dq = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dd = dq + (uint64_t)(T64 >> 4);
 #pragma unroll
@@ -688,15 +735,17 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + VA_COL + kk * 8, dd + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
                 umma_commit(qk_empty + 8 * s);
                 umma_commit(sdp_full + 8 * b);
-            };
-            if (ok) issue_sdp(0);
+            }
+        }
+    } else if (warp == 14) {
+        if (lane == 0) {
+            // ---------------------------------------------------------------- second issuer: dV += P^T dO, dK += dS^T Q
+            const uint32_t idN = idesc_tf32(128, 64, 0, 1);
+            const uint64_t dRN0 = ndesc(ringN, 0, A64);
+            bool ok = true;
             for (int i = 0; i < nqt && ok; i++) {
-                if (i + 1 < nqt) {
-                    issue_sdp(i + 1);
-                    if (!ok) break;
-                }
                 const int s = i % DKV_RING_N, b = i & 1;
-                ok = mbar_wait(qn_full + 8 * s, (i / DKV_RING_N) & 1, status, 34);
+                ok = mbar_wait(qn_full + 8 * s, (i / DKV_RING_N) & 1, status, 35);
                 if (!ok) break;
                 ok = mbar_wait(ds_full + 8 * b, (i >> 1) & 1, status, 35);
                 if (!ok) break;
@@ -707,6 +756,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, dqn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(qn_empty + 8 * s);
+                umma_commit(buf_free + 8 * b);
             }
             umma_commit(acc_full);
         }
@@ -723,20 +773,27 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             tc_fence_before();
             mbar_arrive(a_ready);
         }
+        // Statistics of a tile's 64 query rows: fetched one tile ahead into registers (threads 0..63), so their global
+        // latency overlaps the previous tile instead of sitting in front of every tile.
+        float pm = 0.f, pl = 0.f, pD = 0.f;
+        auto fetch_stats = [&](int i) {
+            pm = -INFINITY; pl = 0.f; pD = 0.f;
+            const int q = (qtBegin + i) * 64 + tid;
+            if (tid < 64 && i < nqt && q < sg.qLen) {
+                const size_t idx = (size_t)(sg.qStart + q) * a.numHeads + head;
+                pm = a.rowMax[idx]; pl = a.rowSum[idx]; pD = a.rowDot[idx];
+            }
+        };
+        fetch_stats(0);
         for (int i = 0; i < nqt; i++) {
             const int s = i & 1, qbase = (qtBegin + i) * 64;
             float* st = stats + s * 192;
-            if (tid < 64) {  // statistics of this tile's 64 query rows
-                float m2 = 0.f, il = 0.f, D = 0.f;
-                const int q = qbase + tid;
-                if (q < sg.qLen) {
-                    const size_t idx = (size_t)(sg.qStart + q) * a.numHeads + head;
-                    const float m = a.rowMax[idx], l = a.rowSum[idx];
-                    if (l > 0.f && m != -INFINITY) { il = 1.f / l; m2 = m * LOG2E_F; }
-                    D = a.rowDot[idx];
-                }
-                st[tid] = m2; st[64 + tid] = il; st[128 + tid] = D;
+            if (tid < 64) {
+                // +inf: P = 0 for query rows outside the segment or without a visible key
+                const float m2l = (pl > 0.f && pm != -INFINITY) ? fmaf(pm, LOG2E_F, log2f(pl)) : INFINITY;
+                st[tid] = -m2l; st[64 + tid] = -pD;
             }
+            fetch_stats(i + 1);
             ok = mbar_wait_warp(sdp_full + 8 * s, (i >> 1) & 1, status, 36);
             if (ew_barrier_or(!ok)) {  // publishes the statistics; a failed wait anywhere stops all 256 threads together
                 ok = false;
@@ -750,18 +807,24 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             tmem_ld32_nowait(tlane + s * 128 + c0, sr);
             tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
             tmem_ld_wait();
+            const bool fullw = __all_sync(0xffffffffu, cmin <= 0 && cmax >= 32);  // no masking anywhere in this warp's slice
+            const float2 sl22 = make_float2(sl2, sl2);
 #pragma unroll
             for (int c = 0; c < 32; c += 4) {
-                const float4 m4 = *reinterpret_cast<const float4*>(st + c0 + c), i4 = *reinterpret_cast<const float4*>(st + 64 + c0 + c),
-                             d4 = *reinterpret_cast<const float4*>(st + 128 + c0 + c);
-                const float mm[4] = {m4.x, m4.y, m4.z, m4.w}, ii[4] = {i4.x, i4.y, i4.z, i4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+                const float4 m4 = *reinterpret_cast<const float4*>(st + c0 + c), d4 = *reinterpret_cast<const float4*>(st + 64 + c0 + c);
+                const float2 nm[2] = {make_float2(m4.x, m4.y), make_float2(m4.z, m4.w)}, nd[2] = {make_float2(d4.x, d4.y), make_float2(d4.z, d4.w)};
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    float v = fmaf(__uint_as_float(sr[c + e]), sl2, -mm[e]);
-                    if (c + e < cmin || c + e >= cmax || ii[e] == 0.f) v = -INFINITY;
-                    const float p = ex2(v) * ii[e];
-                    sr[c + e] = rna_tf32(p);
-                    pr[c + e] = rna_tf32(p * (__uint_as_float(pr[c + e]) - dd[e]));
+                for (int e = 0; e < 2; e++) {
+                    const int i = c + 2 * e;
+                    float2 v = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sl22, nm[e]);
+                    if (!fullw) {
+                        if (i < cmin || i >= cmax) v.x = -INFINITY;
+                        if (i + 1 < cmin || i + 1 >= cmax) v.y = -INFINITY;
+                    }
+                    const float2 pp = make_float2(ex2(v.x), ex2(v.y));
+                    const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), nd[e]));
+                    sr[i] = rna_tf32_add(pp.x); sr[i + 1] = rna_tf32_add(pp.y);
+                    pr[i] = rna_tf32_add(ds.x); pr[i + 1] = rna_tf32_add(ds.y);
                 }
             }
             tmem_st32(tlane + s * 128 + c0, sr);
@@ -797,7 +860,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
             store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid, a.rope_table, a.rope_pos);
         }
-    } else {
+    } else if (warp < 14) {
         // ------------------------------------------------------------------------------ re-swizzle warps: Q, dO -> N-contiguous images
         const int t = threadIdx.x - 320;
         uint8_t* ringK_p = tiles + 2 * T128;
