@@ -270,8 +270,13 @@ def main():
         eng = 1 if prof[1][0] > prof[0][0] and prof[1][2] > 0 else 0
         n_l, fl, ms = prof[eng]
         achieved = fl / (ms / 1e3) / 1e12 if ms > 0 else 0.0
+        # DRAM traffic per launch: ncu capture of the three GEMM layouts of one linear layer (8192 x 1024 x 4096, see
+        # profiles/gemm_tcgen05_8192x4096x1024.md): 595.6 MB of dram read+write for 3 x 68.7 GFLOP, i.e. 2.89 bytes per
+        # kFLOP (0.98-1.27 x the algorithmic bytes); traffic grows with the FLOPs of a launch, so it is scaled by them.
+        traffic = (fl / n_l) * 2.89e-3 if (eng and n_l) else None
         roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_tf32" if eng else "gemm_simt_fp32", "achieved": achieved, "peak": tf32_peak,
-                    "unit": "TFLOP/s", "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / tf32_peak if tf32_peak else None, "traffic": traffic,
+                    "traffic_note": "bytes per average GEMM launch, scaled from an ncu capture of a smaller case by FLOPs",
                     "peak_source": "cuBLAS TF32 8192^3 measured in this run (of measured); bf16 peaks of MEASURED_PEAKS.json: "
                                    + (f"{peaks['bf16_tflops']:.0f} burst / {peaks['bf16_tflops_sustained']:.0f} sustained TFLOP/s" if peaks else "file absent"),
                     "launches": n_l, "gemm_ms_per_step": ms / args.steps,
