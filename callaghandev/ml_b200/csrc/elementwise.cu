@@ -797,6 +797,73 @@ __global__ void __launch_bounds__(THREADS) ce_kernel(const float* __restrict__ l
     }
 }
 
+// Large vocabularies (V a multiple of 4, 16-byte aligned rows): one block of 256 threads per row, several blocks per SM.
+// Pass 1 streams the row once with 128-bit loads and keeps a running (max, sum of exp) pair per thread; pass 2 reads the
+// row again (about a third of those reads still hit L2 with eight blocks per SM in flight; capping the blocks per SM to
+// raise the hit rate cost more in latency hiding than it saved in traffic) and writes the gradient.  The loads of one
+// block overlap the reductions and stores of the others, which the one-block-per-SM register-resident kernel cannot do.
+__global__ void __launch_bounds__(256) ce_twopass_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets,
+                                                         int effRows, const float* __restrict__ row_scale_dev, float row_scale,
+                                                         float* __restrict__ dLogits, float* __restrict__ row_loss,
+                                                         int32_t* __restrict__ row_ok) {
+    __shared__ float red_m[8], red_s[8];
+    __shared__ float s_pt;
+    const int row = blockIdx.x, V4 = V >> 2, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float4* dl4 = reinterpret_cast<float4*>(dLogits + (size_t)row * V);
+    if (row >= effRows) {
+        for (int j = threadIdx.x; j < V4; j += 256) dl4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const float4* l4 = reinterpret_cast<const float4*>(logits + (size_t)row * V);
+    if (threadIdx.x == 0) s_pt = 0.f;
+    float m = -INFINITY, sum = 0.f;
+    for (int j = threadIdx.x; j < V4; j += 256) {
+        const float4 x = l4[j];
+        const float m4 = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
+        if (m4 > m) {  // -inf rows stay at (m = -inf, sum = 0) until a finite value arrives
+            sum *= __expf(m - m4);
+            m = m4;
+        }
+        if (m != -INFINITY) sum += (__expf(x.x - m) + __expf(x.y - m)) + (__expf(x.z - m) + __expf(x.w - m));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, o), so = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mn = fmaxf(m, mo);
+        sum = (mn == -INFINITY) ? 0.f : sum * __expf(m - mn) + so * __expf(mo - mn);
+        m = mn;
+    }
+    if (lane == 0) { red_m[warp] = m; red_s[warp] = sum; }
+    __syncthreads();
+    float M = red_m[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) M = fmaxf(M, red_m[w]);
+    float S = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) S += (red_m[w] == -INFINITY) ? 0.f : red_s[w] * __expf(red_m[w] - M);
+    const float inv = 1.0f / S;
+    const int t = targets[row];
+    const float sc = row_scale_dev ? row_scale_dev[row] : row_scale;
+    int ok = (unsigned)t < (unsigned)V ? 1 : 0;  // a target outside the row marks the row invalid instead of reading out of range
+    for (int j = threadIdx.x; j < V4; j += 256) {
+        const float4 x = l4[j];
+        float e[4] = {expf(x.x - M), expf(x.y - M), expf(x.z - M), expf(x.w - M)};
+        float g[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            g[k] = (e[k] * inv) * sc;
+            if (4 * j + k == t) { s_pt = e[k]; g[k] -= sc; }
+            ok &= isfinite(g[k]) ? 1 : 0;
+        }
+        dl4[j] = make_float4(g[0], g[1], g[2], g[3]);
+    }
+    ok = __syncthreads_and(ok);
+    if (threadIdx.x == 0) {
+        row_loss[row] = -logf(s_pt * inv + 1e-10f);
+        row_ok[row] = ok;
+    }
+}
+
 // Any vocabulary size: three passes over the row in global memory (not in-place safe w.r.t. partial overwrite, so the
 // gradient is written only in the last pass, after every read of the same element by the same thread).
 __global__ void ce_generic_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets, int effRows,
@@ -838,7 +905,9 @@ __global__ void ce_generic_kernel(const float* __restrict__ logits, int V, const
 int k_cross_entropy(b200_ctx* ctx, const float* logits, int rows, int V, const int32_t* targets, int effRows, const float* row_scale_dev,
                     float row_scale, float* dLogits, float* row_loss, int32_t* row_ok) {
     if (rows <= 0 || V <= 0) return B200_OK;
-    if (V <= 128 * CE_ITEMS) ce_kernel<128><<<rows, 128, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
+    const bool big = V >= 8192 && (V % 4 == 0) && aligned16(logits) && aligned16(dLogits);
+    if (big) ce_twopass_kernel<<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
+    else if (V <= 128 * CE_ITEMS) ce_kernel<128><<<rows, 128, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 256 * CE_ITEMS) ce_kernel<256><<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 1024 * CE_ITEMS) ce_kernel<1024><<<rows, 1024, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else ce_generic_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
