@@ -145,6 +145,10 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         for (int i = 0; i < 8; i++) mbar_init(bar0 + 8 * i, i == 6 ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // Q is requested right away: its latency overlaps the TMEM allocation and the first sync.
+        mbar_expect_tx(q_full, U_TILE);
+        tma_load_2d(Qs, &mapQ, q_full, head * UHD, sg.qStart + q0);
+        tma_load_2d(Qs + U_ATOM, &mapQ, q_full, head * UHD + 32, sg.qStart + q0);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(FWD_TMEM_COLS) : "memory");
@@ -159,9 +163,6 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         if (lane == 0) {
             // ---------------------------------------------------------------------------------- TMA producer
             const int col = head * UHD;
-            mbar_expect_tx(q_full, U_TILE);
-            tma_load_2d(Qs, &mapQ, q_full, col, sg.qStart + q0);
-            tma_load_2d(Qs + U_ATOM, &mapQ, q_full, col + 32, sg.qStart + q0);
             bool ok = true;
             int kIssued = 0, vIssued = 0;
             for (int j = 0; j < nkt; j++) {
@@ -442,6 +443,12 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             mbar_init(bar0 + 8 * i, (i == 15 || i == 16 || i == 18) ? 256 : (i >= 4 && i <= 6) ? 129 : (i >= 7 && i <= 9) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
+        mbar_expect_tx(qdo_full, 2 * T128);
+        tma_load_2d(Qs, &mapQ, qdo_full, head * UHD, sg.qStart + q0);
+        tma_load_2d(Qs + A128, &mapQ, qdo_full, head * UHD + 32, sg.qStart + q0);
+        tma_load_2d(dOs, &mapdO, qdo_full, head * UHD, sg.qStart + q0);
+        tma_load_2d(dOs + A128, &mapdO, qdo_full, head * UHD + 32, sg.qStart + q0);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -456,11 +463,6 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     if (warp == 0) {
         if (lane == 0) {
             const int col = head * UHD;
-            mbar_expect_tx(qdo_full, 2 * T128);
-            tma_load_2d(Qs, &mapQ, qdo_full, col, sg.qStart + q0);
-            tma_load_2d(Qs + A128, &mapQ, qdo_full, col + 32, sg.qStart + q0);
-            tma_load_2d(dOs, &mapdO, qdo_full, col, sg.qStart + q0);
-            tma_load_2d(dOs + A128, &mapdO, qdo_full, col + 32, sg.qStart + q0);
             bool ok = true;
             int nk = 0;
             for (; nk < nkt; nk++) {
@@ -675,6 +677,12 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
             mbar_init(bar0 + 8 * i, (i == 13 || i == 14 || i == 16) ? 256 : (i >= 4 && i <= 6) ? 129 : (i == 7 || i == 8) ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
+        mbar_expect_tx(kv_full, 2 * T128);
+        tma_load_2d(Ks, &mapK, kv_full, head * UHD, sg.kStart + k0);
+        tma_load_2d(Ks + A128, &mapK, kv_full, head * UHD + 32, sg.kStart + k0);
+        tma_load_2d(Vs, &mapV, kv_full, head * UHD, sg.kStart + k0);
+        tma_load_2d(Vs + A128, &mapV, kv_full, head * UHD + 32, sg.kStart + k0);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -689,11 +697,6 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
     if (warp == 0) {
         if (lane == 0) {
             const int col = head * UHD;
-            mbar_expect_tx(kv_full, 2 * T128);
-            tma_load_2d(Ks, &mapK, kv_full, col, sg.kStart + k0);
-            tma_load_2d(Ks + A128, &mapK, kv_full, col + 32, sg.kStart + k0);
-            tma_load_2d(Vs, &mapV, kv_full, col, sg.kStart + k0);
-            tma_load_2d(Vs + A128, &mapV, kv_full, col + 32, sg.kStart + k0);
             bool ok = true;
             int nk = 0;
             for (; nk < nqt; nk++) {

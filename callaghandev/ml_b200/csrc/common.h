@@ -38,7 +38,7 @@ struct b200_ctx {
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
-    int gemm_tile_n = 0;  // 0 = choose; 128 forces the narrow tcgen05 tile (set from B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
+    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;
@@ -116,7 +116,7 @@ bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g);
 bool gemm_tcgen05_fuses_rope(b200_ctx* ctx, const Gemm& g);  // the rope_* fields would be applied inside the tcgen05 epilogue
 // Y[rows,outDim] (leading dim ldy) = X[rows,inDim] * W[outDim,inDim]^T + bias
 int linear_fwd(b200_ctx* ctx, const float* X, int rows, int inDim, const float* W, const float* bias, int outDim, float* Y, int ldy);
-// Wg[outDim,inDim] += dY^T X ; bg[outDim] += column sums of dY
+// Wg[outDim,inDim] += dY^T X ; bg[outDim] += column sums of dY (bg may be null when the producer of dY already summed its columns)
 int wgrad(b200_ctx* ctx, const float* dY, int lddy, const float* X, int ldx, int rows, int outDim, int inDim, float* Wg, float* bg);
 // dX[rows,inDim] (+)= dY[rows,outDim] * W[outDim,inDim]
 int dgrad(b200_ctx* ctx, const float* dY, int lddy, const float* W, int rows, int outDim, int inDim, float* dX, int accumulate);
@@ -147,7 +147,8 @@ int k_ln_forward(b200_ctx*, const float* x, const float* sub, const float* gamma
                  float* out, float* mean, float* var, float* normalized, float* residual);
 // LayerNorm backward on dOut = dOutA (+ dOutB).  dGamma/dBeta: accumulate ? += : =.
 int k_ln_backward(b200_ctx*, const float* dOutA, const float* dOutB, const float* x, const float* gamma, const float* mean,
-                  const float* var, int rows, int d, float eps, float* dx, float* dGamma, float* dBeta, int accumulate);
+                  const float* var, int rows, int d, float eps, float* dx, float* dGamma, float* dBeta, int accumulate,
+                  float* dxColSum = nullptr);  // dxColSum (optional): += column sums of dx, computed in the same pass
 // Softmax cross-entropy, in place capable (dLogits may alias logits).  Per row i < effRows:
 //   row_loss[i] = -log(p_t + 1e-10), row_ok[i] = all gradient entries finite, dLogits = (p - onehot) * row_scale[i]
 // (row_scale_dev per row, or the constant row_scale when null).  Rows >= effRows are zeroed.

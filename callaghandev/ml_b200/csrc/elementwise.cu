@@ -484,7 +484,7 @@ int k_ln_forward(b200_ctx* ctx, const float* x, const float* sub, const float* g
 // sums in registers, and the block writes one partial row per block; a second kernel adds the partial rows in block
 // order (deterministic).  dx = dNorm*invStd + (2/n)*dVar*(x-mean) + dMean/n with
 // dVar = -0.5*invStd^3*sum(dNorm*(x-mean)), dMean = -invStd*sum(dNorm)  (the reference's formulation).
-template <bool HAS_B>
+template <bool HAS_B, bool DXSUM = false>
 __global__ void __launch_bounds__(128, 4) ln_bwd_vec_kernel(const float* __restrict__ dOutA, const float* __restrict__ dOutB,
                                                             const float* __restrict__ x, const float* __restrict__ gamma,
                                                             const float* __restrict__ mean, const float* __restrict__ var, int rows,
@@ -492,16 +492,23 @@ __global__ void __launch_bounds__(128, 4) ln_bwd_vec_kernel(const float* __restr
     // The dGamma/dBeta partial sums of a warp live in its own shared-memory slice (every lane owns its columns, so
     // there is nothing to synchronise) instead of 64 registers per thread: the kernel is bound by how many rows are in
     // flight per SM, and the registers it does not hold become resident warps.
-    extern __shared__ float sm[];  // [warps][2*d]
+    // With DXSUM a third slice accumulates the column sums of dx: the bias gradient of the linear layer that feeds
+    // this LayerNorm, which would otherwise cost another pass over dx.
+    constexpr int NACC = DXSUM ? 3 : 2;
+    extern __shared__ float sm[];  // [warps][NACC*d]
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     int d4 = d >> 2;
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    float4* smg = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d);
-    float4* smb = reinterpret_cast<float4*>(sm + (size_t)warp * 2 * d + d);
+    float4* smg = reinterpret_cast<float4*>(sm + (size_t)warp * NACC * d);
+    float4* smb = reinterpret_cast<float4*>(sm + (size_t)warp * NACC * d + d);
+    float4* smx = reinterpret_cast<float4*>(sm + (size_t)warp * NACC * d + 2 * d);  // only touched with DXSUM
 #pragma unroll
     for (int i = 0; i < LN_MAXV; i++) {
         int c = lane + 32 * i;
-        if (c < d4) { smg[c] = make_float4(0, 0, 0, 0); smb[c] = make_float4(0, 0, 0, 0); }
+        if (c < d4) {
+            smg[c] = make_float4(0, 0, 0, 0); smb[c] = make_float4(0, 0, 0, 0);
+            if (DXSUM) smx[c] = make_float4(0, 0, 0, 0);
+        }
     }
     float invN = 1.0f / d;
     for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
@@ -556,14 +563,19 @@ __global__ void __launch_bounds__(128, 4) ln_bwd_vec_kernel(const float* __restr
                 r.z = dn[i].z * inv + dVarScale * xm[i].z + dMeanScale;
                 r.w = dn[i].w * inv + dVarScale * xm[i].w + dMeanScale;
                 reinterpret_cast<float4*>(dx + (size_t)row * d)[c] = r;
+                if (DXSUM) {
+                    float4 sx = smx[c];
+                    sx.x += r.x; sx.y += r.y; sx.z += r.z; sx.w += r.w;
+                    smx[c] = sx;
+                }
             }
         }
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
+    for (int c = threadIdx.x; c < NACC * d; c += blockDim.x) {
         float s = 0.f;
-        for (int w = 0; w < warps; w++) s += sm[(size_t)w * 2 * d + c];
-        partial[(size_t)blockIdx.x * 2 * d + c] = s;
+        for (int w = 0; w < warps; w++) s += sm[(size_t)w * NACC * d + c];
+        partial[(size_t)blockIdx.x * NACC * d + c] = s;
     }
 }
 
@@ -628,8 +640,20 @@ __global__ void ln_bwd_final_kernel(const float* __restrict__ partial, int parts
     *dst = accumulate ? *dst + s : s;
 }
 
+// Same with a third partial array: the column sums of dx, always accumulated into dxColSum.
+__global__ void ln_bwd_final3_kernel(const float* __restrict__ partial, int parts, int d, float* __restrict__ dGamma, float* __restrict__ dBeta,
+                                     float* __restrict__ dxColSum, int accumulate) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= 3 * d) return;
+    float s = 0.f;
+    for (int k = 0; k < parts; k++) s += partial[(size_t)k * 3 * d + c];
+    if (c >= 2 * d) { dxColSum[c - 2 * d] += s; return; }
+    float* dst = c < d ? dGamma + c : dBeta + (c - d);
+    *dst = accumulate ? *dst + s : s;
+}
+
 int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const float* x, const float* gamma, const float* mean,
-                  const float* var, int rows, int d, float eps, float* dx, float* dGamma, float* dBeta, int accumulate) {
+                  const float* var, int rows, int d, float eps, float* dx, float* dGamma, float* dBeta, int accumulate, float* dxColSum) {
     if (d <= 0) return B200_OK;
     if (rows <= 0) {
         if (!accumulate) {
@@ -647,8 +671,17 @@ int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const f
         int cap = ctx->sm_count > 0 ? ctx->sm_count * 4 : 592;
         if (grid > cap) grid = cap;
         parts = grid;
-        B200_TRY(ensure_ws(ctx, (size_t)parts * 2 * d));
-        size_t smem = (size_t)warps * 2 * d * sizeof(float);
+        const int nacc = dxColSum ? 3 : 2;
+        B200_TRY(ensure_ws(ctx, (size_t)parts * nacc * d));
+        size_t smem = (size_t)warps * nacc * d * sizeof(float);
+        if (dxColSum) {
+            if (dOutB) ln_bwd_vec_kernel<true, true><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
+            else ln_bwd_vec_kernel<false, true><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
+            B200_LAUNCH_CHECK(ctx);
+            ln_bwd_final3_kernel<<<(3 * d + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, parts, d, dGamma, dBeta, dxColSum, accumulate);
+            B200_LAUNCH_CHECK(ctx);
+            return B200_OK;
+        }
         if (dOutB) ln_bwd_vec_kernel<true><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
         else ln_bwd_vec_kernel<false><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
         B200_LAUNCH_CHECK(ctx);
@@ -667,6 +700,7 @@ int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const f
     }
     ln_bwd_final_kernel<<<(2 * d + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, parts, d, dGamma, dBeta, accumulate);
     B200_LAUNCH_CHECK(ctx);
+    if (dxColSum) return k_colsum(ctx, dx, rows, d, d, dxColSum, 1);  // paths without the fused column sum
     return B200_OK;
 }
 

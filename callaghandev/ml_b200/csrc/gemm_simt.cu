@@ -164,7 +164,7 @@ int wgrad(b200_ctx* ctx, const float* dY, int lddy, const float* X, int ldx, int
     g.B = X; g.ldb = ldx; g.transB = 0;
     g.C = Wg; g.ldc = inDim; g.accumulate = 1;
     B200_TRY(gemm(ctx, g));
-    return k_colsum(ctx, dY, rows, outDim, lddy, bg, 1);
+    return bg ? k_colsum(ctx, dY, rows, outDim, lddy, bg, 1) : B200_OK;
 }
 int dgrad(b200_ctx* ctx, const float* dY, int lddy, const float* W, int rows, int outDim, int inDim, float* dX, int accumulate) {
     Gemm g;

@@ -297,9 +297,10 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         const LayerOff& L = lm->lay.layer[(size_t)l];
         LayerCache& k = lm->cache[(size_t)l];
         // LN2 backward (:903-906): dFF -> t1, gamma/beta grads accumulate.
-        B200_TRY(k_ln_backward(ctx, dX, nullptr, k.ln2In, P + L.g2, k.mean2, k.var2, N, d, 1e-5f, t1, G + L.g2, G + L.b2n, 1));
+        // The column sums of dFF are the bias gradient of the FFN output layer: taken in the same pass.
+        B200_TRY(k_ln_backward(ctx, dX, nullptr, k.ln2In, P + L.g2, k.mean2, k.var2, N, d, 1e-5f, t1, G + L.g2, G + L.b2n, 1, G + L.fb2));
         // FFN backward (NeuralNetwork.cs:773-884).  delta2 = dFF (output activation None).
-        B200_TRY(wgrad(ctx, t1, d, k.a1, f, N, d, f, G + L.W2, G + L.fb2));
+        B200_TRY(wgrad(ctx, t1, d, k.a1, f, N, d, f, G + L.W2, nullptr));
         {
             Gemm g;  // delta1 = (delta2 * W2) o act'(z1)
             g.M = N; g.N = f; g.K = d; g.A = t1; g.lda = d; g.B = P + L.W2; g.ldb = f; g.C = lm->d1; g.ldc = f;
@@ -314,9 +315,10 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
             B200_TRY(gemm(ctx, g));
         }
         // LN1 backward (:913-916): dAttnResidual -> t3.
-        B200_TRY(k_ln_backward(ctx, t2, nullptr, k.ln1In, P + L.g1, k.mean1, k.var1, N, d, 1e-5f, t3, G + L.g1, G + L.b1n, 1));
+        // Its column sums are the bias gradient of the attention output projection.
+        B200_TRY(k_ln_backward(ctx, t2, nullptr, k.ln1In, P + L.g1, k.mean1, k.var1, N, d, 1e-5f, t3, G + L.g1, G + L.b1n, 1, G + L.bO));
         // BackpropAttention (:933-987): output projection, attention core, inverse rotary, Q/K/V projections.
-        B200_TRY(wgrad(ctx, t3, d, k.attnO, d, N, d, d, G + L.WO, G + L.bO));
+        B200_TRY(wgrad(ctx, t3, d, k.attnO, d, N, d, d, G + L.WO, nullptr));
         {
             Gemm g;  // dConcatenated = dAttnResidual * WO (zero-initialised += in the reference)
             g.M = N; g.N = d; g.K = d; g.A = t3; g.lda = d; g.B = P + L.WO; g.ldb = d; g.C = t1; g.ldc = d;

@@ -92,6 +92,52 @@ def test_fused_epilogues(mgr, oracle):
         assert_close(ee, aa, TF32_TOL, "ProjectQKV (AccelerationManagerParityTests.cs:1202-1218 shapes)")
 
 
+@pytest.mark.parametrize("tile_mode,name", [("1", "one tile per CTA"), ("128", "persistent 128x128"), ("256", "persistent 128x256"), ("512", "two SMs per 256x256 tile")])
+def test_every_tcgen05_gemm_kernel(oracle, tile_mode, name):
+    """The dispatcher picks a kernel by shape; B200_GEMM_TILE_N (read when a context is created) forces one, so that
+    every kernel is checked on all four operand layouts, ragged tile edges, several tiles per CTA, and the fused
+    epilogues (bias, activation + pre-activation, derivative multiply, residual, accumulate)."""
+    import os
+
+    from callaghandev.ml_b200 import GEMM_TF32_TCGEN05, CudaB200AccelerationManager
+
+    old = os.environ.get("B200_GEMM_TILE_N")
+    os.environ["B200_GEMM_TILE_N"] = tile_mode
+    try:
+        m = CudaB200AccelerationManager(0, GEMM_TF32_TCGEN05)
+    finally:
+        if old is None:
+            del os.environ["B200_GEMM_TILE_N"]
+        else:
+            os.environ["B200_GEMM_TILE_N"] = old
+    if not m.has_tcgen05():
+        m.Dispose()
+        pytest.skip("device is not compute capability 10.x")
+    rng = np.random.default_rng(5)
+    for M, K, N in [(300, 260, 516), (2100, 384, 1280), (640, 4100, 256)]:
+        A, B = pt_matrix(M, K, 3), pt_matrix(K, N, 4)
+        emu = tf32(A) @ tf32(B)
+        assert_close(emu, m.MatrixMultiply(A, B), EMU_TOL, f"{name}: NN {M}x{K}x{N}")
+        assert_close(emu, m.MatrixMultiplyTranspose(A, np.ascontiguousarray(B.T)), EMU_TOL, f"{name}: NT {M}x{K}x{N}")
+        x, dy, W = pt_matrix(K, M, 5), pt_matrix(K, N, 6), pt_matrix(N, M, 7)
+        wg0, bg0, di0 = pt_matrix(N, M, 8), pt_vector(N, 9), pt_matrix(K, M, 10)
+        wg, bg, di = wg0.copy(), bg0.copy(), di0.copy()
+        m.BackpropLinearProjection(x, dy, W, wg, bg, di)
+        assert_close(wg0 + tf32(dy).T @ tf32(x), wg, EMU_TOL, f"{name}: dW {M}x{K}x{N}")
+        assert_close(di0 + tf32(dy) @ tf32(W), di, EMU_TOL, f"{name}: dX {M}x{K}x{N}")
+    widths, acts = [256, 512, 256], ["None", "Swish", "None"]
+    Ws = [rng.normal(0, 0.004, (512, 256)).astype(np.float32), rng.normal(0, 0.04, (256, 512)).astype(np.float32)]
+    Bs = [rng.normal(0, 0.5, 512).astype(np.float32), rng.normal(0, 0.1, 256).astype(np.float32)]
+    x, dO = rng.normal(0, 1, (700, 256)).astype(np.float32), rng.normal(0, 0.03, (700, 256)).astype(np.float32)
+    assert_close(oracle.FFNForwardBatch(x, widths, acts, Ws, Bs), m.FFNForwardBatch(x, widths, acts, Ws, Bs), TF32_TOL, name + ": FFN forward")
+    ge = [np.zeros((512, 256), np.float32), np.zeros((256, 512), np.float32)], [np.zeros(512, np.float32), np.zeros(256, np.float32)]
+    ga = [t.copy() for t in ge[0]], [t.copy() for t in ge[1]]
+    assert_close(oracle.FFNInputGradientBatch(x, dO, widths, acts, Ws, Bs, *ge), m.FFNInputGradientBatch(x, dO, widths, acts, Ws, Bs, *ga), TF32_TOL, name + ": FFN dInput")
+    for ee, aa in zip(ge[0] + ge[1], ga[0] + ga[1]):
+        assert_close(ee, aa, TF32_TOL, name + ": FFN gradients")
+    m.Dispose()
+
+
 def test_unqualified_shapes_fall_back_to_simt_in_auto_mode(mgr, oracle):
     from callaghandev.ml_b200 import GEMM_AUTO, CudaB200AccelerationManager
 
