@@ -156,7 +156,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
-    ap.add_argument("--seqs-per-pass", type=int, default=32)
+    ap.add_argument("--seqs-per-pass", type=int, default=128,
+                    help="sequences packed into one forward/backward pass (activation cache ~0.8 GB per sequence at c5; 128 fits one B200)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample (0 disables)")
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (sequences)")
@@ -187,6 +188,7 @@ def main():
         dist.init_process_group("gloo", rank=0, world_size=1)
 
     cfg = make_config(vocab_size=w["vocab"], embedding_dim=w["d"], num_heads=w["H"], num_layers=w["L"], ffn_dim=w["f"], ffn_activation="Relu")
+    args.seqs_per_pass = max(1, min(args.seqs_per_pass, -(-w["batch"] // world)))  # never more than this rank trains per step
     max_rows = args.seqs_per_pass * (w["seq"] - 1)
     mode = {"auto": GEMM_AUTO, "simt": GEMM_FP32_SIMT, "tcgen05": GEMM_TF32_TCGEN05}[args.gemm]
     tr = DataParallelLMTrainer(cfg, max_rows, local, None, mode)
