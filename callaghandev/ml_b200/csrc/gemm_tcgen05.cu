@@ -406,36 +406,38 @@ __global__ void __launch_bounds__(PAIR_THREADS) gemm_tcgen05_pair_kernel(const _
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ------------------------------------------------------------------ TMA producer (both CTAs)
-            int kc = 0;
-            bool ok = true;
-            for (int item = cluster; item < n_items && ok; item += n_clusters) {
-                int m0, n0, split;
-                decode_pair_item(p, item, m0, n0, split);
-                const int my_m = m0 + 128 * (int)rank, my_n = n0 + 128 * (int)rank;
-                const int kb_begin = split * p.kb_per_split;
-                const int kblocks = min(kblocks_total - kb_begin, p.kb_per_split);
-                for (int kb = 0; kb < kblocks; kb++, kc++) {
-                    const int s = kc % STAGES;
-                    ok = mbar_wait(empty0 + 8 * s, ((kc / STAGES) & 1) ^ 1, status, 41);
-                    if (!ok) break;
-                    const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
-                    const uint32_t bar = mapa_cluster(full0 + 8 * s, 0);  // the leader's barrier
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
-                    const int k0 = (kb_begin + kb) * BK;
+        // ------------------------------------------------------------------ TMA producer (both CTAs, whole warp: one copy per lane)
+        const int nA = p.a_mn_major ? 4 : 1, nB = p.b_mn_major ? 4 : 1;
+        int kc = 0;
+        bool ok = true;
+        for (int item = cluster; item < n_items && ok; item += n_clusters) {
+            int m0, n0, split;
+            decode_pair_item(p, item, m0, n0, split);
+            const int my_m = m0 + 128 * (int)rank, my_n = n0 + 128 * (int)rank;
+            const int kb_begin = split * p.kb_per_split;
+            const int kblocks = min(kblocks_total - kb_begin, p.kb_per_split);
+            for (int kb = 0; kb < kblocks; kb++, kc++) {
+                const int s = kc % STAGES;
+                ok = mbar_wait_warp(empty0 + 8 * s, ((kc / STAGES) & 1) ^ 1, status, 41);
+                if (!ok) break;
+                const uint32_t a_dst = tiles_s + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                const uint32_t bar = mapa_cluster(full0 + 8 * s, 0);  // the leader's barrier
+                if (rank == 0 && lane == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                __syncwarp();
+                const int k0 = (kb_begin + kb) * BK;
+                if (lane < nA) {
                     if (!p.a_mn_major) tma_load_2d_pair(a_dst, &mapA, bar, k0, my_m);
-                    else
-                        for (int c = 0; c < 4; c++) tma_load_2d_pair(a_dst + c * (BK * 128), &mapA, bar, my_m + 32 * c, k0);
+                    else tma_load_2d_pair(a_dst + lane * (BK * 128), &mapA, bar, my_m + 32 * lane, k0);
+                } else if (lane < nA + nB) {
+                    const int c = lane - nA;
                     if (!p.b_mn_major) tma_load_2d_pair(b_dst, &mapB, bar, k0, my_n);
-                    else
-                        for (int c = 0; c < 4; c++) tma_load_2d_pair(b_dst + c * (BK * 128), &mapB, bar, my_n + 32 * c, k0);
+                    else tma_load_2d_pair(b_dst + c * (BK * 128), &mapB, bar, my_n + 32 * c, k0);
                 }
             }
-            if (!ok) {  // failure path: give the copies already issued time to land before the CTA may exit
-                const long long t0 = clock64();
-                while (clock64() - t0 < 4000000LL) __nanosleep(256);
-            }
+        }
+        if (!ok) {  // failure path: give the copies already issued time to land before the CTA may exit
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000LL) __nanosleep(256);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
@@ -553,32 +555,37 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ------------------------------------------------------------------ TMA producer
-            int issued = 0;
-            bool ok = true;
-            for (int kb = 0; kb < kblocks && ok; kb++) {
-                const int s = kb % T_STAGES;
-                const uint32_t par = ((kb / T_STAGES) & 1) ^ 1;  // first pass over the ring finds every slot empty
-                ok = mbar_wait(empty0 + 8 * s, par, status, 1);
-                if (!ok) break;
-                const uint32_t a_dst = tiles_s + s * T_STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
-                mbar_expect_tx(bar, T_STAGE_BYTES);
-                const int k0 = (kb_begin + kb) * BK;
+        // ------------------------------------------------------------------ TMA producer (whole warp)
+        // Lane 0 waits for the slot and posts the byte count; then every copy of the stage is issued by its own lane in
+        // one warp instruction -- an M/N-contiguous operand is four 32-column boxes, and a single thread issuing eight
+        // copies per stage was slower than the MMAs that consume them.
+        const int nA = p.a_mn_major ? BM / 32 : 1, nB = p.b_mn_major ? T_BN / 32 : 1;
+        int issued = 0;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks && ok; kb++) {
+            const int s = kb % T_STAGES;
+            const uint32_t par = ((kb / T_STAGES) & 1) ^ 1;  // first pass over the ring finds every slot empty
+            ok = mbar_wait_warp(empty0 + 8 * s, par, status, 1);
+            if (!ok) break;
+            const uint32_t a_dst = tiles_s + s * T_STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * s;
+            if (lane == 0) mbar_expect_tx(bar, T_STAGE_BYTES);
+            __syncwarp();
+            const int k0 = (kb_begin + kb) * BK;
+            if (lane < nA) {
                 if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
-                else
-                    for (int c = 0; c < BM / 32; c++) tma_load_2d(a_dst + c * (BK * 128), &mapA, bar, m0 + 32 * c, k0);
+                else tma_load_2d(a_dst + lane * (BK * 128), &mapA, bar, m0 + 32 * lane, k0);
+            } else if (lane < nA + nB) {
+                const int c = lane - nA;
                 if (!p.b_mn_major) tma_load_2d(b_dst, &mapB, bar, k0, n0);
-                else
-                    for (int c = 0; c < T_BN / 32; c++) tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
-                issued = kb + 1;
+                else tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
             }
-            if (!ok) {
-                // failure path: wait (bounded) until the copies already issued have landed before the CTA may exit
-                for (int kb = (issued > T_STAGES ? issued - T_STAGES : 0); kb < issued; kb++) {
-                    const long long t0 = clock64();
-                    while (!mbar_test(full0 + 8 * (kb % T_STAGES), (kb / T_STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                }
+            issued = kb + 1;
+        }
+        if (!ok && lane == 0) {
+            // failure path: wait (bounded) until the copies already issued have landed before the CTA may exit
+            for (int kb = (issued > T_STAGES ? issued - T_STAGES : 0); kb < issued; kb++) {
+                const long long t0 = clock64();
+                while (!mbar_test(full0 + 8 * (kb % T_STAGES), (kb / T_STAGES) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
@@ -612,8 +619,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
         }
     } else {
         // ---------------------------------------------------------------------- epilogue (warps 2..5)
-        bool ok = mbar_wait(accum_bar, 0, status, 3);
-        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective: the whole warp takes the same path
+        const bool ok = mbar_wait_warp(accum_bar, 0, status, 3);  // one polling lane per warp; tcgen05.ld is warp-collective, so the warp decides together
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             const int q = warp & 3;  // this warp may touch TMEM lanes [32q, 32q+32)
