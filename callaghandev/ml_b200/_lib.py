@@ -106,6 +106,12 @@ PROTOTYPES = {
     "b200_lm_batch_destroy": (_i32, [_vp]),
     "b200_lm_accumulate_batch": (_i32, [_vp, _vp, _f, _i]),
     "b200_lm_train_step_batch": (_i32, [_vp, _vp, _fl, _i32, _fl, _i32, _f, _f, _i]),
+    "b200_lm_validate_discrete": (_i32, [_vp, _i, _i, _i32, _f, _i]),
+    "b200_lm_validate_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _f, _i]),
+    "b200_lm_download_optimizer_state": (_i32, [_vp, _i32, _f, _i64, _i64]),
+    "b200_lm_upload_optimizer_state": (_i32, [_vp, _i32, _f, _i64, _i64]),
+    "b200_lm_get_step_index": (_i32, [_vp, _i]),
+    "b200_lm_set_step_index": (_i32, [_vp, _i32]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),
     "b200_mlp_create": (_i32, [_vp, _i32, _i, _i, _i32, _fl, _fl, _fl, _i32, _pp]),
     "b200_mlp_destroy": (_i32, [_vp]),

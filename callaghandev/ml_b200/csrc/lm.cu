@@ -530,6 +530,52 @@ int accumulate(b200_lm* lm, const Batch& b, int n_seq, float* loss_sum, int32_t*
     return run_plan(lm, b, plan, nullptr, loss_sum, valid_count);
 }
 
+// TransformerTrainer.Validate / ValidateContinuous (TransformerTrainer.cs:1142-1268): forward and loss only.  Every
+// valid sequence contributes (its mean loss) x (its trained rows); a sequence whose loss is not finite is skipped; the
+// result is the sum divided by the contributing rows.  Sequences are packed into passes like in training.
+int validate(b200_lm* lm, const Batch& b, int n_seq, float* mean_loss, int32_t* items) {
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    *mean_loss = 0.f;
+    *items = 0;
+    Plan plan;
+    B200_TRY(plan_batch(lm, b, n_seq, plan));
+    // per-sequence results in input order, so that the summation order is the reference's (sequence by sequence)
+    std::vector<float> seqLoss((size_t)n_seq, 0.f);
+    std::vector<char> seqUsed((size_t)n_seq, 0);
+    std::vector<float> rowLoss((size_t)lm->maxRows);
+    for (const Pass& p : plan.passes) {
+        if (p.seqs.empty()) continue;
+        B200_TRY(stage_pass(lm, b, p, lm->own));
+        lm->cur = lm->own;
+        B200_TRY(forward_pass(lm, p));
+        B200_TRY(loss_pass(lm, p));  // also writes the loss gradient over the logits, which nobody reads here
+        B200_CUDA(ctx, cudaMemcpyAsync(rowLoss.data(), lm->rowLoss, sizeof(float) * p.rows, cudaMemcpyDeviceToHost, ctx->stream));
+        B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        int r = 0;
+        for (const Seq& q : p.seqs) {
+            float sum = 0.f;
+            for (int t = 0; t < q.len; t++, r++) sum += rowLoss[(size_t)r];
+            const float loss = sum / ((float)q.len * (c.loss_kind == 1 ? c.output_dim : 1));  // CPU:2438 / CPU:2489
+            seqLoss[(size_t)q.index] = loss * (float)q.len;
+            seqUsed[(size_t)q.index] = std::isfinite(loss) ? 1 : 0;
+        }
+    }
+    B200_TRY(check_device_status(ctx));
+    float total = 0.f;
+    int32_t count = 0;
+    for (int sidx = 0; sidx < n_seq; sidx++) {
+        if (!seqUsed[(size_t)sidx]) continue;
+        total += seqLoss[(size_t)sidx];
+        count += b.off[sidx + 1] - b.off[sidx] - 1;
+    }
+    *items = count;
+    *mean_loss = count > 0 ? total / (float)count : 0.f;
+    return B200_OK;
+}
+
 int collect_backward_time(b200_lm* lm) {
     // events are laid out in groups of four per attempted pass: forward start, forward end, loss end, backward end
     for (size_t i = 0; i + 3 < lm->t_used; i += 4) {
@@ -754,6 +800,62 @@ int32_t b200_lm_accumulate_continuous(b200_lm* lm, const float* features, const 
     Batch b;
     b.feats = features; b.regT = reg_targets; b.clsT = class_targets; b.off = seq_offsets;
     return accumulate(lm, b, n_seq, loss_sum, valid_count);
+}
+
+int32_t b200_lm_validate_discrete(b200_lm* lm, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float* mean_loss, int32_t* items) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (!lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes continuous inputs");
+    if (!tokens || !seq_offsets || !mean_loss || !items || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    Batch b;
+    b.tokens = tokens; b.off = seq_offsets;
+    return validate(lm, b, n_seq, mean_loss, items);
+}
+
+int32_t b200_lm_validate_continuous(b200_lm* lm, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                    const int32_t* seq_offsets, int32_t n_seq, float* mean_loss, int32_t* items) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (lm->cfg.discrete) return lm_fail(lm, B200_ERR_INVALID_ARG, "model takes token ids");
+    if (!features || !seq_offsets || !mean_loss || !items || n_seq < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "null batch argument");
+    if (lm->cfg.loss_kind == 1 ? !reg_targets : !class_targets) return lm_fail(lm, B200_ERR_INVALID_ARG, "targets missing for the configured loss");
+    Batch b;
+    b.feats = features; b.regT = reg_targets; b.clsT = class_targets; b.off = seq_offsets;
+    return validate(lm, b, n_seq, mean_loss, items);
+}
+
+// Optimiser state for checkpoints: kind 0 = first moments, 1 = second moments (same layout as the parameter arena).
+static int32_t opt_state_copy(b200_lm* lm, int32_t which, float* host_out, const float* host_in, int64_t offset, int64_t count, bool upload) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (which != 0 && which != 1) return lm_fail(lm, B200_ERR_INVALID_ARG, "optimizer state index must be 0 (first moments) or 1 (second moments)");
+    if (lm->opt != B200_OPT_ADAM) return lm_fail(lm, B200_ERR_INVALID_ARG, "the configured optimizer keeps no state");
+    b200_ctx* ctx = lm->ctx;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B200_CUDA(ctx, cudaSetDevice(ctx->device));
+        if (!lm->M) {  // not stepped yet: the moments are zero
+            B200_CUDA(ctx, cudaMalloc(&lm->M, sizeof(float) * (size_t)lm->lay.total));
+            B200_CUDA(ctx, cudaMalloc(&lm->V, sizeof(float) * (size_t)lm->lay.total));
+            B200_CUDA(ctx, cudaMemsetAsync(lm->M, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
+            B200_CUDA(ctx, cudaMemsetAsync(lm->V, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
+        }
+    }
+    return lm_copy(lm, host_out, host_in, which == 0 ? lm->M : lm->V, offset, count, upload);
+}
+int32_t b200_lm_download_optimizer_state(b200_lm* lm, int32_t which, float* host, int64_t offset, int64_t count) {
+    return opt_state_copy(lm, which, host, nullptr, offset, count, false);
+}
+int32_t b200_lm_upload_optimizer_state(b200_lm* lm, int32_t which, const float* host, int64_t offset, int64_t count) {
+    return opt_state_copy(lm, which, nullptr, host, offset, count, true);
+}
+int32_t b200_lm_get_step_index(b200_lm* lm, int32_t* step_index) {
+    if (!lm || !step_index) return B200_ERR_INVALID_ARG;
+    *step_index = lm->step_index;
+    return B200_OK;
+}
+int32_t b200_lm_set_step_index(b200_lm* lm, int32_t step_index) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    if (step_index < 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "step index must not be negative");
+    lm->step_index = step_index;
+    return B200_OK;
 }
 
 int32_t b200_lm_apply_step(b200_lm* lm, int32_t global_valid_count, float lr, int32_t use_clip, float clip_threshold, int32_t do_step, float* grad_norm) {

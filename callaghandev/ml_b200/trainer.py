@@ -107,6 +107,55 @@ class B200LanguageModelTrainer:
                                                             clip_threshold, int(bool(do_step)), C.byref(loss), C.byref(norm), C.byref(valid)))
         return loss.value, norm.value, valid.value
 
+    # ---- TransformerTrainer.Validate / ValidateContinuous: forward + loss only
+    def validate_discrete(self, tokens, seq_offsets):
+        """(token-weighted mean cross-entropy, contributing rows) of the valid sequences."""
+        t, o = _i(tokens), _i(seq_offsets)
+        loss, items = C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_validate_discrete(self.h, _pi(t), _pi(o), len(o) - 1, C.byref(loss), C.byref(items)))
+        return loss.value, items.value
+
+    def validate_continuous(self, features, seq_offsets, reg_targets=None, class_targets=None):
+        x, o = _f(features), _i(seq_offsets)
+        r = None if reg_targets is None else _f(reg_targets)
+        k = None if class_targets is None else _i(class_targets)
+        loss, items = C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_validate_continuous(self.h, _pf(x), _pf(r), None if k is None else _pi(k), _pi(o), len(o) - 1,
+                                                          C.byref(loss), C.byref(items)))
+        return loss.value, items.value
+
+    # ---- optimiser state (checkpoints that resume on the device)
+    def download_optimizer_state(self):
+        """(first moments, second moments, step index) of Adam, in the layout of the parameter arena."""
+        m, v = np.zeros(self.param_count, np.float32), np.zeros(self.param_count, np.float32)
+        self.mgr._ck(self.lib.b200_lm_download_optimizer_state(self.h, 0, _pf(m), 0, m.size))
+        self.mgr._ck(self.lib.b200_lm_download_optimizer_state(self.h, 1, _pf(v), 0, v.size))
+        step = C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_get_step_index(self.h, C.byref(step)))
+        return m, v, step.value
+
+    def upload_optimizer_state(self, m, v, step_index):
+        m, v = _f(m).reshape(-1), _f(v).reshape(-1)
+        self.mgr._ck(self.lib.b200_lm_upload_optimizer_state(self.h, 0, _pf(m), 0, m.size))
+        self.mgr._ck(self.lib.b200_lm_upload_optimizer_state(self.h, 1, _pf(v), 0, v.size))
+        self.mgr._ck(self.lib.b200_lm_set_step_index(self.h, int(step_index)))
+
+    def save_checkpoint(self, path):
+        """Parameters, Adam moments and step index in one .npz (the reference's weights.bin holds the parameters only)."""
+        blobs = {"params": self.download_params()}
+        try:
+            m, v, step = self.download_optimizer_state()
+            blobs.update(adam_m=m, adam_v=v, step_index=np.int64(step))
+        except Exception:  # SGD keeps no state
+            pass
+        np.savez(path, **blobs)
+
+    def load_checkpoint(self, path):
+        z = np.load(path)
+        self.upload_params(z["params"])
+        if "adam_m" in z:
+            self.upload_optimizer_state(z["adam_m"], z["adam_v"], int(z["step_index"]))
+
     # ---- device-resident batches
     def prepare_discrete(self, tokens, seq_offsets):
         """Plan, pack and copy a batch to the device once; returns a handle for train_step_batch / accumulate_batch."""

@@ -270,6 +270,21 @@ B200_API int32_t b200_lm_accumulate_discrete(b200_lm*, const int32_t* tokens, co
 B200_API int32_t b200_lm_accumulate_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
                                                const int32_t* seq_offsets, int32_t n_seq, float* loss_sum, int32_t* valid_count);
 B200_API int32_t b200_lm_apply_step(b200_lm*, int32_t global_valid_count, float lr, int32_t use_clip, float clip_threshold, int32_t do_step, float* grad_norm);
+/* TransformerTrainer.Validate (TransformerTrainer.cs:1142-1184) / ValidateContinuous (:1185-1268): forward and loss
+ * only, on the device.  Every valid sequence contributes its mean loss times its trained rows (len-1); sequences that are
+ * too short, hold invalid ids or produce a non-finite loss are skipped; *mean_loss = sum / contributing rows (0 when
+ * none), *items = contributing rows. */
+B200_API int32_t b200_lm_validate_discrete(b200_lm*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float* mean_loss, int32_t* items);
+B200_API int32_t b200_lm_validate_continuous(b200_lm*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                             const int32_t* seq_offsets, int32_t n_seq, float* mean_loss, int32_t* items);
+/* Optimiser state for checkpoints that resume without leaving the resident path (LanguageModel.Save/Load,
+ * LanguageModel.cs:706-839, write weights only; the Adam moments are this library's extension).  which = 0: first
+ * moments, 1: second moments; same layout and offsets as the parameter arena.  The step index drives the bias
+ * correction. */
+B200_API int32_t b200_lm_download_optimizer_state(b200_lm*, int32_t which, float* host, int64_t offset, int64_t count);
+B200_API int32_t b200_lm_upload_optimizer_state(b200_lm*, int32_t which, const float* host, int64_t offset, int64_t count);
+B200_API int32_t b200_lm_get_step_index(b200_lm*, int32_t* step_index);
+B200_API int32_t b200_lm_set_step_index(b200_lm*, int32_t step_index);
 /* Device time of the phases of the last step in milliseconds: [0] forward, [1] loss, [2] backward, [3] step. */
 B200_API int32_t b200_lm_get_timings(b200_lm*, float* ms4);
 

@@ -1006,6 +1006,53 @@ API real ref_lm_train_step(const ref_lm_config* c, real* P, real* G, const int32
     return totalLoss / validCount;
 }
 
+/* TT:1142-1184 Validate / TT:1185-1268 ValidateContinuous: every valid sequence on its own, forward and loss only
+ * (the forward of a single sequence is the count == 1 path of lm_bucket; its gradients go to a scratch arena and are
+ * dropped).  totalLoss += loss * effectiveLen, totalItems += effectiveLen; sequences with a non-finite loss are skipped.
+ * Returns totalLoss / totalItems (0 when nothing contributed). */
+API real ref_lm_validate(const ref_lm_config* c, const real* P, const int32_t* tokens, const real* contIn, const real* regTgt,
+                         const int32_t* clsTgt, const int32_t* seqOff, int nSeq, int32_t* itemsOut) {
+    lm_off o;
+    lm_layout(c, &o);
+    real* G = ralloc((size_t)o.total);
+    int F = c->input_feature_dim, O = c->output_dim;
+    real totalLoss = 0;
+    int totalItems = 0;
+    for (int s = 0; s < nSeq; s++) {
+        int n = seqOff[s + 1] - seqOff[s];
+        if (n < 2) continue;
+        int base = seqOff[s], len = n - 1, valid = 1;
+        if (c->discrete) /* TT:1467-1478 TokensAreValid */
+            for (int t = 0; t < n; t++) {
+                int id = tokens[base + t];
+                if (id < 0 || id >= c->vocab_size) { valid = 0; break; }
+            }
+        if (!valid) continue;
+        int32_t* ids = (int32_t*)calloc((size_t)len + 1, sizeof(int32_t));
+        int32_t* tgt = (int32_t*)calloc((size_t)len + 1, sizeof(int32_t));
+        real* cont = c->discrete ? NULL : ralloc((size_t)len * F);
+        real* rt = (c->loss_kind == 1) ? ralloc((size_t)len * O) : NULL;
+        for (int t = 0; t < len; t++) {
+            if (c->discrete) { ids[t] = tokens[base + t]; tgt[t] = tokens[base + t + 1]; }
+            else {
+                memcpy(cont + (size_t)t * F, contIn + (size_t)(base + t) * F, sizeof(real) * (size_t)F);
+                if (c->loss_kind == 1) memcpy(rt + (size_t)t * O, regTgt + (size_t)(base + t + 1) * O, sizeof(real) * (size_t)O);
+                else tgt[t] = clsTgt[base + t + 1];
+            }
+        }
+        real loss = 0;
+        lm_bucket(c, &o, P, G, ids, cont, tgt, rt, len, 1, &loss);
+        if (isfinite(loss)) {
+            totalLoss += loss * (real)len;
+            totalItems += len;
+        }
+        free(ids); free(tgt); free(cont); free(rt);
+    }
+    free(G); free(o.layer);
+    if (itemsOut) *itemsOut = totalItems;
+    return totalItems > 0 ? totalLoss / (real)totalItems : 0;
+}
+
 /* ---------------------------------------------------------------- MLP mini-batch step (NN:499-610, GPUB:251-358) */
 
 enum { COST_MSE = 0, COST_ZERO_WEIGHTED_MSE = 1, COST_BCE = 2, COST_MAE = 3, COST_CCE = 4, COST_HUBER = 5 };

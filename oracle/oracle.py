@@ -67,6 +67,7 @@ class Oracle:
         lib.ref_MSELossAndGradient.restype = self.real
         lib.ref_SquaredNorm.restype = self.real
         lib.ref_lm_train_step.restype = self.real
+        lib.ref_lm_validate.restype = self.real
         lib.ref_mlp_learn_batch.restype = self.real
         lib.ref_lm_param_count.restype = C.c_int64
         assert lib.ref_real_size() == np.dtype(self.dt).itemsize
@@ -328,6 +329,19 @@ class Oracle:
                                           self.p(off), len(off) - 1, self.r(lr), int(bool(use_clip)), self.r(clip_thr), int(bool(do_step)),
                                           C.byref(norm), C.byref(valid))
         return float(loss), float(norm.value), int(valid.value)
+
+    def lm_validate(self, cfg: LMConfig, params, seq_offsets, tokens=None, cont=None, reg_targets=None, cls_targets=None):
+        """TransformerTrainer.Validate / ValidateContinuous: (mean loss over contributing rows, contributing rows)."""
+        assert params.dtype == self.dt
+        off = np.ascontiguousarray(np.asarray(seq_offsets, np.int32))
+        tok = None if tokens is None else np.ascontiguousarray(np.asarray(tokens, np.int32))
+        cont = None if cont is None else self.a(cont)
+        reg = None if reg_targets is None else self.a(reg_targets)
+        cls = None if cls_targets is None else np.ascontiguousarray(np.asarray(cls_targets, np.int32))
+        items = C.c_int32(0)
+        loss = self.lib.ref_lm_validate(C.byref(cfg), self.p(params), self.p(tok), self.p(cont), self.p(reg), self.p(cls), self.p(off), len(off) - 1,
+                                        C.byref(items))
+        return float(loss), int(items.value)
 
     # ------------------------------------------------------------------ MLP batch step
     def mlp_learn_batch(self, widths, acts, weights, biases, X, Y, cost="mse", huber_delta=1.0, lr=0.01, lam=0.0, clip_thr=1.0):

@@ -329,3 +329,68 @@ def test_prepared_batch_equals_host_path(mgr, oracle):
     assert np.array_equal(a.download_params(), b.download_params())
     b.release_batch(h)
     a.close(); b.close()
+
+
+def test_validate_discrete_and_continuous(mgr, oracle):
+    """TransformerTrainer.Validate / ValidateContinuous on the device: row-weighted mean loss of the valid sequences,
+    forward and loss only (weights and gradients untouched), packed into several passes."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(21)
+    cfg = lm_config(vocab=200, d=64, H=4, L=2, f=128, act="Relu")
+    toks, off = token_batch(rng, 12, 200, 2, 48)
+    toks = toks.copy()
+    toks[off[3] + 1] = 999          # an id outside the vocabulary: the sequence is skipped (TokensAreValid)
+    off = np.concatenate([off, [off[-1] + 1]]).astype(np.int32)  # and one sequence of a single token: too short
+    toks = np.concatenate([toks, [5]]).astype(np.int32)
+    P = init_params(oracle, cfg, 31)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 100)  # several passes
+    t.upload_params(P)
+    el, ei = oracle.lm_validate(cfg, P, off, tokens=toks)
+    al, ai = t.validate_discrete(toks, off)
+    assert ai == ei and ei > 0
+    assert_close(el, al, 1e-5, "validation loss (discrete)")
+    assert np.array_equal(t.download_params(), P), "validation must not touch the weights"
+    t.close()
+
+    cfg = lm_config(F=5, O=1, d=64, H=4, L=2, f=256, act="Tanh", discrete=False, loss="mse")
+    x, tg, off = random_walk_batch(rng, 5, 30, 5, 3)
+    P = init_params(oracle, cfg, 32)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 64)
+    t.upload_params(P)
+    el, ei = oracle.lm_validate(cfg, P, off, cont=x, reg_targets=tg)
+    al, ai = t.validate_continuous(x, off, reg_targets=tg)
+    assert ai == ei == 5 * 29
+    assert_close(el, al, 1e-5, "validation loss (continuous regression)")
+    t.close()
+
+
+def test_checkpoint_with_optimizer_state_resumes_bit_identically(mgr, oracle, tmp_path):
+    """Parameters + Adam moments + step index survive a save/load round trip: a run that is interrupted after two steps
+    and resumed in a fresh trainer ends with exactly the weights of the uninterrupted run."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(4)
+    cfg = lm_config(vocab=40, d=32, H=4, L=1, f=64)
+    toks, off = token_batch(rng, 4, 40, 4, 20)
+    P = init_params(oracle, cfg, 12)
+    a = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 256)
+    a.set_optimizer("adam", 0.9, 0.999, 1e-8)
+    a.upload_params(P)
+    for _ in range(2):
+        a.train_step_discrete(toks, off, 3e-4, True, 1.0, True)
+    path = str(tmp_path / "ckpt.npz")
+    a.save_checkpoint(path)
+    m, v, step = a.download_optimizer_state()
+    assert step == 2 and np.any(m != 0) and np.all(v >= 0)
+    for _ in range(2):
+        a.train_step_discrete(toks, off, 3e-4, True, 1.0, True)
+    want = a.download_params()
+    a.close()
+    b = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 256)
+    b.set_optimizer("adam", 0.9, 0.999, 1e-8)
+    b.load_checkpoint(path)
+    for _ in range(2):
+        b.train_step_discrete(toks, off, 3e-4, True, 1.0, True)
+    assert np.array_equal(b.download_params(), want)
+    b.close()

@@ -383,3 +383,20 @@ def test_ffn_paths(oracle, oracle64):  # NN:629-716, NN:773-987 incl. the 0.1 Le
         assert_close(d1 @ W[0], dIn, 1e-12, "ffn dIn " + act)
         assert_close(1 + dO.T @ a, wg[1], 1e-12, "ffn W2g"); assert_close(1 + d1.T @ x, wg[0], 1e-12, "ffn W1g")
         assert_close(1 + dO.sum(0), bg[1], 1e-12, "ffn b2g"); assert_close(1 + d1.sum(0), bg[0], 1e-12, "ffn b1g")
+
+
+def test_validate_agrees_with_the_train_step_loss_on_equal_lengths(oracle):
+    """TransformerTrainer.Validate (TransformerTrainer.cs:1142-1184) weights every sequence's mean loss by its rows; for
+    sequences of one length that is the bucket loss the train step reports (TransformerTrainer.cs:294, :326)."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from lmutil import init_params, lm_config, token_batch
+
+    rng = np.random.default_rng(0)
+    cfg = lm_config(vocab=50, d=32, H=2, L=1, f=64)
+    toks, off = token_batch(rng, 3, 50, 9, 9)
+    P = init_params(oracle, cfg, 1)
+    loss, _, valid = oracle.lm_train_step(cfg, P.copy(), np.zeros_like(P), off, tokens=toks, do_step=False)
+    vloss, items = oracle.lm_validate(cfg, P, off, tokens=toks)
+    assert valid == 3 and items == 3 * 8
+    assert abs(loss - vloss) <= 1e-5 * max(1.0, abs(loss))
