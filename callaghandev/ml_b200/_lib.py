@@ -112,6 +112,12 @@ PROTOTYPES = {
     "b200_lm_upload_optimizer_state": (_i32, [_vp, _i32, _f, _i64, _i64]),
     "b200_lm_get_step_index": (_i32, [_vp, _i]),
     "b200_lm_set_step_index": (_i32, [_vp, _i32]),
+    "b200_lm_gen_create": (_i32, [_vp, _i32, _pp]),
+    "b200_lm_gen_destroy": (_i32, [_vp]),
+    "b200_lm_gen_reset": (_i32, [_vp]),
+    "b200_lm_gen_length": (_i32, [_vp, _i]),
+    "b200_lm_gen_step": (_i32, [_vp, _i32, _f]),
+    "b200_lm_gen_greedy": (_i32, [_vp, _i, _i32, _i32, _i, _i]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),
     "b200_mlp_create": (_i32, [_vp, _i32, _i, _i, _i32, _fl, _fl, _fl, _i32, _pp]),
     "b200_mlp_destroy": (_i32, [_vp]),

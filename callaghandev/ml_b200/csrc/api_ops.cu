@@ -124,6 +124,7 @@ int32_t b200_destroy(b200_ctx* ctx) {
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     for (auto& kv : ctx->rope)
         if (kv.second.dev) cudaFree(kv.second.dev);
+    for (float* old : ctx->rope_retired) cudaFree(old);
     for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;

@@ -34,6 +34,7 @@ struct b200_ctx {
     size_t ws_floats = 0;
     float* pinned = nullptr;  // 4 KiB pinned staging for scalars
     std::map<std::pair<int, uint32_t>, RopeTable> rope;  // key: (headDim, bits of baseTheta)
+    std::vector<float*> rope_retired;  // smaller tables replaced by larger ones: trainers may still point at them, freed with the context
     void* tmap_encode = nullptr;                          // cuTensorMapEncodeTiled entry point (resolved lazily)
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
@@ -134,6 +135,7 @@ int k_sqnorm(b200_ctx*, const float* x, int64_t n, float* out_dev);  // out_dev[
 // out[j] (+)= sum_i x[i, j] over rows; x has leading dimension ld.
 int k_colsum(b200_ctx*, const float* x, int rows, int cols, int ld, float* out, int accumulate);
 int k_embed(b200_ctx*, const int32_t* ids_dev, int count, const float* emb, int embDim, float* out);
+int k_argmax(b200_ctx*, const float* x, int n, int32_t* out_dev);  // index of the maximum (lowest index among equals)
 // Deterministic scatter-add: rows of (dXa [+ dXb]) sorted by id on the host.  seg_id[s] = vocabulary row, rows of
 // segment s are perm[seg_off[s] .. seg_off[s+1]) in ascending original order.
 int k_embed_scatter(b200_ctx*, float* eg, const float* dXa, const float* dXb, const int32_t* seg_id, const int32_t* seg_off,

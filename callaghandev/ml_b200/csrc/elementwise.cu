@@ -59,7 +59,7 @@ int rope_table(b200_ctx* ctx, int headDim, float baseTheta, int rows, const floa
             }
         }
         B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        if (t.dev) cudaFree(t.dev);
+        if (t.dev) ctx->rope_retired.push_back(t.dev);  // a trainer or a decoding session may still hold this pointer
         t.dev = nullptr;
         t.rows = 0;
         B200_CUDA(ctx, cudaMalloc(&t.dev, h.size() * sizeof(float)));
@@ -246,6 +246,43 @@ int k_colsum(b200_ctx* ctx, const float* x, int rows, int cols, int ld, float* o
     else colsum_partial_kernel<<<dim3(colTiles, chunks), dim3(32, 8), 0, ctx->stream>>>(x, rows, cols, ld, rowsPerChunk, ctx->ws);
     B200_LAUNCH_CHECK(ctx);
     colsum_final_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, chunks, cols, out, accumulate);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ argmax (greedy decoding)
+// out[0] = index of the largest of x[0..n) (the lowest index among equals); one block.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ x, int n, int32_t* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[i];
+        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { if (v > bv || bi == 0x7fffffff || (v == bv && i < bi)) { bv = v; bi = i; } }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int warps = (blockDim.x + 31) >> 5;
+        bv = threadIdx.x < warps ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < warps ? si[threadIdx.x] : 0x7fffffff;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[0] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+int k_argmax(b200_ctx* ctx, const float* x, int n, int32_t* out) {
+    if (n <= 0) return B200_OK;
+    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(x, n, out);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -1007,3 +1007,176 @@ int32_t b200_lm_get_timings(b200_lm* lm, float* ms4) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ incremental decoding
+// LanguageModel.Generate's decoder path (LanguageModel.cs:270-537) with the key/value cache in device memory: every
+// token is pushed through the blocks at its absolute position (ForwardDecoderTokenFromId), its rotated K and its V rows
+// are appended to the per-layer cache, attention runs over the cached rows (all in the past, so no mask), and
+// ProjectLastTokenOnly gives the next-token logits.  Sampling stays with the caller (the reference draws from its own
+// System.Random); b200_lm_gen_greedy is the arg-max special case that never leaves the device.
+struct b200_lm_gen {
+    b200_lm* lm = nullptr;
+    int maxLen = 0, len = 0;
+    char* block = nullptr;
+    float *K = nullptr, *V = nullptr;  // [layers][maxLen][d]
+    float *x = nullptr, *qkv = nullptr, *attnO = nullptr, *proj = nullptr, *n1 = nullptr, *z1 = nullptr, *a1 = nullptr, *lnIn = nullptr, *stat = nullptr,
+          *logits = nullptr, *rowStat = nullptr;
+    int32_t *tokens = nullptr, *posArr = nullptr;  // device: token ids by position, posArr[i] = i
+    AttnSeg* segs = nullptr;                       // segs[p] = one query row against cached rows 0..p
+    const float* rope = nullptr;
+};
+
+namespace {
+
+// One token through the model.  The id is read from gen->tokens[pos] on the device; logits land in gen->logits.
+int gen_forward_token(b200_lm_gen* g, int pos) {
+    b200_lm* lm = g->lm;
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    const int d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim;
+    const float* P = lm->P;
+    B200_TRY(k_embed(ctx, g->tokens + pos, 1, P + lm->lay.in0, d, g->x));
+    for (int l = 0; l < c.num_layers; l++) {
+        const LayerOff& L = lm->lay.layer[(size_t)l];
+        float* Kc = g->K + (size_t)l * g->maxLen * d;
+        float* Vc = g->V + (size_t)l * g->maxLen * d;
+        const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
+        float* outs[3] = {g->qkv, Kc + (size_t)pos * d, Vc + (size_t)pos * d};  // K and V go straight into their cache rows
+        for (int i = 0; i < 3; i++) B200_TRY(linear_fwd(ctx, g->x, 1, d, P + Ws[i], P + Bs[i], d, outs[i], d));
+        B200_TRY(k_rope(ctx, g->qkv, 0, 1, 1, d, 0, H, hd, g->rope, g->posArr + pos, 0, 0));
+        B200_TRY(k_rope(ctx, Kc + (size_t)pos * d, 0, 1, 1, d, 0, H, hd, g->rope, g->posArr + pos, 0, 0));
+        Attn a;
+        a.Q = g->qkv; a.K = Kc; a.V = Vc; a.ldq = a.ldk = a.ldv = d;
+        a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = 0;
+        a.segs_dev = g->segs + pos; a.nSeg = 1; a.maxQLen = 1; a.maxKLen = pos + 1; a.totalQ = 1; a.totalK = pos + 1;
+        a.O = g->attnO; a.ldo = d; a.rowMax = g->rowStat; a.rowSum = g->rowStat + H;
+        B200_TRY(attn_forward(ctx, a));
+        B200_TRY(linear_fwd(ctx, g->attnO, 1, d, P + L.WO, P + L.bO, d, g->proj, d));
+        B200_TRY(k_ln_forward(ctx, g->x, g->proj, P + L.g1, P + L.b1n, 1, d, 1e-5f, g->n1, g->stat, g->stat + 1, nullptr, g->lnIn));
+        {
+            Gemm gm;
+            gm.M = 1; gm.N = f; gm.K = d; gm.A = g->n1; gm.lda = d; gm.B = P + L.W1; gm.ldb = d; gm.transB = 1;
+            gm.C = g->a1; gm.ldc = f; gm.bias = P + L.fb1; gm.zout = g->z1; gm.ldz = f; gm.act = c.ffn_activation;
+            B200_TRY(gemm(ctx, gm));
+        }
+        B200_TRY(linear_fwd(ctx, g->a1, 1, f, P + L.W2, P + L.fb2, d, g->proj, d));
+        B200_TRY(k_ln_forward(ctx, g->n1, g->proj, P + L.g2, P + L.b2n, 1, d, 1e-5f, g->x, g->stat, g->stat + 1, nullptr, g->lnIn));
+    }
+    return linear_fwd(ctx, g->x, 1, d, P + lm->lay.Wout, P + lm->lay.bout, O, g->logits, O);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
+    if (!lm || !out) return B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    if (!c.discrete) return lm_fail(lm, B200_ERR_UNSUPPORTED, "Generate is only supported for discrete token data types.");
+    if (max_len <= 0) return lm_fail(lm, B200_ERR_INVALID_ARG, "max_len must be positive");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t d = (size_t)c.embedding_dim, f = (size_t)c.ffn_dim, O = (size_t)c.output_dim, Lc = (size_t)c.num_layers, T = (size_t)max_len;
+    auto rnd = [](size_t n) { return (n + 63) & ~(size_t)63; };
+    const size_t floats = 2 * rnd(Lc * T * d) + 6 * rnd(d) + 2 * rnd(f) + rnd(O) + rnd(64) + rnd(4 * (size_t)c.num_heads);
+    const size_t ints = 2 * rnd(T + 1);
+    const size_t bytes = floats * 4 + ints * 4 + rnd(T * sizeof(AttnSeg) / 4 + 1) * 4;
+    b200_lm_gen* g = new b200_lm_gen();
+    g->lm = lm; g->maxLen = max_len;
+    if (cudaMalloc(&g->block, bytes) != cudaSuccess) {
+        delete g;
+        return lm_fail(lm, B200_ERR_CUDA, "out of device memory for the key/value cache");
+    }
+    char* cur = g->block;
+    auto takef = [&](size_t n) { float* r = reinterpret_cast<float*>(cur); cur += rnd(n) * 4; return r; };
+    g->K = takef(Lc * T * d); g->V = takef(Lc * T * d);
+    g->x = takef(d); g->qkv = takef(d); g->attnO = takef(d); g->proj = takef(d); g->n1 = takef(d); g->lnIn = takef(d);
+    g->z1 = takef(f); g->a1 = takef(f); g->logits = takef(O); g->stat = takef(64); g->rowStat = takef(4 * (size_t)c.num_heads);
+    g->tokens = reinterpret_cast<int32_t*>(cur); cur += rnd(T + 1) * 4;
+    g->posArr = reinterpret_cast<int32_t*>(cur); cur += rnd(T + 1) * 4;
+    g->segs = reinterpret_cast<AttnSeg*>(cur);
+    std::vector<int32_t> pos(T);
+    std::vector<AttnSeg> segs(T);
+    for (size_t i = 0; i < T; i++) { pos[i] = (int32_t)i; segs[i] = AttnSeg{0, 1, 0, (int)i + 1}; }
+    int rc = B200_OK;
+    if (cudaMemcpyAsync(g->posArr, pos.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaMemcpyAsync(g->segs, segs.data(), T * sizeof(AttnSeg), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+        rc = lm_fail(lm, B200_ERR_CUDA, "could not initialise the generation session");
+    if (rc == B200_OK) rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_len, &g->rope);
+    if (rc != B200_OK) { cudaFree(g->block); delete g; return rc; }
+    *out = g;
+    return B200_OK;
+}
+
+int32_t b200_lm_gen_destroy(b200_lm_gen* g) {
+    if (!g) return B200_OK;
+    cudaSetDevice(g->lm->ctx->device);
+    cudaStreamSynchronize(g->lm->ctx->stream);
+    cudaFree(g->block);
+    delete g;
+    return B200_OK;
+}
+
+int32_t b200_lm_gen_reset(b200_lm_gen* g) {
+    if (!g) return B200_ERR_INVALID_ARG;
+    g->len = 0;
+    return B200_OK;
+}
+
+int32_t b200_lm_gen_length(b200_lm_gen* g, int32_t* len) {
+    if (!g || !len) return B200_ERR_INVALID_ARG;
+    *len = g->len;
+    return B200_OK;
+}
+
+// ForwardDecoderTokenFromId at position = current length, then ProjectLastTokenOnly; logits (host, [output_dim]) may be null.
+int32_t b200_lm_gen_step(b200_lm_gen* g, int32_t token_id, float* logits) {
+    if (!g) return B200_ERR_INVALID_ARG;
+    b200_lm* lm = g->lm;
+    b200_ctx* ctx = lm->ctx;
+    if ((uint32_t)token_id >= (uint32_t)lm->cfg.vocab_size) return fail(ctx, B200_ERR_OUT_OF_RANGE, "token id %d outside the vocabulary", token_id);
+    if (g->len >= g->maxLen) return lm_fail(lm, B200_ERR_OUT_OF_RANGE, "Decoder KV cache is full.");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200_CUDA(ctx, cudaMemcpyAsync(g->tokens + g->len, &token_id, 4, cudaMemcpyHostToDevice, ctx->stream));
+    B200_TRY(gen_forward_token(g, g->len));
+    g->len++;
+    if (logits) B200_CUDA(ctx, cudaMemcpyAsync(logits, g->logits, sizeof(float) * (size_t)lm->cfg.output_dim, cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return check_device_status(ctx);
+}
+
+// Prompt then arg-max continuation, all launches enqueued without a host round trip per token.  out_tokens receives the
+// prompt followed by the generated ids (at most n_prompt + max_new, never beyond the cache); *n_out their number.
+int32_t b200_lm_gen_greedy(b200_lm_gen* g, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_tokens, int32_t* n_out) {
+    if (!g || !prompt || !out_tokens || !n_out || n_prompt <= 0 || max_new < 0) return B200_ERR_INVALID_ARG;
+    b200_lm* lm = g->lm;
+    b200_ctx* ctx = lm->ctx;
+    for (int i = 0; i < n_prompt; i++)
+        if ((uint32_t)prompt[i] >= (uint32_t)lm->cfg.vocab_size) return fail(ctx, B200_ERR_OUT_OF_RANGE, "token id %d outside the vocabulary", prompt[i]);
+    if (n_prompt > g->maxLen) return lm_fail(lm, B200_ERR_OUT_OF_RANGE, "prompt longer than the key/value cache");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    g->len = 0;
+    B200_CUDA(ctx, cudaMemcpyAsync(g->tokens, prompt, 4 * (size_t)n_prompt, cudaMemcpyHostToDevice, ctx->stream));
+    int total = n_prompt;
+    for (int pos = 0; pos < n_prompt; pos++) B200_TRY(gen_forward_token(g, pos));  // LanguageModel.cs:517-520: the prompt token by token
+    g->len = n_prompt;
+    for (int gen = 0; gen < max_new && total < g->maxLen; gen++) {  // LanguageModel.cs:522-535 with arg-max in place of sampling
+        B200_TRY(k_argmax(ctx, g->logits, lm->cfg.output_dim, g->tokens + total));
+        total++;
+        if (total < g->maxLen && gen + 1 < max_new) {
+            B200_TRY(gen_forward_token(g, total - 1));
+            g->len = total;
+        }
+    }
+    B200_CUDA(ctx, cudaMemcpyAsync(out_tokens, g->tokens, 4 * (size_t)total, cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    *n_out = total;
+    return check_device_status(ctx);
+}
+
+}  // extern "C"

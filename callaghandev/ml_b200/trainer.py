@@ -156,6 +156,10 @@ class B200LanguageModelTrainer:
         if "adam_m" in z:
             self.upload_optimizer_state(z["adam_m"], z["adam_v"], int(z["step_index"]))
 
+    # ---- LanguageModel.Generate (decoder path): incremental decoding with a device key/value cache
+    def generator(self, max_len):
+        return B200Generator(self, max_len)
+
     # ---- device-resident batches
     def prepare_discrete(self, tokens, seq_offsets):
         """Plan, pack and copy a batch to the device once; returns a handle for train_step_batch / accumulate_batch."""
@@ -213,6 +217,50 @@ class B200LanguageModelTrainer:
         out = (C.c_float * 4)()
         self.lib.b200_lm_get_timings(self.h, out)
         return {"forward": out[0], "loss": out[1], "backward": out[2], "step": out[3]}
+
+
+class B200Generator:
+    """One decoding session: `step(token)` returns the next-token logits after pushing the token through the model at
+    the next position (the caller samples, as LanguageModel.Generate does with its own random generator); `greedy`
+    continues a prompt with arg-max choices entirely on the device."""
+
+    def __init__(self, trainer, max_len):
+        self.t, self.lib, self.mgr = trainer, trainer.lib, trainer.mgr
+        self.h = C.c_void_p()
+        self.mgr._ck(self.lib.b200_lm_gen_create(trainer.h, int(max_len), C.byref(self.h)))
+        self.max_len = int(max_len)
+        self.out_dim = int(trainer.cfg.output_dim)
+
+    def reset(self):
+        self.mgr._ck(self.lib.b200_lm_gen_reset(self.h))
+
+    def __len__(self):
+        n = C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_gen_length(self.h, C.byref(n)))
+        return n.value
+
+    def step(self, token_id):
+        out = np.zeros(self.out_dim, np.float32)
+        self.mgr._ck(self.lib.b200_lm_gen_step(self.h, int(token_id), _pf(out)))
+        return out
+
+    def greedy(self, prompt, max_new):
+        p = _i(prompt)
+        out = np.zeros(len(p) + int(max_new), np.int32)
+        n = C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_gen_greedy(self.h, _pi(p), len(p), int(max_new), _pi(out), C.byref(n)))
+        return out[:n.value]
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.b200_lm_gen_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class B200MlpBatchTrainer:

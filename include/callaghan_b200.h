@@ -285,6 +285,18 @@ B200_API int32_t b200_lm_download_optimizer_state(b200_lm*, int32_t which, float
 B200_API int32_t b200_lm_upload_optimizer_state(b200_lm*, int32_t which, const float* host, int64_t offset, int64_t count);
 B200_API int32_t b200_lm_get_step_index(b200_lm*, int32_t* step_index);
 B200_API int32_t b200_lm_set_step_index(b200_lm*, int32_t step_index);
+/* Incremental decoding with a device key/value cache (LanguageModel.Generate, decoder path, LanguageModel.cs:270-537):
+ * b200_lm_gen_step pushes one token through the model at position = current length (ForwardDecoderTokenFromId) and
+ * returns the next-token logits (ProjectLastTokenOnly) -- temperature and sampling stay with the caller, as the
+ * reference draws from its own random generator.  b200_lm_gen_greedy runs prompt + arg-max continuation without a host
+ * round trip per token.  max_len = capacity of the cache (the reference's MaxSequenceLength). */
+typedef struct b200_lm_gen b200_lm_gen;
+B200_API int32_t b200_lm_gen_create(b200_lm*, int32_t max_len, b200_lm_gen** out);
+B200_API int32_t b200_lm_gen_destroy(b200_lm_gen*);
+B200_API int32_t b200_lm_gen_reset(b200_lm_gen*);
+B200_API int32_t b200_lm_gen_length(b200_lm_gen*, int32_t* length);
+B200_API int32_t b200_lm_gen_step(b200_lm_gen*, int32_t token_id, float* logits);
+B200_API int32_t b200_lm_gen_greedy(b200_lm_gen*, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_tokens, int32_t* n_out);
 /* Device time of the phases of the last step in milliseconds: [0] forward, [1] loss, [2] backward, [3] step. */
 B200_API int32_t b200_lm_get_timings(b200_lm*, float* ms4);
 

@@ -1053,6 +1053,92 @@ API real ref_lm_validate(const ref_lm_config* c, const real* P, const int32_t* t
     return totalItems > 0 ? totalLoss / (real)totalItems : 0;
 }
 
+/* LM:293-537 incremental decoding with a per-layer key/value cache: every token (prompt tokens included, LM:517-520) is
+ * pushed through ForwardDecoderTokenFromId at its absolute position; after each one ProjectLastTokenOnly (LM:235-268)
+ * gives the next-token logits.  logitsOut[t*O .. ) = logits after token t.  The rotary angle uses the absolute position
+ * (LM:450-476); attention is the three-pass loop of LM:378-428 over the cached keys, no mask (all keys are in the past).
+ * Returns 0, or -1 for an invalid token id / too many tokens. */
+API int ref_lm_decode_logits(const ref_lm_config* c, const real* P, const int32_t* tokens, int n, int maxLen, real* logitsOut) {
+    if (n > maxLen) return -1;
+    lm_off o;
+    lm_layout(c, &o);
+    int d = c->embedding_dim, H = c->num_heads, hd = d / H, f = c->ffn_dim, Lc = c->num_layers, O = c->output_dim;
+    real eps = (real)1e-5;
+    real** Kc = (real**)calloc((size_t)Lc, sizeof(real*));
+    real** Vc = (real**)calloc((size_t)Lc, sizeof(real*));
+    for (int l = 0; l < Lc; l++) { Kc[l] = ralloc((size_t)maxLen * d); Vc[l] = ralloc((size_t)maxLen * d); }
+    int32_t widths[3] = {d, f, d};
+    int32_t acts[3] = {ACT_NONE, c->ffn_activation, ACT_NONE};
+    real *x = ralloc((size_t)d), *q = ralloc((size_t)d), *k = ralloc((size_t)d), *v = ralloc((size_t)d), *cat = ralloc((size_t)d),
+         *proj = ralloc((size_t)d), *n1 = ralloc((size_t)d), *ff = ralloc((size_t)d), *nx = ralloc((size_t)d), *tmpN = ralloc((size_t)d),
+         *tmpR = ralloc((size_t)d);
+    real mean, var;
+    int rc = 0;
+    for (int pos = 0; pos < n && rc == 0; pos++) {
+        int id = tokens[pos];
+        if (id < 0 || id >= c->vocab_size) { rc = -1; break; }
+        memcpy(x, P + o.in0 + (size_t)id * d, sizeof(real) * (size_t)d);
+        for (int l = 0; l < Lc; l++) {
+            const lm_layer_off* L = &o.layer[l];
+            ref_ProjectQKV(x, 1, d, P + L->WQ, P + L->bQ, P + L->WK, P + L->bK, P + L->WV, P + L->bV, d, q, k, v);
+            for (int h = 0; h < H; h++) /* LM:450-476 ApplyRotaryPositionSingleRow */
+                for (int pr = 0; pr < hd / 2; pr++) {
+                    real theta = (real)pos / R_POW((real)10000, ((real)2 * pr) / hd);
+                    real cs = R_COS(theta), sn = R_SIN(theta);
+                    int e = h * hd + 2 * pr;
+                    real q0 = q[e], q1 = q[e + 1], k0 = k[e], k1 = k[e + 1];
+                    q[e] = q0 * cs - q1 * sn; q[e + 1] = q0 * sn + q1 * cs;
+                    k[e] = k0 * cs - k1 * sn; k[e + 1] = k0 * sn + k1 * cs;
+                }
+            memcpy(Kc[l] + (size_t)pos * d, k, sizeof(real) * (size_t)d);
+            memcpy(Vc[l] + (size_t)pos * d, v, sizeof(real) * (size_t)d);
+            int keyLen = pos + 1;
+            real scale = (real)1 / R_SQRT((real)hd);
+            for (int e = 0; e < d; e++) cat[e] = 0;
+            for (int h = 0; h < H; h++) { /* LM:378-428 */
+                int off = h * hd;
+                real maxS = -INFINITY;
+                for (int kj = 0; kj < keyLen; kj++) {
+                    real dot = 0;
+                    for (int e = 0; e < hd; e++) dot += q[off + e] * Kc[l][(size_t)kj * d + off + e];
+                    real sc = dot * scale;
+                    if (sc > maxS) maxS = sc;
+                }
+                real sumExp = 0;
+                for (int kj = 0; kj < keyLen; kj++) {
+                    real dot = 0;
+                    for (int e = 0; e < hd; e++) dot += q[off + e] * Kc[l][(size_t)kj * d + off + e];
+                    sumExp += R_EXP(dot * scale - maxS);
+                }
+                real inv = sumExp > 0 ? (real)1 / sumExp : 0;
+                for (int kj = 0; kj < keyLen; kj++) {
+                    real dot = 0;
+                    for (int e = 0; e < hd; e++) dot += q[off + e] * Kc[l][(size_t)kj * d + off + e];
+                    real w = R_EXP(dot * scale - maxS) * inv;
+                    if (w == 0) continue;
+                    for (int e = 0; e < hd; e++) cat[off + e] += w * Vc[l][(size_t)kj * d + off + e];
+                }
+            }
+            ref_ProjectOutputBatch(cat, d, P + L->WO, P + L->bO, 1, d, proj);
+            ref_ResidualLayerNormForward(x, proj, P + L->g1, P + L->b1n, 1, d, eps, n1, &mean, &var, tmpN, tmpR);
+            const real* W[3] = {NULL, P + L->W1, P + L->W2};
+            const real* B[3] = {NULL, P + L->fb1, P + L->fb2};
+            ref_FFNForwardBatch(n1, 1, 3, widths, acts, W, B, ff);
+            ref_ResidualLayerNormForward(n1, ff, P + L->g2, P + L->b2n, 1, d, eps, nx, &mean, &var, tmpN, tmpR);
+            memcpy(x, nx, sizeof(real) * (size_t)d);
+        }
+        for (int oi = 0; oi < O; oi++) { /* LM:235-268 ProjectLastTokenOnly: the bias starts the sum */
+            real sum = P[o.bout + oi];
+            for (int e = 0; e < d; e++) sum += P[o.Wout + (size_t)oi * d + e] * x[e];
+            logitsOut[(size_t)pos * O + oi] = sum;
+        }
+    }
+    for (int l = 0; l < Lc; l++) { free(Kc[l]); free(Vc[l]); }
+    free(Kc); free(Vc); free(x); free(q); free(k); free(v); free(cat); free(proj); free(n1); free(ff); free(nx); free(tmpN); free(tmpR);
+    free(o.layer);
+    return rc;
+}
+
 /* ---------------------------------------------------------------- MLP mini-batch step (NN:499-610, GPUB:251-358) */
 
 enum { COST_MSE = 0, COST_ZERO_WEIGHTED_MSE = 1, COST_BCE = 2, COST_MAE = 3, COST_CCE = 4, COST_HUBER = 5 };

@@ -343,6 +343,17 @@ class Oracle:
                                         C.byref(items))
         return float(loss), int(items.value)
 
+    def lm_decode_logits(self, cfg: LMConfig, params, tokens, max_len=None):
+        """LanguageModel incremental decoding (KV cache, one token at a time): logits [len(tokens), output_dim], row t =
+        next-token logits after token t."""
+        assert params.dtype == self.dt
+        tok = np.ascontiguousarray(np.asarray(tokens, np.int32))
+        out = np.zeros((len(tok), cfg.output_dim), self.dt)
+        rc = self.lib.ref_lm_decode_logits(C.byref(cfg), self.p(params), self.p(tok), len(tok), int(max_len or len(tok)), self.p(out))
+        if rc != 0:
+            raise ValueError("invalid token id or sequence longer than the cache")
+        return out
+
     # ------------------------------------------------------------------ MLP batch step
     def mlp_learn_batch(self, widths, acts, weights, biases, X, Y, cost="mse", huber_delta=1.0, lr=0.01, lam=0.0, clip_thr=1.0):
         """weights/biases: lists (per non-input layer) of arrays updated in place.  Returns the delta norm."""

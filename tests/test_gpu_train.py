@@ -394,3 +394,39 @@ def test_checkpoint_with_optimizer_state_resumes_bit_identically(mgr, oracle, tm
         b.train_step_discrete(toks, off, 3e-4, True, 1.0, True)
     assert np.array_equal(b.download_params(), want)
     b.close()
+
+
+def test_incremental_decoding_with_device_kv_cache(mgr, oracle):
+    """LanguageModel.Generate's decoder path: every token goes through the model at its absolute position against the
+    cached keys/values; the next-token logits after each token match the restated reference loop, and an arg-max
+    continuation picks the tokens the oracle's logits pick."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(8)
+    cfg = lm_config(vocab=120, d=64, H=4, L=2, f=128, act="Relu")
+    P = init_params(oracle, cfg, 41)
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 64)
+    t.upload_params(P)
+    prompt = rng.integers(4, 120, 9).astype(np.int32)
+    want = oracle.lm_decode_logits(cfg, P, prompt, max_len=32)
+    g = t.generator(32)
+    for i, tok in enumerate(prompt):
+        assert_close(want[i], g.step(int(tok)), 1e-5, f"logits after token {i}")
+    assert len(g) == len(prompt)
+    # greedy continuation: device arg-max loop vs the oracle driven token by token
+    seq = list(prompt)
+    for _ in range(6):
+        seq.append(int(np.argmax(oracle.lm_decode_logits(cfg, P, np.array(seq, np.int32), max_len=32)[-1])))
+    got = g.greedy(prompt, 6)
+    assert got.tolist() == seq
+    # the cache is full after max_len tokens: generation stops there, a further step is an error
+    got = g.greedy(prompt, 100)
+    assert len(got) == 32
+    g.reset()
+    for tok in got:
+        g.step(int(tok))
+    with pytest.raises(Exception):
+        g.step(5)
+    with pytest.raises(Exception):
+        g.step(9999)
+    g.close(); t.close()

@@ -400,3 +400,24 @@ def test_validate_agrees_with_the_train_step_loss_on_equal_lengths(oracle):
     vloss, items = oracle.lm_validate(cfg, P, off, tokens=toks)
     assert valid == 3 and items == 3 * 8
     assert abs(loss - vloss) <= 1e-5 * max(1.0, abs(loss))
+
+
+def test_incremental_decoding_agrees_with_the_batched_forward(oracle):
+    """LanguageModel.cs:293-537 pushes tokens one at a time through a key/value cache with the rotary angle of the
+    absolute position; the training forward (TransformerTrainer.cs:540-590) does the same sequence in one causal pass.
+    Their next-token distributions must agree: the cross-entropy of the incremental logits equals the step's loss."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from lmutil import init_params, lm_config, token_batch
+
+    rng = np.random.default_rng(0)
+    cfg = lm_config(vocab=50, d=32, H=2, L=2, f=64)
+    toks, off = token_batch(rng, 1, 50, 12, 12)
+    P = init_params(oracle, cfg, 1)
+    lg = oracle.lm_decode_logits(cfg, P, toks[:-1]).astype(np.float64)
+    tg = toks[1:]
+    m = lg.max(1, keepdims=True)
+    ce = -(lg - m - np.log(np.exp(lg - m).sum(1, keepdims=True)))[np.arange(len(tg)), tg]
+    loss, _, valid = oracle.lm_train_step(cfg, P.copy(), np.zeros_like(P), off, tokens=toks, do_step=False)
+    assert valid == 1
+    assert abs(ce.mean() - loss) <= 1e-5 * max(1.0, abs(loss))
