@@ -110,6 +110,57 @@ int gemm_simt(b200_ctx* ctx, const Gemm& g) {
     return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ few-row products
+// C[m,n] = A[m,:] . B[n,:] for M <= 4 rows (incremental decoding: one token at a time): one warp per output column
+// streams its weight row once with 128-bit loads -- the product is bound by reading B, which the tiled kernels above
+// would do at 1/64 efficiency for a single row.  Same fused epilogue.
+template <int MR>
+__global__ void __launch_bounds__(256) gemv_rows_kernel(int M, int N, int K, const float* __restrict__ A, int lda, const float* __restrict__ B,
+                                                        int ldb, int vec, Epilogue ep) {
+    const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const float* w = B + (size_t)n * ldb;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) acc[m] = 0.f;
+    if (vec) {
+        for (int k = lane * 4; k < K; k += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + k);
+#pragma unroll
+            for (int m = 0; m < MR; m++)
+                if (m < M) {
+                    const float4 xv = *reinterpret_cast<const float4*>(A + (size_t)m * lda + k);
+                    acc[m] += (wv.x * xv.x + wv.y * xv.y) + (wv.z * xv.z + wv.w * xv.w);
+                }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int m = 0; m < MR; m++)
+                if (m < M) acc[m] += wv * A[(size_t)m * lda + k];
+        }
+    }
+    float alpha = ep.alpha;
+    if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0 && m < M) epilogue_store(ep, m, n, v, alpha);
+    }
+}
+
+static bool gemv_eligible(const Gemm& g) { return g.M >= 1 && g.M <= 4 && !g.transA && g.transB && g.N >= 1 && g.K >= 1; }
+
+static int gemv_rows(b200_ctx* ctx, const Gemm& g) {
+    Epilogue e = make_epilogue(g);
+    const int vec = (g.K % 4 == 0) && (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
+    const int blocks = (g.N + 7) / 8;
+    gemv_rows_kernel<4><<<blocks, 256, 0, ctx->stream>>>(g.M, g.N, g.K, g.A, g.lda, g.B, g.ldb, vec, e);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 static int gemm_dispatch(b200_ctx* ctx, const Gemm& g0, int* engine) {
     Gemm g = g0;
     const bool rope_after = g.rope_table && !(ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_fuses_rope(ctx, g));
@@ -123,6 +174,10 @@ static int gemm_dispatch(b200_ctx* ctx, const Gemm& g0, int* engine) {
     if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) {
         *engine = 1;
         return gemm_tcgen05(ctx, g);
+    }
+    if (gemv_eligible(g)) {
+        *engine = 0;
+        return gemv_rows(ctx, g);
     }
     if (ctx->gemm_mode == B200_GEMM_TF32_TCGEN05 && g.M >= 128 && g.N >= 128 && g.K >= 128)
         return fail(ctx, B200_ERR_UNSUPPORTED, "TF32 tcgen05 GEMM requested but shape/alignment/device does not qualify (M=%d N=%d K=%d)", g.M, g.N, g.K);

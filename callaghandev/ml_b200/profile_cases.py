@@ -5,6 +5,8 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
   gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
   layernorm   LayerNorm forward + backward on 32768 x 1024
   crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
+  generate    greedy decoding with the device key/value cache on the c5 model (V 32000, d 1024, 16 heads, 12 layers,
+              f 4096): 16-token prompt + 240 generated tokens, prints tokens/s
 """
 import sys
 
@@ -58,7 +60,28 @@ def crossentropy(m, rng):
     return float(r[0])
 
 
-CASES = {"attention": attention, "gemm": gemm, "layernorm": layernorm, "crossentropy": crossentropy}
+def generate(m, rng):
+    import time
+
+    from . import B200LanguageModelTrainer, make_config
+
+    cfg = make_config(vocab_size=32000, embedding_dim=1024, num_heads=16, num_layers=12, ffn_dim=4096, ffn_activation="Relu")
+    t = B200LanguageModelTrainer(m, cfg, max_rows_per_pass=1024)
+    n = t.param_count
+    w = (rng.standard_normal(n, dtype=np.float32) * 0.02)
+    t.upload_params(w)
+    g = t.generator(256)
+    prompt = rng.integers(4, 32000, 16).astype(np.int32)
+    g.greedy(prompt, 8)  # warm-up (module load, first-launch effects)
+    t0 = time.perf_counter()
+    out = g.greedy(prompt, 240)
+    dt = time.perf_counter() - t0
+    print("decode: %d tokens in %.3f s = %.1f tokens/s (prompt included, one token per model pass)" % (len(out), dt, len(out) / dt))
+    g.close(); t.close()
+    return float(out[-1])
+
+
+CASES = {"generate": generate, "attention": attention, "gemm": gemm, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):
