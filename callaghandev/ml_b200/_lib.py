@@ -68,6 +68,8 @@ PROTOTYPES = {
     "b200_ApplyRotaryPositionEmbeddingHeadInPlace": (_i32, [_vp, _f, _i32, _i32, _i32, _i32, _fl, _i32]),
     "b200_ProjectQKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _f, _f, _f, _f, _i32, _f, _f, _f]),
     "b200_BackpropQKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _f, _i32, _f, _f, _f, _f, _f, _f, _f, _f, _f, _f]),
+    "b200_ProjectKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _f, _f, _i32, _f, _f]),
+    "b200_BackpropKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _i32, _f, _f, _f, _f, _f, _f, _f]),
     "b200_BackpropLinearProjection": (_i32, [_vp, _f, _f, _f, _i32, _i32, _i32, _f, _f, _f]),
     "b200_BackpropOutputProjection": (_i32, [_vp, _f, _f, _f, _f, _f, _i32, _i32, _i32, _f]),
     "b200_BackpropInputProjection": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _i32, _f, _f, _i32, _i32, _i32]),

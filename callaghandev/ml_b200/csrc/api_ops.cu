@@ -528,33 +528,76 @@ int32_t b200_ApplyRotaryPositionEmbeddingHeadInPlace(b200_ctx* ctx, float* matri
 }
 
 // ------------------------------------------------------------------------------------------------ projections
-int32_t b200_ProjectQKV(b200_ctx* ctx, const float* input, int32_t rows, int32_t inDim, const float* WQ, const float* bQ, const float* WK, const float* bK,
-                        const float* WV, const float* bV, int32_t outDim, float* Q, float* K, float* V) {
-    if (!ctx) return B200_ERR_INVALID_ARG;
-    NOTNULL(ctx, input); NOTNULL(ctx, WQ); NOTNULL(ctx, WK); NOTNULL(ctx, WV); NOTNULL(ctx, bQ); NOTNULL(ctx, bK); NOTNULL(ctx, bV);
-    NOTNULL(ctx, Q); NOTNULL(ctx, K); NOTNULL(ctx, V);
+// n (2 or 3) projections of the same input with separate weights: staged contiguously so that one [n*out, in] GEMM
+// produces them side by side.
+static int project_many(b200_ctx* ctx, const float* input, int rows, int inDim, int n, const float* const* Ws, const float* const* Bs, int outDim,
+                        float* const* outs) {
     NEED(ctx, rows >= 0 && inDim >= 0 && outDim >= 0, B200_ERR_INVALID_ARG, "negative dimension");
     if (rows == 0 || outDim == 0) return B200_OK;
     int64_t nw = (int64_t)outDim * inDim, ny = (int64_t)rows * outDim;
     Scope s(ctx);
     float* dX = s.up(input, (int64_t)rows * inDim);
-    // Stage the three weight matrices and biases contiguously so that one [3*out, in] GEMM produces Q|K|V.
-    float* dW = s.floats(3 * nw);
-    float* dB = s.floats(3 * (int64_t)outDim);
-    float* dY = s.floats(3 * ny);
+    float* dW = s.floats(n * nw);
+    float* dB = s.floats(n * (int64_t)outDim);
+    float* dY = s.floats(n * ny);
     CHECK_SCOPE(s);
-    const float* Ws[3] = {WQ, WK, WV};
-    const float* Bs[3] = {bQ, bK, bV};
-    for (int i = 0; i < 3; i++) {
+    for (int i = 0; i < n; i++) {
         B200_CUDA(ctx, cudaMemcpyAsync(dW + i * nw, Ws[i], sizeof(float) * nw, cudaMemcpyHostToDevice, ctx->stream));
         B200_CUDA(ctx, cudaMemcpyAsync(dB + i * outDim, Bs[i], sizeof(float) * outDim, cudaMemcpyHostToDevice, ctx->stream));
     }
-    B200_TRY(linear_fwd(ctx, dX, rows, inDim, dW, dB, 3 * outDim, dY, 3 * outDim));
-    float* outs[3] = {Q, K, V};
-    for (int i = 0; i < 3; i++)
-        B200_CUDA(ctx, cudaMemcpy2DAsync(outs[i], sizeof(float) * outDim, dY + i * outDim, sizeof(float) * 3 * outDim, sizeof(float) * outDim, rows,
+    B200_TRY(linear_fwd(ctx, dX, rows, inDim, dW, dB, n * outDim, dY, n * outDim));
+    for (int i = 0; i < n; i++)
+        B200_CUDA(ctx, cudaMemcpy2DAsync(outs[i], sizeof(float) * outDim, dY + i * outDim, sizeof(float) * n * outDim, sizeof(float) * outDim, rows,
                                          cudaMemcpyDeviceToHost, ctx->stream));
     return s.sync();
+}
+
+// Backward of project_many: the 2n parameter gradients accumulate, dInput is assigned.
+static int backprop_many(b200_ctx* ctx, const float* input, int rows, int inDim, int n, const float* const* Ys, int outDim, const float* const* Ws,
+                         float* const* Wg, float* const* Bg, float* dInput) {
+    NEED(ctx, rows >= 0 && inDim >= 0 && outDim >= 0, B200_ERR_INVALID_ARG, "negative dimension");
+    int64_t nw = (int64_t)outDim * inDim, ny = (int64_t)rows * outDim, nx = (int64_t)rows * inDim;
+    if (nx == 0) return B200_OK;
+    Scope s(ctx);
+    float* dX = s.up(input, nx);
+    float *dW = s.floats(n * nw), *dWg = s.floats(n * nw), *dBg = s.floats(n * (int64_t)outDim), *dY = s.floats(n * ny), *dIn = s.floats(nx);
+    CHECK_SCOPE(s);
+    for (int i = 0; i < n; i++) {
+        B200_CUDA(ctx, cudaMemcpyAsync(dW + i * nw, Ws[i], sizeof(float) * nw, cudaMemcpyHostToDevice, ctx->stream));
+        B200_CUDA(ctx, cudaMemcpyAsync(dWg + i * nw, Wg[i], sizeof(float) * nw, cudaMemcpyHostToDevice, ctx->stream));
+        B200_CUDA(ctx, cudaMemcpyAsync(dBg + i * outDim, Bg[i], sizeof(float) * outDim, cudaMemcpyHostToDevice, ctx->stream));
+        B200_CUDA(ctx, cudaMemcpy2DAsync(dY + i * outDim, sizeof(float) * n * outDim, Ys[i], sizeof(float) * outDim, sizeof(float) * outDim, rows,
+                                         cudaMemcpyHostToDevice, ctx->stream));
+    }
+    B200_TRY(wgrad(ctx, dY, n * outDim, dX, inDim, rows, n * outDim, inDim, dWg, dBg));
+    B200_TRY(dgrad(ctx, dY, n * outDim, dW, rows, n * outDim, inDim, dIn, 0));
+    for (int i = 0; i < n; i++) {
+        B200_TRY(s.down(Wg[i], dWg + i * nw, nw));
+        B200_TRY(s.down(Bg[i], dBg + i * outDim, outDim));
+    }
+    B200_TRY(s.down(dInput, dIn, nx));
+    return s.sync();
+}
+
+int32_t b200_ProjectQKV(b200_ctx* ctx, const float* input, int32_t rows, int32_t inDim, const float* WQ, const float* bQ, const float* WK, const float* bK,
+                        const float* WV, const float* bV, int32_t outDim, float* Q, float* K, float* V) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    NOTNULL(ctx, input); NOTNULL(ctx, WQ); NOTNULL(ctx, WK); NOTNULL(ctx, WV); NOTNULL(ctx, bQ); NOTNULL(ctx, bK); NOTNULL(ctx, bV);
+    NOTNULL(ctx, Q); NOTNULL(ctx, K); NOTNULL(ctx, V);
+    const float* Ws[3] = {WQ, WK, WV};
+    const float* Bs[3] = {bQ, bK, bV};
+    float* outs[3] = {Q, K, V};
+    return project_many(ctx, input, rows, inDim, 3, Ws, Bs, outDim, outs);
+}
+
+int32_t b200_ProjectKV(b200_ctx* ctx, const float* input, int32_t rows, int32_t inDim, const float* WK, const float* bK, const float* WV, const float* bV,
+                       int32_t outDim, float* K, float* V) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    NOTNULL(ctx, input); NOTNULL(ctx, WK); NOTNULL(ctx, WV); NOTNULL(ctx, bK); NOTNULL(ctx, bV); NOTNULL(ctx, K); NOTNULL(ctx, V);
+    const float* Ws[2] = {WK, WV};
+    const float* Bs[2] = {bK, bV};
+    float* outs[2] = {K, V};
+    return project_many(ctx, input, rows, inDim, 2, Ws, Bs, outDim, outs);
 }
 
 int32_t b200_BackpropQKV(b200_ctx* ctx, const float* input, int32_t rows, int32_t inDim, const float* dQ, const float* dK, const float* dV, int32_t outDim,
@@ -564,32 +607,23 @@ int32_t b200_BackpropQKV(b200_ctx* ctx, const float* input, int32_t rows, int32_
     NOTNULL(ctx, input); NOTNULL(ctx, dQ); NOTNULL(ctx, dK); NOTNULL(ctx, dV); NOTNULL(ctx, WQ); NOTNULL(ctx, WK); NOTNULL(ctx, WV);
     NOTNULL(ctx, WQGrad); NOTNULL(ctx, bQGrad); NOTNULL(ctx, WKGrad); NOTNULL(ctx, bKGrad); NOTNULL(ctx, WVGrad); NOTNULL(ctx, bVGrad);
     NOTNULL(ctx, dInput);
-    NEED(ctx, rows >= 0 && inDim >= 0 && outDim >= 0, B200_ERR_INVALID_ARG, "negative dimension");
-    int64_t nw = (int64_t)outDim * inDim, ny = (int64_t)rows * outDim, nx = (int64_t)rows * inDim;
-    if (nx == 0) return B200_OK;
-    Scope s(ctx);
-    float* dX = s.up(input, nx);
-    float *dW = s.floats(3 * nw), *dWg = s.floats(3 * nw), *dBg = s.floats(3 * (int64_t)outDim), *dY = s.floats(3 * ny), *dIn = s.floats(nx);
-    CHECK_SCOPE(s);
     const float* Ws[3] = {WQ, WK, WV};
     const float* Ys[3] = {dQ, dK, dV};
     float* Wg[3] = {WQGrad, WKGrad, WVGrad};
     float* Bg[3] = {bQGrad, bKGrad, bVGrad};
-    for (int i = 0; i < 3; i++) {
-        B200_CUDA(ctx, cudaMemcpyAsync(dW + i * nw, Ws[i], sizeof(float) * nw, cudaMemcpyHostToDevice, ctx->stream));
-        B200_CUDA(ctx, cudaMemcpyAsync(dWg + i * nw, Wg[i], sizeof(float) * nw, cudaMemcpyHostToDevice, ctx->stream));
-        B200_CUDA(ctx, cudaMemcpyAsync(dBg + i * outDim, Bg[i], sizeof(float) * outDim, cudaMemcpyHostToDevice, ctx->stream));
-        B200_CUDA(ctx, cudaMemcpy2DAsync(dY + i * outDim, sizeof(float) * 3 * outDim, Ys[i], sizeof(float) * outDim, sizeof(float) * outDim, rows,
-                                         cudaMemcpyHostToDevice, ctx->stream));
-    }
-    B200_TRY(wgrad(ctx, dY, 3 * outDim, dX, inDim, rows, 3 * outDim, inDim, dWg, dBg));
-    B200_TRY(dgrad(ctx, dY, 3 * outDim, dW, rows, 3 * outDim, inDim, dIn, 0));
-    for (int i = 0; i < 3; i++) {
-        B200_TRY(s.down(Wg[i], dWg + i * nw, nw));
-        B200_TRY(s.down(Bg[i], dBg + i * outDim, outDim));
-    }
-    B200_TRY(s.down(dInput, dIn, nx));
-    return s.sync();
+    return backprop_many(ctx, input, rows, inDim, 3, Ys, outDim, Ws, Wg, Bg, dInput);
+}
+
+int32_t b200_BackpropKV(b200_ctx* ctx, const float* input, int32_t rows, int32_t inDim, const float* dK, const float* dV, int32_t outDim, const float* WK,
+                        const float* WV, float* WKGrad, float* bKGrad, float* WVGrad, float* bVGrad, float* dInput) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    NOTNULL(ctx, input); NOTNULL(ctx, dK); NOTNULL(ctx, dV); NOTNULL(ctx, WK); NOTNULL(ctx, WV);
+    NOTNULL(ctx, WKGrad); NOTNULL(ctx, bKGrad); NOTNULL(ctx, WVGrad); NOTNULL(ctx, bVGrad); NOTNULL(ctx, dInput);
+    const float* Ws[2] = {WK, WV};
+    const float* Ys[2] = {dK, dV};
+    float* Wg[2] = {WKGrad, WVGrad};
+    float* Bg[2] = {bKGrad, bVGrad};
+    return backprop_many(ctx, input, rows, inDim, 2, Ys, outDim, Ws, Wg, Bg, dInput);
 }
 
 int32_t b200_BackpropLinearProjection(b200_ctx* ctx, const float* input, const float* dOutput, const float* weights, int32_t seqLen, int32_t inDim,

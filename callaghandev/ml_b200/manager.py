@@ -269,6 +269,39 @@ class CudaB200AccelerationManager:
         self._ck(self.lib.b200_ProjectQKV(self.ctx, _pf(x), rows, x.shape[1], _pf(wq), _pf(bq), _pf(wk), _pf(bk), _pf(wv), _pf(bv), out, _pf(Q), _pf(K), _pf(V)))
         return Q, K, V
 
+    def ProjectKV(self, input, WK, biasK, WV, biasV):
+        x, wk, bk, wv, bv = map(_f, (input, WK, biasK, WV, biasV))
+        if wk.shape[0] != wv.shape[0]:
+            raise ValueError("K and V output dimensions must match.")
+        for w, n in ((wk, "WK"), (wv, "WV")):
+            if w.shape[1] != x.shape[1]:
+                raise ValueError(f"{n} input dimension does not match input width.")
+        for b, w, n in ((bk, wk, "biasK"), (bv, wv, "biasV")):
+            if b.shape[0] != w.shape[0]:
+                raise ValueError(f"{n} length does not match the output dimension.")
+        rows, out = x.shape[0], wk.shape[0]
+        K, V = (np.zeros((rows, out), np.float32) for _ in range(2))
+        self._ck(self.lib.b200_ProjectKV(self.ctx, _pf(x), rows, x.shape[1], _pf(wk), _pf(bk), _pf(wv), _pf(bv), out, _pf(K), _pf(V)))
+        return K, V
+
+    def BackpropKV(self, input, dK, dV, WK, WV, WKGrad, biasKGrad, WVGrad, biasVGrad):
+        x, dk, dv, wk, wv = map(_f, (input, dK, dV, WK, WV))
+        grads = [_inplace(g, "gradient") for g in (WKGrad, biasKGrad, WVGrad, biasVGrad)]
+        rows, inp, out = x.shape[0], x.shape[1], wk.shape[0]
+        if not (wk.shape == wv.shape == (out, inp)):
+            raise ValueError("K/V weight input dimensions must match input width.")
+        if not (dk.shape == dv.shape == (rows, out)):
+            raise ValueError("dK and dV must be [rows, outputDim].")
+        for g in grads[0::2]:
+            if g.shape != (out, inp):
+                raise ValueError("Weight gradient shape mismatch.")
+        for g in grads[1::2]:
+            if g.shape != (out,):
+                raise ValueError("K/V bias gradient lengths must match output dimension.")
+        dIn = np.zeros_like(x)
+        self._ck(self.lib.b200_BackpropKV(self.ctx, _pf(x), rows, inp, _pf(dk), _pf(dv), out, _pf(wk), _pf(wv), *[_pf(g) for g in grads], _pf(dIn)))
+        return dIn
+
     def BackpropQKV(self, input, dQ, dK, dV, WQ, WK, WV, WQGrad, biasQGrad, WKGrad, biasKGrad, WVGrad, biasVGrad):
         x, dq, dk, dv, wq, wk, wv = map(_f, (input, dQ, dK, dV, WQ, WK, WV))
         grads = [_inplace(g, "gradient") for g in (WQGrad, biasQGrad, WKGrad, biasKGrad, WVGrad, biasVGrad)]

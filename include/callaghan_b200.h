@@ -153,6 +153,13 @@ B200_API int32_t b200_ProjectQKV(b200_ctx*, const float* input, int32_t rows, in
 B200_API int32_t b200_BackpropQKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* dQ, const float* dK, const float* dV,
                                   int32_t outDim, const float* WQ, const float* WK, const float* WV, float* WQGrad, float* bQGrad,
                                   float* WKGrad, float* bKGrad, float* WVGrad, float* bVGrad, float* dInput);
+/* ProjectKV (IAccelerationManager.cs:331; AccelerationCPU.cs:4361-4417) and BackpropKV (IAccelerationManager.cs:332;
+ * AccelerationCPU.cs:4419-4560): the key/value halves of the two above, used by the cross-attention of the sibling trainers;
+ * the four gradients accumulate, dInput is assigned. */
+B200_API int32_t b200_ProjectKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* WK, const float* bK, const float* WV,
+                                const float* bV, int32_t outDim, float* K, float* V);
+B200_API int32_t b200_BackpropKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* dK, const float* dV, int32_t outDim,
+                                 const float* WK, const float* WV, float* WKGrad, float* bKGrad, float* WVGrad, float* bVGrad, float* dInput);
 /* BackpropLinearProjection (IAccelerationManager.cs:182; AccelerationCPU.cs:2188-2229): weightGrad, biasGrad AND dInput accumulate. */
 B200_API int32_t b200_BackpropLinearProjection(b200_ctx*, const float* input, const float* dOutput, const float* weights, int32_t seqLen,
                                                int32_t inDim, int32_t outDim, float* weightGrad, float* biasGrad, float* dInput);

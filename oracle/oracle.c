@@ -491,6 +491,37 @@ API void ref_BackpropQKV(const real* x, int rows, int inDim, const real* dQ, con
     }
 }
 
+/* CPU:4361-4417 ProjectKV: K = x WK^T + bK, V = x WV^T + bV (the bias starts each sum). */
+API void ref_ProjectKV(const real* x, int rows, int inDim, const real* WK, const real* bK, const real* WV, const real* bV, int outDim,
+                       real* K, real* V) {
+    PAR
+    for (int i = 0; i < rows; i++)
+        for (int o = 0; o < outDim; o++) {
+            const real* xr = x + (size_t)i * inDim;
+            real sk = 0, sv = 0;
+            for (int d = 0; d < inDim; d++) { sk += WK[(size_t)o * inDim + d] * xr[d]; sv += WV[(size_t)o * inDim + d] * xr[d]; }
+            K[(size_t)i * outDim + o] = bK[o] + sk;
+            V[(size_t)i * outDim + o] = bV[o] + sv;
+        }
+}
+
+/* CPU:4419-4532 BackpropKV: weight and bias gradients accumulate, dInput is a fresh array. */
+API void ref_BackpropKV(const real* x, int rows, int inDim, const real* dK, const real* dV, int outDim, const real* WK, const real* WV,
+                        real* WKg, real* bKg, real* WVg, real* bVg, real* dInput) {
+    accum_wgrad(dK, outDim, x, inDim, rows, outDim, inDim, WKg, bKg);
+    accum_wgrad(dV, outDim, x, inDim, rows, outDim, inDim, WVg, bVg);
+    PAR
+    for (int i = 0; i < rows; i++) {
+        real* dx = dInput + (size_t)i * inDim;
+        for (int d = 0; d < inDim; d++) dx[d] = 0;
+        for (int o = 0; o < outDim; o++) {
+            real dk = dK[(size_t)i * outDim + o], dv = dV[(size_t)i * outDim + o];
+            const real *wk = WK + (size_t)o * inDim, *wv = WV + (size_t)o * inDim;
+            for (int d = 0; d < inDim; d++) dx[d] += dk * wk[d] + dv * wv[d];
+        }
+    }
+}
+
 /* CPU:2188-2229 BackpropLinearProjection: weightGrad, biasGrad and dInput all accumulate. */
 API void ref_BackpropLinearProjection(const real* x, const real* dY, const real* W, int seqLen, int inDim, int outDim,
                                       real* Wg, real* bg, real* dInput) {

@@ -204,6 +204,20 @@ class Oracle:
                                  self.p(WVg), self.p(bVg), self.p(dIn))
         return dIn
 
+    def ProjectKV(self, input, WK, bK, WV, bV):
+        input, WK, bK, WV, bV = map(self.a, (input, WK, bK, WV, bV))
+        rows, out = input.shape[0], WK.shape[0]
+        K, V = (np.zeros((rows, out), self.dt) for _ in range(2))
+        self.lib.ref_ProjectKV(self.p(input), rows, input.shape[1], self.p(WK), self.p(bK), self.p(WV), self.p(bV), out, self.p(K), self.p(V))
+        return K, V
+
+    def BackpropKV(self, input, dK, dV, WK, WV, WKg, bKg, WVg, bVg):
+        input, dK, dV, WK, WV = map(self.a, (input, dK, dV, WK, WV))
+        dIn = np.zeros_like(input)
+        self.lib.ref_BackpropKV(self.p(input), input.shape[0], input.shape[1], self.p(dK), self.p(dV), WK.shape[0], self.p(WK), self.p(WV),
+                                self.p(WKg), self.p(bKg), self.p(WVg), self.p(bVg), self.p(dIn))
+        return dIn
+
     def BackpropLinearProjection(self, input, dOutput, weights, weightGrad, biasGrad, dInput):
         input, dOutput, weights = map(self.a, (input, dOutput, weights))
         self.lib.ref_BackpropLinearProjection(self.p(input), self.p(dOutput), self.p(weights), input.shape[0], input.shape[1],

@@ -226,6 +226,27 @@ def test_qkv_forward_backward(mgr, oracle, rows, inp, out, seed):
         mgr.ProjectQKV(pt_matrix(rows, inp + 1, 140), wq, bq, wk, bk, wv, bv)
 
 
+@pytest.mark.parametrize("rows,inp,out,seed", [(6, 5, 8, 224), (192, 128, 128, 242), (130, 64, 72, 27)])  # IAccelerationManager.cs:331-332
+def test_kv_forward_backward(mgr, oracle, rows, inp, out, seed):
+    x = pt_matrix(rows, inp, seed)
+    wk, wv = (pt_matrix(out, inp, seed + i) for i in (1, 2))
+    bk, bv = (pt_vector(out, seed + i) for i in (3, 4))
+    for ee, aa, n in zip(oracle.ProjectKV(x, wk, bk, wv, bv), mgr.ProjectKV(x, wk, bk, wv, bv), "KV"):
+        assert_close(ee, aa, TOL, "ProjectKV." + n)
+    dK, dV = (pt_matrix(rows, out, seed + i) for i in (5, 6))
+    g0 = [pt_matrix(out, inp, seed + 7), pt_vector(out, seed + 9), pt_matrix(out, inp, seed + 8), pt_vector(out, seed + 10)]  # NON-zero: accumulate semantics
+    ge, ga = [t.copy() for t in g0], [t.copy() for t in g0]
+    de = oracle.BackpropKV(x, dK, dV, wk, wv, *ge)
+    da = mgr.BackpropKV(x, dK, dV, wk, wv, *ga)
+    assert_close(de, da, TOL, "BackpropKV.dInput")
+    for ee, aa, n in zip(ge, ga, ("WK", "bK", "WV", "bV")):
+        assert_close(ee, aa, TOL, f"BackpropKV.{n}Grad")
+    with pytest.raises(ValueError):
+        mgr.ProjectKV(pt_matrix(rows, inp + 1, 240), wk, bk, wv, bv)
+    with pytest.raises(ValueError):
+        mgr.BackpropKV(x, dK, pt_matrix(rows, out + 1, 241), wk, wv, *ga)
+
+
 def test_training_projections(mgr, oracle):  # PT:610-668
     x, dY, W = pt_matrix(4, 5, 34), pt_matrix(4, 3, 35), pt_matrix(3, 5, 36)
     ge = [np.zeros((3, 5), np.float32), np.zeros(3, np.float32), np.zeros((4, 5), np.float32)]

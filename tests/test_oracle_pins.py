@@ -204,6 +204,26 @@ def test_qkv_forward_backward_against_independent_restatement(oracle):  # PT:461
         assert_close(b0 + dY.astype(np.float64).sum(0), b1, CPU_TOL, f"bias{n}Grad")
 
 
+def test_kv_forward_backward_against_independent_restatement(oracle):  # IAccelerationManager.cs:331-332, AccelerationCPU.cs:4361-4560
+    rows, inp, out = 7, 5, 6
+    x = pt_matrix(rows, inp, 224)
+    wk, wv = pt_matrix(out, inp, 225), pt_matrix(out, inp, 226)
+    bk, bv = pt_vector(out, 227), pt_vector(out, 228)
+    K, V = oracle.ProjectKV(x, wk, bk, wv, bv)
+    x64 = x.astype(np.float64)
+    assert_close(x64 @ wk.T + bk, K, CPU_TOL, "K"); assert_close(x64 @ wv.T + bv, V, CPU_TOL, "V")
+    Kq, Vq = oracle.ProjectQKV(x, wk, bk, wk, bk, wv, bv)[1:]  # the two-output form agrees with the pinned three-output one
+    assert np.array_equal(K, Kq) and np.array_equal(V, Vq)
+    dK, dV = pt_matrix(rows, out, 229), pt_matrix(rows, out, 230)
+    g0 = [pt_matrix(out, inp, 231), pt_vector(out, 233), pt_matrix(out, inp, 232), pt_vector(out, 234)]
+    g = [t.copy() for t in g0]
+    dIn = oracle.BackpropKV(x, dK, dV, wk, wv, *g)  # gradient buffers start NON-zero: accumulate semantics
+    assert_close(dK.astype(np.float64) @ wk + dV.astype(np.float64) @ wv, dIn, CPU_TOL, "dInput")
+    for (w0, b0), (w1, b1), dY, n in zip(zip(g0[0::2], g0[1::2]), zip(g[0::2], g[1::2]), (dK, dV), "KV"):
+        assert_close(w0 + dY.astype(np.float64).T @ x64, w1, CPU_TOL, f"W{n}Grad")
+        assert_close(b0 + dY.astype(np.float64).sum(0), b1, CPU_TOL, f"bias{n}Grad")
+
+
 def test_training_ops_against_numpy(oracle):  # PT:610-737
     x, dY, W = pt_matrix(4, 5, 34), pt_matrix(4, 3, 35), pt_matrix(3, 5, 36)
     x64, dY64 = x.astype(np.float64), dY.astype(np.float64)
