@@ -302,6 +302,7 @@ def main():
                 "loss": out[0] if out else None, "grad_norm": out[1] if out else None, "phase_ms_last_step": tr.lm.timings_ms()}
         print(json.dumps(line), flush=True)
     barrier()
+    tr.close()
     if dist.is_initialized():
         dist.destroy_process_group()
 

@@ -115,7 +115,14 @@ int32_t b200_create(int32_t device, b200_ctx** out) {
 }
 
 int32_t b200_destroy(b200_ctx* ctx) {
-    if (!ctx) return B200_OK;
+    if (ctx) ctx_release(ctx);
+    return B200_OK;
+}
+
+}  // extern "C"
+
+void b200::ctx_release(b200_ctx* ctx) {
+    if (ctx->refs.fetch_sub(1) != 1) return;  // a trainer or session still uses it: the last of them frees it
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->pool) cudaFree(ctx->pool);
@@ -128,8 +135,9 @@ int32_t b200_destroy(b200_ctx* ctx) {
     for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
-    return B200_OK;
 }
+
+extern "C" {
 
 const char* b200_last_error(b200_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 

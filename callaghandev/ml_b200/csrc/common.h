@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <map>
 #include <mutex>
+#include <atomic>
 #include <string>
 #include <vector>
 
@@ -18,6 +19,10 @@ struct RopeTable {
 };
 
 struct b200_ctx {
+    // The context outlives every trainer / session created on it, whatever order the caller destroys them in
+    // (finalizers of a garbage-collected host language run in no particular order): each child holds one reference
+    // and b200_destroy only drops the owner's.
+    std::atomic<int> refs{1};
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaStream_t own_stream = nullptr;
@@ -53,6 +58,8 @@ struct b200_ctx {
 namespace b200 {
 
 int fail(b200_ctx* ctx, int code, const char* fmt, ...);
+inline void ctx_retain(b200_ctx* ctx) { ctx->refs.fetch_add(1); }
+void ctx_release(b200_ctx* ctx);  // frees the context when the last reference goes
 
 #define B200_CUDA(ctx, expr)                                                                               \
     do {                                                                                                   \

@@ -95,6 +95,7 @@ struct Batch {  // host views of the caller's batch
 
 struct b200_lm {
     b200_ctx* ctx = nullptr;
+    std::atomic<int> refs{1};  // the owner's handle plus one per generation session
     b200_lm_config cfg{};
     Layout lay;
     float *P = nullptr, *G = nullptr, *M = nullptr, *V = nullptr;
@@ -669,6 +670,7 @@ int32_t b200_lm_create(b200_ctx* ctx, const b200_lm_config* cfg, float* params_d
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     b200_lm* lm = new b200_lm();
     lm->ctx = ctx;
+    ctx_retain(ctx);
     lm->cfg = *cfg;
     if (lm->cfg.align_floats < 1) lm->cfg.align_floats = 1;
     lm->lay = make_layout(lm->cfg);
@@ -728,7 +730,7 @@ int32_t b200_lm_create(b200_ctx* ctx, const b200_lm_config* cfg, float* params_d
 }
 
 int32_t b200_lm_destroy(b200_lm* lm) {
-    if (!lm) return B200_OK;
+    if (!lm || lm->refs.fetch_sub(1) != 1) return B200_OK;  // a generation session still reads the weights: it frees them
     cudaSetDevice(lm->ctx->device);
     cudaStreamSynchronize(lm->ctx->stream);
     if (lm->ownP && lm->P) cudaFree(lm->P);
@@ -740,7 +742,9 @@ int32_t b200_lm_destroy(b200_lm* lm) {
     if (lm->h_float) cudaFreeHost(lm->h_float);
     for (cudaEvent_t e : lm->cb_events) cudaEventDestroy(e);
     for (cudaEvent_t e : lm->t_events) cudaEventDestroy(e);
+    b200_ctx* ctx = lm->ctx;
     delete lm;
+    ctx_release(ctx);
     return B200_OK;
 }
 
@@ -1107,6 +1111,7 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
         rc = lm_fail(lm, B200_ERR_CUDA, "could not initialise the generation session");
     if (rc == B200_OK) rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_len, &g->rope);
     if (rc != B200_OK) { cudaFree(g->block); delete g; return rc; }
+    lm->refs.fetch_add(1);
     *out = g;
     return B200_OK;
 }
@@ -1116,8 +1121,9 @@ int32_t b200_lm_gen_destroy(b200_lm_gen* g) {
     cudaSetDevice(g->lm->ctx->device);
     cudaStreamSynchronize(g->lm->ctx->stream);
     cudaFree(g->block);
+    b200_lm* lm = g->lm;
     delete g;
-    return B200_OK;
+    return b200_lm_destroy(lm);
 }
 
 int32_t b200_lm_gen_reset(b200_lm_gen* g) {

@@ -54,6 +54,7 @@ int32_t b200_mlp_create(b200_ctx* ctx, int32_t nLayers, const int32_t* widths, c
         m->W[l] = take((size_t)widths[l] * widths[l - 1]); m->B[l] = take((size_t)widths[l]);
         m->A[l] = take(Bz * widths[l]); m->D[l] = take(Bz * widths[l]); m->delta[l] = take(Bz * widths[l]);
     }
+    ctx_retain(ctx);
     *out = m;
     return B200_OK;
 }
@@ -63,7 +64,9 @@ int32_t b200_mlp_destroy(b200_mlp* m) {
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     if (m->block) cudaFree(m->block);
+    b200_ctx* ctx = m->ctx;
     delete m;
+    ctx_release(ctx);
     return B200_OK;
 }
 

@@ -352,6 +352,16 @@ class DataParallelLMTrainer:
         self._pending = []
         self.lm.set_grad_ready_callback(self._on_ready if self.world > 1 else None)
 
+    def close(self):
+        """Release the device state now (the callback holds a reference back to this object, so without this the
+        pair is only collected at interpreter exit)."""
+        if getattr(self, "lm", None) is not None:
+            self.torch.cuda.synchronize(self.device)
+            self.lm.set_grad_ready_callback(None)
+            self.lm.close()
+            self.mgr.Dispose()
+            self.lm = None
+
     def _on_ready(self, offset, count, event_ptr):
         torch = self.torch
         ev = torch.cuda.Event()

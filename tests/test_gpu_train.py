@@ -430,3 +430,28 @@ def test_incremental_decoding_with_device_kv_cache(mgr, oracle):
     with pytest.raises(Exception):
         g.step(9999)
     g.close(); t.close()
+
+
+def test_handles_may_be_destroyed_in_any_order(oracle):
+    """A garbage-collected host runs finalizers in no particular order: the context must stay usable until its last
+    trainer / session has gone, and a trainer until its last generation session has."""
+    import ctypes as C
+
+    from callaghandev.ml_b200 import B200LanguageModelTrainer, B200MlpBatchTrainer, CudaB200AccelerationManager
+
+    m = CudaB200AccelerationManager(0)
+    lib, ctx = m.lib, m.ctx
+    cfg = lm_config(vocab=50, d=32, H=2, L=1, f=64, act="Relu")
+    t = B200LanguageModelTrainer(m, _b200_cfg(cfg), 32)
+    t.upload_params(init_params(oracle, cfg, 3))
+    g = t.generator(8)
+    mlp = B200MlpBatchTrainer(m, [4, 3, 2], ["None", "Tanh", "Sigmoid"], max_batch=4)
+    hg, ht, hm = g.h, t.h, mlp.h
+    g.h = t.h = mlp.h = m.ctx = None  # the Python wrappers no longer own anything
+    assert lib.b200_destroy(ctx) == 0        # context first ...
+    assert lib.b200_lm_destroy(ht) == 0      # ... then the trainer under a live session ...
+    out = np.zeros(50, np.float32)
+    assert lib.b200_lm_gen_step(hg, 7, out.ctypes.data_as(C.POINTER(C.c_float))) == 0  # ... which still decodes
+    assert np.isfinite(out).all()
+    assert lib.b200_mlp_destroy(hm) == 0
+    assert lib.b200_lm_gen_destroy(hg) == 0  # the last handle frees trainer and context
