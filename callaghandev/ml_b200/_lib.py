@@ -71,6 +71,24 @@ PROTOTYPES = {
     "b200_ProjectKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _f, _f, _i32, _f, _f]),
     "b200_BackpropKV": (_i32, [_vp, _f, _i32, _i32, _f, _f, _i32, _f, _f, _f, _f, _f, _f, _f]),
     "b200_BackpropLinearProjection": (_i32, [_vp, _f, _f, _f, _i32, _i32, _i32, _f, _f, _f]),
+    # sibling trainers' operators
+    "b200_ContentAwareCrossAttentionForward": (_i32, [_vp, _f, _i32, _f, _f, _i32, _i32, _i32, _fl, _f, _f, _f, _f]),
+    "b200_BackpropTimeDecayedAttention": (_i32, [_vp, _f, _i32, _f, _f, _i32, _f, _f, _i32, _i32, _f, _f, _f, _f]),
+    "b200_ApplyContextTypeEmbedding": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i]),
+    "b200_ComputeTimeDiffMatrix": (_i32, [_vp, _i32, _f, _i32, _f]),
+    "b200_ComputeMemoryAttentionScores": (_i32, [_vp, _f, _i32, _i32, _i32, _f, _i32, _fl, _f]),
+    "b200_ProjectGlobalFeatures": (_i32, [_vp, _f, _i32, _f, _f, _i32, _f]),
+    "b200_MeanPoolRows": (_i32, [_vp, _f, _i32, _i32, _f]),
+    "b200_ExpandMeanPoolGradient": (_i32, [_vp, _f, _i32, _i32, _i32, _i32, _i32, _f]),
+    "b200_SoftmaxVector": (_i32, [_vp, _f, _i32, _f]),
+    "b200_SigmoidInPlace": (_i32, [_vp, _f, _i64]),
+    "b200_ZeroMatrixColumns": (_i32, [_vp, _f, _i32, _i32, _i32]),
+    "b200_VectorUpdateClamped": (_i32, [_vp, _f, _f, _i64, _fl, _fl, _fl]),
+    "b200_AccumulateGlobalProjectionGradients": (_i32, [_vp, _f, _i32, _f, _i32, _f, _f]),
+    "b200_Matrix3DScaleInPlace": (_i32, [_vp, _f, _i64, _fl]),
+    "b200_MatrixSquaredNorm3D": (_i32, [_vp, _f, _i64, _f]),
+    "b200_Matrix3DAddInPlace": (_i32, [_vp, _f, _f, _i64]),
+    "b200_Matrix3DUpdate": (_i32, [_vp, _f, _f, _i64, _fl]),
     "b200_BackpropOutputProjection": (_i32, [_vp, _f, _f, _f, _f, _f, _i32, _i32, _i32, _f]),
     "b200_BackpropInputProjection": (_i32, [_vp, _f, _i32, _i32, _f, _i32, _i32, _i32, _f, _f, _i32, _i32, _i32]),
     "b200_EmbedTokenIds": (_i32, [_vp, _i, _i32, _i32, _i32, _f, _i32, _i32, _f]),

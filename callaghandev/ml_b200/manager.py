@@ -438,3 +438,136 @@ class CudaB200AccelerationManager:
         dIn = np.zeros_like(x)
         self._ck(self.lib.b200_FFNInputGradientBatch(self.ctx, _pf(x), _pf(d), x.shape[0], len(widths), _pi(wd), _pi(ac), wa, ba, ga, gb, _pf(dIn)))
         return dIn
+
+    # ------------------------------------------------------------------ sibling trainers' operators (TACAMT / MMTAC / PriceTAC)
+    def ContentAwareCrossAttentionForward(self, Q, K, V, numHeads, scale, decayBias=None, needBackwardCache=True):
+        """Returns (output, attentionWeights, scoresPreSoftmax); the last two are [numHeads, queryLen, keyLen] arrays
+        (the reference's float[numHeads][,]) or None when needBackwardCache is false."""
+        q, k, v = _f(Q), _f(K), _f(V)
+        qn, e, kn = q.shape[0], q.shape[1], k.shape[0]
+        if k.shape != (kn, e) or v.shape != (kn, e):
+            raise ValueError("K and V must be [keyLen, embDim] with Q's embedding width.")
+        b = None
+        if decayBias is not None:
+            b = _f(decayBias)
+            if b.shape != (qn, kn, numHeads):
+                raise ValueError("decayBias must be [queryLen, keyLen, numHeads].")
+        out = np.zeros((qn, e), np.float32)
+        w = np.zeros((numHeads, qn, kn), np.float32) if needBackwardCache else None
+        s = np.zeros((numHeads, qn, kn), np.float32) if needBackwardCache else None
+        self._ck(self.lib.b200_ContentAwareCrossAttentionForward(self.ctx, _pf(q), qn, _pf(k), _pf(v), kn, e, int(numHeads), float(scale), _pf(b),
+                                                                 _pf(out), _pf(w), _pf(s)))
+        return out, w, s
+
+    def BackpropTimeDecayedAttention(self, q, k, v, dOutput, attentionWeights, timeDiffs, embeddingDim, numHeads):
+        """Returns (dQ, dK, dV, dDecayBias); dDecayBias is None when timeDiffs is None, as in the reference."""
+        qq, kk, vv, do = _f(q), _f(k), _f(v), _f(dOutput)
+        w = _f(attentionWeights)
+        qn, kn = qq.shape[0], kk.shape[0]
+        if w.shape != (numHeads, qn, kn):
+            raise ValueError("attentionWeights must be [numHeads, queryLen, keyLen].")
+        if qq.shape[1] != embeddingDim or kk.shape != (kn, embeddingDim) or vv.shape != (kn, embeddingDim) or do.shape != (qn, embeddingDim):
+            raise ValueError("q, k, v and dOutput must have embeddingDim columns and matching row counts.")
+        dQ, dK, dV = np.zeros_like(qq), np.zeros_like(kk), np.zeros_like(vv)
+        dB = np.zeros((qn, kn, numHeads), np.float32) if timeDiffs is not None else None
+        self._ck(self.lib.b200_BackpropTimeDecayedAttention(self.ctx, _pf(qq), qn, _pf(kk), _pf(vv), kn, _pf(do), _pf(w), int(embeddingDim),
+                                                            int(numHeads), _pf(dQ), _pf(dK), _pf(dV), _pf(dB)))
+        return dQ, dK, dV, dB
+
+    def ApplyContextTypeEmbedding(self, contextHidden, typeEmbedding, typeIndices):
+        h, t, idx = _inplace(contextHidden, "contextHidden"), _f(typeEmbedding), _i(typeIndices)
+        if len(idx) != h.shape[0]:
+            raise ValueError("typeIndices length must match contextHidden row count.")
+        if t.shape[1] != h.shape[1]:
+            raise ValueError("typeEmbedding dimension must match contextHidden embedding dimension.")
+        self._ck(self.lib.b200_ApplyContextTypeEmbedding(self.ctx, _pf(h), h.shape[0], h.shape[1], _pf(t), t.shape[0], _pi(idx)))
+
+    def ComputeTimeDiffMatrix(self, priceSeqLen, keyArrivalTimes):
+        t = _f(keyArrivalTimes)
+        out = np.zeros((max(int(priceSeqLen), 0), len(t)), np.float32)
+        self._ck(self.lib.b200_ComputeTimeDiffMatrix(self.ctx, int(priceSeqLen), _pf(t), len(t), _pf(out)))
+        return out
+
+    def ComputeMemoryAttentionScores(self, priceHidden, lastPos, contextHidden, totalCtx, scale):
+        p, c = _f(priceHidden), _f(contextHidden)
+        if c.shape[0] < totalCtx or c.shape[1] != p.shape[1]:
+            raise IndexError("contextHidden must hold totalCtx rows of priceHidden's width.")
+        out = np.zeros(totalCtx, np.float32)
+        self._ck(self.lib.b200_ComputeMemoryAttentionScores(self.ctx, _pf(p), p.shape[0], p.shape[1], int(lastPos), _pf(c), int(totalCtx),
+                                                            float(scale), _pf(out)))
+        return out
+
+    def ProjectGlobalFeatures(self, globalFeatures, projection, bias):
+        g, P, b = _f(globalFeatures), _f(projection), _f(bias)
+        ed, gd = P.shape
+        if len(g) != gd:
+            raise ValueError(f"Expected global feature length {gd}, got {len(g)}.")
+        if len(b) != ed:
+            raise ValueError(f"Expected bias length {ed}, got {len(b)}.")
+        out = np.zeros(ed, np.float32)
+        self._ck(self.lib.b200_ProjectGlobalFeatures(self.ctx, _pf(g), gd, _pf(P), _pf(b), ed, _pf(out)))
+        return out
+
+    def MeanPoolRows(self, matrix):
+        m = _f(matrix)
+        out = np.zeros(m.shape[1], np.float32)
+        self._ck(self.lib.b200_MeanPoolRows(self.ctx, _pf(m), m.shape[0], m.shape[1], _pf(out)))
+        return out
+
+    def ExpandMeanPoolGradient(self, pooledGradient, rowIndex, rowCount, embeddingDim):
+        g = _f(pooledGradient)
+        out = np.zeros((max(int(rowCount), 0), embeddingDim), np.float32)
+        self._ck(self.lib.b200_ExpandMeanPoolGradient(self.ctx, _pf(g), g.shape[0], g.shape[1], int(rowIndex), int(rowCount), int(embeddingDim),
+                                                      _pf(out)))
+        return out
+
+    def SoftmaxVector(self, scores):
+        s = _f(scores)
+        out = np.zeros(len(s), np.float32)
+        self._ck(self.lib.b200_SoftmaxVector(self.ctx, _pf(s), len(s), _pf(out)))
+        return out
+
+    def SigmoidInPlace(self, matrix):
+        m = _inplace(matrix, "matrix")
+        self._ck(self.lib.b200_SigmoidInPlace(self.ctx, _pf(m), m.size))
+
+    def ZeroMatrixColumns(self, matrix, columnCount):
+        m = _inplace(matrix, "matrix")
+        self._ck(self.lib.b200_ZeroMatrixColumns(self.ctx, _pf(m), m.shape[0], m.shape[1], int(columnCount)))
+
+    def VectorUpdateClamped(self, weights, gradients, learningRate, minValue, maxValue):
+        w, g = _inplace(weights, "weights"), _f(gradients)
+        if g.shape != w.shape:
+            raise ValueError("weights and gradients must have the same length.")
+        self._ck(self.lib.b200_VectorUpdateClamped(self.ctx, _pf(w), _pf(g), w.size, float(learningRate), float(minValue), float(maxValue)))
+
+    def AccumulateGlobalProjectionGradients(self, dGlobalHidden, globalFeatures, projectionGrad, biasGrad):
+        if dGlobalHidden is None or globalFeatures is None or projectionGrad is None or biasGrad is None:
+            return  # the reference returns silently
+        d, g = _f(dGlobalHidden), _f(globalFeatures)
+        pg, bg = _inplace(projectionGrad, "projectionGrad"), _inplace(biasGrad, "biasGrad")
+        if pg.shape != (len(d), len(g)) or bg.shape != (len(d),):
+            raise IndexError("gradient shapes must be [len(dGlobalHidden), len(globalFeatures)] and [len(dGlobalHidden)].")
+        self._ck(self.lib.b200_AccumulateGlobalProjectionGradients(self.ctx, _pf(d), len(d), _pf(g), len(g), _pf(pg), _pf(bg)))
+
+    def Matrix3DScaleInPlace(self, matrix, scale):
+        m = _inplace(matrix, "matrix")
+        self._ck(self.lib.b200_Matrix3DScaleInPlace(self.ctx, _pf(m), m.size, float(scale)))
+
+    def MatrixSquaredNorm3D(self, matrix):
+        m = _f(matrix)
+        out = C.c_float(0)
+        self._ck(self.lib.b200_MatrixSquaredNorm3D(self.ctx, _pf(m), m.size, C.byref(out)))
+        return np.float32(out.value)
+
+    def Matrix3DAddInPlace(self, target, addend):
+        t, a = _inplace(target, "target"), _f(addend)
+        if a.shape != t.shape:
+            raise ValueError("3D tensor shape mismatch.")
+        self._ck(self.lib.b200_Matrix3DAddInPlace(self.ctx, _pf(t), _pf(a), t.size))
+
+    def Matrix3DUpdate(self, weights, gradients, learningRate):
+        w, g = _inplace(weights, "weights"), _f(gradients)
+        if g.shape != w.shape:
+            raise ValueError("3D tensor shape mismatch.")
+        self._ck(self.lib.b200_Matrix3DUpdate(self.ctx, _pf(w), _pf(g), w.size, float(learningRate)))

@@ -3,6 +3,7 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
 
   attention   segmented causal attention forward + backward, 8 sequences x 1024 tokens, 16 heads of 64
   gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
+  wgrad       the weight-gradient layout alone (both operands row-contiguous along M / N, long K): 1024 x 4096 x 65536
   layernorm   LayerNorm forward + backward on 32768 x 1024
   crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
   generate    greedy decoding with the device key/value cache on the c5 model (V 32000, d 1024, 16 heads, 12 layers,
@@ -36,6 +37,17 @@ def gemm(m, rng):
     for _ in range(2):
         m.BackpropLinearProjection(x, dy, W, wg, bg, di)
     return float(np.abs(wg).mean()) + float(np.abs(y).mean())
+
+
+def wgrad(m, rng):
+    rows, inp, out = 65536, 1024, 4096
+    x = rng.normal(0, 1, (rows, inp)).astype(np.float32)
+    W = rng.normal(0, 0.02, (out, inp)).astype(np.float32)
+    dy = rng.normal(0, 1, (rows, out)).astype(np.float32)
+    wg, bg, di = np.zeros_like(W), np.zeros(out, np.float32), np.zeros_like(x)
+    for _ in range(2):
+        m.BackpropLinearProjection(x, dy, W, wg, bg, di)
+    return float(np.abs(wg).mean())
 
 
 def layernorm(m, rng):
@@ -81,7 +93,7 @@ def generate(m, rng):
     return float(out[-1])
 
 
-CASES = {"generate": generate, "attention": attention, "gemm": gemm, "layernorm": layernorm, "crossentropy": crossentropy}
+CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):

@@ -153,7 +153,7 @@ B200_API int32_t b200_ProjectQKV(b200_ctx*, const float* input, int32_t rows, in
 B200_API int32_t b200_BackpropQKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* dQ, const float* dK, const float* dV,
                                   int32_t outDim, const float* WQ, const float* WK, const float* WV, float* WQGrad, float* bQGrad,
                                   float* WKGrad, float* bKGrad, float* WVGrad, float* bVGrad, float* dInput);
-/* ProjectKV (IAccelerationManager.cs:331; AccelerationCPU.cs:4361-4417) and BackpropKV (IAccelerationManager.cs:332;
+/* ProjectKV (IAccelerationManager.cs:329; AccelerationCPU.cs:4361-4417) and BackpropKV (IAccelerationManager.cs:331;
  * AccelerationCPU.cs:4419-4560): the key/value halves of the two above, used by the cross-attention of the sibling trainers;
  * the four gradients accumulate, dInput is assigned. */
 B200_API int32_t b200_ProjectKV(b200_ctx*, const float* input, int32_t rows, int32_t inDim, const float* WK, const float* bK, const float* WV,
@@ -206,6 +206,56 @@ B200_API int32_t b200_FFNForwardBatch(b200_ctx*, const float* input, int32_t row
 B200_API int32_t b200_FFNInputGradientBatch(b200_ctx*, const float* input, const float* dOutput, int32_t rows, int32_t nLayers, const int32_t* widths,
                                             const int32_t* activations, const float* const* weights, const float* const* biases,
                                             float* const* weightGrads, float* const* biasGrads, float* dInput);
+
+/* ------------------------------------------------------------------------------------------------ A2. sibling trainers' ops
+ * The operators the TACAMT / MMTAC / PriceTAC trainers call on the same interface (IAccelerationManager.cs:251-361).
+ * Rank-3 arrays are passed flat in the reference's own element order. */
+/* ContentAwareCrossAttentionForward (IAccelerationManager.cs:263; AccelerationCPU.cs:3076-3270).  decayBias is
+ * [queryLen, keyLen, numHeads] or NULL; attentionWeights and scoresPreSoftmax are [numHeads, queryLen, keyLen] or NULL
+ * (needBackwardCache = false).  -inf scores get weight 0; a row of only -inf scores gives zero weights and output. */
+B200_API int32_t b200_ContentAwareCrossAttentionForward(b200_ctx*, const float* Q, int32_t queryLen, const float* K, const float* V,
+                                                        int32_t keyLen, int32_t embDim, int32_t numHeads, float scale, const float* decayBias,
+                                                        float* output, float* attentionWeights, float* scoresPreSoftmax);
+/* BackpropTimeDecayedAttention (IAccelerationManager.cs:287; AccelerationCPU.cs:3748-3857).  attentionWeights is
+ * [numHeads, queryLen, keyLen]; dDecayBias is [queryLen, keyLen, numHeads], or NULL where the reference is called without
+ * time differences; dQ, dK, dV are assigned.  The scale is 1/sqrt(embeddingDim / numHeads). */
+B200_API int32_t b200_BackpropTimeDecayedAttention(b200_ctx*, const float* q, int32_t queryLen, const float* k, const float* v, int32_t keyLen,
+                                                   const float* dOutput, const float* attentionWeights, int32_t embeddingDim, int32_t numHeads,
+                                                   float* dQ, float* dK, float* dV, float* dDecayBias);
+/* ApplyContextTypeEmbedding (IAccelerationManager.cs:253; AccelerationCPU.cs:2596-2644): contextHidden[i,:] += typeEmbedding[typeIndices[i],:]. */
+B200_API int32_t b200_ApplyContextTypeEmbedding(b200_ctx*, float* contextHidden, int32_t rows, int32_t embDim, const float* typeEmbedding,
+                                                int32_t typeCount, const int32_t* typeIndices);
+/* ComputeTimeDiffMatrix (IAccelerationManager.cs:255; AccelerationCPU.cs:2646-2674): out[p, s] = p - keyArrivalTimes[s]. */
+B200_API int32_t b200_ComputeTimeDiffMatrix(b200_ctx*, int32_t priceSeqLen, const float* keyArrivalTimes, int32_t numKeys, float* out);
+/* ComputeMemoryAttentionScores (IAccelerationManager.cs:257; AccelerationCPU.cs:2676-2692). */
+B200_API int32_t b200_ComputeMemoryAttentionScores(b200_ctx*, const float* priceHidden, int32_t priceRows, int32_t embDim, int32_t lastPos,
+                                                   const float* contextHidden, int32_t totalCtx, float scale, float* scores);
+/* ProjectGlobalFeatures (IAccelerationManager.cs:273; AccelerationCPU.cs:3424-3461): out = bias + projection[embDim, featureDim] * globalFeatures. */
+B200_API int32_t b200_ProjectGlobalFeatures(b200_ctx*, const float* globalFeatures, int32_t featureDim, const float* projection, const float* bias,
+                                            int32_t embDim, float* out);
+/* MeanPoolRows (IAccelerationManager.cs:279; AccelerationCPU.cs:3517-3552) and its gradient ExpandMeanPoolGradient
+ * (IAccelerationManager.cs:360; AccelerationCPU.cs:4321-4359). */
+B200_API int32_t b200_MeanPoolRows(b200_ctx*, const float* matrix, int32_t rows, int32_t cols, float* out);
+B200_API int32_t b200_ExpandMeanPoolGradient(b200_ctx*, const float* pooledGradient, int32_t pooledRows, int32_t pooledCols, int32_t rowIndex,
+                                             int32_t rowCount, int32_t embeddingDim, float* out);
+/* SoftmaxVector (IAccelerationManager.cs:285; AccelerationCPU.cs:3700-3746). */
+B200_API int32_t b200_SoftmaxVector(b200_ctx*, const float* scores, int32_t n, float* out);
+/* SigmoidInPlace (IAccelerationManager.cs:324; AccelerationCPU.cs:143-153, 4985-4992). */
+B200_API int32_t b200_SigmoidInPlace(b200_ctx*, float* matrix, int64_t count);
+/* ZeroMatrixColumns (IAccelerationManager.cs:327; AccelerationCPU.cs:5016-5035): the first min(columnCount, cols) columns of every row. */
+B200_API int32_t b200_ZeroMatrixColumns(b200_ctx*, float* matrix, int32_t rows, int32_t cols, int32_t columnCount);
+/* VectorUpdateClamped (IAccelerationManager.cs:337; AccelerationCPU.cs:5037-5056). */
+B200_API int32_t b200_VectorUpdateClamped(b200_ctx*, float* weights, const float* gradients, int64_t count, float learningRate, float minValue,
+                                          float maxValue);
+/* AccumulateGlobalProjectionGradients (IAccelerationManager.cs:358; AccelerationCPU.cs:4296-4319); any NULL array: no-op, as in the reference. */
+B200_API int32_t b200_AccumulateGlobalProjectionGradients(b200_ctx*, const float* dGlobalHidden, int32_t embDim, const float* globalFeatures,
+                                                          int32_t featureDim, float* projectionGrad, float* biasGrad);
+/* Matrix3DScaleInPlace, MatrixSquaredNorm3D (IAccelerationManager.cs:267,269; AccelerationCPU.cs:3388-3422), Matrix3DAddInPlace,
+ * Matrix3DUpdate (IAccelerationManager.cs:333,335; AccelerationCPU.cs:5058-5130): count = d0 * d1 * d2. */
+B200_API int32_t b200_Matrix3DScaleInPlace(b200_ctx*, float* matrix, int64_t count, float scale);
+B200_API int32_t b200_MatrixSquaredNorm3D(b200_ctx*, const float* matrix, int64_t count, float* out);
+B200_API int32_t b200_Matrix3DAddInPlace(b200_ctx*, float* target, const float* addend, int64_t count);
+B200_API int32_t b200_Matrix3DUpdate(b200_ctx*, float* weights, const float* gradients, int64_t count, float learningRate);
 
 /* ------------------------------------------------------------------------------------------------ B. resident LM */
 /* Model shape = TransformerConfig (Transformers/MultiTypeTransformer/TransformerConfig.cs:17-103). */

@@ -1275,3 +1275,158 @@ API void ref_mlp_scale_inputs(const real* X, int B, int F, const real* mn, const
             out[(size_t)i * F + j] = range <= 0 ? 0 : (X[(size_t)i * F + j] - mn[j]) / range;
         }
 }
+
+/* ===================================================================================================================
+ * Operators of the sibling trainers (TACAMT / MMTAC / PriceTAC) on the same interface, restated in the reference's
+ * loop order.  Rank-3 arrays are flat in the reference's element order. */
+
+/* CPU:3076-3270 ContentAwareCrossAttentionForward.  bias [q,k,H] or NULL; W and S are [H,q,k] (always written here;
+ * the wrapper drops them for needBackwardCache = false, the output is the same on both branches). */
+API void ref_ContentAwareCrossAttentionForward(const real* Q, int qLen, const real* K, const real* V, int kLen, int E, int H, real scale,
+                                               const real* bias, real* out, real* W, real* S) {
+    const int hd = E / H;
+    for (size_t i = 0; i < (size_t)qLen * E; i++) out[i] = 0;
+    for (size_t i = 0; i < (size_t)H * qLen * kLen; i++) { W[i] = 0; S[i] = 0; }
+    for (int h = 0; h < H; h++) {
+        const int off = h * hd;
+        for (int q = 0; q < qLen; q++) {
+            real* s = S + ((size_t)h * qLen + q) * kLen;
+            real* w = W + ((size_t)h * qLen + q) * kLen;
+            real mx = -INFINITY;
+            for (int k = 0; k < kLen; k++) {
+                real dot = 0;
+                for (int d = 0; d < hd; d++) dot += Q[(size_t)q * E + off + d] * K[(size_t)k * E + off + d];
+                real sc = dot * scale;
+                if (bias) sc += bias[((size_t)q * kLen + k) * H + h];
+                s[k] = sc;
+                if (!(isinf(sc) && sc < 0) && sc > mx) mx = sc;
+            }
+            if (isinf(mx) && mx < 0) continue;
+            real sum = 0;
+            for (int k = 0; k < kLen; k++) {
+                if (isinf(s[k]) && s[k] < 0) { w[k] = 0; continue; }
+                w[k] = R_EXP(s[k] - mx);
+                sum += w[k];
+            }
+            if (sum > 0) {
+                const real inv = (real)1 / sum;
+                for (int k = 0; k < kLen; k++) w[k] *= inv;
+            }
+            for (int k = 0; k < kLen; k++)
+                if (w[k] != 0)
+                    for (int d = 0; d < hd; d++) out[(size_t)q * E + off + d] += w[k] * V[(size_t)k * E + off + d];
+        }
+    }
+}
+
+/* CPU:3748-3857 BackpropTimeDecayedAttention.  W is [H,q,k]; dBias [q,k,H] or NULL; dQ, dK, dV start at zero. */
+API void ref_BackpropTimeDecayedAttention(const real* q, int qLen, const real* k, const real* v, int kLen, const real* dO, const real* W, int E,
+                                          int H, real* dQ, real* dK, real* dV, real* dBias) {
+    const int hd = E / H;
+    const real scale = (real)1 / R_SQRT((real)hd);
+    for (size_t i = 0; i < (size_t)qLen * E; i++) dQ[i] = 0;
+    for (size_t i = 0; i < (size_t)kLen * E; i++) { dK[i] = 0; dV[i] = 0; }
+    if (dBias) for (size_t i = 0; i < (size_t)qLen * kLen * H; i++) dBias[i] = 0;
+    real* dW = (real*)malloc(sizeof(real) * (size_t)(kLen > 0 ? kLen : 1));
+    for (int h = 0; h < H; h++) {
+        const int off = h * hd;
+        for (int p = 0; p < qLen; p++) {
+            const real* w = W + ((size_t)h * qLen + p) * kLen;
+            for (int s = 0; s < kLen; s++) {
+                real dot = 0;
+                for (int d = 0; d < hd; d++) {
+                    const real g = dO[(size_t)p * E + off + d];
+                    dV[(size_t)s * E + off + d] += w[s] * g;
+                    dot += g * v[(size_t)s * E + off + d];
+                }
+                dW[s] = dot;
+            }
+            real dotwg = 0;
+            for (int s = 0; s < kLen; s++) dotwg += w[s] * dW[s];
+            for (int s = 0; s < kLen; s++) {
+                const real ds = w[s] * (dW[s] - dotwg), dsc = ds * scale;
+                for (int d = 0; d < hd; d++) {
+                    dQ[(size_t)p * E + off + d] += dsc * k[(size_t)s * E + off + d];
+                    dK[(size_t)s * E + off + d] += dsc * q[(size_t)p * E + off + d];
+                }
+                if (dBias) dBias[((size_t)p * kLen + s) * H + h] += ds;
+            }
+        }
+    }
+    free(dW);
+}
+
+/* CPU:2596-2644 */
+API void ref_ApplyContextTypeEmbedding(real* hidden, int rows, int E, const real* typeEmb, const int* idx) {
+    for (int i = 0; i < rows; i++)
+        for (int d = 0; d < E; d++) hidden[(size_t)i * E + d] += typeEmb[(size_t)idx[i] * E + d];
+}
+/* CPU:2646-2674 */
+API void ref_ComputeTimeDiffMatrix(int rows, const real* keyTimes, int keys, real* out) {
+    for (int p = 0; p < rows; p++)
+        for (int s = 0; s < keys; s++) out[(size_t)p * keys + s] = (real)p - keyTimes[s];
+}
+/* CPU:2676-2692 */
+API void ref_ComputeMemoryAttentionScores(const real* price, int E, int lastPos, const real* ctx, int totalCtx, real scale, real* scores) {
+    for (int s = 0; s < totalCtx; s++) {
+        real dot = 0;
+        for (int d = 0; d < E; d++) dot += price[(size_t)lastPos * E + d] * ctx[(size_t)s * E + d];
+        scores[s] = dot * scale;
+    }
+}
+/* CPU:3424-3461 */
+API void ref_ProjectGlobalFeatures(const real* g, int gd, const real* proj, const real* bias, int ed, real* out) {
+    for (int d = 0; d < ed; d++) {
+        real dot = 0;
+        for (int j = 0; j < gd; j++) dot += proj[(size_t)d * gd + j] * g[j];
+        out[d] = bias[d] + dot;
+    }
+}
+/* CPU:3517-3552 */
+API void ref_MeanPoolRows(const real* m, int rows, int cols, real* out) {
+    for (int d = 0; d < cols; d++) out[d] = 0;
+    if (rows == 0) return;
+    for (int r = 0; r < rows; r++)
+        for (int d = 0; d < cols; d++) out[d] += m[(size_t)r * cols + d];
+    const real inv = (real)1 / (real)rows;
+    for (int d = 0; d < cols; d++) out[d] *= inv;
+}
+/* CPU:4321-4359 */
+API void ref_ExpandMeanPoolGradient(const real* pooled, int pooledCols, int rowIndex, int rowCount, int E, real* out) {
+    const real inv = (real)1 / (real)rowCount;
+    for (int t = 0; t < rowCount; t++)
+        for (int d = 0; d < E; d++) out[(size_t)t * E + d] = pooled[(size_t)rowIndex * pooledCols + d] * inv;
+}
+/* CPU:3700-3746 */
+API void ref_SoftmaxVector(const real* x, int n, real* out) {
+    if (n == 0) return;
+    real mx = -INFINITY, sum = 0;
+    for (int i = 0; i < n; i++) if (x[i] > mx) mx = x[i];
+    for (int i = 0; i < n; i++) { out[i] = R_EXP(x[i] - mx); sum += out[i]; }
+    if (sum <= 0) return;
+    const real inv = (real)1 / sum;
+    for (int i = 0; i < n; i++) out[i] *= inv;
+}
+/* CPU:4985-4992 (StableSigmoidCore, CPU:143-153) */
+API void ref_SigmoidInPlace(real* m, long long n) { for (long long i = 0; i < n; i++) m[i] = stable_sigmoid(m[i]); }
+/* CPU:5016-5035 */
+API void ref_ZeroMatrixColumns(real* m, int rows, int cols, int count) {
+    if (count <= 0) return;
+    if (count > cols) count = cols;
+    for (int i = 0; i < rows; i++)
+        for (int c = 0; c < count; c++) m[(size_t)i * cols + c] = 0;
+}
+/* CPU:5037-5056 */
+API void ref_VectorUpdateClamped(real* w, const real* g, long long n, real lr, real lo, real hi) {
+    for (long long i = 0; i < n; i++) {
+        const real v = w[i] - lr * g[i];
+        w[i] = v < lo ? lo : (v > hi ? hi : v);
+    }
+}
+/* CPU:4296-4319 */
+API void ref_AccumulateGlobalProjectionGradients(const real* dGlobal, int ed, const real* feat, int gd, real* projGrad, real* biasGrad) {
+    for (int d = 0; d < ed; d++) {
+        biasGrad[d] += dGlobal[d];
+        for (int g = 0; g < gd; g++) projGrad[(size_t)d * gd + g] += dGlobal[d] * feat[g];
+    }
+}

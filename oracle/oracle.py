@@ -218,6 +218,82 @@ class Oracle:
                                 self.p(WKg), self.p(bKg), self.p(WVg), self.p(bVg), self.p(dIn))
         return dIn
 
+    # ------------------------------------------------------------------ sibling trainers' operators
+    def ContentAwareCrossAttentionForward(self, Q, K, V, numHeads, scale, decayBias=None, needBackwardCache=True):
+        Q, K, V = self.a(Q), self.a(K), self.a(V)
+        b = None if decayBias is None else self.a(decayBias)
+        qn, e, kn = Q.shape[0], Q.shape[1], K.shape[0]
+        out = np.zeros((qn, e), self.dt)
+        W, S = np.zeros((numHeads, qn, kn), self.dt), np.zeros((numHeads, qn, kn), self.dt)
+        self.lib.ref_ContentAwareCrossAttentionForward(self.p(Q), qn, self.p(K), self.p(V), kn, e, numHeads, self.r(scale), self.p(b),
+                                                       self.p(out), self.p(W), self.p(S))
+        return (out, W, S) if needBackwardCache else (out, None, None)
+
+    def BackpropTimeDecayedAttention(self, q, k, v, dOutput, attentionWeights, timeDiffs, embeddingDim, numHeads):
+        q, k, v, dO, W = map(self.a, (q, k, v, dOutput, attentionWeights))
+        qn, kn = q.shape[0], k.shape[0]
+        dQ, dK, dV = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+        dB = np.zeros((qn, kn, numHeads), self.dt) if timeDiffs is not None else None
+        self.lib.ref_BackpropTimeDecayedAttention(self.p(q), qn, self.p(k), self.p(v), kn, self.p(dO), self.p(W), embeddingDim, numHeads,
+                                                  self.p(dQ), self.p(dK), self.p(dV), self.p(dB))
+        return dQ, dK, dV, dB
+
+    def ApplyContextTypeEmbedding(self, contextHidden, typeEmbedding, typeIndices):
+        t, idx = self.a(typeEmbedding), np.ascontiguousarray(np.asarray(typeIndices, np.int32))
+        self.lib.ref_ApplyContextTypeEmbedding(self.p(contextHidden), contextHidden.shape[0], contextHidden.shape[1], self.p(t), self.p(idx))
+
+    def ComputeTimeDiffMatrix(self, priceSeqLen, keyArrivalTimes):
+        t = self.a(keyArrivalTimes)
+        out = np.zeros((priceSeqLen, len(t)), self.dt)
+        self.lib.ref_ComputeTimeDiffMatrix(priceSeqLen, self.p(t), len(t), self.p(out))
+        return out
+
+    def ComputeMemoryAttentionScores(self, priceHidden, lastPos, contextHidden, totalCtx, scale):
+        p_, c = self.a(priceHidden), self.a(contextHidden)
+        out = np.zeros(totalCtx, self.dt)
+        self.lib.ref_ComputeMemoryAttentionScores(self.p(p_), p_.shape[1], lastPos, self.p(c), totalCtx, self.r(scale), self.p(out))
+        return out
+
+    def ProjectGlobalFeatures(self, globalFeatures, projection, bias):
+        g, P, b = self.a(globalFeatures), self.a(projection), self.a(bias)
+        out = np.zeros(P.shape[0], self.dt)
+        self.lib.ref_ProjectGlobalFeatures(self.p(g), P.shape[1], self.p(P), self.p(b), P.shape[0], self.p(out))
+        return out
+
+    def MeanPoolRows(self, matrix):
+        m = self.a(matrix)
+        out = np.zeros(m.shape[1], self.dt)
+        self.lib.ref_MeanPoolRows(self.p(m), m.shape[0], m.shape[1], self.p(out))
+        return out
+
+    def ExpandMeanPoolGradient(self, pooledGradient, rowIndex, rowCount, embeddingDim):
+        g = self.a(pooledGradient)
+        out = np.zeros((max(rowCount, 0), embeddingDim), self.dt)
+        if rowCount > 0:
+            self.lib.ref_ExpandMeanPoolGradient(self.p(g), g.shape[1], rowIndex, rowCount, embeddingDim, self.p(out))
+        return out
+
+    def SoftmaxVector(self, scores):
+        s = self.a(scores)
+        out = np.zeros(len(s), self.dt)
+        self.lib.ref_SoftmaxVector(self.p(s), len(s), self.p(out))
+        return out
+
+    def SigmoidInPlace(self, matrix):
+        self.lib.ref_SigmoidInPlace(self.p(matrix), C.c_longlong(matrix.size))
+
+    def ZeroMatrixColumns(self, matrix, columnCount):
+        self.lib.ref_ZeroMatrixColumns(self.p(matrix), matrix.shape[0], matrix.shape[1], columnCount)
+
+    def VectorUpdateClamped(self, weights, gradients, learningRate, minValue, maxValue):
+        g = self.a(gradients)
+        self.lib.ref_VectorUpdateClamped(self.p(weights), self.p(g), C.c_longlong(weights.size), self.r(learningRate), self.r(minValue),
+                                         self.r(maxValue))
+
+    def AccumulateGlobalProjectionGradients(self, dGlobalHidden, globalFeatures, projectionGrad, biasGrad):
+        d, g = self.a(dGlobalHidden), self.a(globalFeatures)
+        self.lib.ref_AccumulateGlobalProjectionGradients(self.p(d), len(d), self.p(g), len(g), self.p(projectionGrad), self.p(biasGrad))
+
     def BackpropLinearProjection(self, input, dOutput, weights, weightGrad, biasGrad, dInput):
         input, dOutput, weights = map(self.a, (input, dOutput, weights))
         self.lib.ref_BackpropLinearProjection(self.p(input), self.p(dOutput), self.p(weights), input.shape[0], input.shape[1],
@@ -395,6 +471,14 @@ def pt_matrix(rows, cols, seed, dtype=np.float32):
 def pt_vector(n, seed, dtype=np.float32):
     i = np.arange(1, n + 1, dtype=np.float64)
     return (np.sin(i * 19.19 + seed * 0.313) * 0.25).astype(np.float32).astype(dtype)
+
+
+def pt_tensor3(d0, d1, d2, seed, dtype=np.float32):
+    """Tensor3 of the same test file (AccelerationManagerParityTests.cs:2239-2254)."""
+    i = np.arange(1, d0 + 1, dtype=np.float64)[:, None, None]
+    j = np.arange(1, d1 + 1, dtype=np.float64)[None, :, None]
+    k = np.arange(1, d2 + 1, dtype=np.float64)[None, None, :]
+    return (np.sin(i * 3.1 + j * 5.7 + k * 7.9 + seed * 0.101) * 0.1).astype(np.float32).astype(dtype)
 
 
 def pt_positive_vector(n, seed, dtype=np.float32):

@@ -226,7 +226,7 @@ def test_qkv_forward_backward(mgr, oracle, rows, inp, out, seed):
         mgr.ProjectQKV(pt_matrix(rows, inp + 1, 140), wq, bq, wk, bk, wv, bv)
 
 
-@pytest.mark.parametrize("rows,inp,out,seed", [(6, 5, 8, 224), (192, 128, 128, 242), (130, 64, 72, 27)])  # IAccelerationManager.cs:331-332
+@pytest.mark.parametrize("rows,inp,out,seed", [(6, 5, 8, 224), (192, 128, 128, 242), (130, 64, 72, 27)])  # IAccelerationManager.cs:329-331
 def test_kv_forward_backward(mgr, oracle, rows, inp, out, seed):
     x = pt_matrix(rows, inp, seed)
     wk, wv = (pt_matrix(out, inp, seed + i) for i in (1, 2))

@@ -204,7 +204,7 @@ def test_qkv_forward_backward_against_independent_restatement(oracle):  # PT:461
         assert_close(b0 + dY.astype(np.float64).sum(0), b1, CPU_TOL, f"bias{n}Grad")
 
 
-def test_kv_forward_backward_against_independent_restatement(oracle):  # IAccelerationManager.cs:331-332, AccelerationCPU.cs:4361-4560
+def test_kv_forward_backward_against_independent_restatement(oracle):  # IAccelerationManager.cs:329-331, AccelerationCPU.cs:4361-4560
     rows, inp, out = 7, 5, 6
     x = pt_matrix(rows, inp, 224)
     wk, wv = pt_matrix(out, inp, 225), pt_matrix(out, inp, 226)
