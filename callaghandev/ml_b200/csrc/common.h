@@ -45,6 +45,7 @@ struct b200_ctx {
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
     int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
+    int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;

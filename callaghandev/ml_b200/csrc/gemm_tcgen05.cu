@@ -45,6 +45,7 @@ constexpr int GROUP_M = 16;
 struct TcParams {
     int M, N, K;
     int a_mn_major, b_mn_major;  // 0: K contiguous (one box per stage); 1: M/N contiguous (32-column boxes)
+    int a_box3d, b_box3d;        // M/N-contiguous operand fetched as ONE three-dimensional box (32 columns x BK rows x chunks)
     int* status;                 // host-mapped status word
     int kb_per_split;            // K blocks handled by one work item (split-K); all of them without a split
     long long split_stride;      // elements between the partial outputs of consecutive splits
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(TileCfg<BN>::THREADS) gemm_tcgen05_persistent_
     } else if (warp == 1) {
         if (lane == 0) {
             // ------------------------------------------------------------------ MMA issuer
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.a_mn_major ? 1u : 0u) << 15) | ((p.b_mn_major ? 1u : 0u) << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             // K-major: rows 128 B apart, 8-row groups 1024 B apart (SBO), 32 B per K=8 step inside the swizzle row.
             // MN-major: 32-column chunks BK*128 B apart (LBO), K rows 128 B apart in groups of 4 rows, groups 512 B
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(PAIR_THREADS) gemm_tcgen05_pair_kernel(const _
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (both CTAs, whole warp: one copy per lane)
-        const int nA = p.a_mn_major ? 4 : 1, nB = p.b_mn_major ? 4 : 1;
+        const int nA = (p.a_mn_major && !p.a_box3d) ? 4 : 1, nB = (p.b_mn_major && !p.b_box3d) ? 4 : 1;
         int kc = 0;
         bool ok = true;
         for (int item = cluster; item < n_items && ok; item += n_clusters) {
@@ -427,10 +428,12 @@ __global__ void __launch_bounds__(PAIR_THREADS) gemm_tcgen05_pair_kernel(const _
                 const int k0 = (kb_begin + kb) * BK;
                 if (lane < nA) {
                     if (!p.a_mn_major) tma_load_2d_pair(a_dst, &mapA, bar, k0, my_m);
+                    else if (p.a_box3d) tma_load_3d_pair(a_dst, &mapA, bar, 0, k0, my_m >> 5);
                     else tma_load_2d_pair(a_dst + lane * (BK * 128), &mapA, bar, my_m + 32 * lane, k0);
                 } else if (lane < nA + nB) {
                     const int c = lane - nA;
                     if (!p.b_mn_major) tma_load_2d_pair(b_dst, &mapB, bar, k0, my_n);
+                    else if (p.b_box3d) tma_load_3d_pair(b_dst, &mapB, bar, 0, k0, my_n >> 5);
                     else tma_load_2d_pair(b_dst + c * (BK * 128), &mapB, bar, my_n + 32 * c, k0);
                 }
             }
@@ -442,7 +445,7 @@ __global__ void __launch_bounds__(PAIR_THREADS) gemm_tcgen05_pair_kernel(const _
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.a_mn_major ? 1u : 0u) << 15) | ((p.b_mn_major ? 1u : 0u) << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
             const uint64_t a_d0 = umma_desc(tiles_s, p.a_mn_major ? BK * 128 : 16, p.a_mn_major ? 512 : 1024, p.a_mn_major ? 1 : 2);
             const uint64_t b_d0 = umma_desc(tiles_s + A_BYTES, p.b_mn_major ? BK * 128 : 16, p.b_mn_major ? 512 : 1024, p.b_mn_major ? 1 : 2);
@@ -559,7 +562,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
         // Lane 0 waits for the slot and posts the byte count; then every copy of the stage is issued by its own lane in
         // one warp instruction -- an M/N-contiguous operand is four 32-column boxes, and a single thread issuing eight
         // copies per stage was slower than the MMAs that consume them.
-        const int nA = p.a_mn_major ? BM / 32 : 1, nB = p.b_mn_major ? T_BN / 32 : 1;
+        const int nA = (p.a_mn_major && !p.a_box3d) ? BM / 32 : 1, nB = (p.b_mn_major && !p.b_box3d) ? T_BN / 32 : 1;
         int issued = 0;
         bool ok = true;
         for (int kb = 0; kb < kblocks && ok; kb++) {
@@ -573,10 +576,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
             const int k0 = (kb_begin + kb) * BK;
             if (lane < nA) {
                 if (!p.a_mn_major) tma_load_2d(a_dst, &mapA, bar, k0, m0);
+                else if (p.a_box3d) tma_load_3d(a_dst, &mapA, bar, 0, k0, m0 >> 5);
                 else tma_load_2d(a_dst + lane * (BK * 128), &mapA, bar, m0 + 32 * lane, k0);
             } else if (lane < nA + nB) {
                 const int c = lane - nA;
                 if (!p.b_mn_major) tma_load_2d(b_dst, &mapB, bar, k0, n0);
+                else if (p.b_box3d) tma_load_3d(b_dst, &mapB, bar, 0, k0, n0 >> 5);
                 else tma_load_2d(b_dst + c * (BK * 128), &mapB, bar, n0 + 32 * c, k0);
             }
             issued = kb + 1;
@@ -591,7 +596,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
     } else if (warp == 1) {
         if (lane == 0) {
             // ------------------------------------------------------------------ MMA issuer
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.a_mn_major ? 1u : 0u) << 15) | ((p.b_mn_major ? 1u : 0u) << 16) |
                                    ((uint32_t)(T_BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             // K-major: rows 128 B apart, 8-row groups 1024 B apart (SBO), 32 B per K=8 step inside the swizzle row.
             // MN-major: 32-column chunks BK*128 B apart (LBO), K rows 128 B apart in groups of 4 rows, groups 512 B
@@ -779,6 +784,22 @@ int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner,
     return B200_OK;
 }
 
+// An M/N-contiguous operand as one three-dimensional box: dimension 0 = 32 contiguous elements (one 128-byte swizzle
+// row), dimension 1 = the K rows (stride ld), dimension 2 = the 32-column chunks of the row (stride 128 bytes).  A box
+// of 32 x boxK x chunks lands in shared memory as [chunk][k][32], the layout the M/N-major UMMA descriptors read, with
+// one copy instruction instead of one per chunk.  The chunks are synthetic, so the extent along M/N must be a
+// multiple of 32 (nothing else keeps the last chunk inside the row); rows beyond K are zero-filled by the copy.
+int make_map_mn3d(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxK, uint32_t chunks) {
+    cuuint64_t gdim[3] = {32, outer, inner / 32};
+    cuuint64_t gstride[2] = {ld * sizeof(float), 32 * sizeof(float)};
+    cuuint32_t box[3] = {32, boxK, chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ((EncodeTiledFn)ctx->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void*)base, gdim, gstride, box, estr,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;  // the caller falls back to 32-column boxes
+}
+
 int ensure_status(b200_ctx* ctx) {
     if (ctx->status_host) return B200_OK;
     B200_CUDA(ctx, cudaHostAlloc((void**)&ctx->status_host, sizeof(int), cudaHostAllocMapped));
@@ -817,6 +838,7 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.a_mn_major = g.transA ? 1 : 0;
     p.b_mn_major = g.transB ? 0 : 1;
+    p.a_box3d = p.b_box3d = 0;  // this kernel keeps one box per 32 columns
     p.status = ctx->status_dev;
     const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
     const int kblocks_total = (g.K + BK - 1) / BK;
@@ -888,14 +910,17 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     }
     CUtensorMap mapA, mapB;
     // A: stored [M,K] (K contiguous) or [K,M] (M contiguous).  B: stored [N,K] (transB, K contiguous) or [K,N].
-    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BM, false));
-    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
-    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BN, false));
-    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
     TcParams p;
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.a_mn_major = g.transA ? 1 : 0;
     p.b_mn_major = g.transB ? 0 : 1;
+    p.a_box3d = p.b_box3d = 0;
+    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BM, false));
+    else if (ctx->gemm_box3d && g.M % 32 == 0 && make_map_mn3d(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, BM / 32) == B200_OK) p.a_box3d = 1;
+    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
+    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BN, false));
+    else if (ctx->gemm_box3d && g.N % 32 == 0 && make_map_mn3d(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, BN / 32) == B200_OK) p.b_box3d = 1;
+    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
     p.status = ctx->status_dev;
     const int tiles = ((g.N + BN - 1) / BN) * ((g.M + BM - 1) / BM);
     const int kblocks_total = (g.K + BK - 1) / BK;
@@ -980,14 +1005,17 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
     }
     CUtensorMap mapA, mapB;
     // every CTA loads 128 rows of A and 128 of the tile's 256 B rows per stage
-    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 128, false));
-    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
-    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 128, false));
-    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
     TcParams p;
     p.M = g.M; p.N = g.N; p.K = g.K;
     p.a_mn_major = g.transA ? 1 : 0;
     p.b_mn_major = g.transB ? 0 : 1;
+    p.a_box3d = p.b_box3d = 0;
+    if (!g.transA) B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, 128, false));
+    else if (ctx->gemm_box3d && g.M % 32 == 0 && make_map_mn3d(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, 4) == B200_OK) p.a_box3d = 1;
+    else B200_TRY(make_map(ctx, &mapA, g.A, (uint64_t)g.M, (uint64_t)g.K, (uint64_t)g.lda, BK, true));
+    if (g.transB) B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, 128, false));
+    else if (ctx->gemm_box3d && g.N % 32 == 0 && make_map_mn3d(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, 4) == B200_OK) p.b_box3d = 1;
+    else B200_TRY(make_map(ctx, &mapB, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb, BK, true));
     p.status = ctx->status_dev;
     const int kblocks_total = (g.K + BK - 1) / BK;
     const int tiles = ((g.M + 255) / 256) * ((g.N + PAIR_BN - 1) / PAIR_BN);
@@ -1084,8 +1112,11 @@ int gemm_tcgen05(b200_ctx* ctx, const Gemm& g) {
     // one-CTA persistent kernel for short K (where the epilogue and the pipeline fill are a large share of a tile),
     // one tile per CTA otherwise.
     const int mode = ctx->gemm_tile_n;  // 0 = choose; 1 = always one tile per CTA; 128 / 256 = always one-CTA persistent with that width
-    // (weight gradients -- both operands M/N-contiguous, very long K -- measured 5-12 % faster on the one-tile kernel)
-    if (g.M >= 256 && g.N >= 256 && (mode == 512 || (mode == 0 && !g.transA))) return gemm_tcgen05_pair(ctx, g);  // two SMs per 256 x 256 tile
+    // Weight gradients (both operands M/N-contiguous, very long K) go to the two-SM kernel too when each operand stage
+    // can be fetched as one three-dimensional box (4-8 % faster there than one tile per CTA); with one box per 32
+    // columns the one-tile kernel was the faster of the two.
+    const bool wgrad_pair = ctx->gemm_box3d && g.M % 32 == 0 && g.N % 32 == 0;
+    if (g.M >= 256 && g.N >= 256 && (mode == 512 || (mode == 0 && (!g.transA || wgrad_pair)))) return gemm_tcgen05_pair(ctx, g);  // two SMs per 256 x 256 tile
     if (mode == 128) return gemm_tcgen05_persistent<128>(ctx, g);
     if (mode == 256 && g.N >= 256) return gemm_tcgen05_persistent<256>(ctx, g);
     if (mode == 0 && g.K <= 1024) return g.N >= 256 ? gemm_tcgen05_persistent<256>(ctx, g) : gemm_tcgen05_persistent<128>(ctx, g);
