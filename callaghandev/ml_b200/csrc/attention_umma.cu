@@ -147,8 +147,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // Q is requested right away: its latency overlaps the TMEM allocation and the first sync.
         mbar_expect_tx(q_full, U_TILE);
-        tma_load_2d(Qs, &mapQ, q_full, head * UHD, sg.qStart + q0);
-        tma_load_2d(Qs + U_ATOM, &mapQ, q_full, head * UHD + 32, sg.qStart + q0);
+        tma_load_3d(Qs, &mapQ, q_full, 0, sg.qStart + q0, head * (UHD / 32));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(FWD_TMEM_COLS) : "memory");
@@ -170,14 +169,12 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
                 ok = mbar_wait(k_empty, (j & 1) ^ 1, status, 11);
                 if (!ok) break;
                 mbar_expect_tx(k_full, U_TILE);
-                tma_load_2d(Ks, &mapK, k_full, col, row);
-                tma_load_2d(Ks + U_ATOM, &mapK, k_full, col + 32, row);
+                tma_load_3d(Ks, &mapK, k_full, 0, row, col >> 5);
                 kIssued = j + 1;
                 ok = mbar_wait(v_empty, (j & 1) ^ 1, status, 12);
                 if (!ok) break;
                 mbar_expect_tx(v_full, U_TILE);
-                tma_load_2d(Vs, &mapV, v_full, col, row);
-                tma_load_2d(Vs + U_ATOM, &mapV, v_full, col + 32, row);
+                tma_load_3d(Vs, &mapV, v_full, 0, row, col >> 5);
                 vIssued = j + 1;
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
@@ -445,10 +442,8 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
         mbar_expect_tx(qdo_full, 2 * T128);
-        tma_load_2d(Qs, &mapQ, qdo_full, head * UHD, sg.qStart + q0);
-        tma_load_2d(Qs + A128, &mapQ, qdo_full, head * UHD + 32, sg.qStart + q0);
-        tma_load_2d(dOs, &mapdO, qdo_full, head * UHD, sg.qStart + q0);
-        tma_load_2d(dOs + A128, &mapdO, qdo_full, head * UHD + 32, sg.qStart + q0);
+        tma_load_3d(Qs, &mapQ, qdo_full, 0, sg.qStart + q0, head * (UHD / 32));
+        tma_load_3d(dOs, &mapdO, qdo_full, 0, sg.qStart + q0, head * (UHD / 32));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -472,10 +467,8 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 TR(0, nk, 0);
                 const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
                 mbar_expect_tx(bar, 2 * T64);
-                tma_load_2d(base, &mapK, bar, col, row);
-                tma_load_2d(base + A64, &mapK, bar, col + 32, row);
-                tma_load_2d(base + T64, &mapV, bar, col, row);
-                tma_load_2d(base + T64 + A64, &mapV, bar, col + 32, row);
+                tma_load_3d(base, &mapK, bar, 0, row, col >> 5);
+                tma_load_3d(base + T64, &mapV, bar, 0, row, col >> 5);
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
@@ -679,10 +672,8 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
         mbar_expect_tx(kv_full, 2 * T128);
-        tma_load_2d(Ks, &mapK, kv_full, head * UHD, sg.kStart + k0);
-        tma_load_2d(Ks + A128, &mapK, kv_full, head * UHD + 32, sg.kStart + k0);
-        tma_load_2d(Vs, &mapV, kv_full, head * UHD, sg.kStart + k0);
-        tma_load_2d(Vs + A128, &mapV, kv_full, head * UHD + 32, sg.kStart + k0);
+        tma_load_3d(Ks, &mapK, kv_full, 0, sg.kStart + k0, head * (UHD / 32));
+        tma_load_3d(Vs, &mapV, kv_full, 0, sg.kStart + k0, head * (UHD / 32));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -705,10 +696,8 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
                 if (!ok) break;
                 const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
                 mbar_expect_tx(bar, 2 * T64);
-                tma_load_2d(base, &mapQ, bar, col, row);
-                tma_load_2d(base + A64, &mapQ, bar, col + 32, row);
-                tma_load_2d(base + T64, &mapdO, bar, col, row);
-                tma_load_2d(base + T64 + A64, &mapdO, bar, col + 32, row);
+                tma_load_3d(base, &mapQ, bar, 0, row, col >> 5);
+                tma_load_3d(base + T64, &mapdO, bar, 0, row, col >> 5);
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
@@ -930,6 +919,14 @@ int configure(b200_ctx* ctx) {
 }
 }  // namespace
 
+// A head's 64 columns are two 32-column swizzle rows: one three-dimensional box brings both in one copy.
+static int map2(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t boxRows, bool mn_major) {
+    if (make_map_chunked(ctx, map, base, cols, rows, ld, boxRows, 2, mn_major) != B200_OK)
+        return fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled refused the attention operand map (cols %llu rows %llu ld %llu)",
+                    (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)ld);
+    return B200_OK;
+}
+
 bool attn_umma_bwd_eligible(b200_ctx* ctx, const Attn& t) {
     auto ok = [](const void* p, int ld) { return p && (((uintptr_t)p) & 15) == 0 && (ld & 3) == 0; };
     return attn_umma_eligible(ctx, t) && t.maxKLen >= 128 && t.rowDot && ok(t.dO, t.lddo) && ok(t.dQ, t.lddq) && ok(t.dK, t.lddk) && ok(t.dV, t.lddv);
@@ -940,14 +937,14 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     const uint64_t cols = (uint64_t)t.numHeads * UHD;
     const uint64_t nq = (uint64_t)t.totalQ, nk = (uint64_t)t.totalK;
     CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
-    B200_TRY(make_map(ctx, &q128, t.Q, cols, nq, (uint64_t)t.ldq, 128, false));
-    B200_TRY(make_map(ctx, &do128, t.dO, cols, nq, (uint64_t)t.lddo, 128, false));
-    B200_TRY(make_map(ctx, &k128, t.K, cols, nk, (uint64_t)t.ldk, 128, false));
-    B200_TRY(make_map(ctx, &v128, t.V, cols, nk, (uint64_t)t.ldv, 128, false));
-    B200_TRY(make_map(ctx, &q64, t.Q, cols, nq, (uint64_t)t.ldq, 64, false));
-    B200_TRY(make_map(ctx, &do64, t.dO, cols, nq, (uint64_t)t.lddo, 64, false));
-    B200_TRY(make_map(ctx, &k64, t.K, cols, nk, (uint64_t)t.ldk, 64, false));
-    B200_TRY(make_map(ctx, &v64, t.V, cols, nk, (uint64_t)t.ldv, 64, false));
+    B200_TRY(map2(ctx, &q128, t.Q, cols, nq, (uint64_t)t.ldq, 128, false));
+    B200_TRY(map2(ctx, &do128, t.dO, cols, nq, (uint64_t)t.lddo, 128, false));
+    B200_TRY(map2(ctx, &k128, t.K, cols, nk, (uint64_t)t.ldk, 128, false));
+    B200_TRY(map2(ctx, &v128, t.V, cols, nk, (uint64_t)t.ldv, 128, false));
+    B200_TRY(map2(ctx, &q64, t.Q, cols, nq, (uint64_t)t.ldq, 64, false));
+    B200_TRY(map2(ctx, &do64, t.dO, cols, nq, (uint64_t)t.lddo, 64, false));
+    B200_TRY(map2(ctx, &k64, t.K, cols, nk, (uint64_t)t.ldk, 64, false));
+    B200_TRY(map2(ctx, &v64, t.V, cols, nk, (uint64_t)t.ldv, 64, false));
     UBwdArgs a;
     a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
     a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
@@ -968,9 +965,9 @@ int attn_forward_umma(b200_ctx* ctx, const Attn& t) {
     B200_TRY(configure(ctx));
     const uint64_t cols = (uint64_t)t.numHeads * UHD;
     CUtensorMap mq, mk, mv;
-    B200_TRY(make_map(ctx, &mq, t.Q, cols, (uint64_t)t.totalQ, (uint64_t)t.ldq, 128, false));
-    B200_TRY(make_map(ctx, &mk, t.K, cols, (uint64_t)t.totalK, (uint64_t)t.ldk, 128, false));
-    B200_TRY(make_map(ctx, &mv, t.V, cols, (uint64_t)t.totalK, (uint64_t)t.ldv, 128, true));
+    B200_TRY(map2(ctx, &mq, t.Q, cols, (uint64_t)t.totalQ, (uint64_t)t.ldq, 128, false));
+    B200_TRY(map2(ctx, &mk, t.K, cols, (uint64_t)t.totalK, (uint64_t)t.ldk, 128, false));
+    B200_TRY(map2(ctx, &mv, t.V, cols, (uint64_t)t.totalK, (uint64_t)t.ldv, 128, true));
     UArgs a;
     a.O = t.O; a.ldo = t.ldo; a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
     a.scale = t.scale; a.status = ctx->status_dev;

@@ -784,20 +784,25 @@ int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner,
     return B200_OK;
 }
 
-// An M/N-contiguous operand as one three-dimensional box: dimension 0 = 32 contiguous elements (one 128-byte swizzle
+// Several 32-column chunks of a row-major matrix as one three-dimensional box (used for M/N-contiguous GEMM operands
+// and for the 64-wide head slices of attention): dimension 0 = 32 contiguous elements (one 128-byte swizzle
 // row), dimension 1 = the K rows (stride ld), dimension 2 = the 32-column chunks of the row (stride 128 bytes).  A box
 // of 32 x boxK x chunks lands in shared memory as [chunk][k][32], the layout the M/N-major UMMA descriptors read, with
 // one copy instruction instead of one per chunk.  The chunks are synthetic, so the extent along M/N must be a
 // multiple of 32 (nothing else keeps the last chunk inside the row); rows beyond K are zero-filled by the copy.
-int make_map_mn3d(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxK, uint32_t chunks) {
+int make_map_chunked(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxOuter,
+                     uint32_t chunks, bool mn_major) {
     cuuint64_t gdim[3] = {32, outer, inner / 32};
     cuuint64_t gstride[2] = {ld * sizeof(float), 32 * sizeof(float)};
-    cuuint32_t box[3] = {32, boxK, chunks};
+    cuuint32_t box[3] = {32, boxOuter, chunks};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = ((EncodeTiledFn)ctx->tmap_encode)(map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void*)base, gdim, gstride, box, estr,
-                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;  // the caller falls back to 32-column boxes
+    return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
+}
+int make_map_mn3d(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxK, uint32_t chunks) {
+    return make_map_chunked(ctx, map, base, inner, outer, ld, boxK, chunks, true);  // the caller falls back to 32-column boxes
 }
 
 int ensure_status(b200_ctx* ctx) {

@@ -194,5 +194,8 @@ int ensure_status(b200_ctx* ctx);    // allocates the host-mapped status word th
 // (16-byte atoms for a K-contiguous operand, 32-byte atoms for an M/N-contiguous one, matching the UMMA layout types),
 // out-of-range elements read as zero, FP32 -> TF32 conversion (round to nearest) on load.
 int make_map(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxOuter, bool mn_major);
+// `chunks` consecutive 32-column slices x boxOuter rows in one copy; lands as [chunk][row][32]; inner must be a multiple of 32.
+int make_map_chunked(b200_ctx* ctx, CUtensorMap* map, const float* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t boxOuter,
+                     uint32_t chunks, bool mn_major);
 
 }  // namespace b200
