@@ -109,6 +109,8 @@ struct Gemm {
     int act = B200_ACT_NONE; int act_conv = 0;  // 0: transformer-FFN conventions, 1: batch-MLP conventions
     float* dout = nullptr; int lddo = 0;
     const float* mulz = nullptr; int ldmulz = 0; int mulz_act = B200_ACT_NONE;
+    int act_sign_zero = 0;  // activation outputs that are 0 because z < 0 are stored as -0.0 (lets ReLU'(z) be recovered from a)
+    int mulz_is_act = 0;    // mulz holds the activation OUTPUT (stored with act_sign_zero); its derivative is computed from that
     const float* mulmat = nullptr; int ldmul = 0;
     const float* addmat = nullptr; int ldadd = 0;
     float sgd_lr = 0.f, sgd_lambda = 0.f;

@@ -46,6 +46,20 @@ __device__ __forceinline__ float stable_sigmoid(float x) {
     float z = expf(x);
     return z / (1.0f + z);
 }
+// The same derivative computed from the stored activation instead of the pre-activation, so that the forward pass
+// need not keep both.  It returns exactly what ffn_act_der returns for every activation whose derivative is a function
+// of its output -- all but Swish -- PROVIDED the forward pass marks "z < 0 (or NaN) gave a == 0" with a negative zero
+// (act_sign_zero below): ReLU'(z) is 1 for z >= 0, and +0 / -0 is the one bit that a = max(z, 0) loses.
+__device__ __forceinline__ float ffn_der_from_act(float a, int t) {
+    switch (t) {
+        case B200_ACT_SIGMOID: return a * (1.0f - a);
+        case B200_ACT_TANH: return 1.0f - a * a;
+        case B200_ACT_RELU: return signbit(a) ? 0.f : 1.f;
+        case B200_ACT_LEAKYRELU: return a > 0.f ? 1.f : 0.1f;
+        default: return 1.f;
+    }
+}
+__device__ __forceinline__ float act_sign_zero(float z, float a) { return (a == 0.f && !(z >= 0.f)) ? -0.0f : a; }
 // Transformer-FFN conventions: forward NeuralNetwork.cs:670-702, derivative NeuralNetwork.cs:886-946
 // (ReLU'(0) = 1; LeakyReLU slope 0.01 forward but derivative 0.1 for z <= 0).
 __device__ __forceinline__ void ffn_act_der(float z, int t, float& a, float& d) {

@@ -18,6 +18,7 @@ struct Epilogue {
     const float* addmat; int ldadd;
     float sgd_lr, sgd_lambda;
     int round_tf32;
+    int act_sign_zero, mulz_is_act;
     const float* rope_table; const int32_t* rope_pos; int rope_cols, rope_hd;
 };
 
@@ -49,11 +50,13 @@ __device__ __forceinline__ void epilogue_store(const Epilogue& e, int m, int n, 
         if (e.act_conv) mlp_act_der(v, e.act, a, d);
         else ffn_act_der(v, e.act, a, d);
         if (e.dout) e.dout[(size_t)m * e.lddo + n] = d;
-        v = a;
+        v = e.act_sign_zero ? act_sign_zero(v, a) : a;
     }
     if (e.mulz) {
         float a, d;
-        ffn_act_der(e.mulz[(size_t)m * e.ldmulz + n], e.mulz_act, a, d);
+        const float zv = e.mulz[(size_t)m * e.ldmulz + n];
+        if (e.mulz_is_act) d = ffn_der_from_act(zv, e.mulz_act);
+        else ffn_act_der(zv, e.mulz_act, a, d);
         v *= d;
     }
     if (e.mulmat) v *= e.mulmat[(size_t)m * e.ldmul + n];

@@ -90,6 +90,7 @@ static Epilogue make_epilogue(const Gemm& g) {
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = nullptr; e.rope_pos = nullptr; e.rope_cols = 0; e.rope_hd = 0;  // the rotation is a separate kernel behind this engine
     return e;

@@ -164,15 +164,22 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                             st4(ep.C + (size_t)split * p.split_stride + m * ep.ldc + n, v);
                         } else if (EPI == EPI_ACT) {
                             v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
-                            st4(ep.zout + m * ep.ldz + n, v);
+                            if (ep.zout) st4(ep.zout + m * ep.ldz + n, v);
+                            const float4 z = v;
                             float d;
                             ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
                             ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
+                            if (ep.act_sign_zero) { v.x = act_sign_zero(z.x, v.x); v.y = act_sign_zero(z.y, v.y); v.z = act_sign_zero(z.z, v.z); v.w = act_sign_zero(z.w, v.w); }
                             st4(ep.C + m * ep.ldc + n, v);
                         } else {  // EPI_MULZ
                             float a, dx, dy, dz, dw;
-                            ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
-                            ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                            if (ep.mulz_is_act) {
+                                dx = ffn_der_from_act(ext[i].x, ep.mulz_act); dy = ffn_der_from_act(ext[i].y, ep.mulz_act);
+                                dz = ffn_der_from_act(ext[i].z, ep.mulz_act); dw = ffn_der_from_act(ext[i].w, ep.mulz_act);
+                            } else {
+                                ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
+                                ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                            }
                             v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
                             st4(ep.C + m * ep.ldc + n, v);
                         }
@@ -703,15 +710,22 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_tile_kernel(const __grid
                                 st4(ep.C + (size_t)blockIdx.y * p.split_stride + m * ep.ldc + n, v);
                             } else if (EPI == EPI_ACT) {
                                 v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
-                                st4(ep.zout + m * ep.ldz + n, v);
+                                if (ep.zout) st4(ep.zout + m * ep.ldz + n, v);
+                                const float4 z = v;
                                 float d;
                                 ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
                                 ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
+                                if (ep.act_sign_zero) { v.x = act_sign_zero(z.x, v.x); v.y = act_sign_zero(z.y, v.y); v.z = act_sign_zero(z.z, v.z); v.w = act_sign_zero(z.w, v.w); }
                                 st4(ep.C + m * ep.ldc + n, v);
                             } else {  // EPI_MULZ
                                 float a, dx, dy, dz, dw;
-                                ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
-                                ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                                if (ep.mulz_is_act) {
+                                    dx = ffn_der_from_act(ext[i].x, ep.mulz_act); dy = ffn_der_from_act(ext[i].y, ep.mulz_act);
+                                    dz = ffn_der_from_act(ext[i].z, ep.mulz_act); dw = ffn_der_from_act(ext[i].w, ep.mulz_act);
+                                } else {
+                                    ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
+                                    ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                                }
                                 v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
                                 st4(ep.C + m * ep.ldc + n, v);
                             }
@@ -864,6 +878,7 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     p.items = tiles * splits;
@@ -889,8 +904,8 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     int kind = EPI_GENERIC;
     if (vec_c && no_sgd) {
         if (plain_act && !g.mulz && (!g.addmat || (g.ldadd % 4 == 0 && a16(g.addmat)))) kind = EPI_LINEAR;
-        else if (g.zout && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
-                 g.ldz % 4 == 0 && a16(g.zout))
+        else if (g.act != B200_ACT_NONE && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
+                 (!g.zout || (g.ldz % 4 == 0 && a16(g.zout))))
             kind = EPI_ACT;
         else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
             kind = EPI_MULZ;
@@ -957,6 +972,7 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     dim3 grid((unsigned)tiles, (unsigned)splits);
@@ -981,8 +997,8 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     int kind = EPI_GENERIC;
     if (vec_c && no_sgd) {
         if (plain_act && !g.mulz && (!g.addmat || (g.ldadd % 4 == 0 && a16(g.addmat)))) kind = EPI_LINEAR;
-        else if (g.zout && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
-                 g.ldz % 4 == 0 && a16(g.zout))
+        else if (g.act != B200_ACT_NONE && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
+                 (!g.zout || (g.ldz % 4 == 0 && a16(g.zout))))
             kind = EPI_ACT;
         else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
             kind = EPI_MULZ;
@@ -1049,6 +1065,7 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
     e.C = g.C; e.ldc = g.ldc; e.alpha = g.alpha; e.alpha_dev = g.alpha_dev; e.accumulate = g.accumulate; e.bias = g.bias;
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
+    e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     int clusters = n_pairs;
@@ -1083,8 +1100,8 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
     int kind = EPI_GENERIC;
     if (vec_c && no_sgd) {
         if (plain_act && !g.mulz && (!g.addmat || (g.ldadd % 4 == 0 && a16(g.addmat)))) kind = EPI_LINEAR;
-        else if (g.zout && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
-                 g.ldz % 4 == 0 && a16(g.zout))
+        else if (g.act != B200_ACT_NONE && !g.dout && g.act_conv == 0 && !g.mulz && !g.addmat && !g.accumulate && g.alpha == 1.f && !g.alpha_dev &&
+                 (!g.zout || (g.ldz % 4 == 0 && a16(g.zout))))
             kind = EPI_ACT;
         else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
             kind = EPI_MULZ;

@@ -265,7 +265,10 @@ int forward_pass(b200_lm* lm, const Pass& p) {
         {
             Gemm g;
             g.M = N; g.N = f; g.K = d; g.A = k.n1; g.lda = d; g.B = P + L.W1; g.ldb = d; g.transB = 1;
-            g.C = k.a1; g.ldc = f; g.bias = P + L.fb1; g.zout = k.z1; g.ldz = f; g.act = c.ffn_activation;
+            // Only the activation is cached: the backward pass recovers act'(z) from it (a negative zero marks the
+            // ReLU outputs that came from z < 0).  Swish is the one activation whose derivative needs z itself.
+            g.C = k.a1; g.ldc = f; g.bias = P + L.fb1; g.act = c.ffn_activation; g.act_sign_zero = 1;
+            if (c.ffn_activation == B200_ACT_SWISH) { g.zout = k.z1; g.ldz = f; }
             B200_TRY(gemm(ctx, g));
         }
         B200_TRY(linear_fwd(ctx, k.a1, N, f, P + L.W2, P + L.fb2, d, lm->proj, d));
@@ -305,7 +308,9 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         {
             Gemm g;  // delta1 = (delta2 * W2) o act'(z1)
             g.M = N; g.N = f; g.K = d; g.A = t1; g.lda = d; g.B = P + L.W2; g.ldb = f; g.C = lm->d1; g.ldc = f;
-            g.mulz = k.z1; g.ldmulz = f; g.mulz_act = c.ffn_activation;
+            if (c.ffn_activation == B200_ACT_SWISH) { g.mulz = k.z1; g.ldmulz = f; }
+            else { g.mulz = k.a1; g.ldmulz = f; g.mulz_is_act = 1; }
+            g.mulz_act = c.ffn_activation;
             B200_TRY(gemm(ctx, g));
         }
         B200_TRY(wgrad(ctx, lm->d1, f, k.n1, d, N, f, d, G + L.W1, G + L.fb1));

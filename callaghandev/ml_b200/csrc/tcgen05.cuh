@@ -183,8 +183,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     const uint16_t mask = 3;
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
 }
+// Arrive on a barrier that may live in the peer CTA.  Used to hand an accumulator back to the MMA issuer: what must be
+// ordered before it is the completion of this warp's tcgen05.ld (tcgen05.wait::ld + tcgen05.fence::before_thread_sync
+// do that), not the warp's global stores, so no cluster-scope release -- that form made every epilogue warp wait
+// ~2000 cycles per tile for its outstanding stores to be acknowledged by L2.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
 
 // Host side (defined in gemm_tcgen05.cu).

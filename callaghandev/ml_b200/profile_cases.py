@@ -4,6 +4,8 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
   attention   segmented causal attention forward + backward, 8 sequences x 1024 tokens, 16 heads of 64
   gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
   wgrad       the weight-gradient layout alone (both operands row-contiguous along M / N, long K): 1024 x 4096 x 65536
+  ffn         feed-forward block forward + input gradient (bias+activation and derivative-multiply GEMM epilogues),
+              16384 rows, 1024 -> 4096 -> 1024, ReLU
   layernorm   LayerNorm forward + backward on 32768 x 1024
   crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
   generate    greedy decoding with the device key/value cache on the c5 model (V 32000, d 1024, 16 heads, 12 layers,
@@ -50,6 +52,19 @@ def wgrad(m, rng):
     return float(np.abs(wg).mean())
 
 
+def ffn(m, rng):
+    rows, d, f = 16384, 1024, 4096
+    x = rng.normal(0, 1, (rows, d)).astype(np.float32)
+    dy = rng.normal(0, 1, (rows, d)).astype(np.float32)
+    W = [rng.normal(0, 0.02, (f, d)).astype(np.float32), rng.normal(0, 0.02, (d, f)).astype(np.float32)]
+    B = [np.zeros(f, np.float32), np.zeros(d, np.float32)]
+    r = None
+    for _ in range(2):
+        y = m.FFNForwardBatch(x, [d, f, d], ["None", "Relu", "None"], W, B)
+        r = m.FFNInputGradientBatch(x, dy, [d, f, d], ["None", "Relu", "None"], W, B)
+    return float(np.abs(y).mean()) + float(np.abs(r).mean())
+
+
 def layernorm(m, rng):
     rows, f = 32768, 1024
     x = rng.normal(0, 1, (rows, f)).astype(np.float32)
@@ -93,7 +108,7 @@ def generate(m, rng):
     return float(out[-1])
 
 
-CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "layernorm": layernorm, "crossentropy": crossentropy}
+CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "ffn": ffn, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):

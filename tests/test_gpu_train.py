@@ -455,3 +455,40 @@ def test_handles_may_be_destroyed_in_any_order(oracle):
     assert np.isfinite(out).all()
     assert lib.b200_mlp_destroy(hm) == 0
     assert lib.b200_lm_gen_destroy(hg) == 0  # the last handle frees trainer and context
+
+
+@pytest.mark.parametrize("act", ["Relu", "Leakyrelu"])
+@pytest.mark.parametrize("engine", ["fp32", "tf32"])
+def test_activation_derivative_at_and_below_zero(oracle, act, engine):
+    """Only the activation output is cached for the backward pass.  The reference's FFN conventions make that lossy at
+    one point -- ReLU'(0) is 1 (NeuralNetwork.cs:886-946) while ReLU(0) = ReLU(z<0) = 0 -- so hidden units are pinned
+    to z == 0 exactly (zero weights, zero bias: gradient must flow) and to z < 0 (zero weights, negative bias: no
+    gradient), at sizes the vectorised tcgen05 epilogues take, and the gradients are compared with the oracle."""
+    from callaghandev.ml_b200 import GEMM_AUTO, GEMM_FP32_SIMT, B200LanguageModelTrainer, CudaB200AccelerationManager
+
+    m = CudaB200AccelerationManager(0, GEMM_FP32_SIMT if engine == "fp32" else GEMM_AUTO)
+    d, f = 128, 256
+    cfg = lm_config(vocab=300, d=d, H=2, L=1, f=f, act=act)
+    P = init_params(oracle, cfg, 5)
+    tensors = oracle.lm_tensors(cfg)
+    (w1, r1, c1), (b1, _, _) = tensors[1 + 12], tensors[1 + 13]
+    W1 = P[w1:w1 + r1 * c1].reshape(r1, c1)
+    assert (r1, c1) == (f, d)
+    W1[:64] = 0; P[b1:b1 + 64] = 0          # z == 0 exactly
+    W1[64:128] = 0; P[b1 + 64:b1 + 128] = -0.5  # z < 0
+    rng = np.random.default_rng(3)
+    toks, off = token_batch(rng, 4, 300, 130, 160)  # >= 128 rows per pass: the tensor-core GEMMs and their 128-bit epilogues run
+    t = B200LanguageModelTrainer(m, _b200_cfg(cfg), 1024)
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, use_clip=False, do_step=False)
+    al, an, av = t.train_step_discrete(toks, off, 1e-3, use_clip=False, do_step=False)
+    tol = 2e-5 if engine == "fp32" else 2e-3
+    assert_close(el, al, tol, "loss")
+    ga = t.download_grads()
+    _compare_tensors(oracle, cfg, ge, ga, tol, "grad")
+    gb1 = ga[b1:b1 + f]
+    assert np.all(ge[b1:b1 + 64] != 0) and np.all(gb1[:64] != 0), "units at z == 0 receive gradient (ReLU'(0) = 1 / LeakyReLU'(0) = 0.1)"
+    if act == "Relu":
+        assert np.all(gb1[64:128] == 0), "units below zero receive none"
+    t.close(); m.Dispose()
