@@ -130,6 +130,42 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                 if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
                 const bool rope = EPI == EPI_LINEAR && ep.rope_table && n < ep.rope_cols;
                 const int rows = min(32, p.M - (m0 + 32 * q));
+                if (EPI == EPI_ACT) {
+                    // No operand loads to overlap here, so a rolled loop with ONE activation switch per row keeps the
+                    // code small: the unrolled form below inlines every activation's code 32 times and ran out of
+                    // the instruction cache (the warps spent more time waiting for instructions than storing).
+#pragma unroll 2
+                    for (int rr = rsub; rr < rows; rr += 2) {
+                        const size_t m = (size_t)(m0 + 32 * q + rr);
+                        float4 z = ld4(stage + rr * EPI_STRIDE64 + 4 * l16);
+                        z.x += b4.x; z.y += b4.y; z.z += b4.z; z.w += b4.w;
+                        if (ep.zout) st4(ep.zout + m * ep.ldz + n, z);
+                        float4 a = z;
+                        switch (ep.act) {
+                            case B200_ACT_RELU: a.x = z.x > 0.f ? z.x : 0.f; a.y = z.y > 0.f ? z.y : 0.f; a.z = z.z > 0.f ? z.z : 0.f; a.w = z.w > 0.f ? z.w : 0.f; break;
+                            case B200_ACT_NONE: break;
+                            default: {
+                                float d;
+                                ffn_act_der(z.x, ep.act, a.x, d); ffn_act_der(z.y, ep.act, a.y, d);
+                                ffn_act_der(z.z, ep.act, a.z, d); ffn_act_der(z.w, ep.act, a.w, d);
+                            }
+                        }
+                        if (ep.act_sign_zero) { a.x = act_sign_zero(z.x, a.x); a.y = act_sign_zero(z.y, a.y); a.z = act_sign_zero(z.z, a.z); a.w = act_sign_zero(z.w, a.w); }
+                        st4(ep.C + m * ep.ldc + n, a);
+                    }
+                    continue;
+                }
+                if (EPI == EPI_LINEAR && !ep.accumulate && !ep.addmat && !rope) {  // nothing to fetch: the same compact loop
+#pragma unroll 2
+                    for (int rr = rsub; rr < rows; rr += 2) {
+                        const size_t m = (size_t)(m0 + 32 * q + rr);
+                        float4 v = ld4(stage + rr * EPI_STRIDE64 + 4 * l16);
+                        v.x = alpha * v.x + b4.x; v.y = alpha * v.y + b4.y; v.z = alpha * v.z + b4.z; v.w = alpha * v.w + b4.w;
+                        if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+                        st4(ep.C + (size_t)split * p.split_stride + m * ep.ldc + n, v);
+                    }
+                    continue;
+                }
                 // 16 rows (8 per half warp) per batch: all global loads of the batch are issued before any is consumed
 #pragma unroll 1
                 for (int rb = 0; rb < rows; rb += 16) {
@@ -162,15 +198,6 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                             else { v.x += ext2[i].x; v.y += ext2[i].y; v.z += ext2[i].z; v.w += ext2[i].w; }
                             if (ep.round_tf32) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
                             st4(ep.C + (size_t)split * p.split_stride + m * ep.ldc + n, v);
-                        } else if (EPI == EPI_ACT) {
-                            v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
-                            if (ep.zout) st4(ep.zout + m * ep.ldz + n, v);
-                            const float4 z = v;
-                            float d;
-                            ffn_act_der(v.x, ep.act, v.x, d); ffn_act_der(v.y, ep.act, v.y, d);
-                            ffn_act_der(v.z, ep.act, v.z, d); ffn_act_der(v.w, ep.act, v.w, d);
-                            if (ep.act_sign_zero) { v.x = act_sign_zero(z.x, v.x); v.y = act_sign_zero(z.y, v.y); v.z = act_sign_zero(z.z, v.z); v.w = act_sign_zero(z.w, v.w); }
-                            st4(ep.C + m * ep.ldc + n, v);
                         } else {  // EPI_MULZ
                             float a, dx, dy, dz, dw;
                             if (ep.mulz_is_act) {
