@@ -6,6 +6,8 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
   wgrad       the weight-gradient layout alone (both operands row-contiguous along M / N, long K): 1024 x 4096 x 65536
   ffn         feed-forward block forward + input gradient (bias+activation and derivative-multiply GEMM epilogues),
               16384 rows, 1024 -> 4096 -> 1024, ReLU
+  decayattention  cross-attention with a per-head decay bias, forward + backward over materialised weights:
+              512 queries x 4096 keys, 8 heads of 64
   layernorm   LayerNorm forward + backward on 32768 x 1024
   crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
   generate    greedy decoding with the device key/value cache on the c5 model (V 32000, d 1024, 16 heads, 12 layers,
@@ -65,6 +67,23 @@ def ffn(m, rng):
     return float(np.abs(y).mean()) + float(np.abs(r).mean())
 
 
+def decayattention(m, rng):
+    import time
+
+    qn, kn, e, h = 512, 4096, 512, 8
+    q, do = (rng.normal(0, 1, (qn, e)).astype(np.float32) for _ in range(2))
+    k, v = (rng.normal(0, 1, (kn, e)).astype(np.float32) for _ in range(2))
+    bias = rng.normal(0, 1, (qn, kn, h)).astype(np.float32)
+    r = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        out, w, s = m.ContentAwareCrossAttentionForward(q, k, v, h, 0.125, bias)
+        r = m.BackpropTimeDecayedAttention(q, k, v, do, w, bias, e, h)
+        dt = time.perf_counter() - t0
+    print(f"decay attention forward + backward through host arrays: {dt * 1e3:.2f} ms per call pair")
+    return float(np.abs(r[0]).mean())
+
+
 def layernorm(m, rng):
     rows, f = 32768, 1024
     x = rng.normal(0, 1, (rows, f)).astype(np.float32)
@@ -108,7 +127,7 @@ def generate(m, rng):
     return float(out[-1])
 
 
-CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "ffn": ffn, "layernorm": layernorm, "crossentropy": crossentropy}
+CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "ffn": ffn, "decayattention": decayattention, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):
