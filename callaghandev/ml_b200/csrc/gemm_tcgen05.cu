@@ -17,6 +17,8 @@
 // memory, drains the copies it still has in flight (bounded again), frees its TMEM and returns.
 #include <cstdlib>
 
+#include <type_traits>
+
 #include "tcgen05.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -152,6 +154,49 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                         }
                         if (ep.act_sign_zero) { a.x = act_sign_zero(z.x, a.x); a.y = act_sign_zero(z.y, a.y); a.z = act_sign_zero(z.z, a.z); a.w = act_sign_zero(z.w, a.w); }
                         st4(ep.C + m * ep.ldc + n, a);
+                    }
+                    continue;
+                }
+                if (EPI == EPI_MULZ) {
+                    // One copy of the batched row loop per derivative form, chosen once per pass: with the switch inside
+                    // the unrolled loop every activation's code (exp, tanh) was inlined 32 times and the warps waited on
+                    // instruction fetch.  MODE >= 0: derivative from the cached activation of that kind; -1: from z.
+                    auto run = [&](auto MODE) {
+                        constexpr int mode = decltype(MODE)::value;
+#pragma unroll 1
+                        for (int rb = 0; rb < rows; rb += 16) {
+                            float4 ext[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int rr = rb + 2 * i + rsub;
+                                ext[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (rr < rows) ext[i] = ld4(ep.mulz + (size_t)(m0 + 32 * q + rr) * ep.ldmulz + n);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int rr = rb + 2 * i + rsub;
+                                if (rr >= rows) continue;
+                                float4 v = ld4(stage + rr * EPI_STRIDE64 + 4 * l16);
+                                float a, dx, dy, dz, dw;
+                                if (mode >= 0) {
+                                    dx = ffn_der_from_act(ext[i].x, mode); dy = ffn_der_from_act(ext[i].y, mode);
+                                    dz = ffn_der_from_act(ext[i].z, mode); dw = ffn_der_from_act(ext[i].w, mode);
+                                } else {
+                                    ffn_act_der(ext[i].x, ep.mulz_act, a, dx); ffn_act_der(ext[i].y, ep.mulz_act, a, dy);
+                                    ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
+                                }
+                                v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
+                                st4(ep.C + (size_t)(m0 + 32 * q + rr) * ep.ldc + n, v);
+                            }
+                        }
+                    };
+                    if (!ep.mulz_is_act) run(std::integral_constant<int, -1>{});
+                    else switch (ep.mulz_act) {
+                        case B200_ACT_RELU: run(std::integral_constant<int, B200_ACT_RELU>{}); break;
+                        case B200_ACT_SIGMOID: run(std::integral_constant<int, B200_ACT_SIGMOID>{}); break;
+                        case B200_ACT_TANH: run(std::integral_constant<int, B200_ACT_TANH>{}); break;
+                        case B200_ACT_LEAKYRELU: run(std::integral_constant<int, B200_ACT_LEAKYRELU>{}); break;
+                        default: run(std::integral_constant<int, B200_ACT_NONE>{}); break;
                     }
                     continue;
                 }
