@@ -1278,7 +1278,9 @@ API void ref_mlp_scale_inputs(const real* X, int B, int F, const real* mn, const
 
 /* ===================================================================================================================
  * Operators of the sibling trainers (TACAMT / MMTAC / PriceTAC) on the same interface, restated in the reference's
- * loop order.  Rank-3 arrays are flat in the reference's element order. */
+ * loop order.  Rank-3 arrays are flat in the reference's element order.  PARITY UNPINNED: the reference's tests for
+ * these operators compare its back ends with each other and hold no known-answer values; the restatement is checked
+ * against an independent float64 statement of the same mathematics instead. */
 
 /* CPU:3076-3270 ContentAwareCrossAttentionForward.  bias [q,k,H] or NULL; W and S are [H,q,k] (always written here;
  * the wrapper drops them for needBackwardCache = false, the output is the same on both branches). */
