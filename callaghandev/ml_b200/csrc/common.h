@@ -48,7 +48,8 @@ struct b200_ctx {
     float* colsum_ws = nullptr;   // per-32-row column partials written by a GEMM epilogue that fuses colsum_out
     size_t colsum_ws_floats = 0;
     int fuse_colsum = 1;          // 0: never fuse (B200_FUSE_COLSUM=0, for A/B measurements)
-    int colsum_fused = 0;         // set by the launcher that took care of Gemm::colsum_out itself
+    int colsum_fused = 0;
+    int attn_colsum_rows = 0;     // partial rows the last attention backward left in colsum_ws (0: none)         // set by the launcher that took care of Gemm::colsum_out itself
     int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
@@ -203,6 +204,11 @@ struct Attn {
     // backward only: inverse rotary rotation of dQ and dK (table[pos[row]][i] = (cos, sin)), fused into the stores of
     // the tcgen05 engine, a separate kernel behind the other engines
     const float* rope_table = nullptr; const int32_t* rope_pos = nullptr;
+    // Backward only, optional: dQ, dK, dV live in one row-major buffer (dK = dQ + x, dV = dQ + y) whose column sums (the
+    // bias gradients of the Q/K/V projections) are wanted.  An engine that can take them while it stores the rows
+    // writes partial sums into the context's colsum_ws, [rows][colsum_cols] in the buffer's column layout, and reports
+    // the row count in b200_ctx::attn_colsum_rows; 0 means the caller sums the buffer itself.
+    int colsum_cols = 0;
 };
 int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-core kernels when attn_tc_eligible
 // TF32 mma.sync engine (head dimension <= 64, context not in FP32 mode)
