@@ -408,10 +408,17 @@ __device__ __forceinline__ void store_rows(const float* stage, float* dst, int l
                 v.x = x0 * cs.x + x1 * cs.y; v.y = x1 * cs.x - x0 * cs.y;
                 v.z = x2 * cs.z + x3 * cs.w; v.w = x3 * cs.z - x2 * cs.w;
             }
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            if (cs_dst && rope_table) *reinterpret_cast<float4*>(const_cast<float*>(stage) + r * OUT_STRIDE + c4) = v;  // rotated value, summed below
             *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = v;
         }
     if (cs_dst) {
+        // summed in a loop of its own (from the thread's own staging slots): adding inside the store loop put the adds on
+        // the path of the table loads and slowed the stores down
+        for (int r = tid >> 4; r < 128; r += 16)
+            if (r < nRows) {
+                const float4 v = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
         acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
         acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
         if ((tid & 16) == 0) *reinterpret_cast<float4*>(cs_dst + (size_t)(tid >> 5) * csld + c4) = acc;

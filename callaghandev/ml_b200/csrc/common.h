@@ -44,12 +44,11 @@ struct b200_ctx {
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
-    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
-    float* colsum_ws = nullptr;   // per-32-row column partials written by a GEMM epilogue that fuses colsum_out
+    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)
+    float* colsum_ws = nullptr;   // column-sum partials written by the attention backward as it stores dQ, dK, dV
     size_t colsum_ws_floats = 0;
     int fuse_colsum = 1;          // 0: never fuse (B200_FUSE_COLSUM=0, for A/B measurements)
-    int colsum_fused = 0;
-    int attn_colsum_rows = 0;     // partial rows the last attention backward left in colsum_ws (0: none)         // set by the launcher that took care of Gemm::colsum_out itself
+    int attn_colsum_rows = 0;     // partial rows the last attention backward left in colsum_ws (0: none)
     int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
@@ -114,8 +113,6 @@ struct Gemm {
     int act = B200_ACT_NONE; int act_conv = 0;  // 0: transformer-FFN conventions, 1: batch-MLP conventions
     float* dout = nullptr; int lddo = 0;
     const float* mulz = nullptr; int ldmulz = 0; int mulz_act = B200_ACT_NONE;
-    float* colsum_out = nullptr;  // colsum_out[n] += sum over m of C[m,n] (a bias gradient taken while the tile is in registers,
-                                  // or by a pass over C when the engine that runs the GEMM cannot fuse it)
     int act_sign_zero = 0;  // activation outputs that are 0 because z < 0 are stored as -0.0 (lets ReLU'(z) be recovered from a)
     int mulz_is_act = 0;    // mulz holds the activation OUTPUT (stored with act_sign_zero); its derivative is computed from that
     const float* mulmat = nullptr; int ldmul = 0;

@@ -19,7 +19,6 @@ struct Epilogue {
     float sgd_lr, sgd_lambda;
     int round_tf32;
     int act_sign_zero, mulz_is_act;
-    float* colsum_part;  // [ceil(M/32)][N] column sums of the stored tile rows, or null
     const float* rope_table; const int32_t* rope_pos; int rope_cols, rope_hd;
 };
 

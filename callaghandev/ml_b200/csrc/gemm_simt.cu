@@ -91,7 +91,6 @@ static Epilogue make_epilogue(const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
-    e.colsum_part = nullptr;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = nullptr; e.rope_pos = nullptr; e.rope_cols = 0; e.rope_hd = 0;  // the rotation is a separate kernel behind this engine
     return e;
@@ -172,19 +171,6 @@ static int gemm_dispatch(b200_ctx* ctx, const Gemm& g0, int* engine) {
         B200_TRY(gemm_dispatch(ctx, g, engine));
         const int heads = g0.rope_cols / g0.rope_head_dim;
         return k_rope(ctx, g0.C, 0, 1, g0.M, g0.ldc, 0, heads, g0.rope_head_dim, g0.rope_table, g0.rope_pos, 0, g0.round_tf32);
-    }
-    if (g.colsum_out) {  // column sums of the output: inside the epilogue where the launcher can, else one pass over C
-        Gemm h = g;
-        h.colsum_out = nullptr;
-        ctx->colsum_fused = 0;
-        if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) {
-            *engine = 1;
-            B200_TRY(gemm_tcgen05(ctx, g));  // sets colsum_fused when its epilogue produced the sums
-            if (ctx->colsum_fused) return B200_OK;
-        } else {
-            B200_TRY(gemm_dispatch(ctx, h, engine));
-        }
-        return k_colsum(ctx, g.C, g.M, g.N, g.ldc, g.colsum_out, 1);
     }
     if (ctx->gemm_mode != B200_GEMM_FP32_SIMT && gemm_tcgen05_eligible(ctx, g)) {
         *engine = 1;

@@ -127,7 +127,6 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
             }
             __syncwarp();
             const int n = n0 + colBase + c0 + 4 * l16;  // this lane's four columns; lanes 16..31 take the odd rows
-            const unsigned col_mask = __ballot_sync(0xffffffffu, live && n < p.N);  // lanes l and l+16 share n: both in or both out
             if (live && n < p.N) {
                 float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (EPI != EPI_MULZ && ep.bias) b4 = ld4(ep.bias + n);
@@ -164,7 +163,6 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                     // instruction fetch.  MODE >= 0: derivative from the cached activation of that kind; -1: from z.
                     auto run = [&](auto MODE) {
                         constexpr int mode = decltype(MODE)::value;
-                        float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);  // column sums of the rows this lane stores
 #pragma unroll 1
                         for (int rb = 0; rb < rows; rb += 16) {
                             float4 ext[8];
@@ -188,14 +186,8 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, const TcParams
                                     ffn_act_der(ext[i].z, ep.mulz_act, a, dz); ffn_act_der(ext[i].w, ep.mulz_act, a, dw);
                                 }
                                 v.x *= dx; v.y *= dy; v.z *= dz; v.w *= dw;
-                                cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
                                 st4(ep.C + (size_t)(m0 + 32 * q + rr) * ep.ldc + n, v);
                             }
-                        }
-                        if (ep.colsum_part) {  // even + odd rows (the two half warps own the same columns), one partial per 32 rows
-                            cs.x += __shfl_xor_sync(col_mask, cs.x, 16); cs.y += __shfl_xor_sync(col_mask, cs.y, 16);
-                            cs.z += __shfl_xor_sync(col_mask, cs.z, 16); cs.w += __shfl_xor_sync(col_mask, cs.w, 16);
-                            if (rsub == 0 && rows > 0) st4(ep.colsum_part + (size_t)((m0 + 32 * q) >> 5) * p.N + n, cs);
                         }
                     };
                     if (!ep.mulz_is_act) run(std::integral_constant<int, -1>{});
@@ -959,7 +951,6 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
-    e.colsum_part = nullptr;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     p.items = tiles * splits;
@@ -1054,7 +1045,6 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
-    e.colsum_part = nullptr;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     dim3 grid((unsigned)tiles, (unsigned)splits);
@@ -1148,7 +1138,6 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
     e.zout = g.zout; e.ldz = g.ldz; e.act = g.act; e.act_conv = g.act_conv; e.dout = g.dout; e.lddo = g.lddo;
     e.mulz = g.mulz; e.ldmulz = g.ldmulz; e.mulz_act = g.mulz_act; e.mulmat = g.mulmat; e.ldmul = g.ldmul;
     e.act_sign_zero = g.act_sign_zero; e.mulz_is_act = g.mulz_is_act;
-    e.colsum_part = nullptr;
     e.addmat = g.addmat; e.ldadd = g.ldadd; e.sgd_lr = g.sgd_lr; e.sgd_lambda = g.sgd_lambda; e.round_tf32 = g.round_tf32;
     e.rope_table = g.rope_table; e.rope_pos = g.rope_pos; e.rope_cols = g.rope_cols; e.rope_hd = g.rope_head_dim;
     int clusters = n_pairs;
@@ -1189,20 +1178,6 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
         else if (g.mulz && plain_act && !g.addmat && !g.accumulate && !g.bias && g.alpha == 1.f && !g.alpha_dev && g.ldmulz % 4 == 0 && a16(g.mulz))
             kind = EPI_MULZ;
     }
-    // Column sums of the output (a bias gradient): the derivative-multiply epilogue adds up the rows it stores, one
-    // partial row per 32 output rows, and a pass over those partials (1/32 of the output) finishes the sum.
-    const int part_rows = (g.M + 31) / 32;
-    if (g.colsum_out && kind == EPI_MULZ && ctx->fuse_colsum) {
-        const size_t need = (size_t)part_rows * g.N;
-        if (ctx->colsum_ws_floats < need) {
-            B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            if (ctx->colsum_ws) cudaFree(ctx->colsum_ws);
-            ctx->colsum_ws = nullptr; ctx->colsum_ws_floats = 0;
-            B200_CUDA(ctx, cudaMalloc((void**)&ctx->colsum_ws, need * sizeof(float)));
-            ctx->colsum_ws_floats = need;
-        }
-        e.colsum_part = ctx->colsum_ws;
-    }
     switch (kind) {
         case EPI_LINEAR: B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI_LINEAR>, mapA, mapB, p, e)); break;
         case EPI_ACT: B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI_ACT>, mapA, mapB, p, e)); break;
@@ -1210,10 +1185,6 @@ int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
         default: B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI_GENERIC>, mapA, mapB, p, e)); break;
     }
     B200_LAUNCH_CHECK(ctx);
-    if (e.colsum_part) {
-        B200_TRY(k_colsum(ctx, ctx->colsum_ws, part_rows, g.N, g.N, g.colsum_out, 1));
-        ctx->colsum_fused = 1;
-    }
     return B200_OK;
 }
 

@@ -311,10 +311,9 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
             if (c.ffn_activation == B200_ACT_SWISH) { g.mulz = k.z1; g.ldmulz = f; }
             else { g.mulz = k.a1; g.ldmulz = f; g.mulz_is_act = 1; }
             g.mulz_act = c.ffn_activation;
-            g.colsum_out = G + L.fb1;  // the hidden layer's bias gradient = column sums of delta1, taken as it is produced
             B200_TRY(gemm(ctx, g));
         }
-        B200_TRY(wgrad(ctx, lm->d1, f, k.n1, d, N, f, d, G + L.W1, nullptr));
+        B200_TRY(wgrad(ctx, lm->d1, f, k.n1, d, N, f, d, G + L.W1, G + L.fb1));
         {
             Gemm g;  // dNormed1 = delta1 * W1 + dFF  (:908-909, residual add fused)
             g.M = N; g.N = d; g.K = f; g.A = lm->d1; g.lda = f; g.B = P + L.W1; g.ldb = d; g.C = t2; g.ldc = d;
