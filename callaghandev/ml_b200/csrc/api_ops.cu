@@ -25,7 +25,6 @@ int32_t b200_create(int32_t device, b200_ctx** out) {
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return B200_ERR_CUDA; }
     c->cc_major = prop.major;
     c->sm_count = prop.multiProcessorCount;
-    if (const char* e = getenv("B200_FUSE_COLSUM")) c->fuse_colsum = atoi(e);
     if (const char* e = getenv("B200_GEMM_BOX3D")) c->gemm_box3d = atoi(e);  // A/B switch of the 3-D operand boxes
     if (const char* e = getenv("B200_GEMM_TILE_N")) c->gemm_tile_n = atoi(e);  // forces one tcgen05 GEMM kernel: 1 one tile per CTA, 128 / 256 one-CTA persistent, 512 two-SM (tests, A/B measurements)
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return B200_ERR_CUDA; }
@@ -48,7 +47,6 @@ void b200::ctx_release(b200_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->pool) cudaFree(ctx->pool);
     if (ctx->ws) cudaFree(ctx->ws);
-    if (ctx->colsum_ws) cudaFree(ctx->colsum_ws);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     for (auto& kv : ctx->rope)

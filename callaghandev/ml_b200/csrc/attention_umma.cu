@@ -17,7 +17,6 @@
 // frees its TMEM and returns.
 #include <cstdlib>
 
-#include <algorithm>
 #include "device_math.cuh"
 #include "tcgen05.cuh"
 
@@ -386,17 +385,12 @@ struct UBwdArgs {
     float scale;
     int* status;
     const float* rope_table; const int32_t* rope_pos;  // inverse rotary rotation of dQ and dK on the way out (or null)
-    float *csQ, *csK, *csV; int csld;                  // column-sum partials of dQ / dK / dV: 8 rows per CTA (one per storing warp), or null
 };
 
 // Store a [128 x 64] result staged in shared memory (row stride OUT_STRIDE) with whole-row 128-bit accesses; 256 threads.
-// With cs_dst (this CTA's first partial row, already at colBase) every warp also leaves the column sums of the rows it
-// stored in partial row `warp`; all 32 lanes of each of the 8 warps must make the call.
 __device__ __forceinline__ void store_rows(const float* stage, float* dst, int ld, int rowBase, int nRows, int colBase, int tid,
-                                           const float* rope_table = nullptr, const int32_t* rope_pos = nullptr, float* cs_dst = nullptr,
-                                           int csld = 0) {
+                                           const float* rope_table = nullptr, const int32_t* rope_pos = nullptr) {
     const int c4 = (tid & 15) * 4;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 2
     for (int r = tid >> 4; r < 128; r += 16)
         if (r < nRows) {
@@ -408,21 +402,8 @@ __device__ __forceinline__ void store_rows(const float* stage, float* dst, int l
                 v.x = x0 * cs.x + x1 * cs.y; v.y = x1 * cs.x - x0 * cs.y;
                 v.z = x2 * cs.z + x3 * cs.w; v.w = x3 * cs.z - x2 * cs.w;
             }
-            if (cs_dst && rope_table) *reinterpret_cast<float4*>(const_cast<float*>(stage) + r * OUT_STRIDE + c4) = v;  // rotated value, summed below
             *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = v;
         }
-    if (cs_dst) {
-        // summed in a loop of its own (from the thread's own staging slots): adding inside the store loop put the adds on
-        // the path of the table loads and slowed the stores down
-        for (int r = tid >> 4; r < 128; r += 16)
-            if (r < nRows) {
-                const float4 v = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, 16); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, 16);
-        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, 16); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, 16);
-        if ((tid & 16) == 0) *reinterpret_cast<float4*>(cs_dst + (size_t)(tid >> 5) * csld + c4) = acc;
-    }
 }
 
 __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
@@ -621,11 +602,7 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                                 __uint_as_float(r[i + 3]) * a.scale);
         }
         ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
-        if (__all_sync(0xffffffffu, ok)) {
-            const size_t tile = (size_t)blockIdx.z * gridDim.x + blockIdx.x;
-            store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64, a.rope_table,
-                       a.rope_pos, a.csQ ? a.csQ + tile * 8 * a.csld + head * UHD : nullptr, a.csld);
-        }
+        if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64, a.rope_table, a.rope_pos);
     } else if (warp < 14) {
         // ------------------------------------------------------------------------------ re-swizzle warps: K -> N-contiguous image
         const int t = threadIdx.x - 320;
@@ -870,13 +847,10 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
                                 __uint_as_float(r[c + 3]) * a.scale);
         }
         ew_barrier();
-        if (__all_sync(0xffffffffu, ok)) {
+        if (ok) {
             const int nRows = min(128, sg.kLen - k0);
-            const size_t tile = (size_t)blockIdx.z * gridDim.x + blockIdx.x;
-            store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid, nullptr, nullptr,
-                       a.csV ? a.csV + tile * 8 * a.csld + head * UHD : nullptr, a.csld);
-            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid, a.rope_table, a.rope_pos,
-                       a.csK ? a.csK + tile * 8 * a.csld + head * UHD : nullptr, a.csld);
+            store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
+            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid, a.rope_table, a.rope_pos);
         }
     } else if (warp < 14) {
         // ------------------------------------------------------------------------------ re-swizzle warps: Q, dO -> N-contiguous images
@@ -975,24 +949,6 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
     a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
     a.scale = t.scale; a.status = ctx->status_dev; a.rope_table = t.rope_table; a.rope_pos = t.rope_pos;
-    a.csQ = a.csK = a.csV = nullptr; a.csld = 0;
-    ctx->attn_colsum_rows = 0;
-    const int q_tiles = (t.maxQLen + 127) / 128, k_tiles = (t.maxKLen + 127) / 128;
-    if (ctx->fuse_colsum && t.colsum_cols > 0 && t.lddq == t.colsum_cols && t.lddk == t.colsum_cols && t.lddv == t.colsum_cols) {
-        // column-sum partials: 8 rows per (segment, tile); CTAs that have nothing to do leave their rows at zero
-        const int part_rows = t.nSeg * std::max(q_tiles, k_tiles) * 8;
-        const size_t need = (size_t)part_rows * t.colsum_cols;
-        if (ctx->colsum_ws_floats < need) {
-            B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            if (ctx->colsum_ws) cudaFree(ctx->colsum_ws);
-            ctx->colsum_ws = nullptr; ctx->colsum_ws_floats = 0;
-            B200_CUDA(ctx, cudaMalloc((void**)&ctx->colsum_ws, need * sizeof(float)));
-            ctx->colsum_ws_floats = need;
-        }
-        B200_CUDA(ctx, cudaMemsetAsync(ctx->colsum_ws, 0, need * sizeof(float), ctx->stream));
-        a.csQ = ctx->colsum_ws; a.csK = ctx->colsum_ws + (t.dK - t.dQ); a.csV = ctx->colsum_ws + (t.dV - t.dQ); a.csld = t.colsum_cols;
-        ctx->attn_colsum_rows = part_rows;
-    }
     const int warps = t.totalQ * t.numHeads;
     attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
     B200_LAUNCH_CHECK(ctx);

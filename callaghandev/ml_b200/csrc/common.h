@@ -44,11 +44,7 @@ struct b200_ctx {
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
-    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)
-    float* colsum_ws = nullptr;   // column-sum partials written by the attention backward as it stores dQ, dK, dV
-    size_t colsum_ws_floats = 0;
-    int fuse_colsum = 1;          // 0: never fuse (B200_FUSE_COLSUM=0, for A/B measurements)
-    int attn_colsum_rows = 0;     // partial rows the last attention backward left in colsum_ws (0: none)
+    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
     int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
@@ -201,11 +197,6 @@ struct Attn {
     // backward only: inverse rotary rotation of dQ and dK (table[pos[row]][i] = (cos, sin)), fused into the stores of
     // the tcgen05 engine, a separate kernel behind the other engines
     const float* rope_table = nullptr; const int32_t* rope_pos = nullptr;
-    // Backward only, optional: dQ, dK, dV live in one row-major buffer (dK = dQ + x, dV = dQ + y) whose column sums (the
-    // bias gradients of the Q/K/V projections) are wanted.  An engine that can take them while it stores the rows
-    // writes partial sums into the context's colsum_ws, [rows][colsum_cols] in the buffer's column layout, and reports
-    // the row count in b200_ctx::attn_colsum_rows; 0 means the caller sums the buffer itself.
-    int colsum_cols = 0;
 };
 int attn_forward(b200_ctx*, const Attn& a);   // dispatches to the TF32 tensor-core kernels when attn_tc_eligible
 // TF32 mma.sync engine (head dimension <= 64, context not in FP32 mode)

@@ -339,18 +339,10 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         a.dO = t1; a.lddo = d; a.dQ = lm->dqkv; a.dK = lm->dqkv + d; a.dV = lm->dqkv + 2 * d; a.lddq = a.lddk = a.lddv = 3 * d;
         a.pre_rounded = tf32_attention(lm) ? 1 : 0;
         a.rope_table = lm->rope; a.rope_pos = lm->cur.pos;  // inverse rotation of dQ and dK
-        const bool fusedQKV = qkv_fused(lm, L);
-        if (fusedQKV) a.colsum_cols = 3 * d;  // bQ, bK, bV gradients = column sums of dQKV, taken as the rows are stored if the engine can
-        ctx->attn_colsum_rows = 0;
         B200_TRY(attn_backward(ctx, a));
         float* out = t2;  // dX of the layer input = dQKV * Wqkv + dAttnResidual (:919, residual add fused)
-        if (fusedQKV) {
-            float* bg = G + L.bQ;
-            if (ctx->attn_colsum_rows > 0) {
-                B200_TRY(k_colsum(ctx, ctx->colsum_ws, ctx->attn_colsum_rows, 3 * d, 3 * d, bg, 1));
-                bg = nullptr;
-            }
-            B200_TRY(wgrad(ctx, lm->dqkv, 3 * d, k.x, d, N, 3 * d, d, G + L.WQ, bg));
+        if (qkv_fused(lm, L)) {
+            B200_TRY(wgrad(ctx, lm->dqkv, 3 * d, k.x, d, N, 3 * d, d, G + L.WQ, G + L.bQ));
             Gemm g;
             g.M = N; g.N = d; g.K = 3 * d; g.A = lm->dqkv; g.lda = 3 * d; g.B = P + L.WQ; g.ldb = d; g.C = out; g.ldc = d;
             g.addmat = t3; g.ldadd = d;
