@@ -106,7 +106,8 @@ def cpu_reference_tokens_per_s(w, budget_s, threads=None):
     from oracle import Oracle
 
     orc = Oracle()
-    threads = threads or orc.max_threads()
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: take the cores this process may run on, not OpenMP's default
+    threads = threads or max(orc.max_threads(), len(os.sched_getaffinity(0)))
     orc.set_threads(threads)
     cfg = lm_config(vocab=w["vocab"], d=w["d"], H=w["H"], L=w["L"], f=w["f"], act="Relu")
     P = init_params(orc, cfg, 1)

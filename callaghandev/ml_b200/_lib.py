@@ -15,6 +15,7 @@ LIB_PATH = _HERE / "libcallaghan_b200.so"
 OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_OUT_OF_RANGE, ERR_CUDA, ERR_TIMEOUT, ERR_NONFINITE, ERR_UNSUPPORTED = 0, 1, 2, 3, 4, 6, 7, 8
 GEMM_AUTO, GEMM_FP32_SIMT, GEMM_TF32_TCGEN05 = 0, 1, 2
 OPT_SGD, OPT_ADAM = 0, 1
+ENGINES = ("gemm_simt", "gemm_tile", "gemm_persistent", "gemm_pair", "attn_fp32", "attn_mma_sync", "attn_tcgen05", "ce_fused")
 ACT = {"None": 0, "Sigmoid": 1, "Tanh": 2, "Relu": 3, "Leakyrelu": 4, "Swish": 5}
 COST = {"mse": 0, "ZeroWeightedMSE": 1, "binaryCrossEntropy": 2, "mae": 3, "categoricalCrossEntropy": 4, "huberLoss": 5}
 
@@ -45,6 +46,10 @@ PROTOTYPES = {
     "b200_synchronize": (_i32, [_vp]),
     "b200_kernel_launches": (_i64, [_vp]),
     "b200_has_tcgen05": (_i32, [_vp]),
+    "b200_engine_launches": (_i32, [_vp, C.POINTER(_i64)]),
+    "b200_set_gemm_kernel": (_i32, [_vp, _i32]),
+    "b200_set_wait_budget_us": (_i32, [_vp, _i64]),
+    "b200_probe_wait_timeout": (_i32, [_vp]),
     "b200_profile_gemm": (_i32, [_vp, _i32]),
     "b200_gemm_profile_csv": (_i64, [_vp, C.c_char_p, _i64]),
     "b200_gemm_profile": (_i32, [_vp, _i32, C.POINTER(_i64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

@@ -5,8 +5,6 @@
 #include <algorithm>
 #include <cstring>
 
-#include <cstdlib>
-
 #include "api_scope.cuh"
 
 
@@ -25,8 +23,7 @@ int32_t b200_create(int32_t device, b200_ctx** out) {
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return B200_ERR_CUDA; }
     c->cc_major = prop.major;
     c->sm_count = prop.multiProcessorCount;
-    if (const char* e = getenv("B200_GEMM_BOX3D")) c->gemm_box3d = atoi(e);  // A/B switch of the 3-D operand boxes
-    if (const char* e = getenv("B200_GEMM_TILE_N")) c->gemm_tile_n = atoi(e);  // forces one tcgen05 GEMM kernel: 1 one tile per CTA, 128 / 256 one-CTA persistent, 512 two-SM (tests, A/B measurements)
+    c->clock_khz = prop.clockRate;
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return B200_ERR_CUDA; }
     c->stream = c->own_stream;
     if (cudaMallocHost((void**)&c->pinned, 4096) != cudaSuccess) { cudaStreamDestroy(c->own_stream); delete c; return B200_ERR_CUDA; }
@@ -78,6 +75,33 @@ int32_t b200_synchronize(b200_ctx* ctx) {
     return check_device_status(ctx);
 }
 int64_t b200_kernel_launches(b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+int32_t b200_engine_launches(b200_ctx* ctx, int64_t* out) {
+    if (!ctx || !out) return B200_ERR_INVALID_ARG;
+    for (int i = 0; i < B200_ENGINE_COUNT; i++) out[i] = ctx->engine_launches[i];
+    return B200_OK;
+}
+int32_t b200_set_gemm_kernel(b200_ctx* ctx, int32_t kernel) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    if (kernel != 0 && kernel != 1 && kernel != 128 && kernel != 256 && kernel != 512) return fail(ctx, B200_ERR_INVALID_ARG, "gemm kernel must be 0, 1, 128, 256 or 512");
+    ctx->gemm_tile_n = kernel;
+    return B200_OK;
+}
+int32_t b200_set_wait_budget_us(b200_ctx* ctx, int64_t microseconds) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    if (microseconds <= 0 || microseconds > 60ll * 1000 * 1000) return fail(ctx, B200_ERR_OUT_OF_RANGE, "wait budget must be within (0, 60 s]");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const long long clocks = (long long)((double)microseconds * (double)(ctx->clock_khz > 0 ? ctx->clock_khz : 2000000) / 1000.0);
+    B200_TRY(gemm_tcgen05_set_wait_budget(ctx, clocks));
+    return attn_umma_set_wait_budget(ctx, clocks);
+}
+int32_t b200_probe_wait_timeout(b200_ctx* ctx) {
+    if (!ctx) return B200_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    return gemm_tcgen05_probe_wait(ctx);
+}
 int32_t b200_has_tcgen05(b200_ctx* ctx) { return ctx && ctx->cc_major == 10 ? 1 : 0; }
 
 int32_t b200_profile_gemm(b200_ctx* ctx, int32_t enable) {

@@ -387,6 +387,7 @@ static int launch_bwd(b200_ctx* ctx, const Attn& t) {
 int attn_forward(b200_ctx* ctx, const Attn& t) {
     if (t.nSeg <= 0 || t.maxQLen <= 0 || t.numHeads <= 0) return B200_OK;
     if (attn_tc_eligible(ctx, t)) return attn_forward_tc(ctx, t);
+    ctx->engine_launches[B200_ENGINE_ATTN_FP32]++;
     if (t.headDim <= 16) return launch_fwd<16>(ctx, t);
     if (t.headDim <= 32) return launch_fwd<32>(ctx, t);
     if (t.headDim <= 64) return launch_fwd<64>(ctx, t);
@@ -395,6 +396,7 @@ int attn_forward(b200_ctx* ctx, const Attn& t) {
 }
 static int attn_backward_engine(b200_ctx* ctx, const Attn& t) {
     if (attn_tc_eligible(ctx, t)) return attn_backward_tc(ctx, t);
+    ctx->engine_launches[B200_ENGINE_ATTN_FP32]++;
     if (t.headDim <= 16) return launch_bwd<16>(ctx, t);
     if (t.headDim <= 32) return launch_bwd<32>(ctx, t);
     if (t.headDim <= 64) return launch_bwd<64>(ctx, t);

@@ -686,18 +686,23 @@ int launch_bwd_tc(b200_ctx* ctx, const Attn& t) {
 
 }  // namespace
 
+// The automatic mode keeps models narrower than 128 on the FP32 kernels (their projections run on the FP32 SIMT GEMM
+// as well, so the whole step holds the FP32 tolerance); forcing the tensor-core mode takes every head dim 8..64.
 bool attn_tc_eligible(b200_ctx* ctx, const Attn& t) {
-    return ctx->gemm_mode != B200_GEMM_FP32_SIMT && ctx->cc_major >= 8 && t.headDim >= 8 && t.headDim <= 64 && t.maxQLen >= 32;
+    if (ctx->gemm_mode == B200_GEMM_FP32_SIMT || ctx->cc_major < 8 || t.headDim < 8 || t.headDim > 64 || t.maxQLen < 32) return false;
+    return ctx->gemm_mode == B200_GEMM_TF32_TCGEN05 || t.numHeads * t.headDim >= 128;
 }
 
 int attn_forward_tc(b200_ctx* ctx, const Attn& t) {
-    if (attn_umma_eligible(ctx, t)) return attn_forward_umma(ctx, t);
+    if (attn_umma_eligible(ctx, t)) { ctx->engine_launches[B200_ENGINE_ATTN_TCGEN05]++; return attn_forward_umma(ctx, t); }
+    ctx->engine_launches[B200_ENGINE_ATTN_MMA_SYNC]++;
     if (t.headDim <= 16) return launch_fwd_tc<16>(ctx, t);
     if (t.headDim <= 32) return launch_fwd_tc<32>(ctx, t);
     return launch_fwd_tc<64>(ctx, t);
 }
 int attn_backward_tc(b200_ctx* ctx, const Attn& t) {
-    if (attn_umma_bwd_eligible(ctx, t)) return attn_backward_umma(ctx, t);
+    if (attn_umma_bwd_eligible(ctx, t)) { ctx->engine_launches[B200_ENGINE_ATTN_TCGEN05]++; return attn_backward_umma(ctx, t); }
+    ctx->engine_launches[B200_ENGINE_ATTN_MMA_SYNC]++;
     if (t.headDim <= 16) return launch_bwd_tc<16>(ctx, t);
     if (t.headDim <= 32) return launch_bwd_tc<32>(ctx, t);
     return launch_bwd_tc<64>(ctx, t);

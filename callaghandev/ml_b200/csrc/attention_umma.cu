@@ -89,14 +89,6 @@ __device__ __forceinline__ uint32_t rna_tf32_add(float x) { return __float_as_ui
 // transcendental pipe with ex2, which is the scarce resource of the element-wise step.
 __device__ __forceinline__ uint32_t rna_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 
-#ifdef B200_ATTN_TRACE
-// Development aid: clock64() time stamps of the first CTA's roles, [role][tile][event].
-__device__ long long g_attn_trace[4 * 32 * 8];
-#define TR(role, tile, ev) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tile) < 32) g_attn_trace[((role) * 32 + (tile)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define TR(role, tile, ev) do { } while (0)
-#endif
-
 // Copy one row of a K-contiguous swizzle atom (32 floats, already TF32) into TMEM columns [col, col+32) of the calling
 // thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand read from
 // shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
@@ -193,24 +185,20 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             for (int j = 0; j < nkt && ok; j++) {
                 ok = mbar_wait(k_full, j & 1, status, 14);
                 if (!ok) break;
-                TR(1, j, 0);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < UHD / 8; kk++) umma_tf32(tmem_base + S_COL, dQ0 + koff(kk, U_ATOM), dK0 + koff(kk, U_ATOM), idS, kk > 0 ? 1u : 0u);
                 umma_commit(k_empty);
                 umma_commit(s_full);
-                TR(1, j, 1);
                 ok = mbar_wait(p_full, j & 1, status, 15);
                 if (!ok) break;
                 ok = mbar_wait(v_full, j & 1, status, 16);
                 if (!ok) break;
-                TR(1, j, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < UK / 8; kk++)
                     umma_tf32_ta(tmem_base + O_COL, tmem_base + S_COL + kk * 8, dV0 + noff(kk), idO, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(v_empty);
-                TR(1, j, 3);
             }
             umma_commit(o_full);
         }
@@ -227,7 +215,6 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             ok = mbar_wait_warp(s_full, j & 1, status, 17);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (threadIdx.x == 64) TR(2, j, 0);
             tc_fence_after();
             const int k0 = j * UK;
             const bool full = k0 + UK <= sg.kLen && (!a.causal || k0 + UK - 1 <= q0 + 32 * quarter);  // warp-uniform
@@ -237,7 +224,6 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld32_nowait(tlane + S_COL + 32 * c, r[c]);
             tmem_ld_wait();
-            if (threadIdx.x == 64) TR(2, j, 1);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full) {
 #pragma unroll
@@ -269,7 +255,6 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
                 tmem_st32(tlane + S_COL + 32 * c, r[c]);
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            if (threadIdx.x == 64) TR(2, j, 2);
             l = l * corr + rs;
             m = m_new;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // S(j) complete implies P V(j-1) complete: O is stable
@@ -285,7 +270,6 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full);
-            if (threadIdx.x == 64) TR(2, j, 3);
         }
         if (ok) {
             ok = mbar_wait_warp(o_full, 0, status, 18);
@@ -464,7 +448,6 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 const int s = nk % RING_K, row = sg.kStart + nk * 64;
                 ok = mbar_wait(kk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 21);
                 if (!ok) break;
-                TR(0, nk, 0);
                 const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
                 mbar_expect_tx(bar, 2 * T64);
                 tma_load_3d(base, &mapK, bar, 0, row, col >> 5);
@@ -486,12 +469,10 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
             tc_fence_after();
             for (int j = 0; j < nkt && ok; j++) {
                 const int s = j % RING_K, b = j & 1;
-                TR(1, j, 0);
                 ok = mbar_wait(kk_full + 8 * s, (j / RING_K) & 1, status, 23);
                 if (!ok) break;
                 ok = mbar_wait(buf_free + 8 * b, ((j >> 1) & 1) ^ 1, status, 24);  // dQ(j-2) has consumed the buffer (free at first use)
                 if (!ok) break;
-                TR(1, j, 1);
                 tc_fence_after();
                 const uint64_t dk = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dv = dk + (uint64_t)(T64 >> 4);
 #pragma unroll
@@ -500,7 +481,6 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + DOA_COL + kk * 8, dv + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
                 umma_commit(kk_empty + 8 * s);
                 umma_commit(sdp_full + 8 * b);
-                TR(1, j, 2);
             }
         }
     } else if (warp == 14) {
@@ -513,17 +493,14 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 const int s = j % DQ_RING_N, b = j & 1;
                 ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 25);
                 if (!ok) break;
-                TR(1, j, 3);
                 ok = mbar_wait(ds_full + 8 * b, (j >> 1) & 1, status, 25);
                 if (!ok) break;
-                TR(1, j, 4);
                 tc_fence_after();
                 const uint64_t dn = dRN0 + (uint64_t)(s * (T64 >> 4));
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(kn_empty + 8 * s);
                 umma_commit(buf_free + 8 * b);
-                TR(1, j, 5);
             }
             umma_commit(dq_full);
         }
@@ -554,18 +531,15 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         }
         for (int j = 0; j < nkt; j++) {
             const int s = j & 1;
-            if (threadIdx.x == 64) TR(2, j, 0);
             ok = mbar_wait_warp(sdp_full + 8 * s, (j >> 1) & 1, status, 26);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (threadIdx.x == 64) TR(2, j, 1);
             tc_fence_after();
             const int nvis = lim - j * 64 - c0;  // columns [0, nvis) of this warp's 32 are visible
             uint32_t sr[32], pr[32];
             tmem_ld32_nowait(tlane + s * 128 + c0, sr);
             tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
             tmem_ld_wait();
-            if (threadIdx.x == 64) TR(2, j, 2);
             const bool fullw = __all_sync(0xffffffffu, nvis >= 32);  // no masking anywhere in this warp's slice
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
@@ -580,11 +554,9 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
                 sr[i + 1] = rna_tf32_add(ds.y);
             }
             tmem_st32(tlane + s * 128 + c0, sr);
-            if (threadIdx.x == 64) TR(2, j, 3);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(ds_full + 8 * s);
-            if (threadIdx.x == 64) TR(2, j, 4);
         }
         if (ok) {
             ok = mbar_wait_warp(dq_full, 0, status, 27);
@@ -611,14 +583,11 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
         for (int j = 0; j < nkt; j++) {
             const int sk = j % RING_K, sn = j % DQ_RING_N;
             if (!mbar_wait_warp(kk_full + 8 * sk, (j / RING_K) & 1, status, 29)) break;
-            if (t == 0) TR(3, j, 0);
             if (!mbar_wait_warp(kn_empty + 8 * sn, ((j / DQ_RING_N) & 1) ^ 1, status, 30)) break;
-            if (t == 0) TR(3, j, 1);
             reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * T64, t);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
             mbar_arrive(kn_full + 8 * sn);
             mbar_arrive(kk_empty + 8 * sk);
-            if (t == 0) TR(3, j, 2);
         }
     }
     tc_fence_before();
@@ -888,20 +857,16 @@ __global__ void attn_rowdot_umma_kernel(const float* __restrict__ dO, int lddo, 
     if (lane == 0) rowDot[w] = s;
 }
 
-bool umma_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("B200_ATTN_UMMA");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
 }  // namespace
+
+int attn_umma_set_wait_budget(b200_ctx* ctx, long long clocks) {
+    B200_CUDA(ctx, cudaMemcpyToSymbol(g_wait_budget_clocks, &clocks, sizeof(clocks)));
+    return B200_OK;
+}
 
 bool attn_umma_eligible(b200_ctx* ctx, const Attn& t) {
     auto ok = [](const void* p, int ld) { return (((uintptr_t)p) & 15) == 0 && (ld & 3) == 0; };
-    return umma_enabled() && ctx->cc_major == 10 && ctx->gemm_mode != B200_GEMM_FP32_SIMT && t.headDim == UHD && !t.mask && t.rowMax && t.rowSum && t.scale > 0.f &&
+    return ctx->cc_major == 10 && ctx->gemm_mode != B200_GEMM_FP32_SIMT && t.headDim == UHD && !t.mask && t.rowMax && t.rowSum && t.scale > 0.f &&
            t.maxQLen >= 128 && t.totalQ >= 128 && t.totalK >= 128 && ok(t.Q, t.ldq) && ok(t.K, t.ldk) && ok(t.V, t.ldv) && ok(t.O, t.ldo);
 }
 
@@ -978,9 +943,3 @@ int attn_forward_umma(b200_ctx* ctx, const Attn& t) {
 }
 
 }  // namespace b200
-
-#ifdef B200_ATTN_TRACE
-extern "C" __attribute__((visibility("default"))) int b200_debug_attn_trace(long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, b200::g_attn_trace, sizeof(long long) * (size_t)n);
-}
-#endif

@@ -44,8 +44,11 @@ struct b200_ctx {
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
-    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (B200_GEMM_TILE_N at context creation)  // dynamic shared memory attributes set
+    int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (b200_set_gemm_kernel)
     int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
+    int clock_khz = 0;   // SM clock the bounded-wait budget is converted with
+    // launches per engine since the context was created (b200_engine_launches): which code path a call really took
+    int64_t engine_launches[B200_ENGINE_COUNT] = {0};
     // optional per-launch GEMM timing (b200_profile_gemm): event pairs recorded around every GEMM launch
     int profile = 0;
     std::vector<cudaEvent_t> prof_events;
@@ -122,6 +125,9 @@ struct Gemm {
 };
 int gemm(b200_ctx* ctx, const Gemm& g);            // picks the engine from ctx->gemm_mode and the shape
 int gemm_simt(b200_ctx* ctx, const Gemm& g);       // FP32 SIMT, any shape
+int gemm_tcgen05_set_wait_budget(b200_ctx* ctx, long long clocks);
+int attn_umma_set_wait_budget(b200_ctx* ctx, long long clocks);
+int gemm_tcgen05_probe_wait(b200_ctx* ctx);
 int gemm_tcgen05(b200_ctx* ctx, const Gemm& g);    // TF32 tcgen05/TMEM/TMA; B200_ERR_UNSUPPORTED if the shape does not qualify
 bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g);
 bool gemm_tcgen05_fuses_rope(b200_ctx* ctx, const Gemm& g);  // the rope_* fields would be applied inside the tcgen05 epilogue

@@ -23,7 +23,9 @@ int fail(b200_ctx* ctx, int code, const char* fmt, ...) {
 int check_device_status(b200_ctx* ctx) {
     if (ctx->status_host && *ctx->status_host != 0) {
         int code = *ctx->status_host;
-        return fail(ctx, B200_ERR_TIMEOUT, "a bounded device-side wait expired in the tcgen05 GEMM (role %d: 1 producer, 2 MMA issuer, 3 epilogue)", code);
+        *ctx->status_host = 0;  // reported once: the kernels that saw it have returned, the context stays usable
+        return fail(ctx, B200_ERR_TIMEOUT, "a bounded device-side wait expired in a tcgen05 kernel (wait site %d: 1-3 GEMM producer / MMA issuer / epilogue, "
+                    "9 the wait probe, 10 and above attention)", code);
     }
     return B200_OK;
 }
@@ -789,6 +791,7 @@ extern "C" int32_t b200_LayerNormBackward_noalloc(void* cuda_stream, const float
         scratch = g_noalloc_ln_ptr[dev];
     }
     cudaStream_t st = (cudaStream_t)cuda_stream;
+    (void)cudaGetLastError();  // a stale error of an earlier, unrelated call must not be reported as this call's launch failure
     const int warps = 4;
     int grid = (rows + warps - 1) / warps;
     if (grid > NOALLOC_LN_MAX_PARTS) grid = NOALLOC_LN_MAX_PARTS;

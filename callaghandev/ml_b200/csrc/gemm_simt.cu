@@ -98,6 +98,7 @@ static Epilogue make_epilogue(const Gemm& g) {
 
 int gemm_simt(b200_ctx* ctx, const Gemm& g) {
     if (g.M <= 0 || g.N <= 0) return B200_OK;
+    ctx->engine_launches[B200_ENGINE_GEMM_SIMT]++;
     Epilogue e = make_epilogue(g);
     // K == 0 still runs: the accumulator is zero and the epilogue (bias, assign) must happen.
     if (g.M >= 256 && g.N >= 128) {
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(256) gemv_rows_kernel(int M, int N, int K, con
 static bool gemv_eligible(const Gemm& g) { return g.M >= 1 && g.M <= 4 && !g.transA && g.transB && g.N >= 1 && g.K >= 1; }
 
 static int gemv_rows(b200_ctx* ctx, const Gemm& g) {
+    ctx->engine_launches[B200_ENGINE_GEMM_SIMT]++;
     Epilogue e = make_epilogue(g);
     const int vec = (g.K % 4 == 0) && (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
     const int blocks = (g.N + 7) / 8;

@@ -899,6 +899,42 @@ int ensure_status(b200_ctx* ctx) {
     return B200_OK;
 }
 
+int gemm_tcgen05_set_wait_budget(b200_ctx* ctx, long long clocks) {
+    B200_CUDA(ctx, cudaMemcpyToSymbol(g_wait_budget_clocks, &clocks, sizeof(clocks)));
+    return B200_OK;
+}
+
+namespace {
+// The expiry path of the bounded waits, without any real failure: one thread initialises a barrier that expects one
+// arrival and waits for a phase nobody completes.  mbar_wait gives up after the budget, raises the status word and
+// returns false; the kernel then simply ends (it holds no tensor memory and has no copy in flight).
+__global__ void bounded_wait_probe_kernel(volatile int* status, int* gave_up) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool ok = mbar_wait(smem_u32(&bar), 0, status, 9);
+        *gave_up = ok ? 0 : 1;
+    }
+}
+}  // namespace
+
+int gemm_tcgen05_probe_wait(b200_ctx* ctx) {
+    B200_TRY(ensure_status(ctx));
+    B200_TRY(ensure_ws(ctx, 64));
+    int* flag = (int*)ctx->ws;
+    B200_CUDA(ctx, cudaMemsetAsync(flag, 0, sizeof(int), ctx->stream));
+    bounded_wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, flag);
+    B200_LAUNCH_CHECK(ctx);
+    int gave_up = 0;
+    B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, flag, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    gave_up = *(int*)ctx->pinned;
+    int rc = check_device_status(ctx);
+    if (rc == B200_OK && gave_up) return fail(ctx, B200_ERR_CUDA, "the wait expired but the status word was not raised");
+    return rc;
+}
+
 bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
     if (ctx->cc_major != 10) return false;
     if (g.M < 128 || g.N < 128 || g.K < 128) return false;
@@ -910,6 +946,7 @@ bool gemm_tcgen05_eligible(b200_ctx* ctx, const Gemm& g) {
 namespace {
 template <int BN>
 int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
+    ctx->engine_launches[B200_ENGINE_GEMM_PERSISTENT]++;
     constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
     static bool configured = false;  // per tile width; the attribute belongs to the function, not the context
     if (!configured) {
@@ -992,6 +1029,7 @@ int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     return B200_OK;
 }
 int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
+    ctx->engine_launches[B200_ENGINE_GEMM_TILE]++;
     constexpr int BN = T_BN, SMEM_BYTES = T_SMEM_BYTES;
     if (!ctx->gemm_tc_configured) {
         ctx->gemm_tc_configured = 1;
@@ -1088,6 +1126,7 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
 
 // Two-SM kernel launcher: no split-K; M and N at least 256.
 int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
+    ctx->engine_launches[B200_ENGINE_GEMM_PAIR]++;
     static bool configured = false;
     if (!configured) {
         configured = true;

@@ -157,6 +157,28 @@ void fire(b200_lm* lm, int64_t off, int64_t count) {
     lm->cb(lm->cb_user, off, count, (void*)e);
 }
 
+// The ranges of the gradient arena in the order the last pass's backward finishes them: output projection and bias,
+// the blocks last to first, then the embedding / input projection.  Every rank of a data-parallel job must issue its
+// collectives over exactly this list in exactly this order, whatever happened locally.
+std::vector<std::pair<int64_t, int64_t>> grad_ranges(const b200_lm* lm) {
+    std::vector<std::pair<int64_t, int64_t>> r;
+    const Layout& o = lm->lay;
+    r.emplace_back(o.Wout, o.total - o.Wout);
+    for (int l = lm->cfg.num_layers - 1; l >= 0; l--) {
+        const int64_t end = (l + 1 < lm->cfg.num_layers) ? o.layer[(size_t)l + 1].WQ : o.Wout;
+        r.emplace_back(o.layer[(size_t)l].WQ, end - o.layer[(size_t)l].WQ);
+    }
+    r.emplace_back(0, lm->cfg.num_layers > 0 ? o.layer[0].WQ : o.Wout);
+    return r;
+}
+
+// A rank whose last pass ran no backward (empty shard, every sequence too short or non-finite) still announces every
+// range, one by one and in the same order, so that its peers' collectives find their counterparts.
+void fire_all(b200_lm* lm) {
+    if (!lm->cb) return;
+    for (const auto& r : grad_ranges(lm)) fire(lm, r.first, r.second);
+}
+
 // ---- one packed pass ---------------------------------------------------------------------------------------------
 
 int stage_pass(b200_lm* lm, const Batch& b, const Pass& p, PassDev& dst) {
@@ -225,7 +247,8 @@ bool qkv_fused(const b200_lm* lm, const LayerOff& L) {
 bool tf32_attention(const b200_lm* lm) {
     const b200_ctx* ctx = lm->ctx;
     const int hd = lm->cfg.embedding_dim / lm->cfg.num_heads;
-    return ctx->gemm_mode != B200_GEMM_FP32_SIMT && ctx->cc_major >= 8 && hd >= 8 && hd <= 64;
+    if (ctx->gemm_mode == B200_GEMM_FP32_SIMT || ctx->cc_major < 8 || hd < 8 || hd > 64) return false;
+    return ctx->gemm_mode == B200_GEMM_TF32_TCGEN05 || lm->cfg.embedding_dim >= 128;  // same rule as attn_tc_eligible
 }
 
 int forward_pass(b200_lm* lm, const Pass& p) {
@@ -435,7 +458,7 @@ int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<Pa
     const std::vector<int>& bucketLens = plan.bucketLens;
     const std::vector<Pass>& passes = plan.passes;
     if (passes.empty()) {
-        if (lm->cb) fire(lm, 0, lm->lay.total);
+        fire_all(lm);
         return B200_OK;
     }
     auto bucket_of = [&](int len) { return (size_t)(std::find(bucketLens.begin(), bucketLens.end(), len) - bucketLens.begin()); };
@@ -510,7 +533,7 @@ int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<Pa
             break;
         }
     }
-    if (lm->cb && !notified) fire(lm, 0, lm->lay.total);
+    if (lm->cb && !notified) fire_all(lm);
     float total = 0.f;
     int valid = 0;
     for (size_t bi = 0; bi < bucketLens.size(); bi++) {

@@ -7,7 +7,10 @@
 
 namespace b200 {
 
-constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s at 2 GHz
+// Clock budget of every bounded wait (default ~2 s at 2 GHz).  Each translation unit that includes this header holds
+// its own copy in constant memory; b200_set_wait_budget_us updates them all for the current device.
+static __constant__ long long g_wait_budget_clocks = 4000000000LL;
+#define WAIT_BUDGET_CLOCKS g_wait_budget_clocks
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -194,6 +197,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
 // Host side (defined in gemm_tcgen05.cu).
 int resolve_encode(b200_ctx* ctx);   // looks up cuTensorMapEncodeTiled once per context
 int ensure_status(b200_ctx* ctx);    // allocates the host-mapped status word the bounded waits raise
+// gemm_tcgen05_set_wait_budget / attn_umma_set_wait_budget (common.h) write this header's budget copy of their
+// translation unit; gemm_tcgen05_probe_wait makes one warp wait on a barrier nobody completes.
 // 2-D FP32 tensor [outer, inner] with row pitch ld floats; box = [boxOuter, 32] floats (128 B inner), 128-byte swizzle
 // (16-byte atoms for a K-contiguous operand, 32-byte atoms for an M/N-contiguous one, matching the UMMA layout types),
 // out-of-range elements read as zero, FP32 -> TF32 conversion (round to nearest) on load.

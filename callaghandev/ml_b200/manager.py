@@ -97,6 +97,23 @@ class CudaB200AccelerationManager:
     def has_tcgen05(self) -> bool:
         return bool(self.lib.b200_has_tcgen05(self.ctx))
 
+    def engine_launches(self) -> dict:
+        """Launch counts per kernel family since the context was created (which path a call really took)."""
+        out = (C.c_int64 * len(L.ENGINES))()
+        self._ck(self.lib.b200_engine_launches(self.ctx, out))
+        return dict(zip(L.ENGINES, (int(v) for v in out)))
+
+    def set_gemm_kernel(self, kernel: int):
+        """0 choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (tests, A/B measurements)."""
+        self._ck(self.lib.b200_set_gemm_kernel(self.ctx, int(kernel)))
+
+    def set_wait_budget_us(self, microseconds: int):
+        self._ck(self.lib.b200_set_wait_budget_us(self.ctx, int(microseconds)))
+
+    def probe_wait_timeout(self):
+        """Runs the wait-expiry probe; raises B200Error(status 6, timeout) when the expiry path works."""
+        self._ck(self.lib.b200_probe_wait_timeout(self.ctx))
+
     def Dispose(self):
         if getattr(self, "ctx", None):
             for child in list(self._children):

@@ -317,12 +317,12 @@ def split_sequences(n_seq: int, rank: int, world: int):
     return lo, lo + base + (1 if rank < rem else 0)
 
 
-def reduce_host_scalars(dist, loss_sum: float, valid: int, device=None):
+def reduce_host_scalars(dist, loss_sum: float, valid: int, device=None, group=None):
     """Sum (loss_sum, valid_count) over ranks with one small all-reduce."""
     import torch
 
     t = torch.tensor([float(loss_sum), float(valid)], dtype=torch.float64, device=device if device is not None else "cpu")
-    dist.all_reduce(t)
+    dist.all_reduce(t, group=group)
     return float(t[0].item()), int(round(t[1].item()))
 
 
@@ -388,30 +388,34 @@ class DataParallelLMTrainer:
     def prepare_discrete(self, tokens, seq_offsets):
         """Copy this rank's shard of the global batch to the device once; returns a handle for train_step_prepared."""
         t, o = self.shard(tokens, seq_offsets)
-        return self.lm.prepare_discrete(t, o) if len(o) > 1 else None
+        if t.size == 0:
+            t = np.zeros(1, np.int32)  # an empty shard is still a batch: it announces every gradient range to its peers
+        return self.lm.prepare_discrete(t, o)
 
-    def _finish(self, ls, vc, had_local, lr, use_clip, clip_threshold, do_step):
+    def _finish(self, ls, vc, lr, use_clip, clip_threshold, do_step):
         if self.world > 1:
-            if not had_local:  # nothing local: still contribute (zeros) to every bucket
-                self._on_ready(0, self.lm.param_count, 0)
             with self.torch.cuda.stream(self.compute):  # Work.wait() orders the *current* stream after the collective
                 for w in self._pending:
                     w.wait()
             self.compute.wait_stream(self.comm)
-            ls, vc = reduce_host_scalars(self.dist, ls, vc, self.device)
+            ls, vc = reduce_host_scalars(self.dist, ls, vc, self.device, self.pg)
         norm = self.lm.apply_step(vc, lr, use_clip, clip_threshold, do_step)
         return (ls / vc if vc else 0.0), norm, vc
 
     def train_step_prepared(self, batch, lr, use_clip=True, clip_threshold=1.0, do_step=True):
         self._pending.clear()
         self.lm.zero_grads()
-        ls, vc = self.lm.accumulate_batch(batch) if batch is not None else (0.0, 0)
-        return self._finish(ls, vc, batch is not None, lr, use_clip, clip_threshold, do_step)
+        ls, vc = self.lm.accumulate_batch(batch)
+        return self._finish(ls, vc, lr, use_clip, clip_threshold, do_step)
 
     def train_step_discrete(self, tokens, seq_offsets, lr, use_clip=True, clip_threshold=1.0, do_step=True):
         """tokens/seq_offsets describe the GLOBAL batch in host memory; this rank trains its shard."""
         t, o = self.shard(tokens, seq_offsets)
         self._pending.clear()
         self.lm.zero_grads()
-        ls, vc = self.lm.accumulate_discrete(t, o) if len(o) > 1 else (0.0, 0)
-        return self._finish(ls, vc, len(o) > 1, lr, use_clip, clip_threshold, do_step)
+        if t.size == 0:
+            t = np.zeros(1, np.int32)
+        # An empty or all-invalid shard still goes through the library: it announces the same gradient ranges in the
+        # same order as a rank that trained, so every rank issues identical collectives.
+        ls, vc = self.lm.accumulate_discrete(t, o)
+        return self._finish(ls, vc, lr, use_clip, clip_threshold, do_step)

@@ -73,6 +73,33 @@ B200_API int32_t b200_gemm_profile(b200_ctx* ctx, int32_t engine, int64_t* launc
 B200_API int64_t b200_gemm_profile_csv(b200_ctx* ctx, char* buf, int64_t capacity);
 /* 1 if the device is compute capability 10.x (tcgen05 path usable), else 0. */
 B200_API int32_t b200_has_tcgen05(b200_ctx* ctx);
+/* Launch counts per engine since the context was created, out[B200_ENGINE_COUNT]: lets a caller (and the parity
+ * tests) see which kernel family a call really ran on instead of trusting the dispatcher's rules. */
+enum {
+    B200_ENGINE_GEMM_SIMT = 0,        /* FP32 shared-memory GEMM */
+    B200_ENGINE_GEMM_TILE = 1,        /* tcgen05, one 128x128 tile per CTA */
+    B200_ENGINE_GEMM_PERSISTENT = 2,  /* tcgen05, one persistent CTA per SM */
+    B200_ENGINE_GEMM_PAIR = 3,        /* tcgen05 cta_group::2, two SMs per 256x256 tile */
+    B200_ENGINE_ATTN_FP32 = 4,        /* FP32 attention (forward or backward call) */
+    B200_ENGINE_ATTN_MMA_SYNC = 5,    /* TF32 mma.sync attention */
+    B200_ENGINE_ATTN_TCGEN05 = 6,     /* TF32 tcgen05 attention (head dim 64) */
+    B200_ENGINE_CE_FUSED = 7,         /* soft-max cross-entropy fused with the vocabulary projection, per row chunk */
+    B200_ENGINE_COUNT = 8
+};
+B200_API int32_t b200_engine_launches(b200_ctx* ctx, int64_t* out);
+/* Forces one tcgen05 GEMM kernel for every qualifying shape of this context: 0 = choose by shape (default), 1 = one
+ * tile per CTA, 128 / 256 = one-CTA persistent kernel of that tile width, 512 = two-SM kernel.  For tests and A/B
+ * measurements; the reference has no counterpart. */
+B200_API int32_t b200_set_gemm_kernel(b200_ctx* ctx, int32_t kernel);
+/* Every device-side wait of the tcgen05 kernels (on an mbarrier that a TMA copy, an MMA commit or another warp
+ * completes) is bounded: when the budget runs out the kernel raises a status word, unwinds and returns, and the next
+ * synchronising call reports B200_ERR_TIMEOUT instead of the process hanging.  The budget is held per device by the
+ * library (default 2 s); this call sets it for the context's device, in microseconds.
+ * b200_probe_wait_timeout launches one tiny kernel (one warp, no tensor memory, no copy) that waits on a barrier
+ * nobody completes, so that the expiry path and its host-side reporting can be exercised without any real failure:
+ * it returns B200_ERR_TIMEOUT when the path works, and the context stays usable.  No counterpart in the reference. */
+B200_API int32_t b200_set_wait_budget_us(b200_ctx* ctx, int64_t microseconds);
+B200_API int32_t b200_probe_wait_timeout(b200_ctx* ctx);
 
 /* ------------------------------------------------------------------------------------------------ A. per-op */
 /* IAccelerationManager.MatrixMultiply (IAccelerationManager.cs:20; AccelerationCPU.cs:159-210): C[rowsA,colsB] = A*B. */
@@ -115,7 +142,9 @@ B200_API int32_t b200_LayerNormBackward(b200_ctx*, const float* dOut, const floa
  * stderr); dOut, input, gamma, dInput 16-byte aligned.  The first call on each device looks up the scratch's device
  * address; make that first call before starting any stream capture.  All calls share the one scratch array, so two
  * calls that can overlap on the GPU (different streams without an ordering between them) race: keep calls on one
- * device ordered.  Nothing in the scratch needs clearing between calls. */
+ * device ordered.  Nothing in the scratch needs clearing between calls.  The looked-up address is kept per device
+ * ordinal for the life of the process: after an in-process cudaDeviceReset it is stale, so a process that resets a
+ * device must not call this entry point on it again. */
 B200_API int32_t b200_LayerNormBackward_noalloc(void* cuda_stream, const float* dOut, const float* input, const float* gamma, const float* mean,
                                                 const float* variance, int32_t rows, int32_t features, float eps, float* dInput,
                                                 float* dGamma, float* dBeta);

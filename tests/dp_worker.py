@@ -52,6 +52,7 @@ def main():
     same = bool(torch.equal(lo, hi))
     flag = torch.tensor([1 if (ok and same) else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    tr.close()  # release the device state before the process group goes away
     dist.destroy_process_group()
     sys.exit(0 if flag.item() == 1 else 1)
 

@@ -99,3 +99,45 @@ def random_walk_batch(rng, n_seq, seq_len, F, target_feature=3):
     tgt = x[:, :, target_feature:target_feature + 1].copy()
     off = np.arange(0, (n_seq + 1) * seq_len, seq_len, dtype=np.int32)
     return x.reshape(-1, F), tgt.reshape(-1, 1), off
+
+
+def tensor_names(cfg):
+    return (["emb"] if cfg.discrete else ["inW", "inB"]) + [f"L{l}.{n}" for l in range(cfg.num_layers) for n in
+            ("WQ", "WK", "WV", "WO", "bQ", "bK", "bV", "bO", "g1", "b1", "g2", "b2", "W1", "fb1", "W2", "fb2")] + ["Wout", "bout"]
+
+
+def compare_gradients(tensors, cfg, exp, act, tol, what="grad"):
+    """Every tensor of the gradient arena against the oracle's, each normalised by its own magnitude
+    (max|diff| <= tol*max|ref| and ||diff||_2 <= tol*||ref||_2).  Returns the worst relative max-error seen."""
+    from conftest import assert_tensor_close
+
+    worst = 0.0
+    for (off, r, c), name in zip(tensors, tensor_names(cfg)):
+        worst = max(worst, assert_tensor_close(exp[off:off + r * c], act[off:off + r * c], tol, f"{what} {name}"))
+    return worst
+
+
+def compare_updates(tensors, cfg, exp_before, exp_after, act_before, act_after, tol, what="update"):
+    """The weight UPDATE (after - before, each side from its own starting weights) of every tensor against the oracle's,
+    normalised per tensor.  Each side rounds the stepped weight to FP32, so the observable update is quantised to the
+    weight's last place: one unit of it is allowed per element on top of tol.  Comparing the weights themselves would
+    hide the update (it is orders of magnitude smaller than the weight)."""
+    from conftest import assert_tensor_close, ulp32
+
+    worst = 0.0
+    for (off, r, c), name in zip(tensors, tensor_names(cfg)):
+        s = slice(off, off + r * c)
+        de = np.asarray(exp_after[s], np.float64) - np.asarray(exp_before[s], np.float64)
+        da = np.asarray(act_after[s], np.float64) - np.asarray(act_before[s], np.float64)
+        q = ulp32(np.maximum(np.abs(exp_after[s]), np.abs(exp_before[s])))
+        worst = max(worst, assert_tensor_close(de, da, tol, f"{what} {name}", quantum=q))
+    return worst
+
+
+def expect_failure(fn, *args, **kw):
+    """Negative control: the comparison must reject this input."""
+    try:
+        fn(*args, **kw)
+    except AssertionError:
+        return
+    raise AssertionError("negative control passed: the comparison cannot fail")

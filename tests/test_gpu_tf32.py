@@ -11,13 +11,14 @@ Two bars:
 import numpy as np
 import pytest
 
-from conftest import assert_close
-from lmutil import init_params, lm_config, token_batch
+from conftest import assert_close, assert_tensor_close, ulp32
+from lmutil import compare_gradients, compare_updates, expect_failure, init_params, lm_config, token_batch
 from oracle import pt_matrix, pt_vector
 
 pytestmark = pytest.mark.gpu
 TF32_TOL = 2e-3
 EMU_TOL = 1e-4
+STEP_TOL = 2e-3  # whole-network gradients and updates, relative to each tensor's own magnitude
 
 
 def tf32(x):
@@ -94,22 +95,13 @@ def test_fused_epilogues(mgr, oracle):
 
 @pytest.mark.parametrize("tile_mode,name", [("1", "one tile per CTA"), ("128", "persistent 128x128"), ("256", "persistent 128x256"), ("512", "two SMs per 256x256 tile")])
 def test_every_tcgen05_gemm_kernel(oracle, tile_mode, name):
-    """The dispatcher picks a kernel by shape; B200_GEMM_TILE_N (read when a context is created) forces one, so that
-    every kernel is checked on all four operand layouts, ragged tile edges, several tiles per CTA, and the fused
-    epilogues (bias, activation + pre-activation, derivative multiply, residual, accumulate)."""
-    import os
-
+    """The dispatcher picks a kernel by shape; b200_set_gemm_kernel forces one, so that every kernel is checked on all
+    four operand layouts, ragged tile edges, several tiles per CTA, and the fused epilogues (bias, activation +
+    pre-activation, derivative multiply, residual, accumulate)."""
     from callaghandev.ml_b200 import GEMM_TF32_TCGEN05, CudaB200AccelerationManager
 
-    old = os.environ.get("B200_GEMM_TILE_N")
-    os.environ["B200_GEMM_TILE_N"] = tile_mode
-    try:
-        m = CudaB200AccelerationManager(0, GEMM_TF32_TCGEN05)
-    finally:
-        if old is None:
-            del os.environ["B200_GEMM_TILE_N"]
-        else:
-            os.environ["B200_GEMM_TILE_N"] = old
+    m = CudaB200AccelerationManager(0, GEMM_TF32_TCGEN05)
+    m.set_gemm_kernel(int(tile_mode))
     if not m.has_tcgen05():
         m.Dispose()
         pytest.skip("device is not compute capability 10.x")
@@ -176,7 +168,13 @@ def test_lm_step_on_tensor_cores(oracle, d, H, L, f):
     assert n_tc > 0, "the tensor-core engine must actually have run"
     assert av == ev
     assert_close(el, al, TF32_TOL, "loss"); assert_close(en, an, TF32_TOL, "grad norm")
-    assert_close(ge, t.download_grads(), TF32_TOL, "gradients"); assert_close(pe, t.download_params(), TF32_TOL, "post-step weights")
+    # whole-network quantities: relative, per tensor, on the gradient and on the weight update, each with its negative control
+    T = oracle.lm_tensors(cfg)
+    ga, pa = t.download_grads(), t.download_params()
+    compare_gradients(T, cfg, ge, ga, STEP_TOL)
+    expect_failure(compare_gradients, T, cfg, ge, np.zeros_like(ga), STEP_TOL)
+    compare_updates(T, cfg, P, pe, P, pa, STEP_TOL)
+    expect_failure(compare_updates, T, cfg, P, pe, P, P, STEP_TOL)
     t.close(); m.Dispose()
 
 
@@ -199,7 +197,10 @@ def test_mlp_config2_on_tensor_cores(oracle):
     assert_close(en, an, TF32_TOL, "delta norm")
     for l in range(1, 4):
         w, b = t.download_layer(l)
-        assert_close(we[l - 1], w, TF32_TOL, f"W{l}"); assert_close(be[l - 1], b, TF32_TOL, f"b{l}")
+        for before, exp, act, name in ((W[l - 1], we[l - 1], w, f"W{l}"), (B[l - 1], be[l - 1], b, f"b{l}")):
+            q = ulp32(np.maximum(np.abs(exp), np.abs(before)))
+            assert_tensor_close(exp - before.astype(np.float64), act - before.astype(np.float64), STEP_TOL, name + " update", quantum=q)
+            expect_failure(assert_tensor_close, exp - before.astype(np.float64), np.zeros(before.shape), STEP_TOL, name, quantum=q)
     t.close(); m.Dispose()
 
 

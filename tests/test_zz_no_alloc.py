@@ -1,5 +1,6 @@
 """The allocation-free LayerNorm backward (b200_LayerNormBackward_noalloc), called through the C ABI with device
-pointers, against the ordinary entry point b200_LayerNormBackward on the same data.
+pointers, against the CPU oracle (LayerNormBackward, AccelerationCPU.cs:1516-1564) and against the ordinary entry
+point b200_LayerNormBackward on the same data.
 
 Who needs it: a caller whose device memory is entirely owned by its own pool (here: torch's caching allocator stands
 in for such a host framework), or a step loop that cannot tolerate the device-wide synchronisation of a driver
@@ -34,7 +35,7 @@ def _run_noalloc(lib, torch, dout, x, gamma, mean, var, eps=1e-5):
     return rc, dx.cpu().numpy(), dg.cpu().numpy(), db.cpu().numpy()
 
 
-def test_noalloc_layernorm_backward_matches_regular_entry_point():
+def test_noalloc_layernorm_backward_matches_regular_entry_point(oracle):
     import torch
 
     from callaghandev.ml_b200 import GEMM_FP32_SIMT, CudaB200AccelerationManager, _lib
@@ -54,6 +55,12 @@ def test_noalloc_layernorm_backward_matches_regular_entry_point():
             assert_close(e_dx, dx, 1e-5, "dInput")       # same row kernel: the tolerance of the other LayerNorm tests
             assert_close(e_dg, dg, 3e-5, "dGamma")       # column sums are added in a different block order
             assert_close(e_db, db, 3e-5, "dBeta")
+            # and against the CPU oracle itself, so that a fault shared by the two device entry points cannot pass
+            _, o_mean, o_var, o_norm = oracle.LayerNormForward(x, g, b)
+            o_dx, o_dg, o_db = oracle.LayerNormBackward(dout, o_norm, g, x, o_mean, o_var)
+            assert_close(o_dx, dx, 1e-5, "dInput vs oracle")
+            assert_close(o_dg, dg, 3e-5, "dGamma vs oracle")
+            assert_close(o_db, db, 3e-5, "dBeta vs oracle")
         # sizes beyond the built-in scratch are refused with a status code (and a message on stderr), nothing is launched
         x = np.zeros((4, 2048), np.float32)
         rc, dx, _, _ = _run_noalloc(lib, torch, x, x, np.ones(2048, np.float32), np.zeros(4, np.float32), np.ones(4, np.float32))
