@@ -12,7 +12,7 @@ from pathlib import Path
 _HERE = Path(__file__).resolve().parent
 LIB_PATH = _HERE / "libcallaghan_b200.so"
 
-OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_OUT_OF_RANGE, ERR_CUDA, ERR_TIMEOUT, ERR_NONFINITE, ERR_UNSUPPORTED = 0, 1, 2, 3, 4, 6, 7, 8
+OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_OUT_OF_RANGE, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_NONFINITE, ERR_UNSUPPORTED, ERR_PEER = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
 GEMM_AUTO, GEMM_FP32_SIMT, GEMM_TF32_TCGEN05 = 0, 1, 2
 OPT_SGD, OPT_ADAM = 0, 1
 ENGINES = ("gemm_simt", "gemm_tile", "gemm_persistent", "gemm_pair", "attn_fp32", "attn_mma_sync", "attn_tcgen05", "ce_fused")
@@ -144,6 +144,28 @@ PROTOTYPES = {
     "b200_lm_gen_step": (_i32, [_vp, _i32, _f]),
     "b200_lm_gen_greedy": (_i32, [_vp, _i, _i32, _i32, _i, _i]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),
+    "b200_dp_set_nccl_library": (_i32, [C.c_char_p]),
+    "b200_dp_unique_id": (_i32, [_b]),
+    "b200_dp_create_rank": (_i32, [_vp, _b, _i32, _i32, _pp]),
+    "b200_dp_destroy": (_i32, [_vp]),
+    "b200_dp_shard": (_i32, [_i32, _i32, _i32, _i, _i]),
+    "b200_dp_set_deadline_ms": (_i32, [_vp, _i32]),
+    "b200_dp_broadcast_params": (_i32, [_vp, _i32]),
+    "b200_dp_train_step_discrete": (_i32, [_vp, _i, _i, _i32, _fl, _i32, _fl, _i32, _f, _f, _i]),
+    "b200_dp_train_step_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _fl, _i32, _fl, _i32, _f, _f, _i]),
+    "b200_dp_batch_create_discrete": (_i32, [_vp, _i, _i, _i32, _pp]),
+    "b200_dp_batch_create_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _pp]),
+    "b200_dp_train_step_batch": (_i32, [_vp, _vp, _fl, _i32, _fl, _i32, _f, _f, _i]),
+    "b200_dp_get_timings": (_i32, [_vp, _f]),
+    "b200_dp_group_create": (_i32, [_i, _i32, C.POINTER(LMConfig), _i32, _i32, _pp]),
+    "b200_dp_group_destroy": (_i32, [_vp]),
+    "b200_dp_group_last_error": (C.c_char_p, [_vp]),
+    "b200_dp_group_size": (_i32, [_vp]),
+    "b200_dp_group_trainer": (_vp, [_vp, _i32]),
+    "b200_dp_group_set_optimizer": (_i32, [_vp, _i32, _fl, _fl, _fl]),
+    "b200_dp_group_upload_params": (_i32, [_vp, _f, _i64, _i64]),
+    "b200_dp_group_train_step_discrete": (_i32, [_vp, _i, _i, _i32, _fl, _i32, _fl, _i32, _f, _f, _i]),
+    "b200_dp_group_train_step_continuous": (_i32, [_vp, _f, _f, _i, _i, _i32, _fl, _i32, _fl, _i32, _f, _f, _i]),
     "b200_mlp_create": (_i32, [_vp, _i32, _i, _i, _i32, _fl, _fl, _fl, _i32, _pp]),
     "b200_mlp_destroy": (_i32, [_vp]),
     "b200_mlp_upload_layer": (_i32, [_vp, _i32, _f, _f]),

@@ -222,4 +222,13 @@ int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from th
 int k_fused_step(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
                  int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev);
 
+
+// ------------------------------------------------------------------------------------------------ resident trainer, as seen by the data-parallel layer
+b200_ctx* lm_context(b200_lm* lm);
+void lm_retain(b200_lm* lm);  // released with b200_lm_destroy
+int64_t lm_param_total(const b200_lm* lm);
+const b200_lm_config& lm_config_of(const b200_lm* lm);
+// Ranges of the gradient arena in the order the last pass's backward completes them (and announces them to the callback).
+std::vector<std::pair<int64_t, int64_t>> lm_grad_ranges(const b200_lm* lm);
+
 }  // namespace b200

@@ -660,6 +660,14 @@ int zero_grads(b200_lm* lm) {
 
 }  // namespace
 
+namespace b200 {
+b200_ctx* lm_context(b200_lm* lm) { return lm->ctx; }
+void lm_retain(b200_lm* lm) { lm->refs.fetch_add(1); }
+int64_t lm_param_total(const b200_lm* lm) { return lm->lay.total; }
+const b200_lm_config& lm_config_of(const b200_lm* lm) { return lm->cfg; }
+std::vector<std::pair<int64_t, int64_t>> lm_grad_ranges(const b200_lm* lm) { return grad_ranges(lm); }
+}  // namespace b200
+
 extern "C" {
 
 int64_t b200_lm_param_count(const b200_lm_config* cfg) { return config_ok(cfg) ? make_layout(*cfg).total : -1; }

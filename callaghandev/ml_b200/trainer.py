@@ -311,27 +311,37 @@ class B200MlpBatchTrainer:
 
 
 def split_sequences(n_seq: int, rank: int, world: int):
-    """Contiguous shard of sequence indices for this rank (the batch is split by sequence)."""
-    base, rem = divmod(n_seq, world)
-    lo = rank * base + min(rank, rem)
-    return lo, lo + base + (1 if rank < rem else 0)
+    """Contiguous shard of sequence indices for this rank (the batch is split by sequence): b200_dp_shard."""
+    lo, hi = C.c_int32(), C.c_int32()
+    if L.load().b200_dp_shard(int(n_seq), int(rank), int(world), C.byref(lo), C.byref(hi)) != L.OK:
+        raise ValueError(f"rank {rank} outside a world of {world}")
+    return lo.value, hi.value
 
 
-def reduce_host_scalars(dist, loss_sum: float, valid: int, device=None, group=None):
-    """Sum (loss_sum, valid_count) over ranks with one small all-reduce."""
-    import torch
+def _bundled_nccl():
+    """Path of the NCCL build that ships with the installed torch wheel, if any (one NCCL per process is the aim)."""
+    try:
+        import nvidia.nccl as pkg
+        from pathlib import Path
 
-    t = torch.tensor([float(loss_sum), float(valid)], dtype=torch.float64, device=device if device is not None else "cpu")
-    dist.all_reduce(t, group=group)
-    return float(t[0].item()), int(round(t[1].item()))
+        for base in list(getattr(pkg, "__path__", [])):
+            cand = Path(base) / "lib" / "libnccl.so.2"
+            if cand.exists():
+                return str(cand)
+    except Exception:
+        pass
+    return None
 
 
 class DataParallelLMTrainer:
-    """One process per GPU.  Every rank holds the full model; the batch is split by sequence; gradients are summed with
-    bucketed all-reduces issued on a communication stream as soon as each range of the gradient arena is final
+    """One process per GPU; a thin caller of the library's data-parallel entry points (b200_dp_*).
+
+    Every rank holds the full model; the batch is split by sequence; gradients are summed with bucketed NCCL all-reduces
+    that the LIBRARY issues on its own communication stream as soon as each range of the gradient arena is final
     (output projection first, then the blocks last to first, then the embedding), overlapping the remaining backward;
-    the loss sum and valid-sequence count travel in one small all-reduce; every rank then applies the identical fused
-    clip-and-step kernel to identical data, so no weight broadcast is needed after the first."""
+    loss sum, valid count and a failure flag travel in one small all-reduce; every rank then applies the identical fused
+    clip-and-step kernel to identical data.  torch.distributed is only the rendezvous here: it tells the ranks apart and
+    carries the 128-byte communicator id from rank 0 to the others."""
 
     def __init__(self, config: L.LMConfig, max_rows_per_pass: int, device_index: int, process_group=None, gemm_mode=L.GEMM_AUTO):
         import torch
@@ -342,80 +352,175 @@ class DataParallelLMTrainer:
         self.device = torch.device("cuda", device_index)
         torch.cuda.set_device(self.device)
         self.mgr = CudaB200AccelerationManager(device_index, gemm_mode)
-        n = int(self.mgr.lib.b200_lm_param_count(C.byref(config)))
-        self.params = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.grads = torch.zeros(n, dtype=torch.float32, device=self.device)
-        self.compute = torch.cuda.Stream(device=self.device)
-        self.comm = torch.cuda.Stream(device=self.device)
+        self.compute = torch.cuda.Stream(device=self.device)  # torch-visible, so that callers can time it with torch events
         self.mgr.set_stream(self.compute.cuda_stream)
-        self.lm = B200LanguageModelTrainer(self.mgr, config, max_rows_per_pass, self.params.data_ptr(), self.grads.data_ptr())
-        self._pending = []
-        self.lm.set_grad_ready_callback(self._on_ready if self.world > 1 else None)
+        self.lm = B200LanguageModelTrainer(self.mgr, config, max_rows_per_pass)
+        self.dp = None
+        if self.world > 1:
+            lib = self.mgr.lib
+            path = _bundled_nccl()
+            if path:
+                lib.b200_dp_set_nccl_library(path.encode())  # ignored once a copy is loaded
+            ident = (C.c_uint8 * 128)()
+            if self.rank == 0 and lib.b200_dp_unique_id(ident) != L.OK:
+                raise L.B200Error("NCCL could not be loaded or refused to create a communicator id")
+            box = [bytes(ident)]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(process_group, 0) if process_group is not None else 0, group=process_group)
+            ident = (C.c_uint8 * 128).from_buffer_copy(box[0])
+            h = C.c_void_p()
+            self.mgr._ck(lib.b200_dp_create_rank(self.lm.h, ident, self.rank, self.world, C.byref(h)))
+            self.dp = h
 
     def close(self):
-        """Release the device state now (the callback holds a reference back to this object, so without this the
-        pair is only collected at interpreter exit)."""
+        """Release the device state now, communicator first."""
         if getattr(self, "lm", None) is not None:
             self.torch.cuda.synchronize(self.device)
-            self.lm.set_grad_ready_callback(None)
+            if self.dp is not None:
+                self.mgr.lib.b200_dp_destroy(self.dp)
+                self.dp = None
             self.lm.close()
             self.mgr.Dispose()
             self.lm = None
 
-    def _on_ready(self, offset, count, event_ptr):
-        torch = self.torch
-        ev = torch.cuda.Event()
-        ev.record(self.compute)  # the library recorded its own event on the same stream just before; this one is torch-visible
-        self.comm.wait_event(ev)
-        with torch.cuda.stream(self.comm):
-            self._pending.append(self.dist.all_reduce(self.grads[offset:offset + count], group=self.pg, async_op=True))
+    def set_deadline_ms(self, ms: int):
+        if self.dp is not None:
+            self.mgr._ck(self.mgr.lib.b200_dp_set_deadline_ms(self.dp, int(ms)))
 
     def broadcast_params(self, flat_host=None):
-        torch = self.torch
+        """Rank 0 uploads flat_host (when given); every rank then receives rank 0's parameter arena."""
         if flat_host is not None and self.rank == 0:
-            self.params.copy_(torch.from_numpy(np.ascontiguousarray(flat_host, dtype=np.float32)))
-        torch.cuda.synchronize(self.device)
-        if self.world > 1:
-            self.dist.broadcast(self.params, src=0, group=self.pg)
-        torch.cuda.synchronize(self.device)
-
-    def shard(self, tokens, seq_offsets):
-        """This rank's contiguous slice of a GLOBAL batch, as (tokens, offsets) re-based to zero."""
-        off = np.asarray(seq_offsets, np.int32)
-        lo, hi = split_sequences(len(off) - 1, self.rank, self.world)
-        return np.ascontiguousarray(np.asarray(tokens, np.int32)[off[lo]:off[hi]]), (off[lo:hi + 1] - off[lo]).astype(np.int32)
+            self.lm.upload_params(flat_host)
+        if self.dp is not None:
+            self.mgr._ck(self.mgr.lib.b200_dp_broadcast_params(self.dp, 0))
+        elif flat_host is not None and self.rank != 0:
+            self.lm.upload_params(flat_host)
 
     def prepare_discrete(self, tokens, seq_offsets):
-        """Copy this rank's shard of the global batch to the device once; returns a handle for train_step_prepared."""
-        t, o = self.shard(tokens, seq_offsets)
+        """Copy this rank's shard of the GLOBAL batch to the device once; returns a handle for train_step_prepared."""
+        if self.dp is None:
+            return self.lm.prepare_discrete(tokens, seq_offsets)
+        t, o = _i(tokens), _i(seq_offsets)
         if t.size == 0:
-            t = np.zeros(1, np.int32)  # an empty shard is still a batch: it announces every gradient range to its peers
-        return self.lm.prepare_discrete(t, o)
+            t = np.zeros(1, np.int32)
+        h = C.c_void_p()
+        self.mgr._ck(self.mgr.lib.b200_dp_batch_create_discrete(self.dp, _pi(t), _pi(o), len(o) - 1, C.byref(h)))
+        return h
 
-    def _finish(self, ls, vc, lr, use_clip, clip_threshold, do_step):
-        if self.world > 1:
-            with self.torch.cuda.stream(self.compute):  # Work.wait() orders the *current* stream after the collective
-                for w in self._pending:
-                    w.wait()
-            self.compute.wait_stream(self.comm)
-            ls, vc = reduce_host_scalars(self.dist, ls, vc, self.device, self.pg)
-        norm = self.lm.apply_step(vc, lr, use_clip, clip_threshold, do_step)
-        return (ls / vc if vc else 0.0), norm, vc
+    def prepare_continuous(self, features, seq_offsets, reg_targets=None, class_targets=None):
+        if self.dp is None:
+            return self.lm.prepare_continuous(features, seq_offsets, reg_targets, class_targets)
+        x, o = _f(features), _i(seq_offsets)
+        r = None if reg_targets is None else _f(reg_targets)
+        k = None if class_targets is None else _i(class_targets)
+        h = C.c_void_p()
+        self.mgr._ck(self.mgr.lib.b200_dp_batch_create_continuous(self.dp, _pf(x), _pf(r), None if k is None else _pi(k), _pi(o), len(o) - 1, C.byref(h)))
+        return h
+
+    def train_step_continuous(self, features, seq_offsets, reg_targets=None, class_targets=None, lr=1e-3, use_clip=True, clip_threshold=1.0, do_step=True):
+        """features / targets / seq_offsets describe the GLOBAL batch in host memory; this rank trains its shard."""
+        if self.dp is None:
+            return self.lm.train_step_continuous(features, seq_offsets, reg_targets, class_targets, lr, use_clip, clip_threshold, do_step)
+        x, o = _f(features), _i(seq_offsets)
+        r = None if reg_targets is None else _f(reg_targets)
+        k = None if class_targets is None else _i(class_targets)
+        loss, norm, valid = C.c_float(0), C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.mgr.lib.b200_dp_train_step_continuous(self.dp, _pf(x), _pf(r), None if k is None else _pi(k), _pi(o), len(o) - 1, lr,
+                                                                int(bool(use_clip)), clip_threshold, int(bool(do_step)), C.byref(loss), C.byref(norm),
+                                                                C.byref(valid)))
+        return loss.value, norm.value, valid.value
 
     def train_step_prepared(self, batch, lr, use_clip=True, clip_threshold=1.0, do_step=True):
-        self._pending.clear()
-        self.lm.zero_grads()
-        ls, vc = self.lm.accumulate_batch(batch)
-        return self._finish(ls, vc, lr, use_clip, clip_threshold, do_step)
+        if self.dp is None:
+            return self.lm.train_step_batch(batch, lr, use_clip, clip_threshold, do_step)
+        loss, norm, valid = C.c_float(0), C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.mgr.lib.b200_dp_train_step_batch(self.dp, batch, lr, int(bool(use_clip)), clip_threshold, int(bool(do_step)),
+                                                           C.byref(loss), C.byref(norm), C.byref(valid)))
+        return loss.value, norm.value, valid.value
 
     def train_step_discrete(self, tokens, seq_offsets, lr, use_clip=True, clip_threshold=1.0, do_step=True):
         """tokens/seq_offsets describe the GLOBAL batch in host memory; this rank trains its shard."""
-        t, o = self.shard(tokens, seq_offsets)
-        self._pending.clear()
-        self.lm.zero_grads()
+        if self.dp is None:
+            return self.lm.train_step_discrete(tokens, seq_offsets, lr, use_clip, clip_threshold, do_step)
+        t, o = _i(tokens), _i(seq_offsets)
         if t.size == 0:
             t = np.zeros(1, np.int32)
-        # An empty or all-invalid shard still goes through the library: it announces the same gradient ranges in the
-        # same order as a rank that trained, so every rank issues identical collectives.
-        ls, vc = self.lm.accumulate_discrete(t, o)
-        return self._finish(ls, vc, lr, use_clip, clip_threshold, do_step)
+        loss, norm, valid = C.c_float(0), C.c_float(0), C.c_int32(0)
+        self.mgr._ck(self.mgr.lib.b200_dp_train_step_discrete(self.dp, _pi(t), _pi(o), len(o) - 1, lr, int(bool(use_clip)), clip_threshold,
+                                                              int(bool(do_step)), C.byref(loss), C.byref(norm), C.byref(valid)))
+        return loss.value, norm.value, valid.value
+
+    def timings_ms(self):
+        """Phase times of the last step on the device, with the communication the step had to wait for."""
+        out = self.lm.timings_ms()
+        if self.dp is not None:
+            ms = (C.c_float * 2)()
+            self.mgr.lib.b200_dp_get_timings(self.dp, ms)
+            out["comm_exposed"], out["comm_span"] = ms[0], ms[1]
+        else:
+            out["comm_exposed"], out["comm_span"] = 0.0, 0.0
+        return out
+
+
+class B200DataParallelGroup:
+    """All GPUs of one process behind one handle (b200_dp_group_*): what a single-process host such as the reference's
+    C# trainer calls.  One context, one trainer and one rank per listed device, driven by one host thread each."""
+
+    def __init__(self, devices, config: L.LMConfig, max_rows_per_pass: int, gemm_mode=L.GEMM_AUTO):
+        self.lib = L.load()
+        path = _bundled_nccl()
+        if path:
+            self.lib.b200_dp_set_nccl_library(path.encode())
+        dev = np.asarray(list(devices), np.int32)
+        h = C.c_void_p()
+        rc = self.lib.b200_dp_group_create(_pi(dev), len(dev), C.byref(config), int(max_rows_per_pass), int(gemm_mode), C.byref(h))
+        if rc != L.OK:
+            raise L.B200Error(f"b200_dp_group_create failed with status {rc}")
+        self.h, self.cfg, self.n = h, config, len(dev)
+        self.param_count = int(self.lib.b200_lm_param_count(C.byref(config)))
+
+    def _ck(self, rc):
+        if rc != L.OK:
+            msg = self.lib.b200_dp_group_last_error(self.h).decode("utf-8", "replace")
+            if rc == L.ERR_OUT_OF_RANGE:
+                raise IndexError(msg)
+            if rc in (L.ERR_INVALID_ARG, L.ERR_SHAPE):
+                raise ValueError(msg)
+            raise L.B200Error(f"status {rc}: {msg}")
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.b200_dp_group_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_optimizer(self, kind="sgd", beta1=0.9, beta2=0.999, eps=1e-8):
+        self._ck(self.lib.b200_dp_group_set_optimizer(self.h, L.OPT_ADAM if kind == "adam" else L.OPT_SGD, beta1, beta2, eps))
+
+    def upload_params(self, flat):
+        a = _f(flat).reshape(-1)
+        self._ck(self.lib.b200_dp_group_upload_params(self.h, _pf(a), 0, a.size))
+
+    def download_params(self, rank=0):
+        out = np.zeros(self.param_count, np.float32)
+        rc = self.lib.b200_lm_download_params(C.c_void_p(self.lib.b200_dp_group_trainer(self.h, rank)), _pf(out), 0, out.size)
+        self._ck(rc)
+        return out
+
+    def download_grads(self, rank=0):
+        out = np.zeros(self.param_count, np.float32)
+        self._ck(self.lib.b200_lm_download_grads(C.c_void_p(self.lib.b200_dp_group_trainer(self.h, rank)), _pf(out), 0, out.size))
+        return out
+
+    def train_step_discrete(self, tokens, seq_offsets, lr, use_clip=True, clip_threshold=1.0, do_step=True):
+        t, o = _i(tokens), _i(seq_offsets)
+        if t.size == 0:
+            t = np.zeros(1, np.int32)
+        loss, norm, valid = C.c_float(0), C.c_float(0), C.c_int32(0)
+        self._ck(self.lib.b200_dp_group_train_step_discrete(self.h, _pi(t), _pi(o), len(o) - 1, lr, int(bool(use_clip)), clip_threshold,
+                                                           int(bool(do_step)), C.byref(loss), C.byref(norm), C.byref(valid)))
+        return loss.value, norm.value, valid.value

@@ -34,9 +34,11 @@ enum {
     B200_ERR_SHAPE = 2,        /* dimension mismatch: ArgumentException */
     B200_ERR_OUT_OF_RANGE = 3, /* row window or token id out of range: ArgumentOutOfRangeException */
     B200_ERR_CUDA = 4,         /* CUDA runtime/driver error */
-    B200_ERR_TIMEOUT = 6,      /* a bounded device-side wait gave up */
+    B200_ERR_NCCL = 5,         /* the collective library reported an error (or could not be loaded); the communicator is aborted */
+    B200_ERR_TIMEOUT = 6,      /* a bounded wait gave up: a device-side wait of a kernel, or a data-parallel peer that did not arrive */
     B200_ERR_NONFINITE = 7,    /* reserved */
-    B200_ERR_UNSUPPORTED = 8   /* e.g. head dimension above 128 */
+    B200_ERR_UNSUPPORTED = 8,  /* e.g. head dimension above 128 */
+    B200_ERR_PEER = 9          /* another data-parallel rank failed in this step; the step was discarded on every rank */
 };
 
 /* Activation ids = CallaghanDev.ML.Enums.ActivationType; cost ids = CostFunctionType (Neural Network/Enums). */
@@ -385,6 +387,70 @@ B200_API int32_t b200_lm_gen_step(b200_lm_gen*, int32_t token_id, float* logits)
 B200_API int32_t b200_lm_gen_greedy(b200_lm_gen*, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_tokens, int32_t* n_out);
 /* Device time of the phases of the last step in milliseconds: [0] forward, [1] loss, [2] backward, [3] step. */
 B200_API int32_t b200_lm_get_timings(b200_lm*, float* ms4);
+
+/* ------------------------------------------------------------------------------------------------ D. data parallel */
+/* No counterpart in the reference, which trains on one device (AccelerationFactory.cs:31-45 builds one manager for one
+ * device id).  The batch is split by sequence over the ranks, every rank holds the full model, the gradient arena is
+ * summed with NCCL all-reduces issued on a communication stream as each range becomes final during the last pass's
+ * backward (output projection, blocks last to first, embedding), one more all-reduce carries {loss sum, valid count,
+ * failed ranks}, and every rank applies the identical fused step -- TransformerTrainer.cs:313-326 over the whole
+ * batch.  The collective library is loaded at run time (libnccl.so.2 as already loaded in the process, else from the
+ * loader path, else from b200_dp_set_nccl_library's path); the host needs no NCCL binding of its own.
+ *
+ * Failure rules (TransformerTrainer.cs:298-307, 316-320 carried over to several ranks): every rank issues the same
+ * collectives in the same order whatever happened locally; a rank whose pass failed reports it in the scalar
+ * all-reduce and then every rank zeroes its gradients, leaves the weights untouched and returns an error (its own on
+ * the failing rank, B200_ERR_PEER elsewhere); a peer that does not arrive within the deadline (default 30 s) gives
+ * B200_ERR_TIMEOUT after the communicator has been aborted (the object must then be destroyed); a non-finite gradient
+ * norm skips the update and zeroes the gradients on every rank alike, because all ranks hold identical sums.
+ *
+ * One process per GPU: rank 0 calls b200_dp_unique_id, the host hands the 128 bytes to the other processes (any
+ * channel), every process calls b200_dp_create_rank on its own trainer.  One process for all GPUs:
+ * b200_dp_group_create(devices, n, ...) builds a context, a trainer and a rank per listed device and drives them with
+ * one host thread each. */
+typedef struct b200_dp b200_dp;
+typedef struct b200_dp_group b200_dp_group;
+B200_API int32_t b200_dp_set_nccl_library(const char* path);
+B200_API int32_t b200_dp_unique_id(uint8_t* id128);
+B200_API int32_t b200_dp_create_rank(b200_lm* lm, const uint8_t* id128, int32_t rank, int32_t world, b200_dp** out);
+B200_API int32_t b200_dp_destroy(b200_dp*);
+/* [lo, hi) of the sequences of a global batch that `rank` trains (contiguous; the first n_seq % world ranks take one more). */
+B200_API int32_t b200_dp_shard(int32_t n_seq, int32_t rank, int32_t world, int32_t* lo, int32_t* hi);
+B200_API int32_t b200_dp_set_deadline_ms(b200_dp*, int32_t milliseconds);
+/* Copies rank `root`'s parameter arena to every rank (after root uploaded or loaded weights). */
+B200_API int32_t b200_dp_broadcast_params(b200_dp*, int32_t root);
+/* One step on a GLOBAL batch in host memory (same arrays on every rank; each trains its shard).  Outputs as
+ * b200_lm_train_step_discrete, identical on every rank. */
+B200_API int32_t b200_dp_train_step_discrete(b200_dp*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip,
+                                             float clip_threshold, int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
+B200_API int32_t b200_dp_train_step_continuous(b200_dp*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                               const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip, float clip_threshold,
+                                               int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
+/* The same on a device-resident shard: b200_dp_batch_create_discrete keeps this rank's part of the global batch on
+ * the device (an empty shard is valid); release it with b200_lm_batch_destroy. */
+B200_API int32_t b200_dp_batch_create_discrete(b200_dp*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out);
+B200_API int32_t b200_dp_batch_create_continuous(b200_dp*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                                 const int32_t* seq_offsets, int32_t n_seq, b200_lm_batch** out);
+B200_API int32_t b200_dp_train_step_batch(b200_dp*, b200_lm_batch* shard, float lr, int32_t use_clip, float clip_threshold, int32_t do_step,
+                                          float* loss, float* grad_norm, int32_t* valid_count);
+/* Communication of the last step, milliseconds on the device: [0] exposed = how long the compute stream waited for the
+ * last all-reduce after its own backward had finished; [1] span from the first all-reduce's start to the last one's end. */
+B200_API int32_t b200_dp_get_timings(b200_dp*, float* ms2);
+
+B200_API int32_t b200_dp_group_create(const int32_t* devices, int32_t n_devices, const b200_lm_config* cfg, int32_t max_rows_per_pass,
+                                      int32_t gemm_mode, b200_dp_group** out);
+B200_API int32_t b200_dp_group_destroy(b200_dp_group*);
+B200_API const char* b200_dp_group_last_error(b200_dp_group*);
+B200_API int32_t b200_dp_group_size(b200_dp_group*);
+B200_API b200_lm* b200_dp_group_trainer(b200_dp_group*, int32_t rank);  /* the rank's trainer, e.g. for downloads */
+B200_API int32_t b200_dp_group_set_optimizer(b200_dp_group*, int32_t kind, float beta1, float beta2, float eps);
+B200_API int32_t b200_dp_group_upload_params(b200_dp_group*, const float* host, int64_t offset, int64_t count);  /* to every rank */
+B200_API int32_t b200_dp_group_train_step_discrete(b200_dp_group*, const int32_t* tokens, const int32_t* seq_offsets, int32_t n_seq, float lr,
+                                                   int32_t use_clip, float clip_threshold, int32_t do_step, float* loss, float* grad_norm,
+                                                   int32_t* valid_count);
+B200_API int32_t b200_dp_group_train_step_continuous(b200_dp_group*, const float* features, const float* reg_targets, const int32_t* class_targets,
+                                                     const int32_t* seq_offsets, int32_t n_seq, float lr, int32_t use_clip, float clip_threshold,
+                                                     int32_t do_step, float* loss, float* grad_norm, int32_t* valid_count);
 
 /* ------------------------------------------------------------------------------------------------ C. resident MLP */
 /* NeuralNetwork.TrainBatch state (NeuralNetwork.cs:420-477 + BatchedAccelerationGPU.cs:12-149): weights stay on the

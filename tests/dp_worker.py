@@ -1,6 +1,7 @@
 """Worker of the multi-GPU data-parallel test: one process per GPU (launched by torch.distributed.run).  Every rank
-trains the same global batch for two steps with DataParallelLMTrainer; rank 0 also trains it on one GPU alone and the
-weights must agree."""
+trains the same global batches with DataParallelLMTrainer (the library's b200_dp_* entry points): a host batch, the same
+batch prepared on the device, and a batch with fewer sequences than ranks (some shards are empty and still have to
+issue every collective).  Rank 0 also trains them on one GPU alone and the weights must agree."""
 import os
 import sys
 from pathlib import Path
@@ -33,17 +34,20 @@ def main():
     res = [tr.train_step_discrete(toks, off, 1e-2, True, 1.0, True)]
     batch = tr.prepare_discrete(toks, off)
     res.append(tr.train_step_prepared(batch, 1e-2, True, 1.0, True))
+    toks1, off1 = toks[:off[1]], off[:2]  # one sequence for the whole world: every rank but the first has nothing to train
+    res.append(tr.train_step_discrete(toks1, off1, 1e-2, True, 1.0, True))
+    exposed = tr.timings_ms()
     got = tr.lm.download_params()
     ok = True
     if rank == 0:
         mgr = CudaB200AccelerationManager(local, GEMM_FP32_SIMT)
         one = B200LanguageModelTrainer(mgr, cfg, 96)
         one.upload_params(P)
-        ref = [one.train_step_discrete(toks, off, 1e-2, True, 1.0, True) for _ in range(2)]
+        ref = [one.train_step_discrete(toks, off, 1e-2, True, 1.0, True) for _ in range(2)] + [one.train_step_discrete(toks1, off1, 1e-2, True, 1.0, True)]
         exp = one.download_params()
         err = float(np.max(np.abs(exp - got) / np.maximum(1.0, np.abs(exp))))
         ok = err <= 1e-5 and all(abs(a[0] - b[0]) <= 1e-5 * max(1, abs(b[0])) and a[2] == b[2] for a, b in zip(res, ref))
-        print(f"DP world {world}: max weight error {err:.3e}, losses {res} vs {ref}", flush=True)
+        print(f"DP world {world}: max weight error {err:.3e}, losses {res} vs {ref}, timings {exposed}", flush=True)
         one.close(); mgr.Dispose()
     # all ranks must hold identical weights
     t = torch.from_numpy(got).cuda()
