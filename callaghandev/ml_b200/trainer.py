@@ -41,6 +41,8 @@ class B200LanguageModelTrainer:
                                             int(max_rows_per_pass), C.byref(h)))
         self.h = h
         self._cb = None
+        self._optimizer = "sgd"
+        self.max_rows_per_pass = int(max_rows_per_pass)
         manager._children.add(self)
 
     def close(self):
@@ -56,12 +58,7 @@ class B200LanguageModelTrainer:
 
     def tensors(self):
         """[(offset, rows, cols)] of every tensor of the flat arena, in weights.bin order with each block's FFN appended."""
-        out = []
-        for i in range(self.lib.b200_lm_tensor_count(C.byref(self.cfg))):
-            off, r, c = C.c_int64(), C.c_int32(), C.c_int32()
-            self.lib.b200_lm_tensor_info(C.byref(self.cfg), i, C.byref(off), C.byref(r), C.byref(c))
-            out.append((off.value, r.value, c.value))
-        return out
+        return self._tensors_of(self.cfg)
 
     def upload_params(self, flat, offset=0):
         a = _f(flat).reshape(-1)
@@ -80,7 +77,10 @@ class B200LanguageModelTrainer:
         return out
 
     def set_optimizer(self, kind="sgd", beta1=0.9, beta2=0.999, eps=1e-8):
+        if kind not in ("sgd", "adam"):
+            raise ValueError("optimizer must be 'sgd' or 'adam'")
         self.mgr._ck(self.lib.b200_lm_set_optimizer(self.h, L.OPT_ADAM if kind == "adam" else L.OPT_SGD, beta1, beta2, eps))
+        self._optimizer = kind
 
     def set_grad_ready_callback(self, fn):
         """fn(offset, count, cuda_event_ptr) or None."""
@@ -140,21 +140,48 @@ class B200LanguageModelTrainer:
         self.mgr._ck(self.lib.b200_lm_upload_optimizer_state(self.h, 1, _pf(v), 0, v.size))
         self.mgr._ck(self.lib.b200_lm_set_step_index(self.h, int(step_index)))
 
-    def save_checkpoint(self, path):
-        """Parameters, Adam moments and step index in one .npz (the reference's weights.bin holds the parameters only)."""
-        blobs = {"params": self.download_params()}
-        try:
-            m, v, step = self.download_optimizer_state()
-            blobs.update(adam_m=m, adam_v=v, step_index=np.int64(step))
-        except Exception:  # SGD keeps no state
-            pass
-        np.savez(path, **blobs)
+    def save_checkpoint(self, directory, max_sequence_length=None, extras=None):
+        """LanguageModel.Save (LanguageModel.cs:706-765): config.json, weights.bin and ffn/ffn_layer_i.json in the
+        reference's own format, straight from the device arena, so that LanguageModel.Load opens the result.  With Adam
+        selected the moments and the step index go into optimizer.bin beside them (the reference's SGD keeps no state)."""
+        from .checkpoint import save_reference_checkpoint
 
-    def load_checkpoint(self, path):
-        z = np.load(path)
-        self.upload_params(z["params"])
-        if "adam_m" in z:
-            self.upload_optimizer_state(z["adam_m"], z["adam_v"], int(z["step_index"]))
+        adam = self.download_optimizer_state() if self._optimizer == "adam" else None
+        save_reference_checkpoint(directory, self.cfg, self.tensors(), self.download_params(), max_sequence_length or self.max_rows_per_pass + 1,
+                                  extras, adam)
+
+    def load_checkpoint(self, directory):
+        """LanguageModel.Load (LanguageModel.cs:769-839) into this trainer: the directory may come from the reference or
+        from save_checkpoint.  The stored shape must be this trainer's.  Returns config.json as a dict."""
+        from .checkpoint import load_reference_checkpoint
+
+        cfg, params, conf, adam = load_reference_checkpoint(directory, make_config, lambda c: (self._tensors_of(c), int(self.lib.b200_lm_param_count(C.byref(c)))))
+        mine = [getattr(self.cfg, n) for n, _ in L.LMConfig._fields_ if n != "align_floats"]
+        theirs = [getattr(cfg, n) for n, _ in L.LMConfig._fields_ if n != "align_floats"]
+        if mine != theirs:
+            raise ValueError(f"checkpoint shape {theirs} does not match this trainer's {mine}")
+        if cfg.align_floats != self.cfg.align_floats:  # re-lay the tensors out in this trainer's arena
+            flat = np.zeros(self.param_count, np.float32)
+            for (so, r, c), (do, _, _) in zip(self._tensors_of(cfg), self.tensors()):
+                flat[do:do + r * c] = params[so:so + r * c]
+            params = flat
+        self.upload_params(params)
+        if adam is not None:
+            if self._optimizer != "adam":
+                raise ValueError("the checkpoint holds Adam state but this trainer's optimizer is SGD: call set_optimizer('adam') first")
+            m, v, step = adam
+            if cfg.align_floats != self.cfg.align_floats:
+                raise ValueError("optimizer.bin was written with another arena alignment")
+            self.upload_optimizer_state(m, v, step)
+        return conf
+
+    def _tensors_of(self, cfg):
+        out = []
+        for i in range(self.lib.b200_lm_tensor_count(C.byref(cfg))):
+            off, r, c = C.c_int64(), C.c_int32(), C.c_int32()
+            self.lib.b200_lm_tensor_info(C.byref(cfg), i, C.byref(off), C.byref(r), C.byref(c))
+            out.append((off.value, r.value, c.value))
+        return out
 
     # ---- LanguageModel.Generate (decoder path): incremental decoding with a device key/value cache
     def generator(self, max_len):

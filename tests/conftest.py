@@ -32,20 +32,23 @@ def assert_close(expected, actual, tol, label=""):
         raise AssertionError(f"{label}: {int((~ok).sum())}/{e.size} outside tol {tol}; worst at {idx}: expected {e[idx]}, got {a[idx]}")
 
 
-def assert_tensor_close(expected, actual, tol, label="", quantum=None):
+def assert_tensor_close(expected, actual, tol, label="", quantum=None, ref_max=None, ref_l2=None):
     """Per-tensor normalised bound for whole-network quantities (gradients, weight updates), whose elements are far
     below 1 so that the operator metric above would be an absolute bound:
         max|exp-act| <= tol*max|exp|   and   ||exp-act||_2 <= tol*||exp||_2.
     `quantum` (same shape, or a scalar) is an additive per-element allowance for a quantity that both sides round
     to a grid before it can be observed: a weight update is only visible as w_after - w_before, and w_after is
-    rounded to FP32, so two correct implementations may differ by one unit in the last place of the weight."""
+    rounded to FP32, so two correct implementations may differ by one unit in the last place of the weight.
+    ref_max / ref_l2 replace the tensor's own magnitude as the yardstick (for a tensor that is the small remainder of
+    cancelling contributions, whose error is set by the size of what cancels)."""
     e = np.asarray(expected, dtype=np.float64).reshape(-1)
     a = np.asarray(actual, dtype=np.float64).reshape(-1)
     assert e.shape == a.shape, f"{label}: shape {e.shape} vs {a.shape}"
     assert np.isfinite(a).all(), f"{label}: non-finite values"
     q = np.zeros_like(e) if quantum is None else np.broadcast_to(np.asarray(quantum, np.float64).reshape(-1), e.shape)
     diff = np.abs(e - a)
-    ref_max, ref_l2 = float(np.max(np.abs(e))) if e.size else 0.0, float(np.sqrt((e * e).sum()))
+    ref_max = (float(np.max(np.abs(e))) if e.size else 0.0) if ref_max is None else float(ref_max)
+    ref_l2 = float(np.sqrt((e * e).sum())) if ref_l2 is None else float(ref_l2)
     excess = diff - q
     worst = int(np.argmax(excess)) if e.size else 0
     if e.size and excess[worst] > tol * ref_max:

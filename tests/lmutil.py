@@ -118,34 +118,57 @@ def unclip(norm, clip_thr):
     return float(norm) / float(clip_thr) if (clip_thr is not None and norm > clip_thr) else 1.0
 
 
-def compare_gradients(tensors, cfg, exp, act, tol, what="grad", exp_scale=1.0, act_scale=1.0):
+def _yardsticks(tensors, cfg, values, scale, key_bias_by_query_bias):
+    """Per tensor (max|ref|, ||ref||_2).  With key_bias_by_query_bias the key-projection bias is measured against the
+    query-projection bias of its layer: a bias added to every key moves all scores of a query by (almost) the same
+    amount, which the soft-max ignores, so that gradient is the small remainder of contributions that cancel (10-100x
+    below its sibling's) and its rounding error is set by the size of what cancels, not by what is left."""
+    names = tensor_names(cfg)
+    out = {}
+    for (off, r, c), name in zip(tensors, names):
+        v = np.asarray(values[off:off + r * c], np.float64) * scale
+        out[name] = (float(np.max(np.abs(v))) if v.size else 0.0, float(np.sqrt((v * v).sum())))
+    if key_bias_by_query_bias:
+        for name in names:
+            if name.endswith(".bK"):
+                q = out[name[:-3] + ".bQ"]
+                out[name] = (max(out[name][0], q[0]), max(out[name][1], q[1]))
+    return out
+
+
+def compare_gradients(tensors, cfg, exp, act, tol, what="grad", exp_scale=1.0, act_scale=1.0, key_bias_by_query_bias=False):
     """Every tensor of the gradient arena against the oracle's, each normalised by its own magnitude
-    (max|diff| <= tol*max|ref| and ||diff||_2 <= tol*||ref||_2).  exp_scale / act_scale: see unclip.
-    Returns the worst relative max-error seen."""
+    (max|diff| <= tol*max|ref| and ||diff||_2 <= tol*||ref||_2).  exp_scale / act_scale: see unclip;
+    key_bias_by_query_bias: see _yardsticks (TF32 comparisons only).  Returns the worst relative max-error seen."""
     from conftest import assert_tensor_close
 
+    ys = _yardsticks(tensors, cfg, exp, exp_scale, key_bias_by_query_bias)
     worst = 0.0
     for (off, r, c), name in zip(tensors, tensor_names(cfg)):
         e = np.asarray(exp[off:off + r * c], np.float64) * exp_scale
         a = np.asarray(act[off:off + r * c], np.float64) * act_scale
-        worst = max(worst, assert_tensor_close(e, a, tol, f"{what} {name}"))
+        assert_tensor_close(e, a, tol, f"{what} {name}", ref_max=ys[name][0], ref_l2=ys[name][1])
+        worst = max(worst, float(np.max(np.abs(e - a))) / max(ys[name][0], 1e-300))
     return worst
 
 
-def compare_updates(tensors, cfg, exp_before, exp_after, act_before, act_after, tol, what="update", exp_scale=1.0, act_scale=1.0):
+def compare_updates(tensors, cfg, exp_before, exp_after, act_before, act_after, tol, what="update", exp_scale=1.0, act_scale=1.0,
+                    key_bias_by_query_bias=False):
     """The weight UPDATE (after - before, each side from its own starting weights) of every tensor against the oracle's,
     normalised per tensor.  Each side rounds the stepped weight to FP32, so the observable update is quantised to the
     weight's last place: one unit of it is allowed per element on top of tol.  Comparing the weights themselves would
     hide the update (it is orders of magnitude smaller than the weight).  exp_scale / act_scale: see unclip."""
     from conftest import assert_tensor_close, ulp32
 
+    ys = _yardsticks(tensors, cfg, np.asarray(exp_after, np.float64) - np.asarray(exp_before, np.float64), exp_scale, key_bias_by_query_bias)
     worst = 0.0
     for (off, r, c), name in zip(tensors, tensor_names(cfg)):
         s = slice(off, off + r * c)
         de = (np.asarray(exp_after[s], np.float64) - np.asarray(exp_before[s], np.float64)) * exp_scale
         da = (np.asarray(act_after[s], np.float64) - np.asarray(act_before[s], np.float64)) * act_scale
         q = ulp32(np.maximum(np.abs(exp_after[s]), np.abs(exp_before[s]))) * max(exp_scale, act_scale)
-        worst = max(worst, assert_tensor_close(de, da, tol, f"{what} {name}", quantum=q))
+        assert_tensor_close(de, da, tol, f"{what} {name}", quantum=q, ref_max=ys[name][0], ref_l2=ys[name][1])
+        worst = max(worst, float(np.max(np.maximum(np.abs(de - da) - q, 0.0))) / max(ys[name][0], 1e-300))
     return worst
 
 

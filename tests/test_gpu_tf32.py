@@ -143,14 +143,19 @@ def test_unqualified_shapes_fall_back_to_simt_in_auto_mode(mgr, oracle):
         mgr.MatrixMultiply(a, b)
 
 
+@pytest.mark.parametrize("act", ["Tanh", "Relu"])
 @pytest.mark.parametrize("d,H,L,f", [(128, 4, 2, 512), (256, 4, 1, 512), (128, 8, 1, 256)])  # head dims 32, 64, 16
-def test_lm_step_on_tensor_cores(oracle, d, H, L, f):
+def test_lm_step_on_tensor_cores(oracle, d, H, L, f, act):
     """One train step in AUTO mode (TF32 GEMMs, TF32 attention with operands rounded where they are produced and
-    copied asynchronously): gradients and post-step weights within the TF32 tolerance of the CPU oracle."""
+    copied asynchronously) against the CPU oracle: gradients and weight updates relative to each tensor's own size.
+    With a smooth activation the bound is the TF32 tolerance, 2e-3.  With ReLU the derivative jumps at z = 0 and TF32
+    rounding of the pre-activations flips about 2e-4 of the units, each by 100 % of its delta: sqrt(2e-4 / 0.5) = 2 % in
+    the 2-norm per FFN layer, which no TF32 implementation can avoid -- those steps are held to 5e-2 in the 2-norm."""
     from callaghandev.ml_b200 import GEMM_AUTO, B200LanguageModelTrainer, CudaB200AccelerationManager, LMConfig
+    from lmutil import _yardsticks, tensor_names, unclip
 
     rng = np.random.default_rng(77)
-    cfg = lm_config(vocab=300, d=d, H=H, L=L, f=f, act="Relu")
+    cfg = lm_config(vocab=300, d=d, H=H, L=L, f=f, act=act)
     c = LMConfig()
     for name, _ in LMConfig._fields_:
         setattr(c, name, getattr(cfg, name))
@@ -161,20 +166,27 @@ def test_lm_step_on_tensor_cores(oracle, d, H, L, f):
     t.upload_params(P)
     pe, ge = P.copy(), np.zeros_like(P)
     el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=1e-2, use_clip=True, clip_thr=1.0)
-    m.profile_gemm(True)
     al, an, av = t.train_step_discrete(toks, off, 1e-2, True, 1.0, True)
-    n_tc = m.gemm_profile(1)[0]
-    m.profile_gemm(False)
-    assert n_tc > 0, "the tensor-core engine must actually have run"
+    eng = m.engine_launches()
+    assert eng["gemm_tile"] + eng["gemm_persistent"] + eng["gemm_pair"] > 0 and eng["attn_fp32"] == 0, f"the tensor-core engines must actually have run: {eng}"
     assert av == ev
-    assert_close(el, al, TF32_TOL, "loss"); assert_close(en, an, TF32_TOL, "grad norm")
-    # whole-network quantities: relative, per tensor, on the gradient and on the weight update, each with its negative control
+    assert_close(el, al, TF32_TOL, "loss"); assert_close(en, an, TF32_TOL if act == "Tanh" else 2e-2, "grad norm")
     T = oracle.lm_tensors(cfg)
     ga, pa = t.download_grads(), t.download_params()
-    compare_gradients(T, cfg, ge, ga, STEP_TOL)
-    expect_failure(compare_gradients, T, cfg, ge, np.zeros_like(ga), STEP_TOL)
-    compare_updates(T, cfg, P, pe, P, pa, STEP_TOL)
-    expect_failure(compare_updates, T, cfg, P, pe, P, P, STEP_TOL)
+    es, as_ = unclip(en, 1.0), unclip(an, 1.0)
+    if act == "Tanh":
+        compare_gradients(T, cfg, ge, ga, STEP_TOL, "grad", es, as_, True)
+        expect_failure(compare_gradients, T, cfg, ge, np.zeros_like(ga), STEP_TOL, "grad", es, as_, True)
+        compare_updates(T, cfg, P, pe, P, pa, STEP_TOL, "update", es, as_, True)
+        expect_failure(compare_updates, T, cfg, P, pe, P, P, STEP_TOL, "update", es, as_, True)
+    else:
+        ys = _yardsticks(T, cfg, ge, es, True)
+        for (o, r, cc), name in zip(T, tensor_names(cfg)):
+            rel = np.linalg.norm(ge[o:o + r * cc].astype(np.float64) * es - ga[o:o + r * cc].astype(np.float64) * as_) / ys[name][1]
+            assert rel <= 5e-2, f"grad {name}: {rel:.2e} of its 2-norm"
+            du = np.linalg.norm((pe[o:o + r * cc].astype(np.float64) - pa[o:o + r * cc]) * es) / (np.linalg.norm((pe[o:o + r * cc].astype(np.float64) - P[o:o + r * cc]) * es) + 1e-300)
+            assert du <= 6e-2, f"update {name}: {du:.2e} of its 2-norm"
+        assert np.linalg.norm(pa.astype(np.float64) - P) > 0.5 * np.linalg.norm(pe.astype(np.float64) - P), "the weights must have moved"
     t.close(); m.Dispose()
 
 
@@ -199,8 +211,10 @@ def test_mlp_config2_on_tensor_cores(oracle):
         w, b = t.download_layer(l)
         for before, exp, act, name in ((W[l - 1], we[l - 1], w, f"W{l}"), (B[l - 1], be[l - 1], b, f"b{l}")):
             q = ulp32(np.maximum(np.abs(exp), np.abs(before)))
-            assert_tensor_close(exp - before.astype(np.float64), act - before.astype(np.float64), STEP_TOL, name + " update", quantum=q)
-            expect_failure(assert_tensor_close, exp - before.astype(np.float64), np.zeros(before.shape), STEP_TOL, name, quantum=q)
+            # ReLU hidden layers: TF32 rounding flips the units whose pre-activation is within ~3e-4 of zero, each by 100 % of
+            # its delta (see test_lm_step_on_tensor_cores); measured 7.5e-3 of a tensor's largest update
+            assert_tensor_close(exp - before.astype(np.float64), act - before.astype(np.float64), 2e-2, name + " update", quantum=q)
+            expect_failure(assert_tensor_close, exp - before.astype(np.float64), np.zeros(before.shape), 2e-2, name, quantum=q)
     t.close(); m.Dispose()
 
 
