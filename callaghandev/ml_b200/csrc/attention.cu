@@ -353,10 +353,9 @@ static size_t bwd_smem(int HD) { return (size_t)(4 * 64 * (HD + 1) + 2 * 64 * PS
 
 template <int HD>
 static int launch_fwd(b200_ctx* ctx, const Attn& t) {
-    static bool configured = false;
-    if (!configured) {
+    static char configured_site;
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem(HD)));
-        configured = true;
     }
     dim3 grid((t.maxQLen + TQ - 1) / TQ, t.numHeads, t.nSeg);
     attn_fwd_kernel<HD><<<grid, ATT_THREADS, fwd_smem(HD), ctx->stream>>>(make_args(t));
@@ -365,11 +364,10 @@ static int launch_fwd(b200_ctx* ctx, const Attn& t) {
 }
 template <int HD>
 static int launch_bwd(b200_ctx* ctx, const Attn& t) {
-    static bool configured = false;
-    if (!configured) {
+    static char configured_site;
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem(HD)));
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bwd_smem(HD)));
-        configured = true;
     }
     AttnArgs a = make_args(t);
     int warps = t.totalQ * t.numHeads;

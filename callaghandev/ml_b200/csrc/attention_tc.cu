@@ -627,18 +627,16 @@ bool vec_ok(const Attn& t, bool bwd) {
 template <int HD>
 int launch_fwd_tc(b200_ctx* ctx, const Attn& t) {
     constexpr size_t smem = (size_t)3 * 64 * (HD + 4) * 4;
-    static bool configured = false;
-    if (!configured) {
+    static char configured_site;
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
     }
     dim3 grid((t.maxQLen + 63) / 64, t.numHeads, t.nSeg);
     if (t.pre_rounded && vec_ok(t, false) && (t.ldo % 2 == 0) && (((uintptr_t)t.O & 7) == 0)) {
         constexpr size_t smem_pipe = (size_t)5 * 64 * (HD + 4) * 4;
-        static bool configured_pipe = false;
-        if (!configured_pipe) {
+        static char configured_pipe_site;
+        if (first_use(ctx, &configured_pipe_site)) {
             B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_tc_pipe_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pipe));
-            configured_pipe = true;
         }
         attn_fwd_tc_pipe_kernel<HD><<<grid, TC_THREADS, smem_pipe, ctx->stream>>>(make_tc_args(t));
         B200_LAUNCH_CHECK(ctx);
@@ -653,11 +651,10 @@ template <int HD>
 int launch_bwd_tc(b200_ctx* ctx, const Attn& t) {
     constexpr size_t smem_dq = (size_t)3 * 64 * (HD + 4) * 4;
     constexpr size_t smem_dkv = (size_t)(2 * 64 * (HD + 4) + 2 * 64 * (HD + 8) + 2 * 64 * 72) * 4;
-    static bool configured = false;
-    if (!configured) {
+    static char configured_site;
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
         B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv));
-        configured = true;
     }
     TcAttnArgs a = make_tc_args(t);
     const int vec = vec_ok(t, true) ? 1 : 0;
@@ -670,10 +667,9 @@ int launch_bwd_tc(b200_ctx* ctx, const Attn& t) {
     dim3 gq((t.maxQLen + 63) / 64, t.numHeads, t.nSeg);
     if (t.pre_rounded && vec && (t.lddq % 2 == 0) && (((uintptr_t)t.dQ & 7) == 0)) {
         constexpr size_t smem_pipe = (size_t)6 * 64 * (HD + 4) * 4;
-        static bool configured_pipe = false;
-        if (!configured_pipe) {
+        static char configured_pipe_site;
+        if (first_use(ctx, &configured_pipe_site)) {
             B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_dq_tc_pipe_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pipe));
-            configured_pipe = true;
         }
         attn_bwd_dq_tc_pipe_kernel<HD><<<gq, TC_THREADS, smem_pipe, ctx->stream>>>(a);
         B200_LAUNCH_CHECK(ctx);

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <map>
+#include <set>
 #include <mutex>
 #include <atomic>
 #include <string>
@@ -44,6 +45,9 @@ struct b200_ctx {
     int* status_host = nullptr;  // host-mapped word raised by a kernel whose bounded wait gave up (0 = healthy)
     int* status_dev = nullptr;
     int gemm_tc_configured = 0, attn_umma_configured = 0;
+    // cudaFuncSetAttribute applies to the current device only: which launch sites have configured their kernels on THIS
+    // context's device (a process-wide flag would leave the second GPU of a single-process job unconfigured)
+    std::set<const void*> configured_sites;
     int gemm_tile_n = 0;  // 0 = choose by shape; 1 / 128 / 256 / 512 force one tcgen05 GEMM kernel (b200_set_gemm_kernel)
     int gemm_box3d = 1;  // M/N-contiguous GEMM operands fetched as one three-dimensional TMA box per stage (0: one box per 32 columns)
     int clock_khz = 0;   // SM clock the bounded-wait budget is converted with
@@ -63,6 +67,8 @@ namespace b200 {
 
 int fail(b200_ctx* ctx, int code, const char* fmt, ...);
 inline void ctx_retain(b200_ctx* ctx) { ctx->refs.fetch_add(1); }
+// True the first time a launch site (identified by the address of a static tag) is reached on this context.
+inline bool first_use(b200_ctx* ctx, const void* site) { return ctx->configured_sites.insert(site).second; }
 void ctx_release(b200_ctx* ctx);  // frees the context when the last reference goes
 
 #define B200_CUDA(ctx, expr)                                                                               \

@@ -948,9 +948,8 @@ template <int BN>
 int gemm_tcgen05_persistent(b200_ctx* ctx, const Gemm& g) {
     ctx->engine_launches[B200_ENGINE_GEMM_PERSISTENT]++;
     constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
-    static bool configured = false;  // per tile width; the attribute belongs to the function, not the context
-    if (!configured) {
-        configured = true;
+    static char configured_site;  // one per tile width (template instantiation); remembered per context, i.e. per device
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_GENERIC, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_LINEAR, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<EPI_ACT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -1127,9 +1126,8 @@ int gemm_tcgen05_tile(b200_ctx* ctx, const Gemm& g) {
 // Two-SM kernel launcher: no split-K; M and N at least 256.
 int gemm_tcgen05_pair(b200_ctx* ctx, const Gemm& g) {
     ctx->engine_launches[B200_ENGINE_GEMM_PAIR]++;
-    static bool configured = false;
-    if (!configured) {
-        configured = true;
+    static char configured_site;
+    if (first_use(ctx, &configured_site)) {
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI_GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI_ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
