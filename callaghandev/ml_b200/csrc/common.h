@@ -227,6 +227,13 @@ int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from th
 // out_dev[1] = applied clip factor.  A non-finite norm zeroes g and leaves w untouched.
 int k_fused_step(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
                  int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev);
+// The same step in one pass over HBM, for a gradient whose sums of squares were taken beforehand: partials[0, n_partials)
+// hold sums of UNSCALED squares (unused slots zero); they are added in index order.
+int k_fused_step_presummed(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, const float* partials, int n_partials, float gscale,
+                           float lr, int use_clip, float clip_thr, int do_step, int optimizer, float beta1, float beta2, float eps, int step_index,
+                           float* out_dev);
+// Sums of squares of g[0, n) into partials[0, *blocks) on `stream`, one partial per block, fixed order (deterministic).
+int k_sumsq_partials(b200_ctx*, const float* g, int64_t n, float* partials, int max_blocks, cudaStream_t stream, int* blocks);
 
 
 // ------------------------------------------------------------------------------------------------ resident trainer, as seen by the data-parallel layer
@@ -236,5 +243,10 @@ int64_t lm_param_total(const b200_lm* lm);
 const b200_lm_config& lm_config_of(const b200_lm* lm);
 // Ranges of the gradient arena in the order the last pass's backward completes them (and announces them to the callback).
 std::vector<std::pair<int64_t, int64_t>> lm_grad_ranges(const b200_lm* lm);
+// Data-parallel jobs take the sums of squares for the one-pass step themselves, after each range's all-reduce:
+// lm_set_external_norm(true) stops the trainer from summing its local gradient, lm_sumsq_range enqueues the sum of range
+// `index` (in lm_grad_ranges order) on `stream`.
+void lm_set_external_norm(b200_lm* lm, bool on);
+int lm_sumsq_range(b200_lm* lm, int index, cudaStream_t stream);
 
 }  // namespace b200

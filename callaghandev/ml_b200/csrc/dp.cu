@@ -140,7 +140,7 @@ struct LmEngine {
 struct NcclTransport {
     b200_dp* dp;
 
-    int allreduce_range(size_t, b200dp::Range r) {
+    int allreduce_range(size_t index, b200dp::Range r) {
         cudaEvent_t ev = (cudaEvent_t)dp->cur_event;
         if (!ev) {  // announced by the protocol itself (nothing local, or the local pass stopped early): order after what is enqueued now
             ev = dp->ev_local;
@@ -151,6 +151,8 @@ struct NcclTransport {
         float* g = b200_lm_grads_device(dp->lm) + r.off;
         ncclResult_t res = dp->api->AllReduce(g, g, (size_t)r.count, ncclFloat, ncclSum, dp->comm, dp->comm_stream);
         if (res != ncclSuccess) { dp_fail(dp, B200_ERR_NCCL, "ncclAllReduce of a gradient range failed", res); return b200dp::DP_ERR_COMM; }
+        // the reduced range is final: its sum of squares (for the one-pass step) follows on the same stream
+        if (lm_sumsq_range(dp->lm, (int)index, dp->comm_stream) != B200_OK) return b200dp::DP_ERR_COMM;
         return b200dp::DP_OK;
     }
 
@@ -232,6 +234,7 @@ int dp_init_common(b200_dp* dp) {
     for (cudaEvent_t* e : evs) B200_CUDA(ctx, cudaEventCreate(e));
     B200_CUDA(ctx, cudaEventCreateWithFlags(&dp->ev_done, cudaEventDisableTiming));
     B200_CUDA(ctx, cudaEventCreateWithFlags(&dp->ev_local, cudaEventDisableTiming));
+    lm_set_external_norm(dp->lm, true);
     return b200_lm_set_grad_ready_callback(dp->lm, ready_trampoline, dp);
 }
 
@@ -308,6 +311,7 @@ int32_t b200_dp_destroy(b200_dp* dp) {
     cudaSetDevice(dp->ctx->device);
     cudaStreamSynchronize(dp->ctx->stream);
     b200_lm_set_grad_ready_callback(dp->lm, nullptr, nullptr);
+    lm_set_external_norm(dp->lm, false);
     if (dp->comm) {
         if (dp->comm_stream) cudaStreamSynchronize(dp->comm_stream);
         dp->api->CommDestroy(dp->comm);

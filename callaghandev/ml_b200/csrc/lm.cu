@@ -123,6 +123,14 @@ struct b200_lm {
     size_t t_used = 0;
     float timings[4] = {0, 0, 0, 0};
     const float* rope = nullptr;
+    // Sums of squares of the gradient ranges, taken as each range becomes final in the last pass (on a side stream, under
+    // the remaining backward), so that the step reads the gradient once.  sumsq_done counts the ranges summed since
+    // the last accumulation started; the step falls back to its two-phase form unless all of them are there.
+    float* sumsq_partials = nullptr;  // [ranges][SUMSQ_BLOCKS], unused slots zero
+    int n_ranges = 0, sumsq_next = 0, sumsq_done = 0;
+    bool external_norm = false;       // a data-parallel layer sums after each range's all-reduce instead
+    cudaStream_t norm_stream = nullptr;
+    cudaEvent_t norm_event = nullptr;
 };
 
 // A batch whose inputs have been planned, packed and copied to the device once; it can be trained on repeatedly
@@ -150,11 +158,37 @@ cudaEvent_t next_event(std::vector<cudaEvent_t>& pool, size_t& used) {
     return pool[used++];
 }
 
+constexpr int SUMSQ_BLOCKS = 592;  // partial sums per range (four blocks per SM of a B200)
+
 void fire(b200_lm* lm, int64_t off, int64_t count) {
     if (!lm->cb || count <= 0) return;
     cudaEvent_t e = next_event(lm->cb_events, lm->cb_used);
     cudaEventRecord(e, lm->ctx->stream);
     lm->cb(lm->cb_user, off, count, (void*)e);
+}
+
+int sumsq_range(b200_lm* lm, int index, cudaStream_t stream) {
+    if (index < 0 || index >= lm->n_ranges) return B200_OK;
+    const auto r = lm_grad_ranges(lm)[(size_t)index];
+    int blocks = 0;
+    B200_TRY(k_sumsq_partials(lm->ctx, lm->G + r.first, r.second, lm->sumsq_partials + (size_t)index * SUMSQ_BLOCKS, SUMSQ_BLOCKS, stream, &blocks));
+    lm->sumsq_done++;
+    return B200_OK;
+}
+
+// A range of the gradient arena has received its final contribution of this step (ranges arrive in grad_ranges order):
+// its sum of squares starts on the side stream, and a data-parallel caller is told.
+int range_final(b200_lm* lm, int64_t off, int64_t count) {
+    const int index = lm->sumsq_next++;
+    if (!lm->external_norm && lm->norm_stream) {
+        cudaEvent_t e = next_event(lm->cb_events, lm->cb_used);
+        B200_CUDA(lm->ctx, cudaEventRecord(e, lm->ctx->stream));
+        B200_CUDA(lm->ctx, cudaStreamWaitEvent(lm->norm_stream, e, 0));
+        B200_TRY(sumsq_range(lm, index, lm->norm_stream));
+        B200_CUDA(lm->ctx, cudaEventRecord(lm->norm_event, lm->norm_stream));
+    }
+    fire(lm, off, count);
+    return B200_OK;
 }
 
 // The ranges of the gradient arena in the order the last pass's backward finishes them: output projection and bias,
@@ -319,7 +353,7 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
     // TransformerTrainer.cs:874-879: output projection.
     B200_TRY(wgrad(ctx, lm->logits, O, lm->xFinal, d, N, O, d, G + lm->lay.Wout, G + lm->lay.bout));
     B200_TRY(dgrad(ctx, lm->logits, O, P + lm->lay.Wout, N, O, d, dX, 0));
-    if (notify) fire(lm, lm->lay.Wout, lm->lay.total - lm->lay.Wout);
+    if (notify) B200_TRY(range_final(lm, lm->lay.Wout, lm->lay.total - lm->lay.Wout));
     for (int l = c.num_layers - 1; l >= 0; l--) {
         const LayerOff& L = lm->lay.layer[(size_t)l];
         LayerCache& k = lm->cache[(size_t)l];
@@ -383,7 +417,7 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         std::swap(dX, t2);
         if (notify) {
             int64_t end = (l + 1 < c.num_layers) ? lm->lay.layer[(size_t)l + 1].WQ : lm->lay.Wout;
-            fire(lm, L.WQ, end - L.WQ);
+            B200_TRY(range_final(lm, L.WQ, end - L.WQ));
         }
     }
     // BackpropInput (:887-896)
@@ -393,7 +427,7 @@ int backward_pass(b200_lm* lm, const Pass& p, bool notify) {
         B200_TRY(wgrad(ctx, dX, d, lm->cur.contIn, c.input_feature_dim, N, d, c.input_feature_dim, G + lm->lay.in0, G + lm->lay.in1));
     if (notify) {
         int64_t end = c.num_layers > 0 ? lm->lay.layer[0].WQ : lm->lay.Wout;
-        fire(lm, 0, end);
+        B200_TRY(range_final(lm, 0, end));
     }
     // the swap above rotates local names only; restore the canonical buffer order for the next pass
     return B200_OK;
@@ -455,6 +489,8 @@ int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<Pa
     *valid_count = 0;
     lm->cb_used = 0;
     lm->t_used = 0;
+    lm->sumsq_next = lm->sumsq_done = 0;
+    B200_CUDA(ctx, cudaMemsetAsync(lm->sumsq_partials, 0, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS, ctx->stream));
     const std::vector<int>& bucketLens = plan.bucketLens;
     const std::vector<Pass>& passes = plan.passes;
     if (passes.empty()) {
@@ -526,7 +562,7 @@ int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<Pa
                 for (int t = 0; t < q.len; t++, r++) bucketSum[bi] += rowLoss[(size_t)r];
                 bucketCount[bi]++;
             }
-            B200_TRY(backward_pass(lm, p, last && lm->cb != nullptr));
+            B200_TRY(backward_pass(lm, p, last));
             cudaEventRecord(e3, ctx->stream);
             lm->t_has_bwd[lm->t_used / 4 - 1] = 1;
             if (last && lm->cb) notified = true;
@@ -635,8 +671,16 @@ int apply_step(b200_lm* lm, int valid, float lr, int use_clip, float thr, int do
     }
     cudaEvent_t e0 = next_event(lm->t_events, lm->t_used), e1 = next_event(lm->t_events, lm->t_used);
     cudaEventRecord(e0, ctx->stream);
-    B200_TRY(k_fused_step(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, 1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1,
-                          lm->beta2, lm->adam_eps, lm->step_index, lm->stepOut));
+    if (lm->sumsq_done == lm->n_ranges && lm->n_ranges > 0) {  // every range was summed as it became final: one pass
+        if (!lm->external_norm) B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, lm->norm_event, 0));
+        B200_TRY(k_fused_step_presummed(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, lm->sumsq_partials, lm->n_ranges * SUMSQ_BLOCKS,
+                                        1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1, lm->beta2, lm->adam_eps, lm->step_index,
+                                        lm->stepOut));
+    } else {
+        B200_TRY(k_fused_step(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, 1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1,
+                              lm->beta2, lm->adam_eps, lm->step_index, lm->stepOut));
+    }
+    lm->sumsq_done = 0;  // the gradient has been rescaled in place: the sums are spent
     cudaEventRecord(e1, ctx->stream);
     B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, lm->stepOut, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -654,6 +698,8 @@ int zero_grads(b200_lm* lm) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     for (int i = 0; i < 4; i++) lm->timings[i] = 0.f;
+    lm->sumsq_next = lm->sumsq_done = 0;
+    B200_CUDA(ctx, cudaMemsetAsync(lm->sumsq_partials, 0, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS, ctx->stream));
     B200_CUDA(ctx, cudaMemsetAsync(lm->G, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
     return B200_OK;
 }
@@ -666,6 +712,8 @@ void lm_retain(b200_lm* lm) { lm->refs.fetch_add(1); }
 int64_t lm_param_total(const b200_lm* lm) { return lm->lay.total; }
 const b200_lm_config& lm_config_of(const b200_lm* lm) { return lm->cfg; }
 std::vector<std::pair<int64_t, int64_t>> lm_grad_ranges(const b200_lm* lm) { return grad_ranges(lm); }
+void lm_set_external_norm(b200_lm* lm, bool on) { lm->external_norm = on; }
+int lm_sumsq_range(b200_lm* lm, int index, cudaStream_t stream) { return sumsq_range(lm, index, stream); }
 }  // namespace b200
 
 extern "C" {
@@ -759,6 +807,12 @@ int32_t b200_lm_create(b200_ctx* ctx, const b200_lm_config* cfg, float* params_d
     size_t hFloats = N + N * F + N * O + 8;
     if (cudaMallocHost((void**)&lm->h_int, sizeof(int32_t) * hInts) != cudaSuccess || cudaMallocHost((void**)&lm->h_float, sizeof(float) * hFloats) != cudaSuccess)
         return cleanup(fail(ctx, B200_ERR_CUDA, "pinned staging allocation failed"));
+    lm->n_ranges = c.num_layers + 2;
+    if (cudaMalloc((void**)&lm->sumsq_partials, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&lm->norm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&lm->norm_event, cudaEventDisableTiming) != cudaSuccess)
+        return cleanup(fail(ctx, B200_ERR_CUDA, "could not set up the gradient-norm side stream"));
+    cudaMemsetAsync(lm->sumsq_partials, 0, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS, ctx->stream);
     int rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_rows, &lm->rope);
     if (rc != B200_OK) return cleanup(rc);
     *out = lm;
@@ -776,6 +830,9 @@ int32_t b200_lm_destroy(b200_lm* lm) {
     if (lm->block) cudaFree(lm->block);
     if (lm->h_int) cudaFreeHost(lm->h_int);
     if (lm->h_float) cudaFreeHost(lm->h_float);
+    if (lm->norm_stream) { cudaStreamSynchronize(lm->norm_stream); cudaStreamDestroy(lm->norm_stream); }
+    if (lm->norm_event) cudaEventDestroy(lm->norm_event);
+    if (lm->sumsq_partials) cudaFree(lm->sumsq_partials);
     for (cudaEvent_t e : lm->cb_events) cudaEventDestroy(e);
     for (cudaEvent_t e : lm->t_events) cudaEventDestroy(e);
     b200_ctx* ctx = lm->ctx;

@@ -5,6 +5,12 @@
 //            clip factor min(1, thr/norm), and applies SGD (w -= lr*g, the reference's only optimiser) or Adam to its
 //            slice, leaving the scaled-and-clipped gradient in g as the reference does.
 // A non-finite norm zeroes the gradients and leaves the weights untouched (TransformerTrainer.cs:316-320).
+//
+// One pass over HBM: when the trainer has already summed the squares of every range of the gradient arena -- it does so
+// on a side stream as each range receives its final contribution during the last pass's backward (after the range's
+// all-reduce in a data-parallel job), where the sum hides under the remaining backward -- the step is
+// fused_step_presummed_kernel: no norm phase, no grid barrier, the gradient is read once.  Algorithmic bytes then:
+// SGD read g, read w, write w = 12 B per parameter, Adam 28 B (+ 4 B for leaving the scaled gradient behind).
 // Replaces ScaleGradients + ComputeGradientNorm + ClipGradients + UpdateParameters (TransformerTrainer.cs:1269-1383),
 // which are four passes with one manager call per tensor.
 #include <cooperative_groups.h>
@@ -41,28 +47,9 @@ __device__ __forceinline__ void step_one(const StepArgs& a, int64_t i, float fac
     }
 }
 
-__global__ void __launch_bounds__(256) fused_step_kernel(StepArgs a) {
-    __shared__ float red[32];
-    cg::grid_group grid = cg::this_grid();
-    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+// Phase 2 of the step, shared by both kernels: t = sum of squares of the scaled gradient.
+__device__ __forceinline__ void step_update(const StepArgs& a, float t, int64_t tid, int64_t stride) {
     const int64_t n4 = a.n >> 2;
-    const float4* g4 = reinterpret_cast<const float4*>(a.g);
-    float s = 0.f;
-    for (int64_t k = tid; k < n4; k += stride) {
-        float4 x = g4[k];
-        x.x *= a.gscale; x.y *= a.gscale; x.z *= a.gscale; x.w *= a.gscale;
-        s += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
-    }
-    for (int64_t k = (n4 << 2) + tid; k < a.n; k += stride) {
-        float x = a.g[k] * a.gscale;
-        s += x * x;
-    }
-    s = block_sum(s, red);
-    if (threadIdx.x == 0) a.partials[blockIdx.x] = s;
-    grid.sync();
-    float t = 0.f;
-    for (int k = threadIdx.x; k < (int)gridDim.x; k += blockDim.x) t += a.partials[k];
-    t = block_sum(t, red);
     const float norm = sqrtf(t);
     const bool finite = isfinite(norm);
     const float clip = (a.use_clip && finite && norm > a.clip_thr) ? a.clip_thr / norm : 1.0f;
@@ -117,6 +104,63 @@ __global__ void __launch_bounds__(256) fused_step_kernel(StepArgs a) {
     }
 }
 
+__global__ void __launch_bounds__(256) fused_step_kernel(StepArgs a) {
+    __shared__ float red[32];
+    cg::grid_group grid = cg::this_grid();
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t n4 = a.n >> 2;
+    const float4* g4 = reinterpret_cast<const float4*>(a.g);
+    float s = 0.f;
+    for (int64_t k = tid; k < n4; k += stride) {
+        float4 x = g4[k];
+        x.x *= a.gscale; x.y *= a.gscale; x.z *= a.gscale; x.w *= a.gscale;
+        s += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+    }
+    for (int64_t k = (n4 << 2) + tid; k < a.n; k += stride) {
+        float x = a.g[k] * a.gscale;
+        s += x * x;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) a.partials[blockIdx.x] = s;
+    grid.sync();
+    float t = 0.f;
+    for (int k = threadIdx.x; k < (int)gridDim.x; k += blockDim.x) t += a.partials[k];
+    t = block_sum(t, red);
+    step_update(a, t, tid, stride);
+}
+
+// The same step when the sum of squares has been taken range by range beforehand: `partials` holds n_partials sums of
+// UNSCALED squares in a fixed order; every block adds them in that order (bit-identical norm in all blocks).
+__global__ void __launch_bounds__(256) fused_step_presummed_kernel(StepArgs a, const float* __restrict__ partials, int n_partials) {
+    __shared__ float red[32];
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    float t = 0.f;
+    for (int k = threadIdx.x; k < n_partials; k += blockDim.x) t += partials[k];
+    t = block_sum(t, red) * (a.gscale * a.gscale);
+    step_update(a, t, tid, stride);
+}
+
+// Sum of squares of one range of the gradient arena: block b adds its fixed slice in a fixed order and writes partials[b].
+__global__ void __launch_bounds__(256) sumsq_partials_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ partials) {
+    __shared__ float red[32];
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t head = (4 - (((uintptr_t)g >> 2) & 3)) & 3;  // elements before the first 16-byte boundary
+    const int64_t h = head < n ? head : n;
+    const float4* g4 = reinterpret_cast<const float4*>(g + h);
+    const int64_t n4 = (n - h) >> 2;
+    float s = 0.f;
+    for (int64_t k = tid; k < n4; k += stride) {
+        const float4 x = g4[k];
+        s += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+    }
+    if (blockIdx.x == 0) {
+        for (int64_t k = threadIdx.x; k < h; k += blockDim.x) s += g[k] * g[k];
+        for (int64_t k = h + (n4 << 2) + threadIdx.x; k < n; k += blockDim.x) s += g[k] * g[k];
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
 int k_fused_step(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
                  int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev) {
     if (n <= 0) return B200_OK;
@@ -143,6 +187,41 @@ int k_fused_step(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t 
     void* args[] = {&a};
     B200_CUDA(ctx, cudaLaunchCooperativeKernel((void*)fused_step_kernel, dim3(grid), dim3(256), args, 0, ctx->stream));
     ctx->launches++;
+    return B200_OK;
+}
+
+// Sums of squares of g[0, n) into partials[0, blocks): returns the number of partials written through *blocks.
+int k_sumsq_partials(b200_ctx* ctx, const float* g, int64_t n, float* partials, int max_blocks, cudaStream_t stream, int* blocks) {
+    *blocks = 0;
+    if (n <= 0 || max_blocks <= 0) return B200_OK;
+    int64_t want = (n / 4 + 256 * 8 - 1) / (256 * 8);  // at least eight 128-bit loads per thread
+    if (want < 1) want = 1;
+    if (want > max_blocks) want = max_blocks;
+    sumsq_partials_kernel<<<(int)want, 256, 0, stream>>>(g, n, partials);
+    B200_LAUNCH_CHECK(ctx);
+    *blocks = (int)want;
+    return B200_OK;
+}
+
+int k_fused_step_presummed(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t n, const float* partials, int n_partials, float gscale,
+                           float lr, int use_clip, float clip_thr, int do_step, int optimizer, float beta1, float beta2, float eps, int step_index,
+                           float* out_dev) {
+    if (n <= 0) return B200_OK;
+    if (((uintptr_t)w | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15)
+        return fail(ctx, B200_ERR_INVALID_ARG, "parameter arenas must be 16-byte aligned");
+    int grid = ctx->sm_count * 4;
+    int64_t need = (n / 4 + 255) / 256;
+    if (need < 1) need = 1;
+    if (grid > need) grid = (int)need;
+    StepArgs a;
+    a.w = w; a.g = g; a.m = m; a.v = v; a.n = n; a.gscale = gscale; a.lr = lr; a.clip_thr = clip_thr; a.use_clip = use_clip;
+    a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
+    a.bc1 = 1.0f - powf(beta1, (float)step_index);
+    a.bc2 = 1.0f - powf(beta2, (float)step_index);
+    a.partials = nullptr;
+    a.out = out_dev;
+    fused_step_presummed_kernel<<<grid, 256, 0, ctx->stream>>>(a, partials, n_partials);
+    B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }
 

@@ -118,11 +118,15 @@ def unclip(norm, clip_thr):
     return float(norm) / float(clip_thr) if (clip_thr is not None and norm > clip_thr) else 1.0
 
 
-def _yardsticks(tensors, cfg, values, scale, key_bias_by_query_bias):
+def _yardsticks(tensors, cfg, values, scale, key_bias_by_query_bias, score_path_by_value_path=False):
     """Per tensor (max|ref|, ||ref||_2).  With key_bias_by_query_bias the key-projection bias is measured against the
     query-projection bias of its layer: a bias added to every key moves all scores of a query by (almost) the same
     amount, which the soft-max ignores, so that gradient is the small remainder of contributions that cancel (10-100x
-    below its sibling's) and its rounding error is set by the size of what cancels, not by what is left."""
+    below its sibling's) and its rounding error is set by the size of what cancels, not by what is left.
+    score_path_by_value_path (statistical comparisons of steps with a discontinuous activation derivative only): the
+    query/key projections' gradients pass through the soft-max Jacobian, which at initialisation (near-uniform
+    attention) removes all but 1e-2..1e-4 of what comes in; the units flipped by TF32 rounding perturb what comes in by
+    percents, so those gradients are measured against the value projection's of the same layer."""
     names = tensor_names(cfg)
     out = {}
     for (off, r, c), name in zip(tensors, names):
@@ -133,6 +137,12 @@ def _yardsticks(tensors, cfg, values, scale, key_bias_by_query_bias):
             if name.endswith(".bK"):
                 q = out[name[:-3] + ".bQ"]
                 out[name] = (max(out[name][0], q[0]), max(out[name][1], q[1]))
+    if score_path_by_value_path:
+        for name in names:
+            for mine, sibling in ((".WQ", ".WV"), (".WK", ".WV"), (".bQ", ".bV"), (".bK", ".bV")):
+                if name.endswith(mine):
+                    v = out[name[:-3] + sibling]
+                    out[name] = (max(out[name][0], v[0]), max(out[name][1], v[1]))
     return out
 
 

@@ -180,11 +180,13 @@ def test_lm_step_on_tensor_cores(oracle, d, H, L, f, act):
         compare_updates(T, cfg, P, pe, P, pa, STEP_TOL, "update", es, as_, True)
         expect_failure(compare_updates, T, cfg, P, pe, P, P, STEP_TOL, "update", es, as_, True)
     else:
-        ys = _yardsticks(T, cfg, ge, es, True)
+        # query / key projections against the value projection's magnitude: see lmutil._yardsticks
+        ys = _yardsticks(T, cfg, ge, es, True, True)
+        yu = _yardsticks(T, cfg, pe.astype(np.float64) - P, es, True, True)
         for (o, r, cc), name in zip(T, tensor_names(cfg)):
             rel = np.linalg.norm(ge[o:o + r * cc].astype(np.float64) * es - ga[o:o + r * cc].astype(np.float64) * as_) / ys[name][1]
             assert rel <= 5e-2, f"grad {name}: {rel:.2e} of its 2-norm"
-            du = np.linalg.norm((pe[o:o + r * cc].astype(np.float64) - pa[o:o + r * cc]) * es) / (np.linalg.norm((pe[o:o + r * cc].astype(np.float64) - P[o:o + r * cc]) * es) + 1e-300)
+            du = np.linalg.norm((pe[o:o + r * cc].astype(np.float64) - P[o:o + r * cc]) * es - (pa[o:o + r * cc].astype(np.float64) - P[o:o + r * cc]) * as_) / (yu[name][1] + 1e-300)
             assert du <= 6e-2, f"update {name}: {du:.2e} of its 2-norm"
         assert np.linalg.norm(pa.astype(np.float64) - P) > 0.5 * np.linalg.norm(pe.astype(np.float64) - P), "the weights must have moved"
     t.close(); m.Dispose()

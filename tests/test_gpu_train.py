@@ -243,6 +243,39 @@ def test_adam_extension_against_numpy(mgr, oracle):
     t.close()
 
 
+def test_step_when_the_last_pass_trains_nothing(mgr, oracle):
+    """The parameter step reads the gradient once when every range of the arena was summed as it became final during
+    the last pass's backward.  Here the last pass holds one sequence whose loss is not finite (its token's embedding row
+    is +inf), so that pass runs no backward, nothing is announced, and the step falls back to its two-phase form (norm,
+    grid barrier, update).  Reference rule: a non-finite loss drops the sequences of that length (TransformerTrainer.cs:271-272)."""
+    from callaghandev.ml_b200 import B200LanguageModelTrainer
+
+    rng = np.random.default_rng(21)
+    cfg = lm_config(vocab=60, d=32, H=4, L=2, f=64, act="Tanh")
+    toks, off = token_batch(rng, 5, 58, fixed_len=12)       # ids 4..57
+    toks = np.concatenate([toks, [1, 59, 59, 59, 59, 59, 59, 59, 59, 2]]).astype(np.int32)  # a sixth sequence, of another length, on token 59 only
+    off = np.concatenate([off, [off[-1] + 10]]).astype(np.int32)
+    P = init_params(oracle, cfg, 3)
+    P[59 * 32:59 * 32 + 32] = np.inf
+    t = B200LanguageModelTrainer(mgr, _b200_cfg(cfg), 55)   # five sequences of 11 rows fill one pass; the sixth is alone in the last
+    t.upload_params(P)
+    pe, ge = P.copy(), np.zeros_like(P)
+    el, en, ev = oracle.lm_train_step(cfg, pe, ge, off, tokens=toks, lr=0.05, use_clip=True, clip_thr=0.5)
+    al, an, av = t.train_step_discrete(toks, off, 0.05, True, 0.5, True)
+    assert av == ev == 5
+    assert_close(el, al, 1e-5, "loss"); assert_close(en, an, 2e-5, "norm")
+    finite = np.isfinite(P)
+    ga, pa = t.download_grads(), t.download_params()
+    assert np.array_equal(np.isfinite(pa), finite)
+    T = oracle.lm_tensors(cfg)
+    z = lambda a: np.where(finite, a, 0).astype(np.float32)
+    es, as_ = (en / 0.5 if en > 0.5 else 1.0), (an / 0.5 if an > 0.5 else 1.0)
+    compare_gradients(T, cfg, ge, ga, FP32_TOL, "grad", es, as_)
+    compare_updates(T, cfg, z(P), z(pe), z(P), z(pa), FP32_TOL, "update", es, as_)
+    expect_failure(compare_updates, T, cfg, z(P), z(pe), z(P), z(P), FP32_TOL, "update", es, as_)
+    t.close()
+
+
 def test_run_twice_bit_identical_step(mgr, oracle):
     from callaghandev.ml_b200 import B200LanguageModelTrainer
 
