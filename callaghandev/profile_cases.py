@@ -1,5 +1,5 @@
 """Small, self-contained launches of the hot kernels, sized for a profiler capture (a few hundred MB on the device,
-a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>`` with case one of
+a handful of launches).  ``python -m callaghandev.profile_cases <case>`` with case one of
 
   attention   segmented causal attention forward + backward, 8 sequences x 1024 tokens, 16 heads of 64
   gemm        the three GEMM layouts of a linear layer (forward, dX, dW) at 8192 x 1024 x 4096
@@ -10,6 +10,9 @@ a handful of launches).  ``python -m callaghandev.ml_b200.profile_cases <case>``
               512 queries x 4096 keys, 8 heads of 64
   layernorm   LayerNorm forward + backward on 32768 x 1024
   crossentropy  cross-entropy loss + gradient on 4096 rows x 32000 classes
+  step        the parameter step on a 64 M-parameter arena (Adam): the sums of squares range by range and the one-pass
+              update, then the two-phase fallback; one small LM so that the trainer owns the arenas
+  embedding   token-embedding gather and the deterministic gradient scatter: 65536 rows x 1024, Zipf(1.1) ids over 32000
   generate    greedy decoding with the device key/value cache on the c5 model (V 32000, d 1024, 16 heads, 12 layers,
               f 4096): 16-token prompt + 240 generated tokens, prints tokens/s
 """
@@ -17,7 +20,7 @@ import sys
 
 import numpy as np
 
-from . import CudaB200AccelerationManager, GEMM_AUTO
+from .ml_b200 import CudaB200AccelerationManager, GEMM_AUTO
 
 
 def attention(m, rng):
@@ -106,10 +109,42 @@ def crossentropy(m, rng):
     return float(r[0])
 
 
+def step(m, rng):
+    """A model whose arena is dominated by a 60000 x 1024 embedding and output projection (~124 M parameters, 0.5 GB per
+    arena, four arenas with Adam): a tiny batch is trained so that every range is announced, then the step runs."""
+    from .ml_b200 import B200LanguageModelTrainer, make_config
+
+    cfg = make_config(vocab_size=60000, embedding_dim=1024, num_heads=16, num_layers=1, ffn_dim=1024, ffn_activation="Relu")
+    t = B200LanguageModelTrainer(m, cfg, max_rows_per_pass=256)
+    t.set_optimizer("adam")
+    t.upload_params(rng.standard_normal(t.param_count, dtype=np.float32) * 0.02)
+    toks = np.concatenate([[1], rng.integers(4, 60000, 130), [2]]).astype(np.int32)
+    off = np.array([0, len(toks)], np.int32)
+    r = None
+    for _ in range(3):
+        r = t.train_step_discrete(toks, off, 1e-3, True, 1.0, True)
+    t.close()
+    return float(r[1])
+
+
+def embedding(m, rng):
+    rows, d, vocab = 65536, 1024, 32000
+    ranks = np.arange(1, vocab - 4 + 1, dtype=np.float64)
+    cdf = np.cumsum(ranks ** -1.1); cdf /= cdf[-1]
+    ids = (4 + np.searchsorted(cdf, rng.random(rows))).astype(np.int32)
+    emb = rng.normal(0, 0.02, (vocab, d)).astype(np.float32)
+    dx = rng.normal(0, 1, (rows, d)).astype(np.float32)
+    eg = np.zeros_like(emb)
+    for _ in range(2):
+        x = m.EmbedTokenIds(ids, emb, d)
+        m.AccumulateTokenEmbeddingGrad(eg, dx, ids, rows, d)
+    return float(np.abs(eg).mean()) + float(np.abs(x).mean())
+
+
 def generate(m, rng):
     import time
 
-    from . import B200LanguageModelTrainer, make_config
+    from .ml_b200 import B200LanguageModelTrainer, make_config
 
     cfg = make_config(vocab_size=32000, embedding_dim=1024, num_heads=16, num_layers=12, ffn_dim=4096, ffn_activation="Relu")
     t = B200LanguageModelTrainer(m, cfg, max_rows_per_pass=1024)
@@ -127,7 +162,7 @@ def generate(m, rng):
     return float(out[-1])
 
 
-CASES = {"generate": generate, "attention": attention, "gemm": gemm, "wgrad": wgrad, "ffn": ffn, "decayattention": decayattention, "layernorm": layernorm, "crossentropy": crossentropy}
+CASES = {"generate": generate, "step": step, "embedding": embedding, "attention": attention, "gemm": gemm, "wgrad": wgrad, "ffn": ffn, "decayattention": decayattention, "layernorm": layernorm, "crossentropy": crossentropy}
 
 
 def main(argv):

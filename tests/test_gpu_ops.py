@@ -22,6 +22,14 @@ def mgr():
     m.Dispose()
 
 
+def test_reference_known_answer_vectors_on_the_device(mgr):
+    """tests/golden/reference_known_answers.json: the values the reference's own suites assert (matrix product entries
+    17 / 23 / 67, LayerNorm row statistics, rotary rotations at positions 0, 1, 2), through the C ABI."""
+    from test_oracle_pins import check_known_answers
+
+    check_known_answers(mgr)
+
+
 @pytest.mark.parametrize("shape", [(2, 2, 3), (128, 128, 64), (257, 131, 77), (1, 513, 1), (300, 5, 260)])
 def test_matrix_multiply(mgr, oracle, shape):
     m, k, n = shape

@@ -16,6 +16,37 @@ from oracle import pt_matrix, pt_positive_vector, pt_vector
 CPU_TOL = 1e-5  # PT:34
 
 
+def _golden():
+    import json
+    from pathlib import Path
+
+    return json.loads((Path(__file__).parent / "golden" / "reference_known_answers.json").read_text())
+
+
+def check_known_answers(backend, tol_scale=1.0):
+    """The reference's own known-answer vectors (tests/golden/reference_known_answers.json) against any object with the
+    interface's method names: the CPU oracle here, the device manager in the GPU suite."""
+    g = _golden()
+    c = g["matmul_transpose"]
+    out = backend.MatrixMultiplyTranspose(np.array(c["A"], np.float32), np.array(c["B"], np.float32))
+    for i, j, v in c["expected_entries"]:
+        assert abs(out[i, j] - v) <= c["tolerance"] * tol_scale, (i, j, out[i, j], v)
+    c = g["layernorm_unit_gamma"]
+    x = np.array(c["input"], np.float32)
+    out = backend.LayerNormForward(x, np.ones(x.shape[1], np.float32), np.zeros(x.shape[1], np.float32))[0]
+    assert np.all(np.abs(out.mean(axis=1) - c["row_mean"]) <= c["row_mean_tolerance"])
+    assert np.all(np.abs(out.var(axis=1) - c["row_variance"]) <= c["row_variance_tolerance"])
+    for name in ("rope_known_values", "rope_heads_independent"):
+        c = g[name]
+        x = np.array(c["input"], np.float32)
+        backend.ApplyRotaryPositionEmbeddingInPlace(x, c["num_heads"])
+        assert np.max(np.abs(x - np.array(c["expected"]))) <= c["tolerance"] * tol_scale, name
+
+
+def test_reference_known_answer_vectors(oracle):
+    check_known_answers(oracle)
+
+
 def test_matmul_transpose_known_values(oracle):  # TTT:664-674
     c = oracle.MatrixMultiplyTranspose([[1, 2], [3, 4]], [[5, 6], [7, 8], [9, 10]])
     assert c.shape == (2, 3)
