@@ -226,12 +226,14 @@ int attn_backward(b200_ctx*, const Attn& a);  // needs O, rowMax, rowSum from th
 // One cooperative kernel: sumsq of (g*gscale) -> clip factor -> SGD or Adam update.  out_dev[0] = grad norm,
 // out_dev[1] = applied clip factor.  A non-finite norm zeroes g and leaves w untouched.
 int k_fused_step(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
-                 int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev);
+                 int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev, int write_g = 1);
 // The same step in one pass over HBM, for a gradient whose sums of squares were taken beforehand: partials[0, n_partials)
 // hold sums of UNSCALED squares (unused slots zero); they are added in index order.
 int k_fused_step_presummed(b200_ctx*, float* w, float* g, float* m, float* v, int64_t n, const float* partials, int n_partials, float gscale,
                            float lr, int use_clip, float clip_thr, int do_step, int optimizer, float beta1, float beta2, float eps, int step_index,
-                           float* out_dev);
+                           float* out_dev, int write_g = 1);
+// g[0, n) *= factor (the scaling a step launched with write_g = 0 still owes the gradient arena).
+int k_scale_arena(b200_ctx*, float* g, int64_t n, float factor);
 // Sums of squares of g[0, n) into partials[0, *blocks) on `stream`, one partial per block, fixed order (deterministic).
 int k_sumsq_partials(b200_ctx*, const float* g, int64_t n, float* partials, int max_blocks, cudaStream_t stream, int* blocks);
 

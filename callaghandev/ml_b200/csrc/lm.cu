@@ -129,6 +129,10 @@ struct b200_lm {
     float* sumsq_partials = nullptr;  // [ranges][SUMSQ_BLOCKS], unused slots zero
     int n_ranges = 0, sumsq_next = 0, sumsq_done = 0;
     bool external_norm = false;       // a data-parallel layer sums after each range's all-reduce instead
+    // The step does not write the scaled-and-clipped gradient back (4 bytes per parameter nobody reads in a training
+    // loop, whose next step starts by zeroing the arena): the factor is kept here and applied the moment anything looks
+    // at the gradient arena or adds to it, so the reference's observable state -- gradients left scaled and clipped -- holds.
+    float g_pending = 1.f;
     cudaStream_t norm_stream = nullptr;
     cudaEvent_t norm_event = nullptr;
 };
@@ -165,6 +169,13 @@ void fire(b200_lm* lm, int64_t off, int64_t count) {
     cudaEvent_t e = next_event(lm->cb_events, lm->cb_used);
     cudaEventRecord(e, lm->ctx->stream);
     lm->cb(lm->cb_user, off, count, (void*)e);
+}
+
+int settle_grads(b200_lm* lm) {
+    if (lm->g_pending == 1.f) return B200_OK;
+    const float f = lm->g_pending;
+    lm->g_pending = 1.f;
+    return k_scale_arena(lm->ctx, lm->G, lm->lay.total, f);
 }
 
 int sumsq_range(b200_lm* lm, int index, cudaStream_t stream) {
@@ -489,6 +500,7 @@ int run_plan(b200_lm* lm, const Batch& b, const Plan& plan, const std::vector<Pa
     *valid_count = 0;
     lm->cb_used = 0;
     lm->t_used = 0;
+    B200_TRY(settle_grads(lm));  // adding to a gradient whose scaling is still owed
     lm->sumsq_next = lm->sumsq_done = 0;
     B200_CUDA(ctx, cudaMemsetAsync(lm->sumsq_partials, 0, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS, ctx->stream));
     const std::vector<int>& bucketLens = plan.bucketLens;
@@ -669,23 +681,26 @@ int apply_step(b200_lm* lm, int valid, float lr, int use_clip, float thr, int do
         }
         lm->step_index++;
     }
+    B200_TRY(settle_grads(lm));
     cudaEvent_t e0 = next_event(lm->t_events, lm->t_used), e1 = next_event(lm->t_events, lm->t_used);
     cudaEventRecord(e0, ctx->stream);
     if (lm->sumsq_done == lm->n_ranges && lm->n_ranges > 0) {  // every range was summed as it became final: one pass
         if (!lm->external_norm) B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, lm->norm_event, 0));
         B200_TRY(k_fused_step_presummed(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, lm->sumsq_partials, lm->n_ranges * SUMSQ_BLOCKS,
                                         1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1, lm->beta2, lm->adam_eps, lm->step_index,
-                                        lm->stepOut));
+                                        lm->stepOut, 0));
     } else {
         B200_TRY(k_fused_step(ctx, lm->P, lm->G, lm->M, lm->V, lm->lay.total, 1.0f / (float)valid, lr, use_clip, thr, do_step, lm->opt, lm->beta1,
-                              lm->beta2, lm->adam_eps, lm->step_index, lm->stepOut));
+                              lm->beta2, lm->adam_eps, lm->step_index, lm->stepOut, 0));
     }
-    lm->sumsq_done = 0;  // the gradient has been rescaled in place: the sums are spent
+    lm->sumsq_done = 0;  // one step per set of sums
     cudaEventRecord(e1, ctx->stream);
     B200_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, lm->stepOut, 2 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     B200_TRY(check_device_status(ctx));
     if (grad_norm) *grad_norm = ctx->pinned[0];
+    // the factor the kernel applied to every gradient element on its way into the update (a non-finite norm zeroed the arena instead)
+    lm->g_pending = std::isfinite(ctx->pinned[0]) ? (1.0f / (float)valid) * ctx->pinned[1] : 1.f;
     float ms;
     if (cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) lm->timings[3] += ms;
     lm->t_used -= 2;
@@ -699,6 +714,7 @@ int zero_grads(b200_lm* lm) {
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     for (int i = 0; i < 4; i++) lm->timings[i] = 0.f;
     lm->sumsq_next = lm->sumsq_done = 0;
+    lm->g_pending = 1.f;
     B200_CUDA(ctx, cudaMemsetAsync(lm->sumsq_partials, 0, sizeof(float) * (size_t)lm->n_ranges * SUMSQ_BLOCKS, ctx->stream));
     B200_CUDA(ctx, cudaMemsetAsync(lm->G, 0, sizeof(float) * (size_t)lm->lay.total, ctx->stream));
     return B200_OK;
@@ -855,9 +871,22 @@ static int lm_copy(b200_lm* lm, float* host, const float* chost, float* dev, int
 }
 int32_t b200_lm_upload_params(b200_lm* lm, const float* host, int64_t offset, int64_t count) { return lm_copy(lm, nullptr, host, lm ? lm->P : nullptr, offset, count, true); }
 int32_t b200_lm_download_params(b200_lm* lm, float* host, int64_t offset, int64_t count) { return lm_copy(lm, host, nullptr, lm ? lm->P : nullptr, offset, count, false); }
-int32_t b200_lm_download_grads(b200_lm* lm, float* host, int64_t offset, int64_t count) { return lm_copy(lm, host, nullptr, lm ? lm->G : nullptr, offset, count, false); }
+static int settle_locked(b200_lm* lm) {
+    std::lock_guard<std::mutex> lock(lm->ctx->mu);
+    B200_CUDA(lm->ctx, cudaSetDevice(lm->ctx->device));
+    return settle_grads(lm);
+}
+int32_t b200_lm_download_grads(b200_lm* lm, float* host, int64_t offset, int64_t count) {
+    if (!lm) return B200_ERR_INVALID_ARG;
+    B200_TRY(settle_locked(lm));
+    return lm_copy(lm, host, nullptr, lm->G, offset, count, false);
+}
 float* b200_lm_params_device(b200_lm* lm) { return lm ? lm->P : nullptr; }
-float* b200_lm_grads_device(b200_lm* lm) { return lm ? lm->G : nullptr; }
+float* b200_lm_grads_device(b200_lm* lm) {
+    if (!lm) return nullptr;
+    if (lm->g_pending != 1.f && settle_locked(lm) != B200_OK) return nullptr;  // enqueued on the context's stream, like every other write to the arena
+    return lm->G;
+}
 
 int32_t b200_lm_set_optimizer(b200_lm* lm, int32_t kind, float beta1, float beta2, float eps) {
     if (!lm) return B200_ERR_INVALID_ARG;

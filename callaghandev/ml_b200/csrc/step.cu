@@ -9,8 +9,10 @@
 // One pass over HBM: when the trainer has already summed the squares of every range of the gradient arena -- it does so
 // on a side stream as each range receives its final contribution during the last pass's backward (after the range's
 // all-reduce in a data-parallel job), where the sum hides under the remaining backward -- the step is
-// fused_step_presummed_kernel: no norm phase, no grid barrier, the gradient is read once.  Algorithmic bytes then:
-// SGD read g, read w, write w = 12 B per parameter, Adam 28 B (+ 4 B for leaving the scaled gradient behind).
+// fused_step_presummed_kernel: no norm phase, no grid barrier, the gradient is read once.  The trainer also launches
+// it with write_g = 0: the scaled-and-clipped gradient is not written back (it remembers the factor and applies it
+// only if somebody looks at the gradient arena before the next step zeroes it).  Bytes per parameter then: SGD read g,
+// read w, write w = 12; Adam read g, w, m, v, write w, m, v = 28.
 // Replaces ScaleGradients + ComputeGradientNorm + ClipGradients + UpdateParameters (TransformerTrainer.cs:1269-1383),
 // which are four passes with one manager call per tensor.
 #include <cooperative_groups.h>
@@ -27,6 +29,7 @@ struct StepArgs {
     int64_t n;
     float gscale, lr, clip_thr;
     int use_clip, do_step, optimizer;
+    int write_g;  // 1: leave the scaled-and-clipped gradient in g (the reference's observable state); 0: the caller applies the factor later, on demand
     float beta1, beta2, eps, bc1, bc2;
     float* partials;
     float* out;
@@ -34,7 +37,7 @@ struct StepArgs {
 
 __device__ __forceinline__ void step_one(const StepArgs& a, int64_t i, float factor) {
     float g = a.g[i] * factor;
-    a.g[i] = g;
+    if (a.write_g) a.g[i] = g;
     if (!a.do_step) return;
     if (a.optimizer == B200_OPT_ADAM) {
         float m = a.beta1 * a.m[i] + (1.0f - a.beta1) * g;
@@ -64,13 +67,14 @@ __device__ __forceinline__ void step_update(const StepArgs& a, float t, int64_t 
         return;
     }
     const float factor = a.gscale * clip;
+    if (!a.do_step && !a.write_g) return;  // norm only
     if (a.optimizer == B200_OPT_SGD) {
         float4* gw = reinterpret_cast<float4*>(a.g);
         float4* w4 = reinterpret_cast<float4*>(a.w);
         for (int64_t k = tid; k < n4; k += stride) {
             float4 g = gw[k];
             g.x *= factor; g.y *= factor; g.z *= factor; g.w *= factor;
-            gw[k] = g;
+            if (a.write_g) gw[k] = g;
             if (a.do_step) {
                 float4 w = w4[k];
                 w.x -= a.lr * g.x; w.y -= a.lr * g.y; w.z -= a.lr * g.z; w.w -= a.lr * g.w;
@@ -87,7 +91,7 @@ __device__ __forceinline__ void step_update(const StepArgs& a, float t, int64_t 
         for (int64_t k = tid; k < n4; k += stride) {
             float4 g = gw[k];
             g.x *= factor; g.y *= factor; g.z *= factor; g.w *= factor;
-            gw[k] = g;
+            if (a.write_g) gw[k] = g;
             if (a.do_step) {
                 float4 m = m4[k], v = v4[k], w = w4[k];
                 m.x = a.beta1 * m.x + ob1 * g.x; m.y = a.beta1 * m.y + ob1 * g.y; m.z = a.beta1 * m.z + ob1 * g.z; m.w = a.beta1 * m.w + ob1 * g.w;
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(256) sumsq_partials_kernel(const float* __rest
 }
 
 int k_fused_step(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t n, float gscale, float lr, int use_clip, float clip_thr,
-                 int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev) {
+                 int do_step, int optimizer, float beta1, float beta2, float eps, int step_index, float* out_dev, int write_g) {
     if (n <= 0) return B200_OK;
     if (((uintptr_t)w | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15)
         return fail(ctx, B200_ERR_INVALID_ARG, "parameter arenas must be 16-byte aligned");
@@ -179,7 +183,7 @@ int k_fused_step(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t 
     B200_TRY(ensure_ws(ctx, (size_t)grid));
     StepArgs a;
     a.w = w; a.g = g; a.m = m; a.v = v; a.n = n; a.gscale = gscale; a.lr = lr; a.clip_thr = clip_thr; a.use_clip = use_clip;
-    a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
+    a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.write_g = write_g;
     a.bc1 = 1.0f - powf(beta1, (float)step_index);
     a.bc2 = 1.0f - powf(beta2, (float)step_index);
     a.partials = ctx->ws;
@@ -205,7 +209,7 @@ int k_sumsq_partials(b200_ctx* ctx, const float* g, int64_t n, float* partials, 
 
 int k_fused_step_presummed(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t n, const float* partials, int n_partials, float gscale,
                            float lr, int use_clip, float clip_thr, int do_step, int optimizer, float beta1, float beta2, float eps, int step_index,
-                           float* out_dev) {
+                           float* out_dev, int write_g) {
     if (n <= 0) return B200_OK;
     if (((uintptr_t)w | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15)
         return fail(ctx, B200_ERR_INVALID_ARG, "parameter arenas must be 16-byte aligned");
@@ -215,12 +219,36 @@ int k_fused_step_presummed(b200_ctx* ctx, float* w, float* g, float* m, float* v
     if (grid > need) grid = (int)need;
     StepArgs a;
     a.w = w; a.g = g; a.m = m; a.v = v; a.n = n; a.gscale = gscale; a.lr = lr; a.clip_thr = clip_thr; a.use_clip = use_clip;
-    a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
+    a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.write_g = write_g;
     a.bc1 = 1.0f - powf(beta1, (float)step_index);
     a.bc2 = 1.0f - powf(beta2, (float)step_index);
     a.partials = nullptr;
     a.out = out_dev;
     fused_step_presummed_kernel<<<grid, 256, 0, ctx->stream>>>(a, partials, n_partials);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+// g *= factor over the whole arena: what the step leaves undone when it does not write the gradient back.
+__global__ void __launch_bounds__(256) scale_arena_kernel(float* __restrict__ g, int64_t n, float factor) {
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    float4* g4 = reinterpret_cast<float4*>(g);
+    const int64_t n4 = n >> 2;
+    for (int64_t k = tid; k < n4; k += stride) {
+        float4 x = g4[k];
+        x.x *= factor; x.y *= factor; x.z *= factor; x.w *= factor;
+        g4[k] = x;
+    }
+    for (int64_t k = (n4 << 2) + tid; k < n; k += stride) g[k] *= factor;
+}
+
+int k_scale_arena(b200_ctx* ctx, float* g, int64_t n, float factor) {
+    if (n <= 0) return B200_OK;
+    int64_t need = (n / 4 + 255) / 256;
+    int grid = ctx->sm_count * 8;
+    if (need < 1) need = 1;
+    if (grid > need) grid = (int)need;
+    scale_arena_kernel<<<grid, 256, 0, ctx->stream>>>(g, n, factor);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -319,6 +319,9 @@ B200_API int32_t b200_lm_upload_params(b200_lm*, const float* host, int64_t offs
 B200_API int32_t b200_lm_download_params(b200_lm*, float* host, int64_t offset, int64_t count);
 B200_API int32_t b200_lm_download_grads(b200_lm*, float* host, int64_t offset, int64_t count);
 B200_API float* b200_lm_params_device(b200_lm*);
+/* The gradient arena on the device.  A step does not write the scaled-and-clipped gradient back; the factor is applied
+ * (one kernel on the context's stream) the first time the arena is looked at through this call or b200_lm_download_grads,
+ * or added to by a further b200_lm_accumulate_*, so every observer sees what the reference leaves behind. */
 B200_API float* b200_lm_grads_device(b200_lm*);
 B200_API int32_t b200_lm_set_optimizer(b200_lm*, int32_t kind, float beta1, float beta2, float eps);
 
