@@ -158,6 +158,11 @@ int k_sqnorm(b200_ctx*, const float* x, int64_t n, float* out_dev);  // out_dev[
 int k_colsum(b200_ctx*, const float* x, int rows, int cols, int ld, float* out, int accumulate);
 int k_embed(b200_ctx*, const int32_t* ids_dev, int count, const float* emb, int embDim, float* out);
 int k_argmax(b200_ctx*, const float* x, int n, int32_t* out_dev);  // index of the maximum (lowest index among equals)
+// Single-token decoding with the position in device memory (decode.cu): graph-capturable, no host-dependent argument.
+int k_decode_embed(b200_ctx*, const int32_t* tokens, const int32_t* pos, const float* emb, int d, float* x);
+int k_decode_rope_scatter(b200_ctx*, float* qkv, const int32_t* pos, const float* table, int d, int headDim, float* Kc, float* Vc);
+int k_decode_attn(b200_ctx*, const float* q, const float* Kc, const float* Vc, const int32_t* pos, int numHeads, int headDim, float scale, float* out);
+int k_decode_advance(b200_ctx*, const float* logits, int n, int32_t* tokens, int32_t* pos, int pick);
 // Deterministic scatter-add: rows of (dXa [+ dXb]) sorted by id on the host.  seg_id[s] = vocabulary row, rows of
 // segment s are perm[seg_off[s] .. seg_off[s+1]) in ascending original order.
 int k_embed_scatter(b200_ctx*, float* eg, const float* dXa, const float* dXb, const int32_t* seg_id, const int32_t* seg_off,

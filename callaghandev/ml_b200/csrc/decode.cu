@@ -1,0 +1,162 @@
+// Single-token decoding kernels for the generation session (LanguageModel.Generate's decoder path,
+// LanguageModel.cs:270-537).  Every kernel here takes the token's position from DEVICE memory, so the launch sequence
+// of one token has no host-dependent argument: it is captured once into a CUDA graph and replayed for every token
+// (decoding one token is ~100 launches of a few microseconds each, i.e. launch-bound when issued one by one).
+#include "common.h"
+#include "device_math.cuh"
+
+namespace b200 {
+
+// x[0, d) = embedding row of tokens[*pos]   (EmbedTokenIds for one id, AccelerationCPU.cs:3473-3515)
+__global__ void decode_embed_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ pos, const float* __restrict__ emb, int d,
+                                    float* __restrict__ x) {
+    const int id = tokens[*pos];
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < d; j += gridDim.x * blockDim.x) x[j] = emb[(size_t)id * d + j];
+}
+
+// qkv = [q | k | v] of the current token (3d floats, biases added).  Rotates q and k by the position's angles
+// (pairs (2p, 2p+1) within each head, AccelerationCPU.cs:4855-4982), leaves q in place and appends the rotated k and the
+// v to row *pos of the layer's key / value cache.
+__global__ void decode_rope_scatter_kernel(float* __restrict__ qkv, const int32_t* __restrict__ pos, const float2* __restrict__ table, int d,
+                                           int headDim, float* __restrict__ Kc, float* __restrict__ Vc) {
+    const int p = *pos, pairs = headDim >> 1, total = d >> 1;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const float2 cs = table[(size_t)p * pairs + (i % pairs)];
+        float2 q = reinterpret_cast<float2*>(qkv)[i];
+        const float2 k = reinterpret_cast<const float2*>(qkv + d)[i];
+        const float2 v = reinterpret_cast<const float2*>(qkv + 2 * d)[i];
+        reinterpret_cast<float2*>(qkv)[i] = make_float2(q.x * cs.x - q.y * cs.y, q.x * cs.y + q.y * cs.x);
+        reinterpret_cast<float2*>(Kc + (size_t)p * d)[i] = make_float2(k.x * cs.x - k.y * cs.y, k.x * cs.y + k.y * cs.x);
+        reinterpret_cast<float2*>(Vc + (size_t)p * d)[i] = v;
+    }
+}
+
+// One query row against the cached rows 0..*pos of one layer; a block per head, a warp per key (strided), lanes over
+// the head's columns.  Soft-max with the running-maximum form of AccelerationCPU.cs:1874-1946; every cached row is in
+// the past, so there is no mask.
+template <int MAXHD>  // head dimension hd <= MAXHD
+__global__ void __launch_bounds__(128) decode_attn_kernel(const float* __restrict__ q, const float* __restrict__ Kc, const float* __restrict__ Vc,
+                                                          const int32_t* __restrict__ pos, int d, int HD, float scale, float* __restrict__ out) {
+    constexpr int PER = (MAXHD + 31) / 32;
+    __shared__ float s_m[4], s_l[4], s_o[4][MAXHD];
+    const int head = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nKeys = *pos + 1;
+    float qr[PER], acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int c = lane + 32 * i;
+        qr[i] = c < HD ? q[head * HD + c] : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = warp; j < nKeys; j += 4) {
+        const float* kr = Kc + (size_t)j * d + head * HD;
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int c = lane + 32 * i;
+            if (c < HD) s += qr[i] * kr[c];
+        }
+        s = warp_sum(s) * scale;
+        const float mn = fmaxf(m, s);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - mn), w = expf(s - mn);
+        const float* vr = Vc + (size_t)j * d + head * HD;
+        l = l * corr + w;
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int c = lane + 32 * i;
+            acc[i] = acc[i] * corr + (c < HD ? w * vr[c] : 0.f);
+        }
+        m = mn;
+    }
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int c = lane + 32 * i;
+        if (c < HD) s_o[warp][c] = acc[i];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float M = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+        float L = 0.f;
+        float f[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            f[w] = (s_m[w] == -INFINITY) ? 0.f : expf(s_m[w] - M);
+            L += s_l[w] * f[w];
+        }
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int c = lane + 32 * i;
+            if (c < HD) {
+                const float o = (s_o[0][c] * f[0] + s_o[1][c] * f[1]) + (s_o[2][c] * f[2] + s_o[3][c] * f[3]);
+                out[head * HD + c] = L > 0.f ? o / L : 0.f;
+            }
+        }
+    }
+}
+
+// Arg-max of the logits into tokens[*pos + 1] (when pick != 0: the greedy choice of the next token, lowest index among
+// equals), then the position moves on by one.  One block.
+__global__ void __launch_bounds__(1024) decode_advance_kernel(const float* __restrict__ logits, int n, int32_t* __restrict__ tokens,
+                                                              int32_t* __restrict__ pos, int pick) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int p = *pos;
+    if (pick) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = logits[i];
+            if (bi == 0x7fffffff || v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            bv = sv[threadIdx.x]; bi = si[threadIdx.x];
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            }
+            if (threadIdx.x == 0) tokens[p + 1] = bi == 0x7fffffff ? 0 : bi;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *pos = p + 1;
+}
+
+int k_decode_embed(b200_ctx* ctx, const int32_t* tokens, const int32_t* pos, const float* emb, int d, float* x) {
+    decode_embed_kernel<<<(d + 255) / 256, 256, 0, ctx->stream>>>(tokens, pos, emb, d, x);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int k_decode_rope_scatter(b200_ctx* ctx, float* qkv, const int32_t* pos, const float* table, int d, int headDim, float* Kc, float* Vc) {
+    decode_rope_scatter_kernel<<<(d / 2 + 255) / 256, 256, 0, ctx->stream>>>(qkv, pos, reinterpret_cast<const float2*>(table), d, headDim, Kc, Vc);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int k_decode_attn(b200_ctx* ctx, const float* q, const float* Kc, const float* Vc, const int32_t* pos, int numHeads, int headDim, float scale, float* out) {
+    const int d = numHeads * headDim;
+    if (headDim <= 32) decode_attn_kernel<32><<<numHeads, 128, 0, ctx->stream>>>(q, Kc, Vc, pos, d, headDim, scale, out);
+    else if (headDim <= 64) decode_attn_kernel<64><<<numHeads, 128, 0, ctx->stream>>>(q, Kc, Vc, pos, d, headDim, scale, out);
+    else if (headDim <= 128) decode_attn_kernel<128><<<numHeads, 128, 0, ctx->stream>>>(q, Kc, Vc, pos, d, headDim, scale, out);
+    else return fail(ctx, B200_ERR_UNSUPPORTED, "attention head dimension %d exceeds 128", headDim);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int k_decode_advance(b200_ctx* ctx, const float* logits, int n, int32_t* tokens, int32_t* pos, int pick) {
+    decode_advance_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, tokens, pos, pick);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+}  // namespace b200

@@ -1146,37 +1146,41 @@ struct b200_lm_gen {
     char* block = nullptr;
     float *K = nullptr, *V = nullptr;  // [layers][maxLen][d]
     float *x = nullptr, *qkv = nullptr, *attnO = nullptr, *proj = nullptr, *n1 = nullptr, *z1 = nullptr, *a1 = nullptr, *lnIn = nullptr, *stat = nullptr,
-          *logits = nullptr, *rowStat = nullptr;
-    int32_t *tokens = nullptr, *posArr = nullptr;  // device: token ids by position, posArr[i] = i
-    AttnSeg* segs = nullptr;                       // segs[p] = one query row against cached rows 0..p
+          *logits = nullptr;
+    int32_t* tokens = nullptr;  // device: token ids by position
+    int32_t* d_pos = nullptr;   // device: position of the token the next forward processes (always equal to len)
     const float* rope = nullptr;
+    // The launch sequence of one token has no host-dependent argument (the position is read from d_pos), so it is
+    // captured once into a CUDA graph: the first token runs eagerly (first-use set-up), the second is captured.
+    int forwards = 0;
+    bool graph_failed = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
 };
 
 namespace {
 
-// One token through the model.  The id is read from gen->tokens[pos] on the device; logits land in gen->logits.
-int gen_forward_token(b200_lm_gen* g, int pos) {
+// One token through the model: the token at position *d_pos (id read from gen->tokens on the device); its rotated key
+// and its value go into row *d_pos of every layer's cache; logits land in gen->logits.
+int gen_forward(b200_lm_gen* g) {
     b200_lm* lm = g->lm;
     b200_ctx* ctx = lm->ctx;
     const b200_lm_config& c = lm->cfg;
     const int d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim;
     const float* P = lm->P;
-    B200_TRY(k_embed(ctx, g->tokens + pos, 1, P + lm->lay.in0, d, g->x));
+    B200_TRY(k_decode_embed(ctx, g->tokens, g->d_pos, P + lm->lay.in0, d, g->x));
     for (int l = 0; l < c.num_layers; l++) {
         const LayerOff& L = lm->lay.layer[(size_t)l];
         float* Kc = g->K + (size_t)l * g->maxLen * d;
         float* Vc = g->V + (size_t)l * g->maxLen * d;
-        const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
-        float* outs[3] = {g->qkv, Kc + (size_t)pos * d, Vc + (size_t)pos * d};  // K and V go straight into their cache rows
-        for (int i = 0; i < 3; i++) B200_TRY(linear_fwd(ctx, g->x, 1, d, P + Ws[i], P + Bs[i], d, outs[i], d));
-        B200_TRY(k_rope(ctx, g->qkv, 0, 1, 1, d, 0, H, hd, g->rope, g->posArr + pos, 0, 0));
-        B200_TRY(k_rope(ctx, Kc + (size_t)pos * d, 0, 1, 1, d, 0, H, hd, g->rope, g->posArr + pos, 0, 0));
-        Attn a;
-        a.Q = g->qkv; a.K = Kc; a.V = Vc; a.ldq = a.ldk = a.ldv = d;
-        a.numHeads = H; a.headDim = hd; a.scale = 1.0f / sqrtf((float)hd); a.causal = 0;
-        a.segs_dev = g->segs + pos; a.nSeg = 1; a.maxQLen = 1; a.maxKLen = pos + 1; a.totalQ = 1; a.totalK = pos + 1;
-        a.O = g->attnO; a.ldo = d; a.rowMax = g->rowStat; a.rowSum = g->rowStat + H;
-        B200_TRY(attn_forward(ctx, a));
+        if (qkv_fused(lm, L)) {
+            B200_TRY(linear_fwd(ctx, g->x, 1, d, P + L.WQ, P + L.bQ, 3 * d, g->qkv, 3 * d));
+        } else {
+            const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
+            for (int i = 0; i < 3; i++) B200_TRY(linear_fwd(ctx, g->x, 1, d, P + Ws[i], P + Bs[i], d, g->qkv + i * d, d));
+        }
+        B200_TRY(k_decode_rope_scatter(ctx, g->qkv, g->d_pos, g->rope, d, hd, Kc, Vc));
+        B200_TRY(k_decode_attn(ctx, g->qkv, Kc, Vc, g->d_pos, H, hd, 1.0f / sqrtf((float)hd), g->attnO));
         B200_TRY(linear_fwd(ctx, g->attnO, 1, d, P + L.WO, P + L.bO, d, g->proj, d));
         B200_TRY(k_ln_forward(ctx, g->x, g->proj, P + L.g1, P + L.b1n, 1, d, 1e-5f, g->n1, g->stat, g->stat + 1, nullptr, g->lnIn));
         {
@@ -1189,6 +1193,43 @@ int gen_forward_token(b200_lm_gen* g, int pos) {
         B200_TRY(k_ln_forward(ctx, g->n1, g->proj, P + L.g2, P + L.b2n, 1, d, 1e-5f, g->x, g->stat, g->stat + 1, nullptr, g->lnIn));
     }
     return linear_fwd(ctx, g->x, 1, d, P + lm->lay.Wout, P + lm->lay.bout, O, g->logits, O);
+}
+
+// The same through the captured graph once it exists.  Anything that prevents the capture (a legacy default stream, a
+// driver that refuses) leaves the session on plain launches of the very same kernels.
+int gen_run(b200_lm_gen* g) {
+    b200_ctx* ctx = g->lm->ctx;
+    g->forwards++;
+    if (g->graph_exec) {
+        B200_CUDA(ctx, cudaGraphLaunch(g->graph_exec, ctx->stream));
+        ctx->launches++;
+        return B200_OK;
+    }
+    if (g->forwards < 2 || g->graph_failed || ctx->stream == nullptr) return gen_forward(g);
+    const int profile = ctx->profile;
+    ctx->profile = 0;  // no event pairs inside a capture
+    int rc = B200_OK;
+    if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        (void)cudaGetLastError();
+        g->graph_failed = true;
+        ctx->profile = profile;
+        return gen_forward(g);
+    }
+    rc = gen_forward(g);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    ctx->profile = profile;
+    if (rc != B200_OK || e != cudaSuccess || !graph || cudaGraphInstantiate(&g->graph_exec, graph, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (graph) cudaGraphDestroy(graph);
+        g->graph_exec = nullptr;
+        g->graph_failed = true;
+        return rc != B200_OK ? rc : gen_forward(g);  // nothing ran during the capture: do the work now
+    }
+    g->graph = graph;
+    B200_CUDA(ctx, cudaGraphLaunch(g->graph_exec, ctx->stream));
+    ctx->launches++;
+    return B200_OK;
 }
 
 }  // namespace
@@ -1206,9 +1247,9 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t d = (size_t)c.embedding_dim, f = (size_t)c.ffn_dim, O = (size_t)c.output_dim, Lc = (size_t)c.num_layers, T = (size_t)max_len;
     auto rnd = [](size_t n) { return (n + 63) & ~(size_t)63; };
-    const size_t floats = 2 * rnd(Lc * T * d) + 6 * rnd(d) + 2 * rnd(f) + rnd(O) + rnd(64) + rnd(4 * (size_t)c.num_heads);
-    const size_t ints = 2 * rnd(T + 1);
-    const size_t bytes = floats * 4 + ints * 4 + rnd(T * sizeof(AttnSeg) / 4 + 1) * 4;
+    const size_t floats = 2 * rnd(Lc * T * d) + 5 * rnd(d) + rnd(3 * d) + 2 * rnd(f) + rnd(O) + rnd(64);
+    const size_t ints = rnd(T + 1) + rnd(1);
+    const size_t bytes = floats * 4 + ints * 4;
     b200_lm_gen* g = new b200_lm_gen();
     g->lm = lm; g->maxLen = max_len;
     if (cudaMalloc(&g->block, bytes) != cudaSuccess) {
@@ -1218,18 +1259,12 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
     char* cur = g->block;
     auto takef = [&](size_t n) { float* r = reinterpret_cast<float*>(cur); cur += rnd(n) * 4; return r; };
     g->K = takef(Lc * T * d); g->V = takef(Lc * T * d);
-    g->x = takef(d); g->qkv = takef(d); g->attnO = takef(d); g->proj = takef(d); g->n1 = takef(d); g->lnIn = takef(d);
-    g->z1 = takef(f); g->a1 = takef(f); g->logits = takef(O); g->stat = takef(64); g->rowStat = takef(4 * (size_t)c.num_heads);
+    g->x = takef(d); g->qkv = takef(3 * d); g->attnO = takef(d); g->proj = takef(d); g->n1 = takef(d); g->lnIn = takef(d);
+    g->z1 = takef(f); g->a1 = takef(f); g->logits = takef(O); g->stat = takef(64);
     g->tokens = reinterpret_cast<int32_t*>(cur); cur += rnd(T + 1) * 4;
-    g->posArr = reinterpret_cast<int32_t*>(cur); cur += rnd(T + 1) * 4;
-    g->segs = reinterpret_cast<AttnSeg*>(cur);
-    std::vector<int32_t> pos(T);
-    std::vector<AttnSeg> segs(T);
-    for (size_t i = 0; i < T; i++) { pos[i] = (int32_t)i; segs[i] = AttnSeg{0, 1, 0, (int)i + 1}; }
+    g->d_pos = reinterpret_cast<int32_t*>(cur); cur += rnd(1) * 4;
     int rc = B200_OK;
-    if (cudaMemcpyAsync(g->posArr, pos.data(), T * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
-        cudaMemcpyAsync(g->segs, segs.data(), T * sizeof(AttnSeg), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
-        cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+    if (cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream) != cudaSuccess || cudaStreamSynchronize(ctx->stream) != cudaSuccess)
         rc = lm_fail(lm, B200_ERR_CUDA, "could not initialise the generation session");
     if (rc == B200_OK) rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_len, &g->rope);
     if (rc != B200_OK) { cudaFree(g->block); delete g; return rc; }
@@ -1242,6 +1277,8 @@ int32_t b200_lm_gen_destroy(b200_lm_gen* g) {
     if (!g) return B200_OK;
     cudaSetDevice(g->lm->ctx->device);
     cudaStreamSynchronize(g->lm->ctx->stream);
+    if (g->graph_exec) cudaGraphExecDestroy(g->graph_exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
     cudaFree(g->block);
     b200_lm* lm = g->lm;
     delete g;
@@ -1250,6 +1287,10 @@ int32_t b200_lm_gen_destroy(b200_lm_gen* g) {
 
 int32_t b200_lm_gen_reset(b200_lm_gen* g) {
     if (!g) return B200_ERR_INVALID_ARG;
+    b200_ctx* ctx = g->lm->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200_CUDA(ctx, cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream));
     g->len = 0;
     return B200_OK;
 }
@@ -1270,7 +1311,8 @@ int32_t b200_lm_gen_step(b200_lm_gen* g, int32_t token_id, float* logits) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     B200_CUDA(ctx, cudaMemcpyAsync(g->tokens + g->len, &token_id, 4, cudaMemcpyHostToDevice, ctx->stream));
-    B200_TRY(gen_forward_token(g, g->len));
+    B200_TRY(gen_run(g));
+    B200_TRY(k_decode_advance(ctx, g->logits, lm->cfg.output_dim, g->tokens, g->d_pos, 0));
     g->len++;
     if (logits) B200_CUDA(ctx, cudaMemcpyAsync(logits, g->logits, sizeof(float) * (size_t)lm->cfg.output_dim, cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -1289,15 +1331,21 @@ int32_t b200_lm_gen_greedy(b200_lm_gen* g, const int32_t* prompt, int32_t n_prom
     std::lock_guard<std::mutex> lock(ctx->mu);
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     g->len = 0;
+    B200_CUDA(ctx, cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream));
     B200_CUDA(ctx, cudaMemcpyAsync(g->tokens, prompt, 4 * (size_t)n_prompt, cudaMemcpyHostToDevice, ctx->stream));
     int total = n_prompt;
-    for (int pos = 0; pos < n_prompt; pos++) B200_TRY(gen_forward_token(g, pos));  // LanguageModel.cs:517-520: the prompt token by token
+    const int V = lm->cfg.output_dim;
+    for (int pos = 0; pos < n_prompt; pos++) {  // LanguageModel.cs:517-520: the prompt token by token
+        B200_TRY(gen_run(g));
+        // after the last prompt token the first new token is chosen (it lands in tokens[n_prompt]); every advance moves d_pos on
+        B200_TRY(k_decode_advance(ctx, g->logits, V, g->tokens, g->d_pos, (pos == n_prompt - 1 && max_new > 0 && total < g->maxLen) ? 1 : 0));
+    }
     g->len = n_prompt;
     for (int gen = 0; gen < max_new && total < g->maxLen; gen++) {  // LanguageModel.cs:522-535 with arg-max in place of sampling
-        B200_TRY(k_argmax(ctx, g->logits, lm->cfg.output_dim, g->tokens + total));
-        total++;
+        total++;  // the token chosen by the previous advance
         if (total < g->maxLen && gen + 1 < max_new) {
-            B200_TRY(gen_forward_token(g, total - 1));
+            B200_TRY(gen_run(g));
+            B200_TRY(k_decode_advance(ctx, g->logits, V, g->tokens, g->d_pos, 1));
             g->len = total;
         }
     }

@@ -30,7 +30,8 @@ struct StepArgs {
     float gscale, lr, clip_thr;
     int use_clip, do_step, optimizer;
     int write_g;  // 1: leave the scaled-and-clipped gradient in g (the reference's observable state); 0: the caller applies the factor later, on demand
-    float beta1, beta2, eps, bc1, bc2;
+    float beta1, beta2, eps;
+    float alpha, rsbc2;  // Adam with the bias corrections folded in: w -= alpha * m / (sqrt(v) * rsbc2 + eps), alpha = lr / (1 - beta1^t), rsbc2 = 1 / sqrt(1 - beta2^t)
     float* partials;
     float* out;
 };
@@ -44,7 +45,7 @@ __device__ __forceinline__ void step_one(const StepArgs& a, int64_t i, float fac
         float v = a.beta2 * a.v[i] + (1.0f - a.beta2) * g * g;
         a.m[i] = m;
         a.v[i] = v;
-        a.w[i] -= a.lr * (m / a.bc1) / (sqrtf(v / a.bc2) + a.eps);
+        a.w[i] -= a.alpha * m / (sqrtf(v) * a.rsbc2 + a.eps);
     } else {
         a.w[i] -= a.lr * g;
     }
@@ -97,10 +98,10 @@ __device__ __forceinline__ void step_update(const StepArgs& a, float t, int64_t 
                 m.x = a.beta1 * m.x + ob1 * g.x; m.y = a.beta1 * m.y + ob1 * g.y; m.z = a.beta1 * m.z + ob1 * g.z; m.w = a.beta1 * m.w + ob1 * g.w;
                 v.x = a.beta2 * v.x + ob2 * g.x * g.x; v.y = a.beta2 * v.y + ob2 * g.y * g.y;
                 v.z = a.beta2 * v.z + ob2 * g.z * g.z; v.w = a.beta2 * v.w + ob2 * g.w * g.w;
-                w.x -= a.lr * (m.x / a.bc1) / (sqrtf(v.x / a.bc2) + a.eps);
-                w.y -= a.lr * (m.y / a.bc1) / (sqrtf(v.y / a.bc2) + a.eps);
-                w.z -= a.lr * (m.z / a.bc1) / (sqrtf(v.z / a.bc2) + a.eps);
-                w.w -= a.lr * (m.w / a.bc1) / (sqrtf(v.w / a.bc2) + a.eps);
+                w.x -= a.alpha * m.x / (sqrtf(v.x) * a.rsbc2 + a.eps);
+                w.y -= a.alpha * m.y / (sqrtf(v.y) * a.rsbc2 + a.eps);
+                w.z -= a.alpha * m.z / (sqrtf(v.z) * a.rsbc2 + a.eps);
+                w.w -= a.alpha * m.w / (sqrtf(v.w) * a.rsbc2 + a.eps);
                 m4[k] = m; v4[k] = v; w4[k] = w;
             }
         }
@@ -184,8 +185,8 @@ int k_fused_step(b200_ctx* ctx, float* w, float* g, float* m, float* v, int64_t 
     StepArgs a;
     a.w = w; a.g = g; a.m = m; a.v = v; a.n = n; a.gscale = gscale; a.lr = lr; a.clip_thr = clip_thr; a.use_clip = use_clip;
     a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.write_g = write_g;
-    a.bc1 = 1.0f - powf(beta1, (float)step_index);
-    a.bc2 = 1.0f - powf(beta2, (float)step_index);
+    a.alpha = (float)((double)lr / (1.0 - pow((double)beta1, (double)step_index)));
+    a.rsbc2 = (float)(1.0 / sqrt(1.0 - pow((double)beta2, (double)step_index)));
     a.partials = ctx->ws;
     a.out = out_dev;
     void* args[] = {&a};
@@ -213,15 +214,15 @@ int k_fused_step_presummed(b200_ctx* ctx, float* w, float* g, float* m, float* v
     if (n <= 0) return B200_OK;
     if (((uintptr_t)w | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) & 15)
         return fail(ctx, B200_ERR_INVALID_ARG, "parameter arenas must be 16-byte aligned");
-    int grid = ctx->sm_count * 4;
+    int grid = ctx->sm_count * 5;  // 48 registers x 256 threads: five blocks per SM are resident
     int64_t need = (n / 4 + 255) / 256;
     if (need < 1) need = 1;
     if (grid > need) grid = (int)need;
     StepArgs a;
     a.w = w; a.g = g; a.m = m; a.v = v; a.n = n; a.gscale = gscale; a.lr = lr; a.clip_thr = clip_thr; a.use_clip = use_clip;
     a.do_step = do_step; a.optimizer = optimizer; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.write_g = write_g;
-    a.bc1 = 1.0f - powf(beta1, (float)step_index);
-    a.bc2 = 1.0f - powf(beta2, (float)step_index);
+    a.alpha = (float)((double)lr / (1.0 - pow((double)beta1, (double)step_index)));
+    a.rsbc2 = (float)(1.0 / sqrt(1.0 - pow((double)beta2, (double)step_index)));
     a.partials = nullptr;
     a.out = out_dev;
     fused_step_presummed_kernel<<<grid, 256, 0, ctx->stream>>>(a, partials, n_partials);
