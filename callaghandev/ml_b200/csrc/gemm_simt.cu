@@ -113,42 +113,73 @@ int gemm_simt(b200_ctx* ctx, const Gemm& g) {
 }
 
 // ------------------------------------------------------------------------------------------------ few-row products
-// C[m,n] = A[m,:] . B[n,:] for M <= 4 rows (incremental decoding: one token at a time): one warp per output column
-// streams its weight row once with 128-bit loads -- the product is bound by reading B, which the tiled kernels above
-// would do at 1/64 efficiency for a single row.  Same fused epilogue.
+// C[m,n] = A[m,:] . B[n,:] for M <= 4 rows (incremental decoding: one token at a time).  The product is bound by
+// reading B once, which the tiled kernels above would do at 1/64 efficiency for a single row; what bounds a single
+// launch, though, is latency: a weight row is a chain of dependent loop iterations for its warp, and a layer has only
+// 1024..4096 rows.  So `wpc` warps share one output column (each a contiguous slice of K, summed in slice order through
+// shared memory: deterministic), every lane keeps four independent 128-bit loads in flight, and the grid is sized so
+// that a few thousand warps are resident whatever N is.  Same fused epilogue.
 template <int MR>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(int M, int N, int K, const float* __restrict__ A, int lda, const float* __restrict__ B,
-                                                        int ldb, int vec, Epilogue ep) {
-    const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (n >= N) return;
-    const float* w = B + (size_t)n * ldb;
+                                                        int ldb, int vec, int wpc, Epilogue ep) {
+    __shared__ float part[8][MR];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (8 / wpc) + warp / wpc, seg = warp % wpc;
     float acc[MR];
 #pragma unroll
     for (int m = 0; m < MR; m++) acc[m] = 0.f;
-    if (vec) {
-        for (int k = lane * 4; k < K; k += 128) {
-            const float4 wv = *reinterpret_cast<const float4*>(w + k);
+    if (n < N) {
+        const float* w = B + (size_t)n * ldb;
+        int chunk = (K + wpc - 1) / wpc;
+        chunk = (chunk + 127) & ~127;  // whole 128-element strides per warp slice
+        const int k0 = seg * chunk, k1 = min(K, k0 + chunk);
+        if (vec) {
+            int k = k0 + lane * 4;
+            for (; k + 384 < k1; k += 512) {
+                float4 wv[4];
 #pragma unroll
-            for (int m = 0; m < MR; m++)
-                if (m < M) {
-                    const float4 xv = *reinterpret_cast<const float4*>(A + (size_t)m * lda + k);
-                    acc[m] += (wv.x * xv.x + wv.y * xv.y) + (wv.z * xv.z + wv.w * xv.w);
-                }
-        }
-    } else {
-        for (int k = lane; k < K; k += 32) {
-            const float wv = w[k];
+                for (int u = 0; u < 4; u++) wv[u] = *reinterpret_cast<const float4*>(w + k + 128 * u);
 #pragma unroll
-            for (int m = 0; m < MR; m++)
-                if (m < M) acc[m] += wv * A[(size_t)m * lda + k];
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (m < M) {
+                            const float4 xv = *reinterpret_cast<const float4*>(A + (size_t)m * lda + k + 128 * u);
+                            acc[m] += (wv[u].x * xv.x + wv[u].y * xv.y) + (wv[u].z * xv.z + wv[u].w * xv.w);
+                        }
+            }
+            for (; k < k1; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+                    if (m < M) {
+                        const float4 xv = *reinterpret_cast<const float4*>(A + (size_t)m * lda + k);
+                        acc[m] += (wv.x * xv.x + wv.y * xv.y) + (wv.z * xv.z + wv.w * xv.w);
+                    }
+            }
+        } else {
+            for (int k = k0 + lane; k < k1; k += 32) {
+                const float wv = w[k];
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+                    if (m < M) acc[m] += wv * A[(size_t)m * lda + k];
+            }
         }
     }
-    float alpha = ep.alpha;
-    if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
 #pragma unroll
     for (int m = 0; m < MR; m++) {
         const float v = warp_sum(acc[m]);
-        if (lane == 0 && m < M) epilogue_store(ep, m, n, v, alpha);
+        if (lane == 0) part[warp][m] = v;
+    }
+    __syncthreads();
+    if (n < N && seg == 0 && lane == 0) {
+        float alpha = ep.alpha;
+        if (ep.alpha_dev) alpha *= ep.alpha_dev[0];
+        for (int m = 0; m < MR && m < M; m++) {
+            float v = part[warp][m];
+            for (int s2 = 1; s2 < wpc; s2++) v += part[warp + s2][m];
+            epilogue_store(ep, m, n, v, alpha);
+        }
     }
 }
 
@@ -158,8 +189,11 @@ static int gemv_rows(b200_ctx* ctx, const Gemm& g) {
     ctx->engine_launches[B200_ENGINE_GEMM_SIMT]++;
     Epilogue e = make_epilogue(g);
     const int vec = (g.K % 4 == 0) && (g.lda % 4 == 0) && (g.ldb % 4 == 0) && (((uintptr_t)g.A | (uintptr_t)g.B) & 15) == 0;
-    const int blocks = (g.N + 7) / 8;
-    gemv_rows_kernel<4><<<blocks, 256, 0, ctx->stream>>>(g.M, g.N, g.K, g.A, g.lda, g.B, g.ldb, vec, e);
+    int wpc = 1;  // warps per output column: aim at ~8192 warps in the grid, never less than 256 elements of K per warp
+    while (wpc < 8 && (int64_t)g.N * wpc < 8192 && g.K / (2 * wpc) >= 256) wpc *= 2;
+    const int cols_per_block = 8 / wpc;
+    const int blocks = (g.N + cols_per_block - 1) / cols_per_block;
+    gemv_rows_kernel<4><<<blocks, 256, 0, ctx->stream>>>(g.M, g.N, g.K, g.A, g.lda, g.B, g.ldb, vec, wpc, e);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }
