@@ -163,6 +163,10 @@ int k_decode_embed(b200_ctx*, const int32_t* tokens, const int32_t* pos, const f
 int k_decode_rope_scatter(b200_ctx*, float* qkv, const int32_t* pos, const float* table, int d, int headDim, float* Kc, float* Vc);
 int k_decode_attn(b200_ctx*, const float* q, const float* Kc, const float* Vc, const int32_t* pos, int numHeads, int headDim, float scale, float* out);
 int k_decode_advance(b200_ctx*, const float* logits, int n, int32_t* tokens, int32_t* pos, int pick);
+// y = act(W v + bias) for one token; with sub != NULL v = LayerNorm(x + sub) * gamma + beta, also stored to v_out.  K a
+// multiple of 4 and at most 12288, all pointers 16-byte aligned, W rows K floats apart.
+int k_decode_gemv(b200_ctx*, const float* x, const float* sub, const float* gamma, const float* beta, float eps, float* v_out, const float* W,
+                  const float* bias, int N, int K, int act, float* y);
 // Deterministic scatter-add: rows of (dXa [+ dXb]) sorted by id on the host.  seg_id[s] = vocabulary row, rows of
 // segment s are perm[seg_off[s] .. seg_off[s+1]) in ascending original order.
 int k_embed_scatter(b200_ctx*, float* eg, const float* dXa, const float* dXb, const int32_t* seg_id, const int32_t* seg_off,

@@ -131,6 +131,102 @@ __global__ void __launch_bounds__(1024) decode_advance_kernel(const float* __res
     if (threadIdx.x == 0) *pos = p + 1;
 }
 
+// y[n] = act(W[n,:] . v + bias[n]) for one token, v of length K.  With LN the input is v = LayerNorm(x + sub) * gamma + beta
+// (ResidualLayerNormForward for one row, AccelerationCPU.cs:1440-1514: biased variance, eps inside the root), computed
+// by every block into shared memory -- 8 KB of reads that hit L2 -- so that the normalisation costs no launch of its own;
+// block 0 stores v to v_out, where the next residual addition finds it.  Without LN v = x.  As in the few-row product
+// of the trainer, `wpc` warps share an output column and every lane keeps four 128-bit weight loads in flight.
+template <bool LN>
+__global__ void __launch_bounds__(256) decode_gemv_kernel(const float* __restrict__ x, const float* __restrict__ sub, const float* __restrict__ gamma,
+                                                          const float* __restrict__ beta, float eps, float* __restrict__ v_out,
+                                                          const float* __restrict__ W, const float* __restrict__ bias, int N, int K, int wpc, int act,
+                                                          float* __restrict__ y) {
+    extern __shared__ float sv[];  // the input vector
+    __shared__ float red[32];
+    __shared__ float part[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, K4 = K >> 2;
+    float4* sv4 = reinterpret_cast<float4*>(sv);
+    if (LN) {
+        float s = 0.f;
+        for (int i = tid; i < K4; i += 256) {
+            float4 a = reinterpret_cast<const float4*>(x)[i];
+            const float4 b = reinterpret_cast<const float4*>(sub)[i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            sv4[i] = a;
+            s += (a.x + a.y) + (a.z + a.w);
+        }
+        const float mu = block_sum(s, red) / (float)K;
+        float q = 0.f;
+        for (int i = tid; i < K4; i += 256) {
+            const float4 a = sv4[i];
+            const float d0 = a.x - mu, d1 = a.y - mu, d2 = a.z - mu, d3 = a.w - mu;
+            q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+        }
+        const float inv = 1.0f / sqrtf(block_sum(q, red) / (float)K + eps);
+        for (int i = tid; i < K4; i += 256) {
+            const float4 a = sv4[i], g = reinterpret_cast<const float4*>(gamma)[i], b = reinterpret_cast<const float4*>(beta)[i];
+            float4 o;
+            o.x = g.x * ((a.x - mu) * inv) + b.x; o.y = g.y * ((a.y - mu) * inv) + b.y;
+            o.z = g.z * ((a.z - mu) * inv) + b.z; o.w = g.w * ((a.w - mu) * inv) + b.w;
+            sv4[i] = o;
+            if (blockIdx.x == 0 && v_out) reinterpret_cast<float4*>(v_out)[i] = o;
+        }
+    } else {
+        for (int i = tid; i < K4; i += 256) sv4[i] = reinterpret_cast<const float4*>(x)[i];
+    }
+    __syncthreads();
+    const int n = blockIdx.x * (8 / wpc) + warp / wpc, seg = warp % wpc;
+    float acc = 0.f;
+    if (n < N) {
+        const float* w = W + (size_t)n * K;
+        int chunk = (K + wpc - 1) / wpc;
+        chunk = (chunk + 127) & ~127;
+        const int k0 = seg * chunk, k1 = min(K, k0 + chunk);
+        int k = k0 + lane * 4;
+        for (; k + 384 < k1; k += 512) {
+            float4 wv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) wv[u] = *reinterpret_cast<const float4*>(w + k + 128 * u);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float4 xv = *reinterpret_cast<const float4*>(sv + k + 128 * u);
+                acc += (wv[u].x * xv.x + wv[u].y * xv.y) + (wv[u].z * xv.z + wv[u].w * xv.w);
+            }
+        }
+        for (; k < k1; k += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + k);
+            const float4 xv = *reinterpret_cast<const float4*>(sv + k);
+            acc += (wv.x * xv.x + wv.y * xv.y) + (wv.z * xv.z + wv.w * xv.w);
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (n < N && seg == 0 && lane == 0) {
+        float v = part[warp];
+        for (int s2 = 1; s2 < wpc; s2++) v += part[warp + s2];
+        v += bias[n];
+        if (act != B200_ACT_NONE) {
+            float a, dd;
+            ffn_act_der(v, act, a, dd);
+            v = a;
+        }
+        y[n] = v;
+    }
+}
+
+int k_decode_gemv(b200_ctx* ctx, const float* x, const float* sub, const float* gamma, const float* beta, float eps, float* v_out, const float* W,
+                  const float* bias, int N, int K, int act, float* y) {
+    int wpc = 1;  // warps per output column: a few thousand warps in the grid, never less than 256 elements of K per warp
+    while (wpc < 8 && (int64_t)N * wpc < 8192 && K / (2 * wpc) >= 256) wpc *= 2;
+    const int cols = 8 / wpc, blocks = (N + cols - 1) / cols;
+    const size_t smem = sizeof(float) * (size_t)K;
+    if (sub) decode_gemv_kernel<true><<<blocks, 256, smem, ctx->stream>>>(x, sub, gamma, beta, eps, v_out, W, bias, N, K, wpc, act, y);
+    else decode_gemv_kernel<false><<<blocks, 256, smem, ctx->stream>>>(x, nullptr, nullptr, nullptr, eps, nullptr, W, bias, N, K, wpc, act, y);
+    B200_LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 int k_decode_embed(b200_ctx* ctx, const int32_t* tokens, const int32_t* pos, const float* emb, int d, float* x) {
     decode_embed_kernel<<<(d + 255) / 256, 256, 0, ctx->stream>>>(tokens, pos, emb, d, x);
     B200_LAUNCH_CHECK(ctx);

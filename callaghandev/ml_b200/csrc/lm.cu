@@ -1145,8 +1145,8 @@ struct b200_lm_gen {
     int maxLen = 0, len = 0;
     char* block = nullptr;
     float *K = nullptr, *V = nullptr;  // [layers][maxLen][d]
-    float *x = nullptr, *qkv = nullptr, *attnO = nullptr, *proj = nullptr, *n1 = nullptr, *z1 = nullptr, *a1 = nullptr, *lnIn = nullptr, *stat = nullptr,
-          *logits = nullptr;
+    float *x = nullptr, *xn = nullptr, *qkv = nullptr, *attnO = nullptr, *proj = nullptr, *proj2 = nullptr, *n1 = nullptr, *z1 = nullptr, *a1 = nullptr,
+          *lnIn = nullptr, *stat = nullptr, *logits = nullptr;
     int32_t* tokens = nullptr;  // device: token ids by position
     int32_t* d_pos = nullptr;   // device: position of the token the next forward processes (always equal to len)
     const float* rope = nullptr;
@@ -1160,9 +1160,9 @@ struct b200_lm_gen {
 
 namespace {
 
-// One token through the model: the token at position *d_pos (id read from gen->tokens on the device); its rotated key
-// and its value go into row *d_pos of every layer's cache; logits land in gen->logits.
-int gen_forward(b200_lm_gen* g) {
+// The same sequence with the general-purpose kernels (one launch per LayerNorm and per product): arenas whose tensors
+// are not 16-byte aligned, or widths that are not multiples of 4.
+int gen_forward_plain(b200_lm_gen* g) {
     b200_lm* lm = g->lm;
     b200_ctx* ctx = lm->ctx;
     const b200_lm_config& c = lm->cfg;
@@ -1193,6 +1193,44 @@ int gen_forward(b200_lm_gen* g) {
         B200_TRY(k_ln_forward(ctx, g->n1, g->proj, P + L.g2, P + L.b2n, 1, d, 1e-5f, g->x, g->stat, g->stat + 1, nullptr, g->lnIn));
     }
     return linear_fwd(ctx, g->x, 1, d, P + lm->lay.Wout, P + lm->lay.bout, O, g->logits, O);
+}
+
+// One token through the model: the token at position *d_pos (id read from gen->tokens on the device); its rotated key
+// and its value go into row *d_pos of every layer's cache; logits land in gen->logits.  Six launches per layer: the two
+// LayerNorms ride in the prologue of the product that consumes them (k_decode_gemv).
+int gen_forward(b200_lm_gen* g) {
+    b200_lm* lm = g->lm;
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    const int d = c.embedding_dim, H = c.num_heads, hd = d / H, f = c.ffn_dim, O = c.output_dim, Lc = c.num_layers;
+    const float* P = lm->P;
+    const bool fast = d % 4 == 0 && f % 4 == 0 && c.align_floats % 4 == 0 && d <= 12288 && f <= 12288 && (((uintptr_t)P) & 15) == 0;
+    if (!fast) return gen_forward_plain(g);
+    B200_TRY(k_decode_embed(ctx, g->tokens, g->d_pos, P + lm->lay.in0, d, g->x));
+    // input of the next product that follows a LayerNorm: LN(res + sub) with these parameters; none before the first layer
+    const float *res = nullptr, *sub = nullptr, *gam = nullptr, *bet = nullptr;
+    for (int l = 0; l < Lc; l++) {
+        const LayerOff& L = lm->lay.layer[(size_t)l];
+        float* Kc = g->K + (size_t)l * g->maxLen * d;
+        float* Vc = g->V + (size_t)l * g->maxLen * d;
+        // x_l = embedding (first layer) or LN2 of the previous block, formed inside the Q/K/V product and stored to g->x
+        if (qkv_fused(lm, L)) {
+            B200_TRY(k_decode_gemv(ctx, sub ? res : g->x, sub, gam, bet, 1e-5f, g->x, P + L.WQ, P + L.bQ, 3 * d, d, B200_ACT_NONE, g->qkv));
+        } else {
+            const int64_t Ws[3] = {L.WQ, L.WK, L.WV}, Bs[3] = {L.bQ, L.bK, L.bV};
+            for (int i = 0; i < 3; i++)  // the first product stores x_l; the other two recompute it from the same inputs (g->n1, g->proj are still intact)
+                B200_TRY(k_decode_gemv(ctx, sub ? res : g->x, sub, gam, bet, 1e-5f, i == 0 ? g->xn : nullptr, P + Ws[i], P + Bs[i], d, d, B200_ACT_NONE, g->qkv + i * d));
+            if (sub) B200_CUDA(ctx, cudaMemcpyAsync(g->x, g->xn, sizeof(float) * (size_t)d, cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        B200_TRY(k_decode_rope_scatter(ctx, g->qkv, g->d_pos, g->rope, d, hd, Kc, Vc));
+        B200_TRY(k_decode_attn(ctx, g->qkv, Kc, Vc, g->d_pos, H, hd, 1.0f / sqrtf((float)hd), g->attnO));
+        B200_TRY(k_decode_gemv(ctx, g->attnO, nullptr, nullptr, nullptr, 0.f, nullptr, P + L.WO, P + L.bO, d, d, B200_ACT_NONE, g->proj));
+        // n1 = LN1(x_l + attention projection), formed inside the first FFN product and stored to g->n1
+        B200_TRY(k_decode_gemv(ctx, g->x, g->proj, P + L.g1, P + L.b1n, 1e-5f, g->n1, P + L.W1, P + L.fb1, f, d, c.ffn_activation, g->a1));
+        B200_TRY(k_decode_gemv(ctx, g->a1, nullptr, nullptr, nullptr, 0.f, nullptr, P + L.W2, P + L.fb2, d, f, B200_ACT_NONE, g->proj2));
+        res = g->n1; sub = g->proj2; gam = P + L.g2; bet = P + L.b2n;  // LN2(n1 + FFN output) is formed by whoever consumes it
+    }
+    return k_decode_gemv(ctx, sub ? res : g->x, sub, gam, bet, 1e-5f, nullptr, P + lm->lay.Wout, P + lm->lay.bout, O, d, B200_ACT_NONE, g->logits);
 }
 
 // The same through the captured graph once it exists.  Anything that prevents the capture (a legacy default stream, a
@@ -1247,7 +1285,7 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t d = (size_t)c.embedding_dim, f = (size_t)c.ffn_dim, O = (size_t)c.output_dim, Lc = (size_t)c.num_layers, T = (size_t)max_len;
     auto rnd = [](size_t n) { return (n + 63) & ~(size_t)63; };
-    const size_t floats = 2 * rnd(Lc * T * d) + 5 * rnd(d) + rnd(3 * d) + 2 * rnd(f) + rnd(O) + rnd(64);
+    const size_t floats = 2 * rnd(Lc * T * d) + 7 * rnd(d) + rnd(3 * d) + 2 * rnd(f) + rnd(O) + rnd(64);
     const size_t ints = rnd(T + 1) + rnd(1);
     const size_t bytes = floats * 4 + ints * 4;
     b200_lm_gen* g = new b200_lm_gen();
@@ -1259,7 +1297,7 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
     char* cur = g->block;
     auto takef = [&](size_t n) { float* r = reinterpret_cast<float*>(cur); cur += rnd(n) * 4; return r; };
     g->K = takef(Lc * T * d); g->V = takef(Lc * T * d);
-    g->x = takef(d); g->qkv = takef(3 * d); g->attnO = takef(d); g->proj = takef(d); g->n1 = takef(d); g->lnIn = takef(d);
+    g->x = takef(d); g->xn = takef(d); g->qkv = takef(3 * d); g->attnO = takef(d); g->proj = takef(d); g->proj2 = takef(d); g->n1 = takef(d); g->lnIn = takef(d);
     g->z1 = takef(f); g->a1 = takef(f); g->logits = takef(O); g->stat = takef(64);
     g->tokens = reinterpret_cast<int32_t*>(cur); cur += rnd(T + 1) * 4;
     g->d_pos = reinterpret_cast<int32_t*>(cur); cur += rnd(1) * 4;
@@ -1292,6 +1330,18 @@ int32_t b200_lm_gen_reset(b200_lm_gen* g) {
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     B200_CUDA(ctx, cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream));
     g->len = 0;
+    return B200_OK;
+}
+
+// Number of kernel launches replayed per token from the captured graph (0: the session issues plain launches, either
+// because fewer than two tokens have been processed or because the capture was refused).
+int32_t b200_lm_gen_graph_nodes(b200_lm_gen* g, int32_t* nodes) {
+    if (!g || !nodes) return B200_ERR_INVALID_ARG;
+    *nodes = 0;
+    if (g->graph) {
+        size_t n = 0;
+        if (cudaGraphGetNodes(g->graph, nullptr, &n) == cudaSuccess) *nodes = (int32_t)n;
+    }
     return B200_OK;
 }
 

@@ -266,6 +266,12 @@ class B200Generator:
         self.mgr._ck(self.lib.b200_lm_gen_length(self.h, C.byref(n)))
         return n.value
 
+    def graph_nodes(self):
+        """Kernel launches replayed per token from the captured CUDA graph (0 while the session still issues plain launches)."""
+        n = C.c_int32(0)
+        self.mgr._ck(self.lib.b200_lm_gen_graph_nodes(self.h, C.byref(n)))
+        return n.value
+
     def step(self, token_id):
         out = np.zeros(self.out_dim, np.float32)
         self.mgr._ck(self.lib.b200_lm_gen_step(self.h, int(token_id), _pf(out)))

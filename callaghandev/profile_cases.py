@@ -157,7 +157,8 @@ def generate(m, rng):
     t0 = time.perf_counter()
     out = g.greedy(prompt, 240)
     dt = time.perf_counter() - t0
-    print("decode: %d tokens in %.3f s = %.1f tokens/s (prompt included, one token per model pass)" % (len(out), dt, len(out) / dt))
+    print("decode: %d tokens in %.3f s = %.1f tokens/s (prompt included, one token per model pass, %d graph nodes per token)"
+          % (len(out), dt, len(out) / dt, g.graph_nodes()))
     g.close(); t.close()
     return float(out[-1])
 

@@ -386,6 +386,9 @@ B200_API int32_t b200_lm_gen_create(b200_lm*, int32_t max_len, b200_lm_gen** out
 B200_API int32_t b200_lm_gen_destroy(b200_lm_gen*);
 B200_API int32_t b200_lm_gen_reset(b200_lm_gen*);
 B200_API int32_t b200_lm_gen_length(b200_lm_gen*, int32_t* length);
+/* The launch sequence of one token takes its position from device memory, so it is captured into a CUDA graph when the
+ * session processes its second token and replayed afterwards; *nodes = kernel launches per replay (0 = plain launches). */
+B200_API int32_t b200_lm_gen_graph_nodes(b200_lm_gen*, int32_t* nodes);
 B200_API int32_t b200_lm_gen_step(b200_lm_gen*, int32_t token_id, float* logits);
 B200_API int32_t b200_lm_gen_greedy(b200_lm_gen*, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_tokens, int32_t* n_out);
 /* Device time of the phases of the last step in milliseconds: [0] forward, [1] loss, [2] backward, [3] step. */

@@ -490,6 +490,7 @@ def test_incremental_decoding_with_device_kv_cache(mgr, oracle):
     for i, tok in enumerate(prompt):
         assert_close(want[i], g.step(int(tok)), 1e-5, f"logits after token {i}")
     assert len(g) == len(prompt)
+    assert g.graph_nodes() > 0, "from the second token on the launch sequence is replayed from a CUDA graph"
     # greedy continuation: device arg-max loop vs the oracle driven token by token
     seq = list(prompt)
     for _ in range(6):
