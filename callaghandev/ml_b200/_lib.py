@@ -142,6 +142,8 @@ PROTOTYPES = {
     "b200_lm_gen_reset": (_i32, [_vp]),
     "b200_lm_gen_length": (_i32, [_vp, _i]),
     "b200_lm_gen_graph_nodes": (_i32, [_vp, _i]),
+    "b200_lm_gen_single_kernel": (_i32, [_vp]),
+    "b200_lm_gen_set_single_kernel": (_i32, [_vp, _i32]),
     "b200_lm_gen_step": (_i32, [_vp, _i32, _f]),
     "b200_lm_gen_greedy": (_i32, [_vp, _i, _i32, _i32, _i, _i]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),

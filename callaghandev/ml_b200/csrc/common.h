@@ -163,6 +163,20 @@ int k_decode_embed(b200_ctx*, const int32_t* tokens, const int32_t* pos, const f
 int k_decode_rope_scatter(b200_ctx*, float* qkv, const int32_t* pos, const float* table, int d, int headDim, float* Kc, float* Vc);
 int k_decode_attn(b200_ctx*, const float* q, const float* Kc, const float* Vc, const int32_t* pos, int numHeads, int headDim, float scale, float* out);
 int k_decode_advance(b200_ctx*, const float* logits, int n, int32_t* tokens, int32_t* pos, int pick);
+// One token through the whole model as one cooperative kernel (decode.cu).
+struct DecodeLayer {
+    const float *Wqkv, *bqkv, *WO, *bO, *g1, *b1n, *W1, *fb1, *W2, *fb2, *g2, *b2n;
+    float *Kc, *Vc;  // this layer's key / value cache, [maxLen][d]
+};
+struct DecodeArgs {
+    const DecodeLayer* layers;  // device array
+    int L, d, f, H, hd, V, act, pick;
+    float scale;
+    const float *emb, *Wout, *bout, *rope;
+    int32_t *tokens, *pos;
+    float *x, *qkv, *attnO, *proj, *proj2, *n1, *a1, *logits;
+};
+int k_decode_token(b200_ctx*, const DecodeArgs& args, int* blocks_cache);
 // y = act(W v + bias) for one token; with sub != NULL v = LayerNorm(x + sub) * gamma + beta, also stored to v_out.  K a
 // multiple of 4 and at most 12288, all pointers 16-byte aligned, W rows K floats apart.
 int k_decode_gemv(b200_ctx*, const float* x, const float* sub, const float* gamma, const float* beta, float eps, float* v_out, const float* W,

@@ -1156,6 +1156,11 @@ struct b200_lm_gen {
     bool graph_failed = false;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
+    // Preferred path: the whole token as one cooperative kernel (k_decode_token); the graph of separate launches above
+    // serves arenas it cannot take (unaligned tensors, Q/K/V weights not back to back) or devices without cooperative launch.
+    DecodeLayer* dec_layers = nullptr;  // device array, one entry per block
+    int coop_blocks = 0;                // 0 not tried yet, -1 unavailable, else the grid size
+    int use_single_kernel = 1;
 };
 
 namespace {
@@ -1233,6 +1238,26 @@ int gen_forward(b200_lm_gen* g) {
     return k_decode_gemv(ctx, sub ? res : g->x, sub, gam, bet, 1e-5f, nullptr, P + lm->lay.Wout, P + lm->lay.bout, O, d, B200_ACT_NONE, g->logits);
 }
 
+// One token, position advanced, next token picked when asked: a single cooperative launch when possible.
+int gen_run(b200_lm_gen* g);
+int gen_token(b200_lm_gen* g, int pick) {
+    b200_lm* lm = g->lm;
+    b200_ctx* ctx = lm->ctx;
+    const b200_lm_config& c = lm->cfg;
+    if (g->dec_layers && g->use_single_kernel && g->coop_blocks >= 0) {
+        DecodeArgs a;
+        a.layers = g->dec_layers; a.L = c.num_layers; a.d = c.embedding_dim; a.f = c.ffn_dim; a.H = c.num_heads; a.hd = c.embedding_dim / c.num_heads;
+        a.V = c.output_dim; a.act = c.ffn_activation; a.pick = pick; a.scale = 1.0f / sqrtf((float)a.hd);
+        a.emb = lm->P + lm->lay.in0; a.Wout = lm->P + lm->lay.Wout; a.bout = lm->P + lm->lay.bout; a.rope = g->rope;
+        a.tokens = g->tokens; a.pos = g->d_pos;
+        a.x = g->x; a.qkv = g->qkv; a.attnO = g->attnO; a.proj = g->proj; a.proj2 = g->proj2; a.n1 = g->n1; a.a1 = g->a1; a.logits = g->logits;
+        const int rc = k_decode_token(ctx, a, &g->coop_blocks);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+    }
+    B200_TRY(gen_run(g));
+    return k_decode_advance(ctx, g->logits, c.output_dim, g->tokens, g->d_pos, pick);
+}
+
 // The same through the captured graph once it exists.  Anything that prevents the capture (a legacy default stream, a
 // driver that refuses) leaves the session on plain launches of the very same kernels.
 int gen_run(b200_lm_gen* g) {
@@ -1305,6 +1330,25 @@ int32_t b200_lm_gen_create(b200_lm* lm, int32_t max_len, b200_lm_gen** out) {
     if (cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream) != cudaSuccess || cudaStreamSynchronize(ctx->stream) != cudaSuccess)
         rc = lm_fail(lm, B200_ERR_CUDA, "could not initialise the generation session");
     if (rc == B200_OK) rc = rope_table(ctx, c.embedding_dim / c.num_heads, 10000.0f, max_len, &g->rope);
+    if (rc == B200_OK) {
+        bool ok = c.num_layers > 0 && d % 4 == 0 && f % 4 == 0 && c.align_floats % 4 == 0 && d <= 12288 && f <= 12288 && (((uintptr_t)lm->P) & 15) == 0;
+        for (int l = 0; l < c.num_layers && ok; l++) ok = qkv_fused(lm, lm->lay.layer[(size_t)l]);
+        if (ok) {
+            std::vector<DecodeLayer> host((size_t)c.num_layers);
+            const float* P = lm->P;
+            for (int l = 0; l < c.num_layers; l++) {
+                const LayerOff& L = lm->lay.layer[(size_t)l];
+                host[(size_t)l] = DecodeLayer{P + L.WQ, P + L.bQ, P + L.WO, P + L.bO, P + L.g1, P + L.b1n, P + L.W1, P + L.fb1, P + L.W2, P + L.fb2,
+                                              P + L.g2, P + L.b2n, g->K + (size_t)l * T * d, g->V + (size_t)l * T * d};
+            }
+            if (cudaMalloc((void**)&g->dec_layers, sizeof(DecodeLayer) * host.size()) != cudaSuccess ||
+                cudaMemcpy(g->dec_layers, host.data(), sizeof(DecodeLayer) * host.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+                (void)cudaGetLastError();
+                if (g->dec_layers) cudaFree(g->dec_layers);
+                g->dec_layers = nullptr;  // the separate-launch path needs no table
+            }
+        }
+    }
     if (rc != B200_OK) { cudaFree(g->block); delete g; return rc; }
     lm->refs.fetch_add(1);
     *out = g;
@@ -1317,6 +1361,7 @@ int32_t b200_lm_gen_destroy(b200_lm_gen* g) {
     cudaStreamSynchronize(g->lm->ctx->stream);
     if (g->graph_exec) cudaGraphExecDestroy(g->graph_exec);
     if (g->graph) cudaGraphDestroy(g->graph);
+    if (g->dec_layers) cudaFree(g->dec_layers);
     cudaFree(g->block);
     b200_lm* lm = g->lm;
     delete g;
@@ -1345,6 +1390,15 @@ int32_t b200_lm_gen_graph_nodes(b200_lm_gen* g, int32_t* nodes) {
     return B200_OK;
 }
 
+// 1 when the session runs each token as one cooperative kernel, 0 when it issues the phases as separate launches (through
+// the captured graph from the second token on).  b200_lm_gen_set_single_kernel(g, 0) selects the latter on purpose.
+int32_t b200_lm_gen_single_kernel(b200_lm_gen* g) { return (g && g->dec_layers && g->use_single_kernel && g->coop_blocks >= 0) ? 1 : 0; }
+int32_t b200_lm_gen_set_single_kernel(b200_lm_gen* g, int32_t on) {
+    if (!g) return B200_ERR_INVALID_ARG;
+    g->use_single_kernel = on ? 1 : 0;
+    return B200_OK;
+}
+
 int32_t b200_lm_gen_length(b200_lm_gen* g, int32_t* len) {
     if (!g || !len) return B200_ERR_INVALID_ARG;
     *len = g->len;
@@ -1361,8 +1415,7 @@ int32_t b200_lm_gen_step(b200_lm_gen* g, int32_t token_id, float* logits) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     B200_CUDA(ctx, cudaMemcpyAsync(g->tokens + g->len, &token_id, 4, cudaMemcpyHostToDevice, ctx->stream));
-    B200_TRY(gen_run(g));
-    B200_TRY(k_decode_advance(ctx, g->logits, lm->cfg.output_dim, g->tokens, g->d_pos, 0));
+    B200_TRY(gen_token(g, 0));
     g->len++;
     if (logits) B200_CUDA(ctx, cudaMemcpyAsync(logits, g->logits, sizeof(float) * (size_t)lm->cfg.output_dim, cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -1384,18 +1437,15 @@ int32_t b200_lm_gen_greedy(b200_lm_gen* g, const int32_t* prompt, int32_t n_prom
     B200_CUDA(ctx, cudaMemsetAsync(g->d_pos, 0, sizeof(int32_t), ctx->stream));
     B200_CUDA(ctx, cudaMemcpyAsync(g->tokens, prompt, 4 * (size_t)n_prompt, cudaMemcpyHostToDevice, ctx->stream));
     int total = n_prompt;
-    const int V = lm->cfg.output_dim;
     for (int pos = 0; pos < n_prompt; pos++) {  // LanguageModel.cs:517-520: the prompt token by token
-        B200_TRY(gen_run(g));
-        // after the last prompt token the first new token is chosen (it lands in tokens[n_prompt]); every advance moves d_pos on
-        B200_TRY(k_decode_advance(ctx, g->logits, V, g->tokens, g->d_pos, (pos == n_prompt - 1 && max_new > 0 && total < g->maxLen) ? 1 : 0));
+        // after the last prompt token the first new token is chosen (it lands in tokens[n_prompt]); every token moves d_pos on
+        B200_TRY(gen_token(g, (pos == n_prompt - 1 && max_new > 0 && total < g->maxLen) ? 1 : 0));
     }
     g->len = n_prompt;
     for (int gen = 0; gen < max_new && total < g->maxLen; gen++) {  // LanguageModel.cs:522-535 with arg-max in place of sampling
         total++;  // the token chosen by the previous advance
         if (total < g->maxLen && gen + 1 < max_new) {
-            B200_TRY(gen_run(g));
-            B200_TRY(k_decode_advance(ctx, g->logits, V, g->tokens, g->d_pos, 1));
+            B200_TRY(gen_token(g, 1));
             g->len = total;
         }
     }

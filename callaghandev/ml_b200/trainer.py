@@ -266,6 +266,14 @@ class B200Generator:
         self.mgr._ck(self.lib.b200_lm_gen_length(self.h, C.byref(n)))
         return n.value
 
+    def single_kernel(self) -> bool:
+        """True when each token runs as one cooperative kernel (the preferred path)."""
+        return bool(self.lib.b200_lm_gen_single_kernel(self.h))
+
+    def set_single_kernel(self, on: bool):
+        """False selects the separate-launch path (CUDA graph from the second token on) on purpose."""
+        self.mgr._ck(self.lib.b200_lm_gen_set_single_kernel(self.h, int(bool(on))))
+
     def graph_nodes(self):
         """Kernel launches replayed per token from the captured CUDA graph (0 while the session still issues plain launches)."""
         n = C.c_int32(0)

@@ -151,15 +151,18 @@ def generate(m, rng):
     n = t.param_count
     w = (rng.standard_normal(n, dtype=np.float32) * 0.02)
     t.upload_params(w)
-    g = t.generator(256)
     prompt = rng.integers(4, 32000, 16).astype(np.int32)
-    g.greedy(prompt, 8)  # warm-up (module load, first-launch effects)
-    t0 = time.perf_counter()
-    out = g.greedy(prompt, 240)
-    dt = time.perf_counter() - t0
-    print("decode: %d tokens in %.3f s = %.1f tokens/s (prompt included, one token per model pass, %d graph nodes per token)"
-          % (len(out), dt, len(out) / dt, g.graph_nodes()))
-    g.close(); t.close()
+    for single in (True, False):
+        g = t.generator(256)
+        g.set_single_kernel(single)
+        g.greedy(prompt, 8)  # warm-up (module load, first-launch effects, graph capture)
+        t0 = time.perf_counter()
+        out = g.greedy(prompt, 240)
+        dt = time.perf_counter() - t0
+        how = "one cooperative kernel per token" if g.single_kernel() else "CUDA graph of %d launches per token" % g.graph_nodes()
+        print("decode: %d tokens in %.3f s = %.1f tokens/s (prompt included, one token per model pass, %s)" % (len(out), dt, len(out) / dt, how))
+        g.close()
+    t.close()
     return float(out[-1])
 
 

@@ -386,8 +386,14 @@ B200_API int32_t b200_lm_gen_create(b200_lm*, int32_t max_len, b200_lm_gen** out
 B200_API int32_t b200_lm_gen_destroy(b200_lm_gen*);
 B200_API int32_t b200_lm_gen_reset(b200_lm_gen*);
 B200_API int32_t b200_lm_gen_length(b200_lm_gen*, int32_t* length);
-/* The launch sequence of one token takes its position from device memory, so it is captured into a CUDA graph when the
- * session processes its second token and replayed afterwards; *nodes = kernel launches per replay (0 = plain launches). */
+/* How a token is executed.  Every decoding kernel takes the token's position from device memory, so nothing in the
+ * launch sequence depends on the host.  Preferred: ONE cooperative kernel per token, its phases separated by grid barriers
+ * (b200_lm_gen_single_kernel returns 1).  Otherwise -- tensors of the arena not 16-byte aligned, Q/K/V weights not back to
+ * back, no cooperative launch, or b200_lm_gen_set_single_kernel(g, 0) -- the phases are separate launches (six per block),
+ * captured into a CUDA graph when the session processes its second token and replayed afterwards; *nodes = launches per
+ * replay (0 = plain launches so far). */
+B200_API int32_t b200_lm_gen_single_kernel(b200_lm_gen*);
+B200_API int32_t b200_lm_gen_set_single_kernel(b200_lm_gen*, int32_t on);
 B200_API int32_t b200_lm_gen_graph_nodes(b200_lm_gen*, int32_t* nodes);
 B200_API int32_t b200_lm_gen_step(b200_lm_gen*, int32_t token_id, float* logits);
 B200_API int32_t b200_lm_gen_greedy(b200_lm_gen*, const int32_t* prompt, int32_t n_prompt, int32_t max_new, int32_t* out_tokens, int32_t* n_out);

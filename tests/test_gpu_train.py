@@ -473,7 +473,8 @@ def test_checkpoint_with_optimizer_state_resumes_bit_identically(mgr, oracle, tm
     b.close()
 
 
-def test_incremental_decoding_with_device_kv_cache(mgr, oracle):
+@pytest.mark.parametrize("single_kernel", [True, False])
+def test_incremental_decoding_with_device_kv_cache(mgr, oracle, single_kernel):
     """LanguageModel.Generate's decoder path: every token goes through the model at its absolute position against the
     cached keys/values; the next-token logits after each token match the restated reference loop, and an arg-max
     continuation picks the tokens the oracle's logits pick."""
@@ -487,10 +488,14 @@ def test_incremental_decoding_with_device_kv_cache(mgr, oracle):
     prompt = rng.integers(4, 120, 9).astype(np.int32)
     want = oracle.lm_decode_logits(cfg, P, prompt, max_len=32)
     g = t.generator(32)
+    g.set_single_kernel(single_kernel)
     for i, tok in enumerate(prompt):
         assert_close(want[i], g.step(int(tok)), 1e-5, f"logits after token {i}")
     assert len(g) == len(prompt)
-    assert g.graph_nodes() > 0, "from the second token on the launch sequence is replayed from a CUDA graph"
+    if single_kernel:
+        assert g.single_kernel(), "one cooperative kernel per token"
+    else:
+        assert not g.single_kernel() and g.graph_nodes() > 0, "from the second token on the launch sequence is replayed from a CUDA graph"
     # greedy continuation: device arg-max loop vs the oracle driven token by token
     seq = list(prompt)
     for _ in range(6):
