@@ -15,7 +15,9 @@
 //
 // Every mbarrier wait is bounded (see mbar_wait); on expiry the roles stop, the status word is raised, and the CTA
 // frees its TMEM and returns.
+#include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "device_math.cuh"
 #include "tcgen05.cuh"
@@ -89,17 +91,17 @@ __device__ __forceinline__ uint32_t rna_tf32_add(float x) { return __float_as_ui
 // transcendental pipe with ex2, which is the scarce resource of the element-wise step.
 __device__ __forceinline__ uint32_t rna_tf32(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
 
-// Copy one row of a K-contiguous swizzle atom (32 floats, already TF32) into TMEM columns [col, col+32) of the calling
-// thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand read from
-// shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
-__device__ __forceinline__ void row_to_tmem(const uint8_t* atom, int row, uint32_t taddr) {
-    uint32_t r[32];
+// Copy half a row of a K-contiguous swizzle atom (16 floats, already TF32; h = which half) into TMEM columns [col, col+16)
+// of the calling thread's lane, so the tile can serve as the A operand of tcgen05.mma from tensor memory: an A operand
+// read from shared memory costs 4 KiB of shared-memory bandwidth per K step, which is what bounds TF32 MMAs with a narrow N.
+__device__ __forceinline__ void half_row_to_tmem(const uint8_t* atom, int row, int h, uint32_t taddr) {
+    uint32_t r[16];
 #pragma unroll
-    for (int c = 0; c < 8; c++) {
-        const uint4 v = *reinterpret_cast<const uint4*>(atom + row * 128 + ((c ^ (row & 7)) << 4));
+    for (int c = 0; c < 4; c++) {
+        const uint4 v = *reinterpret_cast<const uint4*>(atom + row * 128 + (((4 * h + c) ^ (row & 7)) << 4));
         r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
     }
-    tmem_st32(taddr, r);
+    tmem_st16(taddr, r);
 }
 
 __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 8; i++) mbar_init(bar0 + 8 * i, i == 6 ? 128 : 1);
+        for (int i = 0; i < 8; i++) mbar_init(bar0 + 8 * i, i == 6 ? 4 : 1);  // p_full: one arrival per softmax warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // Q is requested right away: its latency overlaps the TMEM allocation and the first sync.
@@ -269,7 +271,8 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(p_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
         }
         if (ok) {
             ok = mbar_wait_warp(o_full, 0, status, 18);
@@ -314,15 +317,23 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
 }
 
 // ------------------------------------------------------------------------------------------------------ backward
-// Two deterministic passes, as in the other engines (dQ per query tile, dK/dV per key tile; no atomics).  The softmax
-// statistics are known, so the element-wise step has no row reduction and is split over eight warps (lane quarter x
-// column half).  The inner tiles are 64 wide and S/dP are double-buffered in TMEM.  Two threads issue MMAs: one
-// the S and dP products (running up to two tiles ahead), the other the products that consume P and dS -- a single
-// thread issues a narrow TF32 MMA only every ~50 cycles (more when its scheduler is busy with the element-wise
-// warps), which is slower than the tensor pipe executes them.  These kernels are bound by the L2 -> shared-memory traffic of the streamed tiles (FP32 storage, 64-wide
-// heads), so an operand that is needed both K-contiguous (for S / dP) and N-contiguous (for dQ, dK, dV) is loaded
-// once, K-contiguous, and four extra warps rewrite it into the N-contiguous swizzle image inside shared memory.
-constexpr int B_THREADS = 64 + 256 + 128 + 32;  // producer, first MMA issuer, 8 element-wise warps, 4 re-swizzle warps, second MMA issuer
+// Two deterministic passes, as in the other engines (dQ per query tile, dK/dV per key tile; no atomics), each a
+// persistent kernel: one CTA per SM walks a static list of (segment, head, tile) items (see ItemWalk).
+// The inner tiles are 64 wide and S/dP are double-buffered in TMEM.  Roles: one TMA producer thread; two threads that issue
+// MMAs -- one the S and dP products, the other the products that consume P and dS (a single thread issues a narrow TF32
+// MMA every ~55-65 cycles, the tensor pipe executes one in 32, so two issuers are what keeps it fed); sixteen
+// element-wise warps (the softmax statistics are known, so this step has no row reduction and is split lane quarter x
+// column quarter); four re-swizzle warps.  An operand that is needed both K-contiguous (for S / dP) and N-contiguous (for
+// dQ, dK, dV) is loaded once, K-contiguous, and the re-swizzle warps rewrite it into the N-contiguous image inside
+// shared memory (FP32 storage and 64-wide heads make the L2 -> shared-memory traffic of the streamed tiles the scarce
+// resource after the element-wise step).
+// What bounds them, from per-role wait counters of a development build (c5 shapes, 32 sequences of 1024): the element-wise
+// warps are busy ~80 % of the time -- ex2 throughput (16 per cycle per SM) and packed FP32 arithmetic, ~800 cycles per
+// 128 x 64 tile in the dQ pass -- and the first issuer needs ~1100 cycles per tile to issue its 16 MMAs; loads and the
+// tensor pipe (768-1024 cycles of work per tile) wait for them.
+constexpr int EW_THREADS = 512;                          // 16 element-wise warps: lane quarter (= warp % 4, the TMEM lanes a warp may touch) x column quarter
+constexpr int B_THREADS = 64 + EW_THREADS + 128 + 32;    // producer, first MMA issuer, element-wise warps, 4 re-swizzle warps, second MMA issuer
+constexpr int RESWIZZLE_T0 = 64 + EW_THREADS, ISSUER2_WARP = (64 + EW_THREADS + 128) / 32;
 constexpr int A128 = 128 * 128, T128 = 2 * A128;  // atom column / tile with 128 rows
 constexpr int A64 = 64 * 128, T64 = 2 * A64;      // atom column / tile with 64 rows
 // Streamed operands live in two rings per kernel, because their consumers differ: the K-contiguous images feed the
@@ -336,11 +347,17 @@ constexpr int BWD_TMEM_COLS = 512;
 
 __device__ __forceinline__ uint64_t kdesc(uint32_t tile, int kk, int atom) { return umma_desc(tile + (kk >> 2) * atom + (kk & 3) * 32, 16, 1024, 2); }
 __device__ __forceinline__ uint64_t ndesc(uint32_t tile, int kk, int atom) { return umma_desc(tile + kk * 1024, atom, 512, 1); }
-// Named barrier of the 256 element-wise threads, and the same barrier with an OR vote (true when any thread passes true).
-__device__ __forceinline__ void ew_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// One arrival per warp: 32 lanes arriving on the same mbarrier are 32 serialised shared-memory atomics, and with every
+// element-wise thread arriving the phase completes hundreds of cycles after the first of them.  Each lane has made its own
+// accesses complete (tcgen05.wait, proxy fence) before this call; __syncwarp orders them before lane 0's arrival.
+__device__ __forceinline__ void warp_arrive(uint32_t bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+// Named barrier of the element-wise threads with an OR vote (true when any thread passes true).
 __device__ __forceinline__ bool ew_barrier_or(bool pred) {
     uint32_t r;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.or.pred q, 1, 512, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                  : "=r"(r)
                  : "r"((uint32_t)pred)
                  : "memory");
@@ -371,63 +388,112 @@ struct UBwdArgs {
     const float* rope_table; const int32_t* rope_pos;  // inverse rotary rotation of dQ and dK on the way out (or null)
 };
 
-// Store a [128 x 64] result staged in shared memory (row stride OUT_STRIDE) with whole-row 128-bit accesses; 256 threads.
-__device__ __forceinline__ void store_rows(const float* stage, float* dst, int ld, int rowBase, int nRows, int colBase, int tid,
-                                           const float* rope_table = nullptr, const int32_t* rope_pos = nullptr) {
-    const int c4 = (tid & 15) * 4;
-#pragma unroll 2
-    for (int r = tid >> 4; r < 128; r += 16)
-        if (r < nRows) {
-            float4 v = *reinterpret_cast<const float4*>(stage + r * OUT_STRIDE + c4);
-            if (rope_table) {  // gradient of a rotation = rotation by the opposite angle
-                const int pos = rope_pos ? rope_pos[rowBase + r] : rowBase + r;
-                const float4 cs = *reinterpret_cast<const float4*>(rope_table + ((size_t)pos * (UHD / 2) + (c4 >> 1)) * 2);
-                const float x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
-                v.x = x0 * cs.x + x1 * cs.y; v.y = x1 * cs.x - x0 * cs.y;
-                v.z = x2 * cs.z + x3 * cs.w; v.w = x3 * cs.z - x2 * cs.w;
+// ---- work items of the persistent backward kernels.  A CTA stays on its SM and walks a static list of (segment, head,
+// tile) items, so an item's fixed cost (resident operands -> shared memory -> TMEM, pipeline fill, output) runs under
+// the tiles of its neighbours instead of standing alone: the loads of item n+1 are requested while item n streams,
+// its first S / dP products are issued while the element-wise warps still write item n's result.
+// Under a causal mask the work of tile t of n grows (dQ) or shrinks (dK/dV) linearly with t, so the list pairs tile p
+// with tile n-1-p of the same (segment, head): every pair costs the same, a plain round-robin over the pairs balances
+// the CTAs, and the CTAs that run at the same time work on the same few (segment, head) slices, which stay in L2.
+struct ItemWalk {
+    int u, second, nTiles, pairsPerGroup, nPairs, stride;
+    __device__ ItemWalk(int nTiles_, int nGroups)
+        : u(blockIdx.x), second(0), nTiles(nTiles_), pairsPerGroup((nTiles_ + 1) >> 1), nPairs(nGroups * ((nTiles_ + 1) >> 1)), stride(gridDim.x) {}
+    // next (group, tile); `longFirstHigh`: the high tile of a pair is the long one (dQ) and goes first
+    __device__ bool next(int& group, int& tile, bool longFirstHigh) {
+        while (u < nPairs) {
+            group = u / pairsPerGroup;
+            const int p = u - group * pairsPerGroup, hi = nTiles - 1 - p;
+            if (!second) {
+                second = 1;
+                tile = longFirstHigh ? hi : p;
+                return true;
             }
-            *reinterpret_cast<float4*>(dst + (size_t)(rowBase + r) * ld + colBase + c4) = v;
+            second = 0;
+            u += stride;
+            if (p != hi) {
+                tile = longFirstHigh ? p : hi;
+                return true;
+            }
         }
+        return false;
+    }
+};
+// A segment descriptor through the read-only path: every role of a CTA reads the same few entries for each of its items,
+// and after the first time they come from L1 instead of L2.
+__device__ __forceinline__ AttnSeg load_seg(const AttnSeg* p) {
+    const int4 v = __ldg(reinterpret_cast<const int4*>(p));
+    AttnSeg s;
+    s.qStart = v.x; s.qLen = v.y; s.kStart = v.z; s.kLen = v.w;
+    return s;
+}
+struct BwdItem { AttnSeg sg; int head, t0, n, aux; };  // t0: first row of the resident tile; n: streamed tiles; aux: first streamed tile
+
+// dQ items: 128 query rows against the 64-key tiles they can see.  Items without rows are skipped by every role alike;
+// rows without any key get zeros from the caller of this function when `zeroFillTid` >= 0 (the element-wise threads).
+__device__ __forceinline__ bool next_dq_item(ItemWalk& w, const UBwdArgs& a, BwdItem& it, int zeroFillTid) {
+    int group, tile;
+    while (w.next(group, tile, true)) {
+        const int seg = group / a.numHeads, head = group - seg * a.numHeads;
+        const AttnSeg sg = load_seg(a.segs + seg);
+        const int q0 = tile * 128;
+        if (q0 >= sg.qLen) continue;
+        const int kEnd = a.causal ? min(sg.kLen, q0 + 128) : sg.kLen;
+        const int nkt = (kEnd + 63) / 64;
+        if (nkt == 0) {
+            if (zeroFillTid >= 0)
+                for (int idx = zeroFillTid; idx < 128 * 16; idx += EW_THREADS) {
+                    const int r = idx >> 4, c = (idx & 15) * 4;
+                    if (q0 + r < sg.qLen) *reinterpret_cast<float4*>(a.dQ + (size_t)(sg.qStart + q0 + r) * a.lddq + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            continue;
+        }
+        it.sg = sg; it.head = head; it.t0 = q0; it.n = nkt;
+        return true;
+    }
+    return false;
+}
+
+// One thread's 16 consecutive result columns of one row, scaled, optionally rotated back (gradient of a rotary rotation =
+// rotation by the opposite angle; cs = the row's (cos, sin) pairs for these columns), written with 128-bit stores: the
+// thread covers half a 128-byte line.
+__device__ __forceinline__ void store_row_slice(const uint32_t (&r)[16], float scale, float* dst, const float4* cs) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+        float4 v = make_float4(__uint_as_float(r[i]) * scale, __uint_as_float(r[i + 1]) * scale, __uint_as_float(r[i + 2]) * scale,
+                               __uint_as_float(r[i + 3]) * scale);
+        if (cs) {
+            const float4 c = cs[i >> 2];
+            const float x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
+            v.x = x0 * c.x + x1 * c.y; v.y = x1 * c.x - x0 * c.y;
+            v.z = x2 * c.z + x3 * c.w; v.w = x3 * c.z - x2 * c.w;
+        }
+        *reinterpret_cast<float4*>(dst + i) = v;
+    }
 }
 
 __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
                                                                 const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
-                                                                UBwdArgs a) {
+                                                                UBwdArgs a, int nTiles, int nGroups) {
     extern __shared__ uint8_t smem_raw[];
-    const AttnSeg sg = a.segs[blockIdx.z];
-    const int head = blockIdx.y;
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * 128;
-    if (q0 >= sg.qLen) return;
-    const int kEnd = a.causal ? min(sg.kLen, q0 + 128) : sg.kLen;
-    const int nkt = (kEnd + 63) / 64;
-    if (nkt == 0) {
-        for (int idx = threadIdx.x; idx < 128 * 16; idx += B_THREADS) {
-            const int r = idx >> 4, c = (idx & 15) * 4;
-            if (q0 + r < sg.qLen) *reinterpret_cast<float4*>(a.dQ + (size_t)(sg.qStart + q0 + r) * a.lddq + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        return;
-    }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DQ_RING_N * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 23);
     const uint32_t Qs = smem_u32(tiles), dOs = Qs + T128;
     const uint32_t ringK = dOs + T128;                 // slot: K tile then V tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: K tile, N-contiguous
     const uint32_t bar0 = smem_u32(bars);
+    // per item: qdo_full, a_ready, dq_full, acc_free; per streamed tile (counted across items): the rest
     const uint32_t qdo_full = bar0, kk_full = bar0 + 8, kk_empty = bar0 + 32, kn_full = bar0 + 56, kn_empty = bar0 + 80, sdp_full = bar0 + 104,
-                   ds_full = bar0 + 120, dq_full = bar0 + 136, a_ready = bar0 + 144, buf_free = bar0 + 152;
+                   ds_full = bar0 + 120, dq_full = bar0 + 136, a_ready = bar0 + 144, buf_free = bar0 + 152, acc_free = bar0 + 168, ds_free = bar0 + 176;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 21; i++)  // a_ready: 256; kk_empty: MMA commit + 128 re-swizzle readers; kn_full: 128 re-swizzle writers; ds_full: 256
-            mbar_init(bar0 + 8 * i, (i == 15 || i == 16 || i == 18) ? 256 : (i >= 4 && i <= 6) ? 129 : (i >= 7 && i <= 9) ? 128 : 1);
+        for (int i = 0; i < 23; i++)  // ds_full (15; 16 unused), a_ready, buf_free, acc_free: one arrival per element-wise warp; kk_empty: MMA commit + 4 re-swizzle warps; kn_full: 4 re-swizzle warps
+            mbar_init(bar0 + 8 * i, (i == 15 || i == 16 || (i >= 18 && i <= 21)) ? EW_THREADS / 32 : (i >= 4 && i <= 6) ? 5 : (i >= 7 && i <= 9) ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
-        mbar_expect_tx(qdo_full, 2 * T128);
-        tma_load_3d(Qs, &mapQ, qdo_full, 0, sg.qStart + q0, head * (UHD / 32));
-        tma_load_3d(dOs, &mapdO, qdo_full, 0, sg.qStart + q0, head * (UHD / 32));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -437,157 +503,257 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tm = *tmem_slot;
-    constexpr uint32_t DQ_COL = 256, QA_COL = 320, DOA_COL = 384;  // Q and dO live in TMEM as A operands
+    // S / dP: two buffers of 128 columns from 0; Q and dO live in TMEM as A operands; dS has a buffer of its own, so an
+    // S / dP buffer is free again as soon as the element-wise warps have read it (not only after the dQ product that
+    // consumes dS), and the first issuer runs ahead of the rest of the pipeline instead of in lockstep with it
+    constexpr uint32_t DQ_COL = 256, QA_COL = 320, DOA_COL = 384, DS_COL = 448;
 
     if (warp == 0) {
         if (lane == 0) {
-            const int col = head * UHD;
+            // ---------------------------------------------------------------- TMA producer
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
             bool ok = true;
-            int nk = 0;
-            for (; nk < nkt; nk++) {
-                const int s = nk % RING_K, row = sg.kStart + nk * 64;
-                ok = mbar_wait(kk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 21);
-                if (!ok) break;
-                const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
-                mbar_expect_tx(bar, 2 * T64);
-                tma_load_3d(base, &mapK, bar, 0, row, col >> 5);
-                tma_load_3d(base + T64, &mapV, bar, 0, row, col >> 5);
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dq_item(w, a, it, -1)) {
+                if (n > 0) {  // the element-wise threads have copied the previous item's Q and dO out of shared memory
+                    ok = mbar_wait(a_ready, (n - 1) & 1, status, 20);
+                    if (!ok) break;
+                }
+                mbar_expect_tx(qdo_full, 2 * T128);
+                tma_load_3d(Qs, &mapQ, qdo_full, 0, it.sg.qStart + it.t0, it.head * (UHD / 32));
+                tma_load_3d(dOs, &mapdO, qdo_full, 0, it.sg.qStart + it.t0, it.head * (UHD / 32));
+                n++;
+                for (int j = 0; j < it.n; j++) {
+                    const int s = g % RING_K, row = it.sg.kStart + j * 64;
+                    ok = mbar_wait(kk_empty + 8 * s, ((g / RING_K) & 1) ^ 1, status, 21);
+                    if (!ok) break;
+                    const uint32_t base = ringK + s * 2 * T64, bar = kk_full + 8 * s;
+                    mbar_expect_tx(bar, 2 * T64);
+                    tma_load_3d(base, &mapK, bar, 0, row, it.head * (UHD / 32));
+                    tma_load_3d(base + T64, &mapV, bar, 0, row, it.head * (UHD / 32));
+                    g++;
+                }
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
-                while (!mbar_test(qdo_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int j = max(0, nk - RING_K); j < nk; j++)
+                while (n > 0 && !mbar_test(qdo_full, (n - 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (uint32_t j = g > RING_K ? g - RING_K : 0; j < g; j++)
                     while (!mbar_test(kk_full + 8 * (j % RING_K), (j / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // ---------------------------------------------------------------- first issuer: S(j) and dP(j) into TMEM buffer g&1
             const uint32_t idS = idesc_tf32(128, 64, 0, 0);
             const uint64_t dRK0 = kdesc(ringK, 0, A64);
-            // ---------------------------------------------------------------- first issuer: S(j) and dP(j) into TMEM buffer j&1
-            bool ok = mbar_wait(a_ready, 0, status, 22);
-            tc_fence_after();
-            for (int j = 0; j < nkt && ok; j++) {
-                const int s = j % RING_K, b = j & 1;
-                ok = mbar_wait(kk_full + 8 * s, (j / RING_K) & 1, status, 23);
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
+            bool ok = true;
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dq_item(w, a, it, -1)) {
+                ok = mbar_wait(a_ready, n & 1, status, 22);  // this item's Q and dO are in TMEM
                 if (!ok) break;
-                ok = mbar_wait(buf_free + 8 * b, ((j >> 1) & 1) ^ 1, status, 24);  // dQ(j-2) has consumed the buffer (free at first use)
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t dk = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dv = dk + (uint64_t)(T64 >> 4);
+                n++;
+                for (int j = 0; j < it.n; j++) {
+                    const int s = g % RING_K, b = g & 1;
+                    ok = mbar_wait(kk_full + 8 * s, (g / RING_K) & 1, status, 23);
+                    if (!ok) break;
+                    ok = mbar_wait(buf_free + 8 * b, ((g >> 1) & 1) ^ 1, status, 24);  // the element-wise warps have read the tile two back out of the buffer
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t dk = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dv = dk + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + QA_COL + kk * 8, dk + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + QA_COL + kk * 8, dk + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + DOA_COL + kk * 8, dv + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
-                umma_commit(kk_empty + 8 * s);
-                umma_commit(sdp_full + 8 * b);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + DOA_COL + kk * 8, dv + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                    umma_commit(kk_empty + 8 * s);
+                    umma_commit(sdp_full + 8 * b);
+                    g++;
+                }
             }
         }
-    } else if (warp == 14) {
+    } else if (warp == ISSUER2_WARP) {
         if (lane == 0) {
             // ---------------------------------------------------------------- second issuer: dQ += dS(j) K(j)
             const uint32_t idN = idesc_tf32(128, 64, 0, 1);
             const uint64_t dRN0 = ndesc(ringN, 0, A64);
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
             bool ok = true;
-            for (int j = 0; j < nkt && ok; j++) {
-                const int s = j % DQ_RING_N, b = j & 1;
-                ok = mbar_wait(kn_full + 8 * s, (j / DQ_RING_N) & 1, status, 25);
-                if (!ok) break;
-                ok = mbar_wait(ds_full + 8 * b, (j >> 1) & 1, status, 25);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t dn = dRN0 + (uint64_t)(s * (T64 >> 4));
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dq_item(w, a, it, -1)) {
+                for (int j = 0; j < it.n; j++) {
+                    const int s = g % DQ_RING_N;
+                    ok = mbar_wait(kn_full + 8 * s, (g / DQ_RING_N) & 1, status, 25);
+                    if (!ok) break;
+                    ok = mbar_wait(ds_full, g & 1, status, 25);
+                    if (!ok) break;
+                    if (j == 0 && n > 0) {  // the previous item's dQ has been read out of the accumulator
+                        ok = mbar_wait(acc_free, (n - 1) & 1, status, 28);
+                        if (!ok) break;
+                    }
+                    tc_fence_after();
+                    const uint64_t dn = dRN0 + (uint64_t)(s * (T64 >> 4));
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + b * 128 + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(kn_empty + 8 * s);
-                umma_commit(buf_free + 8 * b);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DQ_COL, tm + DS_COL + kk * 8, dn + noff(kk), idN, (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(kn_empty + 8 * s);
+                    umma_commit(ds_free);
+                    g++;
+                }
+                if (!ok) break;
+                umma_commit(dq_full);
+                n++;
             }
-            umma_commit(dq_full);
         }
-    } else if (warp < 10) {
-        const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half;
-        const int row = 32 * quarter + lane, qi = q0 + row;
+    } else if (warp < 2 + EW_THREADS / 32) {
+        // ------------------------------------------------------------------------------ element-wise warps and output
+        const int quarter = warp & 3, colq = (warp - 2) >> 2, c0 = 16 * colq;
+        const int row = 32 * quarter + lane;
         const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
         const float sl2 = a.scale * LOG2E_F;
+        const float2 sl22 = make_float2(sl2, sl2);
         // P = 2^(s*sl2 - m2l) with m2l = rowMax*log2(e) + log2(rowSum): the normalisation rides in the exponent.
         // Rows without any visible key (or outside the segment) get m2l = +inf, i.e. P = 0.
         float m2l = INFINITY, D = 0.f;
         bool live = false;
-        if (qi < sg.qLen) {
-            const size_t idx = (size_t)(sg.qStart + qi) * a.numHeads + head;
-            const float m = a.rowMax[idx], l = a.rowSum[idx];
-            if (l > 0.f && m != -INFINITY) { m2l = fmaf(m, LOG2E_F, log2f(l)); live = true; }
-            D = a.rowDot[idx];
-        }
-        const int lim = live ? (a.causal ? min(sg.kLen, qi + 1) : sg.kLen) : 0;  // keys [0, lim) are visible to this row
-        const float2 sl22 = make_float2(sl2, sl2), nm2 = make_float2(-m2l, -m2l), nD2 = make_float2(-D, -D);
-        bool ok = mbar_wait_warp(qdo_full, 0, status, 20);
-        if (__all_sync(0xffffffffu, ok)) {  // move this thread's half rows of Q and dO into TMEM
-            row_to_tmem(tiles + half * A128, row, tlane + QA_COL + c0);
-            row_to_tmem(tiles + T128 + half * A128, row, tlane + DOA_COL + c0);
+        // A row's statistics are requested one item ahead (raw values in registers) and turned into (m2l, D) at the boundary.
+        float rm = -INFINITY, rl = 0.f, rD = 0.f;
+        int rpos = 0, pos = 0;  // rotary position of this thread's row (next item / current item)
+        auto request_stats = [&](const BwdItem& it) {
+            rm = -INFINITY; rl = 0.f; rD = 0.f; rpos = 0;
+            const int qi = it.t0 + row;
+            if (qi < it.sg.qLen) {
+                const size_t idx = (size_t)(it.sg.qStart + qi) * a.numHeads + it.head;
+                rm = a.rowMax[idx]; rl = a.rowSum[idx]; rD = a.rowDot[idx];
+                if (a.rope_table) rpos = a.rope_pos ? a.rope_pos[it.sg.qStart + qi] : it.sg.qStart + qi;
+            }
+        };
+        auto take_stats = [&]() {
+            live = rl > 0.f && rm != -INFINITY;
+            m2l = live ? fmaf(rm, LOG2E_F, log2f(rl)) : INFINITY;
+            D = rD;
+            pos = rpos;
+        };
+        auto operands_to_tmem = [&](int n) -> bool {  // this thread's quarter rows of Q and dO: shared memory -> TMEM
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_warp(qdo_full, n & 1, status, 20));
+            if (!ok) return false;
+            half_row_to_tmem(tiles + (colq >> 1) * A128, row, colq & 1, tlane + QA_COL + c0);
+            half_row_to_tmem(tiles + T128 + (colq >> 1) * A128, row, colq & 1, tlane + DOA_COL + c0);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(a_ready);
+            warp_arrive(a_ready);
+            return true;
+        };
+        ItemWalk w(nTiles, nGroups);
+        BwdItem cur, nxt;
+        const int tid = threadIdx.x - 64;
+        bool have = next_dq_item(w, a, cur, tid);
+        bool ok = true;
+        int n = 0;
+        uint32_t g = 0;
+        if (have) {
+            request_stats(cur);
+            ok = operands_to_tmem(0);
         }
-        for (int j = 0; j < nkt; j++) {
-            const int s = j & 1;
-            ok = mbar_wait_warp(sdp_full + 8 * s, (j >> 1) & 1, status, 26);
-            ok = __all_sync(0xffffffffu, ok);
+        while (have && ok) {
+            take_stats();
+            const bool haveN = next_dq_item(w, a, nxt, tid);
+            if (haveN) request_stats(nxt);
+            const int qi = cur.t0 + row;
+            const int lim = live ? (a.causal ? min(cur.sg.kLen, qi + 1) : cur.sg.kLen) : 0;  // keys [0, lim) are visible to this row
+            const float2 nm2 = make_float2(-m2l, -m2l), nD2 = make_float2(-D, -D);
+            for (int j = 0; j < cur.n; j++, g++) {
+                const int s = g & 1;
+                ok = mbar_wait_warp(sdp_full + 8 * s, (g >> 1) & 1, status, 26);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const int nvis = lim - j * 64 - c0;  // columns [0, nvis) of this warp's 16 are visible
+                uint32_t sr[16], pr[16];
+                tmem_ld16_nowait(tlane + s * 128 + c0, sr);
+                tmem_ld16_nowait(tlane + s * 128 + 64 + c0, pr);
+                tmem_ld_wait();
+                tc_fence_before();
+                warp_arrive(buf_free + 8 * s);  // S and dP are in registers: the buffer may be refilled
+                // Two copies of the loop, chosen once per tile: a branch inside the unrolled body would fence the scheduling
+                // of everything around it, and only the tiles on the diagonal (or at a segment's end) need the masks.
+                auto tile_math = [&](auto masked) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        float2 v = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sl22, nm2);
+                        if (decltype(masked)::value) {
+                            if (i >= nvis) v.x = -INFINITY;
+                            if (i + 1 >= nvis) v.y = -INFINITY;
+                        }
+                        const float2 pp = make_float2(ex2(v.x), ex2(v.y));
+                        const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), nD2));
+                        sr[i] = rna_tf32_add(ds.x);
+                        sr[i + 1] = rna_tf32_add(ds.y);
+                    }
+                };
+                if (__all_sync(0xffffffffu, nvis >= 16)) tile_math(std::false_type());  // no masking anywhere in this warp's slice
+                else tile_math(std::true_type());
+                ok = __all_sync(0xffffffffu, mbar_wait_warp(ds_free, (g & 1) ^ 1, status, 31));  // the previous dQ product has read dS
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st16(tlane + DS_COL + c0, sr);
+                tmem_st_wait();
+                tc_fence_before();
+                warp_arrive(ds_full);
+            }
+            if (!ok) break;
+            // The S / dP products of this item are complete (its last sdp_full was seen), so the next item's Q and dO may
+            // replace it in TMEM right away: the first issuer starts on the next item while this one's result is written.
+            // this row's rotation factors (its position came with the statistics) are requested before the next item's operands
+            // are moved and the accumulator is waited for, which hides their latency
+            const bool rot = a.rope_table != nullptr && qi < cur.sg.qLen;
+            float4 cs[4];
+            if (rot) {
+                const float4* cs4 = reinterpret_cast<const float4*>(a.rope_table + ((size_t)pos * (UHD / 2) + (c0 >> 1)) * 2);
+#pragma unroll
+                for (int i = 0; i < 4; i++) cs[i] = cs4[i];
+            }
+            if (haveN) {
+                ok = operands_to_tmem(n + 1);
+                if (!ok) break;
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait_warp(dq_full, n & 1, status, 27));
             if (!ok) break;
             tc_fence_after();
-            const int nvis = lim - j * 64 - c0;  // columns [0, nvis) of this warp's 32 are visible
-            uint32_t sr[32], pr[32];
-            tmem_ld32_nowait(tlane + s * 128 + c0, sr);
-            tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
+            uint32_t r[16];
+            tmem_ld16_nowait(tlane + DQ_COL + c0, r);
             tmem_ld_wait();
-            const bool fullw = __all_sync(0xffffffffu, nvis >= 32);  // no masking anywhere in this warp's slice
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float2 v = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sl22, nm2);
-                if (!fullw) {
-                    if (i >= nvis) v.x = -INFINITY;
-                    if (i + 1 >= nvis) v.y = -INFINITY;
-                }
-                const float2 pp = make_float2(ex2(v.x), ex2(v.y));
-                const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), nD2));
-                sr[i] = rna_tf32_add(ds.x);
-                sr[i + 1] = rna_tf32_add(ds.y);
-            }
-            tmem_st32(tlane + s * 128 + c0, sr);
-            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(ds_full + 8 * s);
+            warp_arrive(acc_free);
+            // a lane writes its own row slice: the stores retire in the background while the next item's tiles are worked on
+            if (qi < cur.sg.qLen) store_row_slice(r, a.scale, a.dQ + (size_t)(cur.sg.qStart + qi) * a.lddq + cur.head * UHD + c0, rot ? cs : nullptr);
+            cur = nxt;
+            have = haveN;
+            n++;
         }
-        if (ok) {
-            ok = mbar_wait_warp(dq_full, 0, status, 27);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            tc_fence_after();
-            float* stage = reinterpret_cast<float*>(tiles);  // every MMA has completed: the operand tiles are free
-            uint32_t r[32];
-            tmem_ld32(tlane + DQ_COL + c0, r);
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(stage + row * OUT_STRIDE + c0 + i) =
-                    make_float4(__uint_as_float(r[i]) * a.scale, __uint_as_float(r[i + 1]) * a.scale, __uint_as_float(r[i + 2]) * a.scale,
-                                __uint_as_float(r[i + 3]) * a.scale);
-        }
-        ew_barrier();  // reached exactly once by every element-wise thread, whatever its status
-        if (ok) store_rows(reinterpret_cast<const float*>(tiles), a.dQ, a.lddq, sg.qStart + q0, min(128, sg.qLen - q0), head * UHD, threadIdx.x - 64, a.rope_table, a.rope_pos);
-    } else if (warp < 14) {
+    } else if (warp < ISSUER2_WARP) {
         // ------------------------------------------------------------------------------ re-swizzle warps: K -> N-contiguous image
-        const int t = threadIdx.x - 320;
+        const int t = threadIdx.x - RESWIZZLE_T0;
         uint8_t* ringK_p = tiles + 2 * T128;
         uint8_t* ringN_p = ringK_p + RING_K * 2 * T64;
-        for (int j = 0; j < nkt; j++) {
-            const int sk = j % RING_K, sn = j % DQ_RING_N;
-            if (!mbar_wait_warp(kk_full + 8 * sk, (j / RING_K) & 1, status, 29)) break;
-            if (!mbar_wait_warp(kn_empty + 8 * sn, ((j / DQ_RING_N) & 1) ^ 1, status, 30)) break;
-            reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * T64, t);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
-            mbar_arrive(kn_full + 8 * sn);
-            mbar_arrive(kk_empty + 8 * sk);
+        ItemWalk w(nTiles, nGroups);
+        BwdItem it;
+        bool ok = true;
+        uint32_t g = 0;
+        while (ok && next_dq_item(w, a, it, -1)) {
+            for (int j = 0; j < it.n; j++, g++) {
+                const int sk = g % RING_K, sn = g % DQ_RING_N;
+                ok = mbar_wait_warp(kk_full + 8 * sk, (g / RING_K) & 1, status, 29) && mbar_wait_warp(kn_empty + 8 * sn, ((g / DQ_RING_N) & 1) ^ 1, status, 30);
+                if (!ok) break;
+                reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * T64, t);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+                warp_arrive(kn_full + 8 * sn);
+                warp_arrive(kk_empty + 8 * sk);
+            }
         }
     }
     tc_fence_before();
@@ -598,51 +764,58 @@ __global__ void __launch_bounds__(B_THREADS) attn_dq_umma_kernel(const __grid_co
     }
 }
 
+// dK / dV items: 128 keys (one per TMEM lane) against the 64-row query tiles that can see them; aux = first such tile.
+__device__ __forceinline__ bool next_dkv_item(ItemWalk& w, const UBwdArgs& a, BwdItem& it, int zeroFillTid) {
+    int group, tile;
+    while (w.next(group, tile, false)) {
+        const int seg = group / a.numHeads, head = group - seg * a.numHeads;
+        const AttnSeg sg = load_seg(a.segs + seg);
+        const int k0 = tile * 128;  // under a causal mask the first key tiles see the most queries
+        if (k0 >= sg.kLen) continue;
+        const int qtBegin = a.causal ? k0 / 64 : 0, nqt = (sg.qLen + 63) / 64 - qtBegin;
+        if (nqt <= 0) {  // keys no query can see
+            if (zeroFillTid >= 0)
+                for (int idx = zeroFillTid; idx < 128 * 16; idx += EW_THREADS) {
+                    const int r = idx >> 4, c = (idx & 15) * 4;
+                    if (k0 + r < sg.kLen) {
+                        *reinterpret_cast<float4*>(a.dK + (size_t)(sg.kStart + k0 + r) * a.lddk + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        *reinterpret_cast<float4*>(a.dV + (size_t)(sg.kStart + k0 + r) * a.lddv + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            continue;
+        }
+        it.sg = sg; it.head = head; it.t0 = k0; it.n = nqt; it.aux = qtBegin;
+        return true;
+    }
+    return false;
+}
+
 // dK / dV for 128 keys (one key per TMEM lane) against the query tiles (64 rows each) that can see them:
 //   S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T (element-wise, per-column statistics from shared memory)
 //   dV += P^T dO,  dK += dS^T Q   (A from TMEM, Q / dO as N-contiguous shared-memory operands)
 __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                                                                  const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
-                                                                 UBwdArgs a) {
+                                                                 UBwdArgs a, int nTiles, int nGroups) {
     extern __shared__ uint8_t smem_raw[];
-    const AttnSeg sg = a.segs[blockIdx.z];
-    const int head = blockIdx.y;
-    const int k0 = blockIdx.x * 128;  // under a causal mask the first key tiles see the most queries
-    if (k0 >= sg.kLen) return;
-    const int qtBegin = a.causal ? k0 / 64 : 0, qtEnd = (sg.qLen + 63) / 64;
-    const int nqt = qtEnd - qtBegin;
-    if (nqt <= 0) {  // keys no query can see
-        for (int idx = threadIdx.x; idx < 128 * 16; idx += B_THREADS) {
-            const int r = idx >> 4, c = (idx & 15) * 4;
-            if (k0 + r < sg.kLen) {
-                *reinterpret_cast<float4*>(a.dK + (size_t)(sg.kStart + k0 + r) * a.lddk + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4*>(a.dV + (size_t)(sg.kStart + k0 + r) * a.lddv + head * UHD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        return;
-    }
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 2 * T128 + RING_K * 2 * T64 + DKV_RING_N * 2 * T64);
-    uint32_t* tmem_slot = (uint32_t*)(bars + 19);
-    float* stats = reinterpret_cast<float*>(bars + 20);  // [2 buffers][-(m2 + log2 l) | -D][64] (stride 192 floats)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
+    float* stats = reinterpret_cast<float*>(bars + 24);  // [2 buffers][-(m2 + log2 l) | -D][64] (stride 192 floats)
     const uint32_t Ks = smem_u32(tiles), Vs = Ks + T128;
     const uint32_t ringK = Vs + T128;                  // slot: Q tile then dO tile, both K-contiguous
     const uint32_t ringN = ringK + RING_K * 2 * T64;   // slot: Q tile then dO tile, both N-contiguous
     const uint32_t bar0 = smem_u32(bars);
+    // per item: kv_full, a_ready, acc_full, acc_free; per streamed tile (counted across items): the rest
     const uint32_t kv_full = bar0, qk_full = bar0 + 8, qk_empty = bar0 + 32, qn_full = bar0 + 56, qn_empty = bar0 + 72, sdp_full = bar0 + 88,
-                   ds_full = bar0 + 104, acc_full = bar0 + 120, a_ready = bar0 + 128, buf_free = bar0 + 136;
+                   ds_full = bar0 + 104, acc_full = bar0 + 120, a_ready = bar0 + 128, buf_free = bar0 + 136, acc_free = bar0 + 152;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 19; i++)  // a_ready: 256; qk_empty: MMA commit + 128 re-swizzle readers; qn_full: 128 re-swizzle writers; ds_full: 256
-            mbar_init(bar0 + 8 * i, (i == 13 || i == 14 || i == 16) ? 256 : (i >= 4 && i <= 6) ? 129 : (i == 7 || i == 8) ? 128 : 1);
+        for (int i = 0; i < 20; i++)  // a_ready, ds_full, acc_free: one arrival per element-wise warp; qk_empty: MMA commit + 4 re-swizzle warps; qn_full: 4 re-swizzle warps
+            mbar_init(bar0 + 8 * i, (i == 13 || i == 14 || i == 16 || i == 19) ? EW_THREADS / 32 : (i >= 4 && i <= 6) ? 5 : (i == 7 || i == 8) ? 4 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // The resident operands are requested right away: their latency overlaps the TMEM allocation and the first sync.
-        mbar_expect_tx(kv_full, 2 * T128);
-        tma_load_3d(Ks, &mapK, kv_full, 0, sg.kStart + k0, head * (UHD / 32));
-        tma_load_3d(Vs, &mapV, kv_full, 0, sg.kStart + k0, head * (UHD / 32));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BWD_TMEM_COLS) : "memory");
@@ -656,185 +829,252 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            const int col = head * UHD;
+            // ---------------------------------------------------------------- TMA producer
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
             bool ok = true;
-            int nk = 0;
-            for (; nk < nqt; nk++) {
-                const int s = nk % RING_K, row = sg.qStart + (qtBegin + nk) * 64;
-                ok = mbar_wait(qk_empty + 8 * s, ((nk / RING_K) & 1) ^ 1, status, 31);
-                if (!ok) break;
-                const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
-                mbar_expect_tx(bar, 2 * T64);
-                tma_load_3d(base, &mapQ, bar, 0, row, col >> 5);
-                tma_load_3d(base + T64, &mapdO, bar, 0, row, col >> 5);
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dkv_item(w, a, it, -1)) {
+                if (n > 0) {  // the element-wise threads have copied the previous item's K and V out of shared memory
+                    ok = mbar_wait(a_ready, (n - 1) & 1, status, 30);
+                    if (!ok) break;
+                }
+                mbar_expect_tx(kv_full, 2 * T128);
+                tma_load_3d(Ks, &mapK, kv_full, 0, it.sg.kStart + it.t0, it.head * (UHD / 32));
+                tma_load_3d(Vs, &mapV, kv_full, 0, it.sg.kStart + it.t0, it.head * (UHD / 32));
+                n++;
+                for (int i = 0; i < it.n; i++) {
+                    const int s = g % RING_K, row = it.sg.qStart + (it.aux + i) * 64;
+                    ok = mbar_wait(qk_empty + 8 * s, ((g / RING_K) & 1) ^ 1, status, 31);
+                    if (!ok) break;
+                    const uint32_t base = ringK + s * 2 * T64, bar = qk_full + 8 * s;
+                    mbar_expect_tx(bar, 2 * T64);
+                    tma_load_3d(base, &mapQ, bar, 0, row, it.head * (UHD / 32));
+                    tma_load_3d(base + T64, &mapdO, bar, 0, row, it.head * (UHD / 32));
+                    g++;
+                }
             }
             if (!ok) {  // failure path: let the copies already issued land (bounded) before the CTA may exit
                 const long long t0 = clock64();
-                while (!mbar_test(kv_full, 0) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
-                for (int i = max(0, nk - RING_K); i < nk; i++)
-                    while (!mbar_test(qk_full + 8 * (i % RING_K), (i / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                while (n > 0 && !mbar_test(kv_full, (n - 1) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
+                for (uint32_t j = g > RING_K ? g - RING_K : 0; j < g; j++)
+                    while (!mbar_test(qk_full + 8 * (j % RING_K), (j / RING_K) & 1) && clock64() - t0 < WAIT_BUDGET_CLOCKS) __nanosleep(64);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // ---------------------------------------------------------------- first issuer: S^T(i) and dP^T(i) into TMEM buffer g&1
             const uint32_t idS = idesc_tf32(128, 64, 0, 0);
             const uint64_t dRK0 = kdesc(ringK, 0, A64);
-            // ---------------------------------------------------------------- first issuer: S^T(i) and dP^T(i) into TMEM buffer i&1
-            bool ok = mbar_wait(a_ready, 0, status, 32);
-            tc_fence_after();
-            for (int i = 0; i < nqt && ok; i++) {
-                const int s = i % RING_K, b = i & 1;
-                ok = mbar_wait(qk_full + 8 * s, (i / RING_K) & 1, status, 33);
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
+            bool ok = true;
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dkv_item(w, a, it, -1)) {
+                ok = mbar_wait(a_ready, n & 1, status, 32);  // this item's K and V are in TMEM
                 if (!ok) break;
-                ok = mbar_wait(buf_free + 8 * b, ((i >> 1) & 1) ^ 1, status, 34);  // dV, dK of tile i-2 have consumed the buffer
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t dq = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dd = dq + (uint64_t)(T64 >> 4);
+                n++;
+                for (int i = 0; i < it.n; i++) {
+                    const int s = g % RING_K, b = g & 1;
+                    ok = mbar_wait(qk_full + 8 * s, (g / RING_K) & 1, status, 33);
+                    if (!ok) break;
+                    ok = mbar_wait(buf_free + 8 * b, ((g >> 1) & 1) ^ 1, status, 34);  // the dV, dK products two tiles back have consumed the buffer
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t dq = dRK0 + (uint64_t)(s * ((2 * T64) >> 4)), dd = dq + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + KA_COL + kk * 8, dq + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128, tm + KA_COL + kk * 8, dq + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + VA_COL + kk * 8, dd + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
-                umma_commit(qk_empty + 8 * s);
-                umma_commit(sdp_full + 8 * b);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + b * 128 + 64, tm + VA_COL + kk * 8, dd + koff(kk, A64), idS, kk > 0 ? 1u : 0u);
+                    umma_commit(qk_empty + 8 * s);
+                    umma_commit(sdp_full + 8 * b);
+                    g++;
+                }
             }
         }
-    } else if (warp == 14) {
+    } else if (warp == ISSUER2_WARP) {
         if (lane == 0) {
             // ---------------------------------------------------------------- second issuer: dV += P^T dO, dK += dS^T Q
             const uint32_t idN = idesc_tf32(128, 64, 0, 1);
             const uint64_t dRN0 = ndesc(ringN, 0, A64);
+            ItemWalk w(nTiles, nGroups);
+            BwdItem it;
             bool ok = true;
-            for (int i = 0; i < nqt && ok; i++) {
-                const int s = i % DKV_RING_N, b = i & 1;
-                ok = mbar_wait(qn_full + 8 * s, (i / DKV_RING_N) & 1, status, 35);
-                if (!ok) break;
-                ok = mbar_wait(ds_full + 8 * b, (i >> 1) & 1, status, 35);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t dqn = dRN0 + (uint64_t)(s * ((2 * T64) >> 4)), ddn = dqn + (uint64_t)(T64 >> 4);
+            int n = 0;
+            uint32_t g = 0;
+            while (ok && next_dkv_item(w, a, it, -1)) {
+                for (int i = 0; i < it.n; i++) {
+                    const int s = g % DKV_RING_N, b = g & 1;
+                    ok = mbar_wait(qn_full + 8 * s, (g / DKV_RING_N) & 1, status, 35);
+                    if (!ok) break;
+                    ok = mbar_wait(ds_full + 8 * b, (g >> 1) & 1, status, 35);
+                    if (!ok) break;
+                    if (i == 0 && n > 0) {  // the previous item's dV and dK have been read out of the accumulators
+                        ok = mbar_wait(acc_free, (n - 1) & 1, status, 38);
+                        if (!ok) break;
+                    }
+                    tc_fence_after();
+                    const uint64_t dqn = dRN0 + (uint64_t)(s * ((2 * T64) >> 4)), ddn = dqn + (uint64_t)(T64 >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + b * 128 + kk * 8, ddn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DV_COL, tm + b * 128 + kk * 8, ddn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, dqn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(qn_empty + 8 * s);
-                umma_commit(buf_free + 8 * b);
+                    for (int kk = 0; kk < 8; kk++) umma_tf32_ta(tm + DK_COL, tm + b * 128 + 64 + kk * 8, dqn + noff(kk), idN, (i > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(qn_empty + 8 * s);
+                    umma_commit(buf_free + 8 * b);
+                    g++;
+                }
+                if (!ok) break;
+                umma_commit(acc_full);
+                n++;
             }
-            umma_commit(acc_full);
         }
-    } else if (warp < 10) {
-        const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 32 * half, tid = threadIdx.x - 64;
-        const int row = 32 * quarter + lane, kj = k0 + row;
+    } else if (warp < 2 + EW_THREADS / 32) {
+        // ------------------------------------------------------------------------------ element-wise warps and output
+        const int quarter = warp & 3, colq = (warp - 2) >> 2, c0 = 16 * colq, tid = threadIdx.x - 64;
+        const int row = 32 * quarter + lane;
         const uint32_t tlane = tm + ((uint32_t)(32 * quarter) << 16);
         const float sl2 = a.scale * LOG2E_F;
-        bool ok = mbar_wait_warp(kv_full, 0, status, 30);
-        if (__all_sync(0xffffffffu, ok)) {  // move this thread's half rows of K and V into TMEM
-            row_to_tmem(tiles + half * A128, row, tlane + KA_COL + c0);
-            row_to_tmem(tiles + T128 + half * A128, row, tlane + VA_COL + c0);
+        const float2 sl22 = make_float2(sl2, sl2);
+        auto operands_to_tmem = [&](int n) -> bool {  // this thread's quarter rows of K and V: shared memory -> TMEM
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_warp(kv_full, n & 1, status, 30));
+            if (!ok) return false;
+            half_row_to_tmem(tiles + (colq >> 1) * A128, row, colq & 1, tlane + KA_COL + c0);
+            half_row_to_tmem(tiles + T128 + (colq >> 1) * A128, row, colq & 1, tlane + VA_COL + c0);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(a_ready);
-        }
-        // Statistics of a tile's 64 query rows: fetched one tile ahead into registers (threads 0..63), so their global
-        // latency overlaps the previous tile instead of sitting in front of every tile.
-        float pm = 0.f, pl = 0.f, pD = 0.f;
-        auto fetch_stats = [&](int i) {
+            warp_arrive(a_ready);
+            return true;
+        };
+        // Statistics of a tile's 64 query rows: fetched one tile ahead into registers (threads 0..63), across item
+        // boundaries too, so their global latency overlaps the previous tile instead of sitting in front of every tile.
+        float pm = -INFINITY, pl = 0.f, pD = 0.f;
+        auto fetch_stats = [&](const BwdItem& it, int i) {
             pm = -INFINITY; pl = 0.f; pD = 0.f;
-            const int q = (qtBegin + i) * 64 + tid;
-            if (tid < 64 && i < nqt && q < sg.qLen) {
-                const size_t idx = (size_t)(sg.qStart + q) * a.numHeads + head;
+            const int q = (it.aux + i) * 64 + tid;
+            if (tid < 64 && q < it.sg.qLen) {
+                const size_t idx = (size_t)(it.sg.qStart + q) * a.numHeads + it.head;
                 pm = a.rowMax[idx]; pl = a.rowSum[idx]; pD = a.rowDot[idx];
             }
         };
-        fetch_stats(0);
-        for (int i = 0; i < nqt; i++) {
-            const int s = i & 1, qbase = (qtBegin + i) * 64;
-            float* st = stats + s * 192;
-            if (tid < 64) {
-                // +inf: P = 0 for query rows outside the segment or without a visible key
-                const float m2l = (pl > 0.f && pm != -INFINITY) ? fmaf(pm, LOG2E_F, log2f(pl)) : INFINITY;
-                st[tid] = -m2l; st[64 + tid] = -pD;
+        ItemWalk w(nTiles, nGroups);
+        BwdItem cur, nxt;
+        bool have = next_dkv_item(w, a, cur, tid);
+        bool ok = true;
+        int n = 0;
+        uint32_t g = 0;
+        if (have) {
+            fetch_stats(cur, 0);
+            ok = !ew_barrier_or(!operands_to_tmem(0));
+        }
+        while (have && ok) {
+            const bool haveN = next_dkv_item(w, a, nxt, tid);
+            const int kj = cur.t0 + row;
+            int kpos = cur.sg.kStart + kj;  // rotary position of this thread's key, requested a whole item before its use
+            if (a.rope_table && a.rope_pos && kj < cur.sg.kLen) kpos = a.rope_pos[kpos];
+            for (int i = 0; i < cur.n; i++, g++) {
+                const int s = g & 1, qbase = (cur.aux + i) * 64;
+                float* st = stats + s * 192;
+                if (tid < 64) {
+                    // +inf: P = 0 for query rows outside the segment or without a visible key
+                    const float m2l = (pl > 0.f && pm != -INFINITY) ? fmaf(pm, LOG2E_F, log2f(pl)) : INFINITY;
+                    st[tid] = -m2l; st[64 + tid] = -pD;
+                }
+                if (i + 1 < cur.n) fetch_stats(cur, i + 1);
+                else if (haveN) fetch_stats(nxt, 0);
+                ok = mbar_wait_warp(sdp_full + 8 * s, (g >> 1) & 1, status, 36);
+                if (ew_barrier_or(!ok)) {  // publishes the statistics; a failed wait anywhere stops all 256 threads together
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                // visible columns of this warp's 16: query index >= key index (causal), query inside the segment, key inside it
+                int cmin = a.causal ? kj - qbase - c0 : 0, cmax = cur.sg.qLen - qbase - c0;
+                if (kj >= cur.sg.kLen) cmax = 0;
+                uint32_t sr[16], pr[16];
+                tmem_ld16_nowait(tlane + s * 128 + c0, sr);
+                tmem_ld16_nowait(tlane + s * 128 + 64 + c0, pr);
+                tmem_ld_wait();
+                // Two copies of the loop, chosen once per tile: a branch inside the unrolled body would keep the loads of the
+                // per-column statistics from moving ahead of the arithmetic that precedes them.
+                auto tile_math = [&](auto masked) {
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4) {
+                        const float4 m4 = *reinterpret_cast<const float4*>(st + c0 + c), d4 = *reinterpret_cast<const float4*>(st + 64 + c0 + c);
+                        const float2 nm[2] = {make_float2(m4.x, m4.y), make_float2(m4.z, m4.w)}, nd[2] = {make_float2(d4.x, d4.y), make_float2(d4.z, d4.w)};
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int ii = c + 2 * e;
+                            float2 v = fma2(make_float2(__uint_as_float(sr[ii]), __uint_as_float(sr[ii + 1])), sl22, nm[e]);
+                            if (decltype(masked)::value) {
+                                if (ii < cmin || ii >= cmax) v.x = -INFINITY;
+                                if (ii + 1 < cmin || ii + 1 >= cmax) v.y = -INFINITY;
+                            }
+                            const float2 pp = make_float2(ex2(v.x), ex2(v.y));
+                            const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[ii]), __uint_as_float(pr[ii + 1])), nd[e]));
+                            sr[ii] = rna_tf32_add(pp.x); sr[ii + 1] = rna_tf32_add(pp.y);
+                            pr[ii] = rna_tf32_add(ds.x); pr[ii + 1] = rna_tf32_add(ds.y);
+                        }
+                    }
+                };
+                if (__all_sync(0xffffffffu, cmin <= 0 && cmax >= 16)) tile_math(std::false_type());  // no masking anywhere in this warp's slice
+                else tile_math(std::true_type());
+                tmem_st16(tlane + s * 128 + c0, sr);
+                tmem_st16(tlane + s * 128 + 64 + c0, pr);
+                tmem_st_wait();
+                tc_fence_before();
+                warp_arrive(ds_full + 8 * s);
             }
-            fetch_stats(i + 1);
-            ok = mbar_wait_warp(sdp_full + 8 * s, (i >> 1) & 1, status, 36);
-            if (ew_barrier_or(!ok)) {  // publishes the statistics; a failed wait anywhere stops all 256 threads together
+            if (!ok) break;
+            // The S^T / dP^T products of this item are complete (its last sdp_full was seen), so the next item's K and V may
+            // replace it in TMEM right away: the first issuer starts on the next item while this one's results are written.
+            bool okb = true;
+            if (haveN) okb = operands_to_tmem(n + 1);
+            if (okb) okb = __all_sync(0xffffffffu, mbar_wait_warp(acc_full, n & 1, status, 37));
+            if (okb) {
+                tc_fence_after();
+                uint32_t rv[16], rk[16];
+                tmem_ld16_nowait(tlane + DV_COL + c0, rv);
+                tmem_ld16_nowait(tlane + DK_COL + c0, rk);
+                tmem_ld_wait();
+                tc_fence_before();
+                warp_arrive(acc_free);
+                if (kj < cur.sg.kLen) {  // a lane writes its own row slices: the stores retire in the background while the next item's tiles are worked on
+                    const size_t grow = (size_t)(cur.sg.kStart + kj);
+                    store_row_slice(rv, 1.f, a.dV + grow * a.lddv + cur.head * UHD + c0, nullptr);
+                    store_row_slice(rk, a.scale, a.dK + grow * a.lddk + cur.head * UHD + c0,
+                                    a.rope_table ? reinterpret_cast<const float4*>(a.rope_table + ((size_t)kpos * (UHD / 2) + (c0 >> 1)) * 2) : nullptr);
+                }
+            }
+            if (ew_barrier_or(!okb)) {  // every element-wise thread votes once per item, whatever its status
                 ok = false;
                 break;
             }
-            tc_fence_after();
-            // visible columns of this warp's 32: query index >= key index (causal), query inside the segment, key inside it
-            int cmin = a.causal ? kj - qbase - c0 : 0, cmax = sg.qLen - qbase - c0;
-            if (kj >= sg.kLen) cmax = 0;
-            uint32_t sr[32], pr[32];
-            tmem_ld32_nowait(tlane + s * 128 + c0, sr);
-            tmem_ld32_nowait(tlane + s * 128 + 64 + c0, pr);
-            tmem_ld_wait();
-            const bool fullw = __all_sync(0xffffffffu, cmin <= 0 && cmax >= 32);  // no masking anywhere in this warp's slice
-            const float2 sl22 = make_float2(sl2, sl2);
-#pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-                const float4 m4 = *reinterpret_cast<const float4*>(st + c0 + c), d4 = *reinterpret_cast<const float4*>(st + 64 + c0 + c);
-                const float2 nm[2] = {make_float2(m4.x, m4.y), make_float2(m4.z, m4.w)}, nd[2] = {make_float2(d4.x, d4.y), make_float2(d4.z, d4.w)};
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int i = c + 2 * e;
-                    float2 v = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sl22, nm[e]);
-                    if (!fullw) {
-                        if (i < cmin || i >= cmax) v.x = -INFINITY;
-                        if (i + 1 < cmin || i + 1 >= cmax) v.y = -INFINITY;
-                    }
-                    const float2 pp = make_float2(ex2(v.x), ex2(v.y));
-                    const float2 ds = mul2(pp, add2(make_float2(__uint_as_float(pr[i]), __uint_as_float(pr[i + 1])), nd[e]));
-                    sr[i] = rna_tf32_add(pp.x); sr[i + 1] = rna_tf32_add(pp.y);
-                    pr[i] = rna_tf32_add(ds.x); pr[i + 1] = rna_tf32_add(ds.y);
-                }
-            }
-            tmem_st32(tlane + s * 128 + c0, sr);
-            tmem_st32(tlane + s * 128 + 64 + c0, pr);
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(ds_full + 8 * s);
+            cur = nxt;
+            have = haveN;
+            n++;
         }
-        if (ok) {
-            ok = mbar_wait_warp(acc_full, 0, status, 37);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        float* stageV = reinterpret_cast<float*>(tiles);                 // every MMA has completed: K and V tiles are free
-        float* stageK = reinterpret_cast<float*>(tiles + 36864);
-        if (ok) {
-            tc_fence_after();
-            uint32_t r[32];
-            tmem_ld32(tlane + DV_COL + c0, r);
-#pragma unroll
-            for (int c = 0; c < 32; c += 4)
-                *reinterpret_cast<float4*>(stageV + row * OUT_STRIDE + c0 + c) =
-                    make_float4(__uint_as_float(r[c]), __uint_as_float(r[c + 1]), __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
-            tmem_ld32(tlane + DK_COL + c0, r);
-#pragma unroll
-            for (int c = 0; c < 32; c += 4)
-                *reinterpret_cast<float4*>(stageK + row * OUT_STRIDE + c0 + c) =
-                    make_float4(__uint_as_float(r[c]) * a.scale, __uint_as_float(r[c + 1]) * a.scale, __uint_as_float(r[c + 2]) * a.scale,
-                                __uint_as_float(r[c + 3]) * a.scale);
-        }
-        ew_barrier();
-        if (ok) {
-            const int nRows = min(128, sg.kLen - k0);
-            store_rows(stageV, a.dV, a.lddv, sg.kStart + k0, nRows, head * UHD, tid);
-            store_rows(stageK, a.dK, a.lddk, sg.kStart + k0, nRows, head * UHD, tid, a.rope_table, a.rope_pos);
-        }
-    } else if (warp < 14) {
+    } else if (warp < ISSUER2_WARP) {
         // ------------------------------------------------------------------------------ re-swizzle warps: Q, dO -> N-contiguous images
-        const int t = threadIdx.x - 320;
+        const int t = threadIdx.x - RESWIZZLE_T0;
         uint8_t* ringK_p = tiles + 2 * T128;
         uint8_t* ringN_p = ringK_p + RING_K * 2 * T64;
-        for (int i = 0; i < nqt; i++) {
-            const int sk = i % RING_K, sn = i % DKV_RING_N;
-            if (!mbar_wait_warp(qk_full + 8 * sk, (i / RING_K) & 1, status, 39)) break;
-            if (!mbar_wait_warp(qn_empty + 8 * sn, ((i / DKV_RING_N) & 1) ^ 1, status, 40)) break;
-            reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * 2 * T64, t);
-            reswizzle_tile(ringK_p + sk * 2 * T64 + T64, ringN_p + sn * 2 * T64 + T64, t);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
-            mbar_arrive(qn_full + 8 * sn);
-            mbar_arrive(qk_empty + 8 * sk);
+        ItemWalk w(nTiles, nGroups);
+        BwdItem it;
+        bool ok = true;
+        uint32_t g = 0;
+        while (ok && next_dkv_item(w, a, it, -1)) {
+            for (int i = 0; i < it.n; i++, g++) {
+                const int sk = g % RING_K, sn = g % DKV_RING_N;
+                ok = mbar_wait_warp(qk_full + 8 * sk, (g / RING_K) & 1, status, 39) && mbar_wait_warp(qn_empty + 8 * sn, ((g / DKV_RING_N) & 1) ^ 1, status, 40);
+                if (!ok) break;
+                reswizzle_tile(ringK_p + sk * 2 * T64, ringN_p + sn * 2 * T64, t);
+                reswizzle_tile(ringK_p + sk * 2 * T64 + T64, ringN_p + sn * 2 * T64 + T64, t);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the MMA's reads
+                warp_arrive(qn_full + 8 * sn);
+                warp_arrive(qk_empty + 8 * sk);
+            }
         }
     }
     tc_fence_before();
@@ -917,11 +1157,12 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     const int warps = t.totalQ * t.numHeads;
     attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
     B200_LAUNCH_CHECK(ctx);
-    dim3 gk((t.maxKLen + 127) / 128, t.numHeads, t.nSeg);
-    attn_dkv_umma_kernel<<<gk, B_THREADS, DKV_SMEM, ctx->stream>>>(k128, v128, q64, do64, a);
+    // persistent kernels: one CTA per SM walks its share of the (segment, head, tile) pairs
+    const int nGroups = t.numHeads * t.nSeg, sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int kTiles = (t.maxKLen + 127) / 128, qTiles = (t.maxQLen + 127) / 128;
+    attn_dkv_umma_kernel<<<std::min(sms, nGroups * ((kTiles + 1) / 2)), B_THREADS, DKV_SMEM, ctx->stream>>>(k128, v128, q64, do64, a, kTiles, nGroups);
     B200_LAUNCH_CHECK(ctx);
-    dim3 gq((t.maxQLen + 127) / 128, t.numHeads, t.nSeg);
-    attn_dq_umma_kernel<<<gq, B_THREADS, DQ_SMEM, ctx->stream>>>(q128, do128, k64, v64, a);
+    attn_dq_umma_kernel<<<std::min(sms, nGroups * ((qTiles + 1) / 2)), B_THREADS, DQ_SMEM, ctx->stream>>>(q128, do128, k64, v64, a, qTiles, nGroups);
     B200_LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -718,13 +718,26 @@ __global__ void ln_bwd_final_kernel(const float* __restrict__ partial, int parts
     *dst = accumulate ? *dst + s : s;
 }
 
-// Same with a third partial array: the column sums of dx, always accumulated into dxColSum.
-__global__ void ln_bwd_final3_kernel(const float* __restrict__ partial, int parts, int d, float* __restrict__ dGamma, float* __restrict__ dBeta,
-                                     float* __restrict__ dxColSum, int accumulate) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 3 * d) return;
+// The same final reduction for the training path, where it runs twice per block and pass: 32 columns x 8 slices of
+// the partial rows per CTA (a thread of the kernels above walks every partial row of its column, one dependent load
+// after the other, which costs ~28 us for 592 rows).  The order of the adds is fixed, so results repeat bit for bit.
+// Column index c runs over [dGamma | dBeta | dxColSum] (the third only when dxColSum is given, always accumulated).
+__global__ void __launch_bounds__(256) ln_bwd_final_sliced_kernel(const float* __restrict__ partial, int parts, int d, int nacc, float* __restrict__ dGamma,
+                                                                  float* __restrict__ dBeta, float* __restrict__ dxColSum, int accumulate) {
+    __shared__ float sm[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x, width = nacc * d;
+    float s0 = 0.f, s1 = 0.f;
+    if (c < width) {
+        int k = threadIdx.y;
+        for (; k + 8 < parts; k += 16) { s0 += partial[(size_t)k * width + c]; s1 += partial[(size_t)(k + 8) * width + c]; }
+        if (k < parts) s0 += partial[(size_t)k * width + c];
+    }
+    sm[threadIdx.y][threadIdx.x] = s0 + s1;
+    __syncthreads();
+    if (threadIdx.y != 0 || c >= width) return;
     float s = 0.f;
-    for (int k = 0; k < parts; k++) s += partial[(size_t)k * 3 * d + c];
+#pragma unroll
+    for (int y = 0; y < 8; y++) s += sm[y][threadIdx.x];
     if (c >= 2 * d) { dxColSum[c - 2 * d] += s; return; }
     float* dst = c < d ? dGamma + c : dBeta + (c - d);
     *dst = accumulate ? *dst + s : s;
@@ -756,7 +769,7 @@ int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const f
             if (dOutB) ln_bwd_vec_kernel<true, true><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
             else ln_bwd_vec_kernel<false, true><<<grid, warps * 32, smem, ctx->stream>>>(dOutA, dOutB, x, gamma, mean, var, rows, d, eps, dx, ctx->ws);
             B200_LAUNCH_CHECK(ctx);
-            ln_bwd_final3_kernel<<<(3 * d + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, parts, d, dGamma, dBeta, dxColSum, accumulate);
+            ln_bwd_final_sliced_kernel<<<(3 * d + 31) / 32, dim3(32, 8), 0, ctx->stream>>>(ctx->ws, parts, d, 3, dGamma, dBeta, dxColSum, accumulate);
             B200_LAUNCH_CHECK(ctx);
             return B200_OK;
         }
@@ -776,7 +789,7 @@ int k_ln_backward(b200_ctx* ctx, const float* dOutA, const float* dOutB, const f
                                                                                          rowsPerChunk, ctx->ws);
         B200_LAUNCH_CHECK(ctx);
     }
-    ln_bwd_final_kernel<<<(2 * d + 255) / 256, 256, 0, ctx->stream>>>(ctx->ws, parts, d, dGamma, dBeta, accumulate);
+    ln_bwd_final_sliced_kernel<<<(2 * d + 31) / 32, dim3(32, 8), 0, ctx->stream>>>(ctx->ws, parts, d, 2, dGamma, dBeta, nullptr, accumulate);
     B200_LAUNCH_CHECK(ctx);
     if (dxColSum) return k_colsum(ctx, dx, rows, d, d, dxColSum, 1);  // paths without the fused column sum
     return B200_OK;
