@@ -346,13 +346,20 @@ __global__ void __launch_bounds__(128) embed_scatter_vec_kernel(float* __restric
     float4* dst = reinterpret_cast<float4*>(eg + (size_t)seg_id[s] * d + c);
     float4 acc = *dst;
     int k = lo;
-    for (; k + U <= hi; k += U) {
-        int rows[U];
-        float4 v[U];
+    // the row indices of a group are fetched while the previous group's rows travel: index -> row is a chain of two loads
+    int rows[U];
+    if (k + U <= hi) {
 #pragma unroll
         for (int u = 0; u < U; u++) rows[u] = perm[k + u];
+    }
+    for (; k + U <= hi; k += U) {
+        float4 v[U];
 #pragma unroll
         for (int u = 0; u < U; u++) v[u] = *reinterpret_cast<const float4*>(a + (size_t)rows[u] * d + c);
+        if (k + 2 * U <= hi) {
+#pragma unroll
+            for (int u = 0; u < U; u++) rows[u] = perm[k + U + u];
+        }
 #pragma unroll
         for (int u = 0; u < U; u++) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
     }

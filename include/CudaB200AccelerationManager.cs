@@ -175,6 +175,9 @@ namespace CallaghanDev.ML.AccelerationManagers
     [DllImport(Lib)] internal static extern int b200_lm_gen_length(IntPtr h, int* length);
     [DllImport(Lib)] internal static extern int b200_lm_gen_step(IntPtr h, int token_id, float* logits);
     [DllImport(Lib)] internal static extern int b200_lm_gen_greedy(IntPtr h, int* prompt, int n_prompt, int max_new, int* out_tokens, int* n_out);
+    [DllImport(Lib)] internal static extern int b200_lm_gen_graph_nodes(IntPtr h, int* nodes);
+    [DllImport(Lib)] internal static extern int b200_lm_gen_single_kernel(IntPtr h);
+    [DllImport(Lib)] internal static extern int b200_lm_gen_set_single_kernel(IntPtr h, int on);
     [DllImport(Lib)] internal static extern int b200_lm_get_timings(IntPtr h, float* ms4);
     [DllImport(Lib)] internal static extern int b200_dp_set_nccl_library(byte* path);
     [DllImport(Lib)] internal static extern int b200_dp_unique_id(byte* id128);
