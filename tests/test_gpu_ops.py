@@ -306,7 +306,8 @@ def test_embedding_gather_scatter_bit_exact(mgr, oracle):  # PT:660-668 + Zipf-l
         mgr.AccumulateTokenEmbeddingGrad(aa, dX, ids, 10, 96, 4995)
 
 
-@pytest.mark.parametrize("rows,V,eff", [(4, 5, 4), (64, 200, 64), (30, 8000, 21), (5, 32000, 5), (3, 40000, 3)])
+@pytest.mark.parametrize("rows,V,eff", [(4, 5, 4), (64, 200, 64), (30, 8000, 21), (5, 32000, 5), (3, 40000, 3),
+                                        (7, 8192, 6), (3, 32768, 3), (400, 32000, 390)])  # the last: several rows per persistent block
 def test_cross_entropy(mgr, oracle, rows, V, eff):  # PT:670-678
     logits = pt_matrix(rows, V, 40) * 8
     targets = np.arange(7, 7 + rows + 3, dtype=np.int32) * 37 % V
