@@ -306,6 +306,7 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample (0 disables)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch (sequences; global for c5/c1, per GPU for c3/c4)")
+    ap.add_argument("--nccl-ctas", type=int, default=-1, help="CTAs the data-parallel communicator may use (-1: the library's default of 8, 0: NCCL's own choice)")
     ap.add_argument("--gemm-csv", default="", help="write the per-shape GEMM timing table of the timed region to this file")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
@@ -346,6 +347,9 @@ def main():
     args.seqs_per_pass = max(1, min(args.seqs_per_pass, -(-global_batch // world)))  # never more than this rank trains per step
     max_rows = args.seqs_per_pass * T
     mode = {"auto": GEMM_AUTO, "simt": GEMM_FP32_SIMT, "tcgen05": GEMM_TF32_TCGEN05}[args.gemm]
+    if args.nccl_ctas >= 0:
+        from callaghandev.ml_b200 import _lib as _b200lib
+        _b200lib.load().b200_dp_set_nccl_max_ctas(args.nccl_ctas)
     tr = DataParallelLMTrainer(cfg, max_rows, local, None, mode)
     if w["opt"] == "adam":
         tr.lm.set_optimizer("adam", 0.9, 0.999, 1e-8)

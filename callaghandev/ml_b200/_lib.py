@@ -148,6 +148,7 @@ PROTOTYPES = {
     "b200_lm_gen_greedy": (_i32, [_vp, _i, _i32, _i32, _i, _i]),
     "b200_lm_get_timings": (_i32, [_vp, _f]),
     "b200_dp_set_nccl_library": (_i32, [C.c_char_p]),
+    "b200_dp_set_nccl_max_ctas": (_i32, [_i32]),
     "b200_dp_unique_id": (_i32, [_b]),
     "b200_dp_create_rank": (_i32, [_vp, _b, _i32, _i32, _pp]),
     "b200_dp_destroy": (_i32, [_vp]),

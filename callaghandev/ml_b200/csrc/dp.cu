@@ -24,6 +24,9 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;  // optional (NCCL >= 2.14)
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
@@ -35,6 +38,21 @@ struct NcclApi {
 
 std::mutex g_nccl_mu;
 std::string g_nccl_path;
+// CTAs the communicators may use.  The all-reduce of a step moves 4 bytes per parameter in the shadow of a backward pass
+// that lasts tens of milliseconds, so it needs a small fraction of NVLink's bandwidth; what it costs is the SMs its
+// kernels occupy beside the GEMMs while they wait for peers.  At eight GPUs (c5) the default took 8 % off the GEMM rate
+// of the overlapped pass, eight CTAs took 3 % and shortened the exposed tail as well.
+int g_nccl_max_ctas = 8;
+
+// ncclCommInitRank, with the CTA limit where the library supports per-communicator configuration
+ncclResult_t comm_init_rank(NcclApi* api, ncclComm_t* comm, int world, ncclUniqueId id, int rank) {
+    if (api->CommInitRankConfig && g_nccl_max_ctas > 0) {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.maxCTAs = g_nccl_max_ctas;
+        return api->CommInitRankConfig(comm, world, id, rank, &cfg);
+    }
+    return api->CommInitRank(comm, world, id, rank);
+}
 NcclApi* g_nccl = nullptr;
 
 NcclApi* nccl_api(std::string* why) {
@@ -58,6 +76,9 @@ NcclApi* nccl_api(std::string* why) {
     a->GetUniqueId = (decltype(a->GetUniqueId))sym("ncclGetUniqueId");
     a->CommInitRank = (decltype(a->CommInitRank))sym("ncclCommInitRank");
     a->CommInitAll = (decltype(a->CommInitAll))sym("ncclCommInitAll");
+    a->CommInitRankConfig = (decltype(a->CommInitRankConfig))dlsym(h, "ncclCommInitRankConfig");
+    a->GroupStart = (decltype(a->GroupStart))dlsym(h, "ncclGroupStart");
+    a->GroupEnd = (decltype(a->GroupEnd))dlsym(h, "ncclGroupEnd");
     a->CommDestroy = (decltype(a->CommDestroy))sym("ncclCommDestroy");
     a->CommAbort = (decltype(a->CommAbort))sym("ncclCommAbort");
     a->CommGetAsyncError = (decltype(a->CommGetAsyncError))sym("ncclCommGetAsyncError");
@@ -261,6 +282,13 @@ int32_t b200_dp_set_nccl_library(const char* path) {
     return B200_OK;
 }
 
+int32_t b200_dp_set_nccl_max_ctas(int32_t n) {
+    if (n < 0) return B200_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(g_nccl_mu);
+    g_nccl_max_ctas = n;
+    return B200_OK;
+}
+
 int32_t b200_dp_shard(int32_t n_seq, int32_t rank, int32_t world, int32_t* lo, int32_t* hi) {
     if (!lo || !hi || n_seq < 0 || world <= 0 || rank < 0 || rank >= world) return B200_ERR_INVALID_ARG;
     int l, h;
@@ -293,7 +321,7 @@ int32_t b200_dp_create_rank(b200_lm* lm, const uint8_t* id128, int32_t rank, int
     b200_dp* dp = dp_new(lm, api, rank, world);
     ncclUniqueId id;
     memcpy(&id, id128, 128);
-    ncclResult_t r = api->CommInitRank(&dp->comm, world, id, rank);
+    ncclResult_t r = comm_init_rank(api, &dp->comm, world, id, rank);
     if (r != ncclSuccess) {
         int rc = dp_fail(dp, B200_ERR_NCCL, "ncclCommInitRank failed", r);
         dp->comm = nullptr;
@@ -468,7 +496,21 @@ int32_t b200_dp_group_create(const int32_t* devices, int32_t n, const b200_lm_co
     if (rc == B200_OK) {
         std::vector<ncclComm_t> comms((size_t)n);
         std::vector<int> devs(devices, devices + n);
-        ncclResult_t r = api->CommInitAll(comms.data(), n, devs.data());
+        ncclResult_t r;
+        if (api->CommInitRankConfig && api->GroupStart && api->GroupEnd && g_nccl_max_ctas > 0) {
+            // ncclCommInitAll takes no configuration: the same thing by hand (one id, every rank inside one group call)
+            ncclUniqueId id;
+            r = api->GetUniqueId(&id);
+            if (r == ncclSuccess) r = api->GroupStart();
+            for (int i = 0; i < n && r == ncclSuccess; i++) {
+                cudaSetDevice(devs[(size_t)i]);
+                r = comm_init_rank(api, &comms[(size_t)i], n, id, i);
+            }
+            if (r == ncclSuccess) r = api->GroupEnd();
+            else api->GroupEnd();
+        } else {
+            r = api->CommInitAll(comms.data(), n, devs.data());
+        }
         if (r != ncclSuccess) rc = B200_ERR_NCCL;
         for (int i = 0; i < n && rc == B200_OK; i++) {
             cudaSetDevice(devices[i]);

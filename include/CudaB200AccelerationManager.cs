@@ -180,6 +180,7 @@ namespace CallaghanDev.ML.AccelerationManagers
     [DllImport(Lib)] internal static extern int b200_lm_gen_set_single_kernel(IntPtr h, int on);
     [DllImport(Lib)] internal static extern int b200_lm_get_timings(IntPtr h, float* ms4);
     [DllImport(Lib)] internal static extern int b200_dp_set_nccl_library(byte* path);
+    [DllImport(Lib)] internal static extern int b200_dp_set_nccl_max_ctas(int n);
     [DllImport(Lib)] internal static extern int b200_dp_unique_id(byte* id128);
     [DllImport(Lib)] internal static extern int b200_dp_create_rank(IntPtr lm, byte* id128, int rank, int world, out IntPtr @out);
     [DllImport(Lib)] internal static extern int b200_dp_destroy(IntPtr h);
