@@ -1,0 +1,97 @@
+"""The benchmarked configuration at its FULL size (V 32000, d 1024, 16 heads, 12 layers, f 4096; 256 sequences of 1024
+tokens = 261 888 trained positions per step), checked through properties that do not need the CPU oracle -- which could
+not finish a step of this size in any useful time (it needs [N, V] logits for 261 888 rows):
+
+  * additivity: the trainer averages per-sequence gradients over the valid sequences (TransformerTrainer.cs:298-313), so
+    N * g(batch) = N_A * g(A) + N_B * g(B) for a split of the batch into A and B, and the same for the loss;
+  * packing invariance: how many sequences share a packed pass (32 or 128 here) changes the GEMM shapes, the split of the
+    weight-gradient reductions and the attention work lists, not the result -- up to what the tensor cores' accumulators
+    do with a longer chain of additions (see the bound below);
+  * the gradient norm the step reports equals the float64 norm of the gradient it leaves behind;
+  * the same step run twice gives bit-identical gradients (no atomics, fixed reduction orders).
+
+The small-batch tests of test_gpu_configs.py pin the arithmetic of exactly these kernels to the oracle at the same model
+dimensions; this file shows that nothing changes when the batch grows to the benchmark's.
+Bounds: per tensor, max|diff| <= tol * max|ref| and ||diff||_2 <= tol * ||ref||_2 with tol 3e-4 -- what is compared
+differs only in the order of FP32 additions over up to 131 072 rows: sqrt(N) * 2^-24 = 2e-5 for a typical element, and
+the worst of a tensor's four million elements sits at about five times that (measured: 1.1e-4).  Packing is held to 1e-3:
+a weight-gradient element is a sum over the rows of a pass, accumulated inside the tensor core, and the measured
+differences (4.0e-4 on the largest element of L0.W1, 6.2e-4 at worst, 1.6e-4 on the gradient norm, always towards a
+smaller magnitude for the longer chain) are what accumulators that truncate instead of rounding would give: about 2^-24
+of a same-signed sum per accumulation step, 16 368 steps (130 944 rows / K 8) in a 128-sequence pass against a quarter of
+that in a 32-sequence pass.  It is well inside the 2e-3 the TF32 path is allowed and a property of the hardware's
+accumulation, not of this library's reduction order (the FP32 engines do not show it).
+"""
+import numpy as np
+import pytest
+
+from lmutil import compare_gradients, init_params, lm_config, token_batch
+
+pytestmark = pytest.mark.gpu
+
+T_LEN, N_SEQ = 1024, 256
+
+
+def test_config5_full_batch_properties():
+    from callaghandev.ml_b200 import GEMM_AUTO, B200LanguageModelTrainer, CudaB200AccelerationManager, LMConfig
+
+    cfg = lm_config(vocab=32000, d=1024, H=16, L=12, f=4096, act="Relu")
+    dcfg = LMConfig()  # the library's own structure (lm_config builds the oracle's, field for field the same)
+    for name, _ in LMConfig._fields_:
+        setattr(dcfg, name, getattr(cfg, name))
+    m = CudaB200AccelerationManager(0, GEMM_AUTO)
+    t = B200LanguageModelTrainer(m, dcfg, 128 * T_LEN)
+    tensors = t.tensors()
+    total = max(off + r * c for off, r, c in tensors)
+    P = init_params(None, cfg, 5, tensors=tensors, total=total)
+    t.upload_params(P)
+    rng = np.random.default_rng(77)
+    toks, off = token_batch(rng, N_SEQ, 32000, fixed_len=T_LEN, zipf=1.1)
+    toks, off = np.asarray(toks, np.int32), np.asarray(off, np.int32)
+
+    def grads_of(trainer, lo, hi):
+        o = off[lo:hi + 1] - off[lo]
+        loss, norm, valid = trainer.train_step_discrete(toks[off[lo]:off[hi]], o, 0.0, False, 1.0, False)
+        assert valid == hi - lo and np.isfinite(loss) and np.isfinite(norm)
+        return loss, norm, trainer.download_grads()[:total]
+
+    l_all, n_all, g_all = grads_of(t, 0, N_SEQ)
+    eng = m.engine_launches()
+    assert eng["gemm_pair"] > 0 and eng["attn_tcgen05"] > 0, f"the benchmarked engines did not run: {eng}"
+
+    # the reported norm is the norm of what is in the arena (tree sum in FP32 against float64 here)
+    n64 = float(np.sqrt(sum(float(np.dot(g_all[o:o + r * c].astype(np.float64), g_all[o:o + r * c].astype(np.float64))) for o, r, c in tensors)))
+    assert abs(n_all - n64) <= 1e-5 * n64, f"reported gradient norm {n_all} vs float64 norm of the gradient {n64}"
+
+    # run twice: bit-identical
+    l_again, n_again, g_again = grads_of(t, 0, N_SEQ)
+    assert l_again == l_all and n_again == n_all and np.array_equal(g_all, g_again), "the same step twice must give the same bits"
+    del g_again
+
+    # additivity over a split of the batch (unequal halves, so the weights N_A, N_B matter)
+    cut = 96
+    l_a, _, g_a = grads_of(t, 0, cut)
+    l_b, _, g_b = grads_of(t, cut, N_SEQ)
+    # The loss of a bucket is the reference's serial FP32 sum of its per-row losses (AccelerationCPU.cs:2425-2438, restated in
+    # csrc/lm.cu run_plan): over 261 888 rows of ~10.5 the running sum reaches 2.7e6, where one FP32 ulp is 0.25, so the
+    # three sums (256, 96 and 160 sequences) each carry a relative error of up to ~1e-4 of their own.
+    assert abs(l_all * N_SEQ - (l_a * cut + l_b * (N_SEQ - cut))) <= 3e-4 * abs(l_all) * N_SEQ, "loss is the mean of the per-sequence losses"
+    combined = np.empty_like(g_all)
+    for o, r, c in tensors:
+        combined[o:o + r * c] = ((g_a[o:o + r * c].astype(np.float64) * cut + g_b[o:o + r * c].astype(np.float64) * (N_SEQ - cut)) / N_SEQ).astype(np.float32)
+    del g_a, g_b
+    worst_add = compare_gradients(tensors, cfg, combined, g_all, 3e-4, "additivity")
+    with pytest.raises(AssertionError):  # the check bites: the gradient of one part alone is not the gradient of the batch
+        compare_gradients(tensors, cfg, combined * np.float32(0.5), g_all, 3e-4, "additivity (negative control)")
+    del combined
+
+    # packing invariance: 32 instead of 128 sequences per packed pass
+    t32 = B200LanguageModelTrainer(m, dcfg, 32 * T_LEN)
+    t32.upload_params(P)
+    l_32, n_32, g_32 = grads_of(t32, 0, N_SEQ)
+    assert abs(l_32 - l_all) <= 1e-6 * abs(l_all), "the same rows in the same order: the serial sum of their losses is the same"
+    assert abs(n_32 - n_all) <= 1e-3 * n_all
+    worst_pack = compare_gradients(tensors, cfg, g_32, g_all, 1e-3, "packing")
+    print(f"full-size c5 step: loss {l_all:.6f}, gradient norm {n_all:.5f}; worst per-tensor relative difference: additivity {worst_add:.2e}, "
+          f"packing {worst_pack:.2e}")
+    t32.close(); t.close(); m.Dispose()
