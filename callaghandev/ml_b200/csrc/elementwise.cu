@@ -930,11 +930,14 @@ __global__ void __launch_bounds__(THREADS) ce_kernel(const float* __restrict__ l
     }
 }
 
-// Vocabularies above 32768 classes (V a multiple of 4, 16-byte aligned rows): one block of 256 threads per row, several blocks per SM.
+// Large vocabularies (V a multiple of 4, 16-byte aligned rows): one block of 256 threads per row, several blocks per SM.
 // Pass 1 streams the row once with 128-bit loads and keeps a running (max, sum of exp) pair per thread; pass 2 reads the
 // row again (about a third of those reads still hit L2 with eight blocks per SM in flight; capping the blocks per SM to
 // raise the hit rate cost more in latency hiding than it saved in traffic) and writes the gradient.  The loads of one
 // block overlap the reductions and stores of the others, which the one-block-per-SM register-resident kernel cannot do.
+// (A persistent block per SM that stages the row through shared memory with cp.async and prefetches the next row moves
+// only the algorithmic 8 B per element and ran 10 % faster than this kernel alone under the profiler, but 5-9 % slower
+// inside the power-capped step, where its single block per SM cannot hide latency at the lower clock: not kept.)
 __global__ void __launch_bounds__(256) ce_twopass_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets,
                                                          int effRows, const float* __restrict__ row_scale_dev, float row_scale,
                                                          float* __restrict__ dLogits, float* __restrict__ row_loss,
@@ -997,85 +1000,6 @@ __global__ void __launch_bounds__(256) ce_twopass_kernel(const float* __restrict
     }
 }
 
-// Vocabularies of 8192..32768 classes (V a multiple of 4, 16-byte aligned rows): one persistent block of 1024 threads
-// per SM.  A row is copied asynchronously into shared memory (cp.async, no registers held while it travels), moved from
-// there into registers (8 x float4 per thread), and the copy of the block's NEXT row is started before the arithmetic
-// on this one; the gradient is stored from registers.  HBM sees each logit read once and each gradient written once
-// (8 B per element, the algorithmic figure; the two-pass kernel below costs 12), reads of the next row overlap the
-// reductions and stores of this one, and writing the gradient over the logits stays safe: a row is complete in
-// registers before its first store, and the row being prefetched belongs to this block alone.
-constexpr int CE_STAGED_ITEMS = 8;
-__global__ void __launch_bounds__(1024, 1) ce_staged_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets,
-                                                            int rows, int effRows, const float* __restrict__ row_scale_dev, float row_scale,
-                                                            float* __restrict__ dLogits, float* __restrict__ row_loss,
-                                                            int32_t* __restrict__ row_ok) {
-    extern __shared__ float4 ce_row[];
-    __shared__ float red[32];
-    __shared__ float s_pt;
-    const int V4 = V >> 2, tid = threadIdx.x;
-    auto prefetch = [&](int row) {
-        const float4* src = reinterpret_cast<const float4*>(logits + (size_t)row * V);
-        for (int j = tid; j < V4; j += 1024) {
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ce_row + j);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + j) : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    int row = blockIdx.x;
-    if (row < effRows) prefetch(row);
-    for (; row < effRows; row += gridDim.x) {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // every thread's part of the row has landed
-        float4 v[CE_STAGED_ITEMS];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < CE_STAGED_ITEMS; i++) {
-            const int j = tid + i * 1024;
-            v[i] = j < V4 ? ce_row[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-            mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
-        }
-        if (tid == 0) s_pt = 0.f;
-        __syncthreads();  // the buffer has been read: the next row may land in it
-        if (row + (int)gridDim.x < effRows) prefetch(row + gridDim.x);
-        mx = block_max(mx, red);
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < CE_STAGED_ITEMS; i++) {  // padding lanes hold -inf: exp gives 0
-            v[i].x = expf(v[i].x - mx); v[i].y = expf(v[i].y - mx); v[i].z = expf(v[i].z - mx); v[i].w = expf(v[i].w - mx);
-            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        }
-        sum = block_sum(sum, red);
-        const float inv = 1.0f / sum;
-        const int t = targets[row];
-        const float sc = row_scale_dev ? row_scale_dev[row] : row_scale;
-        int ok = (unsigned)t < (unsigned)V ? 1 : 0;  // a target outside the row marks the row invalid instead of reading out of range
-        float4* dl4 = reinterpret_cast<float4*>(dLogits + (size_t)row * V);
-#pragma unroll
-        for (int i = 0; i < CE_STAGED_ITEMS; i++) {
-            const int j = tid + i * 1024;
-            if (j < V4) {
-                float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, g[4];
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    g[k] = (e[k] * inv) * sc;
-                    if (4 * j + k == t) { s_pt = e[k]; g[k] -= sc; }
-                    ok &= isfinite(g[k]) ? 1 : 0;
-                }
-                dl4[j] = make_float4(g[0], g[1], g[2], g[3]);
-            }
-        }
-        ok = __syncthreads_and(ok);
-        if (tid == 0) {
-            row_loss[row] = -logf(s_pt * inv + 1e-10f);
-            row_ok[row] = ok;
-        }
-    }
-    for (row = effRows + blockIdx.x; row < rows; row += gridDim.x) {  // rows beyond the effective length: zero gradient
-        float4* dl4 = reinterpret_cast<float4*>(dLogits + (size_t)row * V);
-        for (int j = tid; j < V4; j += 1024) dl4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-}
-
 // Any vocabulary size: three passes over the row in global memory (not in-place safe w.r.t. partial overwrite, so the
 // gradient is written only in the last pass, after every read of the same element by the same thread).
 __global__ void ce_generic_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets, int effRows,
@@ -1118,14 +1042,7 @@ int k_cross_entropy(b200_ctx* ctx, const float* logits, int rows, int V, const i
                     float row_scale, float* dLogits, float* row_loss, int32_t* row_ok) {
     if (rows <= 0 || V <= 0) return B200_OK;
     const bool big = V >= 8192 && (V % 4 == 0) && aligned16(logits) && aligned16(dLogits);
-    if (big && V <= CE_STAGED_ITEMS * 4 * 1024) {
-        static char configured_site;
-        if (first_use(ctx, &configured_site))
-            B200_CUDA(ctx, cudaFuncSetAttribute(ce_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CE_STAGED_ITEMS * 4 * 1024 * (int)sizeof(float)));
-        const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
-        ce_staged_kernel<<<rows < sms ? rows : sms, 1024, (size_t)V * sizeof(float), ctx->stream>>>(logits, V, targets, rows, effRows, row_scale_dev, row_scale, dLogits,
-                                                                                                   row_loss, row_ok);
-    } else if (big) ce_twopass_kernel<<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
+    if (big) ce_twopass_kernel<<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 128 * CE_ITEMS) ce_kernel<128><<<rows, 128, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 256 * CE_ITEMS) ce_kernel<256><<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 1024 * CE_ITEMS) ce_kernel<1024><<<rows, 1024, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);

@@ -307,7 +307,7 @@ def test_embedding_gather_scatter_bit_exact(mgr, oracle):  # PT:660-668 + Zipf-l
 
 
 @pytest.mark.parametrize("rows,V,eff", [(4, 5, 4), (64, 200, 64), (30, 8000, 21), (5, 32000, 5), (3, 40000, 3),
-                                        (7, 8192, 6), (3, 32768, 3), (400, 32000, 390)])  # the last: several rows per persistent block
+                                        (7, 8192, 6), (3, 32768, 3), (400, 32000, 390)])
 def test_cross_entropy(mgr, oracle, rows, V, eff):  # PT:670-678
     logits = pt_matrix(rows, V, 40) * 8
     targets = np.arange(7, 7 + rows + 3, dtype=np.int32) * 37 % V
