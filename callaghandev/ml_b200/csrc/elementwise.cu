@@ -930,14 +930,14 @@ __global__ void __launch_bounds__(THREADS) ce_kernel(const float* __restrict__ l
     }
 }
 
-// Large vocabularies (V a multiple of 4, 16-byte aligned rows): one block of 256 threads per row, several blocks per SM.
+// Larger vocabularies, or V not a multiple of 16 (V a multiple of 4, 16-byte aligned rows): one block of 256 threads per row, several blocks per SM.
 // Pass 1 streams the row once with 128-bit loads and keeps a running (max, sum of exp) pair per thread; pass 2 reads the
 // row again (about a third of those reads still hit L2 with eight blocks per SM in flight; capping the blocks per SM to
 // raise the hit rate cost more in latency hiding than it saved in traffic) and writes the gradient.  The loads of one
 // block overlap the reductions and stores of the others, which the one-block-per-SM register-resident kernel cannot do.
-// (A persistent block per SM that stages the row through shared memory with cp.async and prefetches the next row moves
-// only the algorithmic 8 B per element and ran 10 % faster than this kernel alone under the profiler, but 5-9 % slower
-// inside the power-capped step, where its single block per SM cannot hide latency at the lower clock: not kept.)
+// (Up to 32768 classes ce_cluster_kernel reads the row once.  A persistent block per SM that stages the row through shared
+// memory and prefetches the next one was built too: 10 % faster than this kernel alone under the profiler, 5-9 % slower
+// inside the power-capped step, where a single block per SM cannot hide latency at the lower clock: not kept.)
 __global__ void __launch_bounds__(256) ce_twopass_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets,
                                                          int effRows, const float* __restrict__ row_scale_dev, float row_scale,
                                                          float* __restrict__ dLogits, float* __restrict__ row_loss,
@@ -1000,6 +1000,108 @@ __global__ void __launch_bounds__(256) ce_twopass_kernel(const float* __restrict
     }
 }
 
+// Vocabularies of 8192..32768 classes (V a multiple of 16, 16-byte aligned rows) on devices with thread-block clusters:
+// a cluster of four blocks of 256 threads per row, each block holding its quarter of the row in registers (8 x float4
+// per thread).  The quarter maxima and the quarter sums of exp are exchanged through distributed shared memory (two
+// cluster barriers per row); logits are read once and the gradient is written once from registers -- 8 B per element,
+// against the 12 B of the two-pass kernel below, whose second read misses L2 two times out of three -- and with five
+// blocks resident per SM the loads of one row overlap the reductions and stores of the others.  Same arithmetic as
+// ce_kernel: maximum, exp(x - max), sum, p / sum.  A row is non-finite exactly when its sum of exp (or its scale) is:
+// every exp lies in [0, sum], and a NaN or +inf logit makes the sum NaN.
+constexpr int CE_CL = 4, CE_CL_THREADS = 256, CE_CL_ITEMS = 8;
+__global__ void __launch_bounds__(CE_CL_THREADS, 5) ce_cluster_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets,
+                                                                      int effRows, const float* __restrict__ row_scale_dev, float row_scale,
+                                                                      float* __restrict__ dLogits, float* __restrict__ row_loss,
+                                                                      int32_t* __restrict__ row_ok) {
+    __shared__ float red[8];
+    __shared__ float xmax[CE_CL], xsum[CE_CL];  // written by the four blocks of the cluster, one slot each
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int row = blockIdx.x / CE_CL, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int Q4 = V >> 4;                 // float4 per quarter row
+    const int base4 = (int)rank * Q4;      // this block's first float4 of the row
+    float4* dl4 = reinterpret_cast<float4*>(dLogits + (size_t)row * V) + base4;
+    if (row >= effRows) {  // all four blocks of a cluster take this branch together: no barrier is skipped by a part of it
+        for (int j = tid; j < Q4; j += CE_CL_THREADS) dl4[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const float4* l4 = reinterpret_cast<const float4*>(logits + (size_t)row * V) + base4;
+    float4 v[CE_CL_ITEMS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < CE_CL_ITEMS; i++) {
+        const int j = tid + i * CE_CL_THREADS;
+        v[i] = j < Q4 ? l4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    }
+    auto publish = [&](float* slot_array, float value) {  // value of this block into slot [rank] of every block of the cluster
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(slot_array + rank);
+#pragma unroll
+        for (uint32_t r = 0; r < CE_CL; r++) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(value) : "memory");
+        }
+    };
+    auto cluster_barrier = [] {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    };
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (tid == 0) {
+        float m = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]);
+        publish(xmax, m);
+    }
+    cluster_barrier();
+    const float M = fmaxf(fmaxf(xmax[0], xmax[1]), fmaxf(xmax[2], xmax[3]));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < CE_CL_ITEMS; i++) {  // padding lanes hold -inf: exp gives 0
+        v[i].x = expf(v[i].x - M); v[i].y = expf(v[i].y - M); v[i].z = expf(v[i].z - M); v[i].w = expf(v[i].w - M);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;  // the maxima in red were consumed before the cluster barrier
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) t += red[w];
+        publish(xsum, t);
+    }
+    cluster_barrier();
+    const float S = (xsum[0] + xsum[1]) + (xsum[2] + xsum[3]);
+    const float inv = 1.0f / S;
+    const int t = targets[row];
+    const float sc = row_scale_dev ? row_scale_dev[row] : row_scale;
+    const int tq = t - 4 * base4;  // the target's column within this quarter (outside [0, 4*Q4): another block's, or invalid)
+#pragma unroll
+    for (int i = 0; i < CE_CL_ITEMS; i++) {
+        const int j = tid + i * CE_CL_THREADS;
+        if (j < Q4) {
+            float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, g[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                g[k] = (e[k] * inv) * sc;
+                if (4 * j + k == tq) {  // exactly one thread of the cluster owns the target column: it reports the row
+                    g[k] -= sc;
+                    row_loss[row] = -logf(e[k] * inv + 1e-10f);
+                }
+            }
+            dl4[j] = make_float4(g[0], g[1], g[2], g[3]);
+        }
+    }
+    if (rank == 0 && tid == 0) {
+        const bool in_range = (unsigned)t < (unsigned)V;  // a target outside the row marks the row invalid instead of reading out of range
+        if (!in_range) row_loss[row] = -logf(1e-10f);     // what the other kernels report when no column matches (s_pt = 0)
+        row_ok[row] = (in_range && isfinite(S) && isfinite(sc)) ? 1 : 0;
+    }
+}
+
 // Any vocabulary size: three passes over the row in global memory (not in-place safe w.r.t. partial overwrite, so the
 // gradient is written only in the last pass, after every read of the same element by the same thread).
 __global__ void ce_generic_kernel(const float* __restrict__ logits, int V, const int32_t* __restrict__ targets, int effRows,
@@ -1042,7 +1144,18 @@ int k_cross_entropy(b200_ctx* ctx, const float* logits, int rows, int V, const i
                     float row_scale, float* dLogits, float* row_loss, int32_t* row_ok) {
     if (rows <= 0 || V <= 0) return B200_OK;
     const bool big = V >= 8192 && (V % 4 == 0) && aligned16(logits) && aligned16(dLogits);
-    if (big) ce_twopass_kernel<<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
+    if (big && V % 16 == 0 && V <= CE_CL * CE_CL_THREADS * CE_CL_ITEMS * 4 && ctx->cc_major >= 9) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)rows * CE_CL);
+        cfg.blockDim = dim3(CE_CL_THREADS);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CE_CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, ce_cluster_kernel, logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok));
+    } else if (big) ce_twopass_kernel<<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 128 * CE_ITEMS) ce_kernel<128><<<rows, 128, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 256 * CE_ITEMS) ce_kernel<256><<<rows, 256, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
     else if (V <= 1024 * CE_ITEMS) ce_kernel<1024><<<rows, 1024, 0, ctx->stream>>>(logits, V, targets, effRows, row_scale_dev, row_scale, dLogits, row_loss, row_ok);
