@@ -4,10 +4,11 @@
 //
 // Forward.  A CTA owns 128 query rows of one (segment, head) and walks the key tiles (128 keys each) it can see:
 //   S  = Q K^T          tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle), S in TMEM columns 0..127
-//   P  = softmax tile   128 threads, one query row each: tcgen05.ld -> max / exp2 / sum -> tcgen05.st back over S
+//   P  = softmax tile   256 threads, two per query row (64 columns each; the row maximum crosses through shared memory, the row
+//                       sum stays split until the end): tcgen05.ld -> max / exp2 / sum -> tcgen05.st back over S
 //   O += P V            tcgen05.mma with the A operand read from TMEM (P) and V as an N-contiguous shared-memory
 //                       operand (TMA, 128-byte swizzle with 32-byte atoms), O in TMEM columns 128..191
-// Warp roles: warp 0 = TMA producer, warp 1 = TMEM allocator and MMA issuer, warps 2..5 = softmax / output.  K and V
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM allocator and MMA issuer, warps 2..9 = softmax / output.  K and V
 // are single-buffered with separate barriers, so the load of K(j+1) overlaps softmax(j) and P V(j), and V(j+1)
 // overlaps S(j+1); two CTAs share an SM (96 KiB of tiles, 256 TMEM columns each) and fill each other's gaps.
 // Rows of a packed batch that lie outside the segment are loaded (they are finite: other segments' rows, or zeros
@@ -29,9 +30,9 @@ namespace {
 constexpr int UQ = 128, UK = 128, UHD = 64;
 constexpr int U_ATOM = 128 * 128;     // bytes of one 128-row x 32-float swizzle atom column
 constexpr int U_TILE = 2 * U_ATOM;    // a 128 x 64 operand tile
-constexpr int U_THREADS = 192;
+constexpr int U_THREADS = 64 + 256;  // producer warp, MMA warp, eight softmax warps (lane quarter x column half)
 constexpr int S_COL = 0, O_COL = 128, FWD_TMEM_COLS = 256;
-constexpr int FWD_SMEM = 3 * U_TILE + 1024 + 256;
+constexpr int FWD_SMEM = 3 * U_TILE + 1024 + 256 + 3 * 2 * 128 * 4;  // + row statistics exchanged between the two halves of a row
 constexpr int OUT_STRIDE = 68;        // floats per staged output row (16-byte aligned, conflict-free 128-bit accesses)
 constexpr float LOG2E_F = 1.4426950408889634f;
 
@@ -104,6 +105,17 @@ __device__ __forceinline__ void half_row_to_tmem(const uint8_t* atom, int row, i
     tmem_st16(taddr, r);
 }
 
+// Named barrier of the forward kernel's 256 softmax threads, plain and with an OR vote.
+__device__ __forceinline__ void sm_barrier() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+__device__ __forceinline__ bool sm_barrier_or(bool pred) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.or.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(r)
+                 : "r"((uint32_t)pred)
+                 : "memory");
+    return r != 0;
+}
+
 __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                                                                  const __grid_constant__ CUtensorMap mapV, UArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -128,6 +140,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + 3 * U_TILE);
     uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+    float* xch = reinterpret_cast<float*>(bars + 16);  // [3][2 halves][128 rows]: tile maxima (two buffers, alternating) and final sums
     const uint32_t Qs = smem_u32(tiles), Ks = Qs + U_TILE, Vs = Ks + U_TILE;
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 16, v_full = bar0 + 24, v_empty = bar0 + 32, s_full = bar0 + 40,
@@ -136,7 +149,7 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
     volatile int* status = a.status;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 8; i++) mbar_init(bar0 + 8 * i, i == 6 ? 4 : 1);  // p_full: one arrival per softmax warp
+        for (int i = 0; i < 8; i++) mbar_init(bar0 + 8 * i, i == 6 ? 8 : 1);  // p_full: one arrival per softmax warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // Q is requested right away: its latency overlaps the TMEM allocation and the first sync.
@@ -206,7 +219,10 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         }
     } else {
         // -------------------------------------------------------------------------------------- softmax and output
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32)
+        // Two threads per query row, 64 score columns each (a thread alone walks a chain of 128 max / exp / add steps per
+        // tile, and with one warp per scheduler nothing hides it).  The halves agree on the row maximum through shared
+        // memory once per tile; each keeps its own partial row sum, which the correction factor scales alike.
+        const int quarter = warp & 3, half = (warp - 2) >> 2, c0 = 64 * half;  // TMEM lanes [32*quarter, +32), columns [c0, +64)
         const int row = 32 * quarter + lane, qi = q0 + row;
         const uint32_t tlane = tmem_base + ((uint32_t)(32 * quarter) << 16);
         const float sl2 = a.scale * LOG2E_F;
@@ -216,58 +232,61 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
         for (int j = 0; j < nkt; j++) {
             ok = mbar_wait_warp(s_full, j & 1, status, 17);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (sm_barrier_or(!ok)) {  // also orders the previous tile's reads of the exchange buffer before its reuse two tiles on
+                ok = false;
+                break;
+            }
             tc_fence_after();
-            const int k0 = j * UK;
-            const bool full = k0 + UK <= sg.kLen && (!a.causal || k0 + UK - 1 <= q0 + 32 * quarter);  // warp-uniform
-            const int nvis = lim - k0;  // columns [0, nvis) of this tile are visible
-            // the whole score row of this tile in registers: one TMEM read, four independent max / sum chains
-            uint32_t r[4][32];
+            const int k0 = j * UK + c0;
+            const bool full = k0 + 64 <= sg.kLen && (!a.causal || k0 + 63 <= q0 + 32 * quarter);  // warp-uniform
+            const int nvis = lim - k0;  // columns [0, nvis) of this half are visible
+            uint32_t r[2][32];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32_nowait(tlane + S_COL + 32 * c, r[c]);
+            for (int c = 0; c < 2; c++) tmem_ld32_nowait(tlane + S_COL + c0 + 32 * c, r[c]);
             tmem_ld_wait();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full) {
 #pragma unroll
-                for (int c = 0; c < 4; c++)
+                for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; c++)
+                for (int c = 0; c < 2; c++)
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
                         if (32 * c + i >= nvis) r[c][i] = 0xff800000u;  // -inf
                         mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
                     }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float* xm = xch + (j & 1) * 256;
+            xm[half * 128 + row] = mx;
+            sm_barrier();
+            mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
             const float m_new = fmaxf(m, mx * sl2);  // scale > 0, so the maximum commutes with the scaling
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = ex2(m - m_safe);
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 2; c++) {
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     const float p = ex2(fmaf(__uint_as_float(r[c][i]), sl2, -m_safe));  // masked entries are -inf: p = 0
                     rs4[i & 3] += p;
                     r[c][i] = rna_tf32(p);
                 }
-                tmem_st32(tlane + S_COL + 32 * c, r[c]);
+                tmem_st32(tlane + S_COL + c0 + 32 * c, r[c]);
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-            l = l * corr + rs;
+            l = l * corr + rs;  // this half's share of the row sum
             m = m_new;
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // S(j) complete implies P V(j-1) complete: O is stable
-#pragma unroll 1
-                for (int c = 0; c < UHD; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tlane + O_COL + c, r);
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {  // S(j) complete implies P V(j-1) complete: O is stable; this half's 32 columns
+                uint32_t o[32];
+                tmem_ld32(tlane + O_COL + 32 * half, o);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                    tmem_st32(tlane + O_COL + c, r);
-                }
+                for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                tmem_st32(tlane + O_COL + 32 * half, o);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -278,29 +297,33 @@ __global__ void __launch_bounds__(U_THREADS, 2) attn_fwd_umma_kernel(const __gri
             ok = mbar_wait_warp(o_full, 0, status, 18);
             ok = __all_sync(0xffffffffu, ok);
         }
+        float* xl = xch + 512;
+        xl[half * 128 + row] = l;
+        if (sm_barrier_or(!ok)) ok = false;  // the partial sums cross; a failed wait anywhere stops every softmax warp together
         if (ok) {
             tc_fence_after();
-            // every MMA has completed, so the operand tiles are free: stage this warp's 32 rows and store whole rows
+            l += xl[(half ^ 1) * 128 + row];
+            // every MMA has completed, so the operand tiles are free: stage this quarter's 32 rows and store whole rows
             float* stage = reinterpret_cast<float*>(tiles) + quarter * (32 * OUT_STRIDE);
             const float il = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll 1
-            for (int c = 0; c < UHD; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tlane + O_COL + c, r);
+            uint32_t o[32];
+            tmem_ld32(tlane + O_COL + 32 * half, o);
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4*>(stage + lane * OUT_STRIDE + c + i) =
-                        make_float4(__uint_as_float(r[i]) * il, __uint_as_float(r[i + 1]) * il, __uint_as_float(r[i + 2]) * il, __uint_as_float(r[i + 3]) * il);
-            }
-            if (qi < sg.qLen) {
+            for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(stage + lane * OUT_STRIDE + 32 * half + i) =
+                    make_float4(__uint_as_float(o[i]) * il, __uint_as_float(o[i + 1]) * il, __uint_as_float(o[i + 2]) * il, __uint_as_float(o[i + 3]) * il);
+            if (half == 0 && qi < sg.qLen) {
                 const size_t idx = (size_t)(sg.qStart + qi) * a.numHeads + head;
                 a.rowMax[idx] = (m == -INFINITY) ? -INFINITY : m / LOG2E_F;
                 a.rowSum[idx] = l;
             }
-            __syncwarp();
+        }
+        sm_barrier();  // both halves of every row are staged
+        if (ok) {
+            const float* stage = reinterpret_cast<const float*>(tiles) + quarter * (32 * OUT_STRIDE);
             const int sub = lane >> 4, c4 = (lane & 15) * 4;
 #pragma unroll 4
-            for (int rr = 0; rr < 32; rr += 2) {
+            for (int rr = 16 * half; rr < 16 * half + 16; rr += 2) {  // each warp of the pair stores half of the quarter's rows
                 const int r = rr + sub;
                 if (q0 + 32 * quarter + r < sg.qLen)
                     *reinterpret_cast<float4*>(a.O + (size_t)(sg.qStart + q0 + 32 * quarter + r) * a.ldo + head * UHD + c4) =
