@@ -79,3 +79,13 @@ def test_split_sequences_covers_batch():
             assert spans[0][0] == 0 and spans[-1][1] == n
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             assert max(h - l for l, h in spans) - min(h - l for l, h in spans) <= 1
+
+
+def test_communicator_cta_limit_is_validated_without_a_device():
+    """b200_dp_set_nccl_max_ctas only records the limit for communicators created later: it needs neither a GPU nor NCCL."""
+    from callaghandev.ml_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.b200_dp_set_nccl_max_ctas(-1) == _lib.ERR_INVALID_ARG
+    assert lib.b200_dp_set_nccl_max_ctas(0) == _lib.OK   # 0: leave the choice to NCCL
+    assert lib.b200_dp_set_nccl_max_ctas(8) == _lib.OK   # back to the default
