@@ -306,7 +306,7 @@ def main():
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline sample (0 disables)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch (sequences; global for c5/c1, per GPU for c3/c4)")
-    ap.add_argument("--nccl-ctas", type=int, default=-1, help="CTAs the data-parallel communicator may use (-1: the library's default of 8, 0: NCCL's own choice)")
+    ap.add_argument("--nccl-ctas", type=int, default=-1, help="CTAs the data-parallel communicator may use (-1: the library's default of 16, 0: NCCL's own choice)")
     ap.add_argument("--gemm-csv", default="", help="write the per-shape GEMM timing table of the timed region to this file")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])

@@ -40,9 +40,10 @@ std::mutex g_nccl_mu;
 std::string g_nccl_path;
 // CTAs the communicators may use.  The all-reduce of a step moves 4 bytes per parameter in the shadow of a backward pass
 // that lasts tens of milliseconds, so it needs a small fraction of NVLink's bandwidth; what it costs is the SMs its
-// kernels occupy beside the GEMMs while they wait for peers.  At eight GPUs (c5) the default took 8 % off the GEMM rate
-// of the overlapped pass, eight CTAs took 3 % and shortened the exposed tail as well.
-int g_nccl_max_ctas = 8;
+// kernels occupy beside the GEMMs while they wait for peers, against the length of the tail that no backward hides.
+// Eight GPUs, c5, ms per step: NCCL's own choice 96.2; 4 CTAs 97.7 (the tail grows to 4 ms); 8 CTAs 93.9-94.2;
+// 16 CTAs 92.9 (same GEMM rate as with 8, 1.1 ms of tail).
+int g_nccl_max_ctas = 16;
 
 // ncclCommInitRank, with the CTA limit where the library supports per-communicator configuration
 ncclResult_t comm_init_rank(NcclApi* api, ncclComm_t* comm, int world, ncclUniqueId id, int rank) {

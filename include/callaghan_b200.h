@@ -423,7 +423,7 @@ B200_API int32_t b200_lm_get_timings(b200_lm*, float* ms4);
 typedef struct b200_dp b200_dp;
 typedef struct b200_dp_group b200_dp_group;
 B200_API int32_t b200_dp_set_nccl_library(const char* path);
-/* CTAs a communicator created after this call may use (ncclConfig_t.maxCTAs; default 8, 0 = NCCL's own choice).  A step's
+/* CTAs a communicator created after this call may use (ncclConfig_t.maxCTAs; default 16, 0 = NCCL's own choice).  A step's
  * all-reduce needs a small fraction of NVLink's bandwidth; what it costs is the SMs its kernels hold beside the backward
  * GEMMs while they wait for peers. */
 B200_API int32_t b200_dp_set_nccl_max_ctas(int32_t n);

@@ -88,4 +88,4 @@ def test_communicator_cta_limit_is_validated_without_a_device():
     lib = _lib.load()
     assert lib.b200_dp_set_nccl_max_ctas(-1) == _lib.ERR_INVALID_ARG
     assert lib.b200_dp_set_nccl_max_ctas(0) == _lib.OK   # 0: leave the choice to NCCL
-    assert lib.b200_dp_set_nccl_max_ctas(8) == _lib.OK   # back to the default
+    assert lib.b200_dp_set_nccl_max_ctas(16) == _lib.OK  # back to the default
