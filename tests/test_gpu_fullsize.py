@@ -85,7 +85,8 @@ def test_config5_full_batch_properties():
         compare_gradients(tensors, cfg, combined * np.float32(0.5), g_all, 3e-4, "additivity (negative control)")
     del combined
 
-    # packing invariance: 32 instead of 128 sequences per packed pass
+    # packing invariance: 32 instead of 128 sequences per packed pass (the first trainer's 120 GB go back first)
+    t.close()
     t32 = B200LanguageModelTrainer(m, dcfg, 32 * T_LEN)
     t32.upload_params(P)
     l_32, n_32, g_32 = grads_of(t32, 0, N_SEQ)
@@ -94,4 +95,4 @@ def test_config5_full_batch_properties():
     worst_pack = compare_gradients(tensors, cfg, g_32, g_all, 1e-3, "packing")
     print(f"full-size c5 step: loss {l_all:.6f}, gradient norm {n_all:.5f}; worst per-tensor relative difference: additivity {worst_add:.2e}, "
           f"packing {worst_pack:.2e}")
-    t32.close(); t.close(); m.Dispose()
+    t32.close(); m.Dispose()
