@@ -1108,16 +1108,30 @@ __global__ void __launch_bounds__(B_THREADS) attn_dkv_umma_kernel(const __grid_c
     }
 }
 
-// rowDot[row, head] = sum_c dO[row, head*64 + c] * O[row, head*64 + c]; one warp per (row, head)
-__global__ void attn_rowdot_umma_kernel(const float* __restrict__ dO, int lddo, const float* __restrict__ O, int ldo, int rows, int numHeads,
-                                        float* __restrict__ rowDot) {
-    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (w >= rows * numHeads) return;
-    const int row = w / numHeads, head = w - row * numHeads;
-    const float2 x = *reinterpret_cast<const float2*>(dO + (size_t)row * lddo + head * UHD + 2 * lane);
-    const float2 y = *reinterpret_cast<const float2*>(O + (size_t)row * ldo + head * UHD + 2 * lane);
-    const float s = warp_sum(x.x * y.x + x.y * y.y);
-    if (lane == 0) rowDot[w] = s;
+// rowDot[row, head] = sum_c dO[row, head*64 + c] * O[row, head*64 + c].  One warp per row: a lane owns one 16-byte piece of
+// each 512-byte stretch of the row (two heads), so all its loads are issued before the first product, and the 16 lanes
+// that share a head add up with four shuffles.
+__global__ void __launch_bounds__(256) attn_rowdot_umma_kernel(const float* __restrict__ dO, int lddo, const float* __restrict__ O, int ldo, int rows,
+                                                               int numHeads, float* __restrict__ rowDot) {
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4* a = reinterpret_cast<const float4*>(dO + (size_t)row * lddo) + lane;
+    const float4* b = reinterpret_cast<const float4*>(O + (size_t)row * ldo) + lane;
+    for (int h0 = 0; h0 < numHeads; h0 += 16) {  // 16 heads (eight stretches of two) per round
+        float4 x[8], y[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (h0 + 2 * i + (lane >> 4) < numHeads) { x[i] = a[(h0 / 2 + i) * 32]; y[i] = b[(h0 / 2 + i) * 32]; }  // an odd head count ends in half a stretch
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (h0 + 2 * i >= numHeads) break;  // warp-uniform
+            const int head = h0 + 2 * i + (lane >> 4);
+            float s = head < numHeads ? (x[i].x * y[i].x + x[i].y * y[i].y) + (x[i].z * y[i].z + x[i].w * y[i].w) : 0.f;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if ((lane & 15) == 0 && head < numHeads) rowDot[(size_t)row * numHeads + head] = s;
+        }
+    }
 }
 
 }  // namespace
@@ -1177,8 +1191,7 @@ int attn_backward_umma(b200_ctx* ctx, const Attn& t) {
     a.dQ = t.dQ; a.dK = t.dK; a.dV = t.dV; a.lddq = t.lddq; a.lddk = t.lddk; a.lddv = t.lddv;
     a.rowMax = t.rowMax; a.rowSum = t.rowSum; a.rowDot = t.rowDot; a.segs = t.segs_dev; a.numHeads = t.numHeads; a.causal = t.causal;
     a.scale = t.scale; a.status = ctx->status_dev; a.rope_table = t.rope_table; a.rope_pos = t.rope_pos;
-    const int warps = t.totalQ * t.numHeads;
-    attn_rowdot_umma_kernel<<<(warps * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
+    attn_rowdot_umma_kernel<<<(t.totalQ * 32 + 255) / 256, 256, 0, ctx->stream>>>(t.dO, t.lddo, t.O, t.ldo, t.totalQ, t.numHeads, t.rowDot);
     B200_LAUNCH_CHECK(ctx);
     // persistent kernels: one CTA per SM walks its share of the (segment, head, tile) pairs
     const int nGroups = t.numHeads * t.nSeg, sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
