@@ -346,22 +346,35 @@ __global__ void __launch_bounds__(128) embed_scatter_vec_kernel(float* __restric
     float4* dst = reinterpret_cast<float4*>(eg + (size_t)seg_id[s] * d + c);
     float4 acc = *dst;
     int k = lo;
-    // the row indices of a group are fetched while the previous group's rows travel: index -> row is a chain of two loads
-    int rows[U];
+    // Index -> row is a chain of two loads, and one group's rows in flight do not fill the memory pipeline of a block that
+    // owns a long segment: the indices run two groups ahead of the additions, and the rows of the NEXT group are asked
+    // of L2 (prefetch, no registers) while this group's rows travel.
+    int cur[U], nx[U];
     if (k + U <= hi) {
 #pragma unroll
-        for (int u = 0; u < U; u++) rows[u] = perm[k + u];
+        for (int u = 0; u < U; u++) cur[u] = perm[k + u];
+    }
+    if (k + 2 * U <= hi) {
+#pragma unroll
+        for (int u = 0; u < U; u++) nx[u] = perm[k + U + u];
     }
     for (; k + U <= hi; k += U) {
         float4 v[U];
 #pragma unroll
-        for (int u = 0; u < U; u++) v[u] = *reinterpret_cast<const float4*>(a + (size_t)rows[u] * d + c);
+        for (int u = 0; u < U; u++) v[u] = *reinterpret_cast<const float4*>(a + (size_t)cur[u] * d + c);
+        int nn[U];
         if (k + 2 * U <= hi) {
 #pragma unroll
-            for (int u = 0; u < U; u++) rows[u] = perm[k + U + u];
+            for (int u = 0; u < U; u++) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + (size_t)nx[u] * d + c));
+        }
+        if (k + 3 * U <= hi) {
+#pragma unroll
+            for (int u = 0; u < U; u++) nn[u] = perm[k + 2 * U + u];
         }
 #pragma unroll
         for (int u = 0; u < U; u++) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+#pragma unroll
+        for (int u = 0; u < U; u++) { cur[u] = nx[u]; nx[u] = nn[u]; }
     }
     for (; k < hi; k++) {
         const float4 x = *reinterpret_cast<const float4*>(a + (size_t)perm[k] * d + c);
@@ -602,6 +615,20 @@ __global__ void __launch_bounds__(128, 4) ln_bwd_vec_kernel(const float* __restr
         const float4* x4 = reinterpret_cast<const float4*>(x + (size_t)row * d);
         float mu = mean[row];
         float inv = 1.0f / sqrtf(var[row] + eps);
+        {   // ask L2 for this warp's next row while this one is worked on (one lane per 128-byte line)
+            const int nrow = row + gridDim.x * warps;
+            if (nrow < rows && (lane & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < LN_MAXV; i++) {
+                    const int c = lane + 32 * i;
+                    if (c < d4) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(dOutA + (size_t)nrow * d + 4 * c));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(x + (size_t)nrow * d + 4 * c));
+                        if (HAS_B) asm volatile("prefetch.global.L2 [%0];" ::"l"(dOutB + (size_t)nrow * d + 4 * c));
+                    }
+                }
+            }
+        }
         float4 dn[LN_MAXV], xm[LN_MAXV];
 #pragma unroll
         for (int i = 0; i < LN_MAXV; i++) {  // all loads of the row first
